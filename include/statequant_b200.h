@@ -1,0 +1,160 @@
+/*
+ * statequant_b200 - C ABI of the fused packed-state decode step (Gated DeltaNet, Mamba2/SSD, KDA).
+ *
+ * Every entry point launches hand-written sm_100a CUDA kernels on the given stream and returns at once:
+ * no allocation, no host synchronisation, so a call can be captured in a CUDA graph and replayed with
+ * different slot tables.  All pointers in the argument structs are DEVICE pointers (the CPU oracle under
+ * oracle/ takes the same structs with HOST pointers and is test infrastructure only).  Strides are in BYTES.
+ *
+ * What each entry point replaces in the reference (HallerPatrick/StateQuant, paths inside that project):
+ *   sqb_gdn_step     the Triton launch `_fused_step[(BH,)](...)`   src/statequant/kernels/fold.py:401-407,
+ *                                                                   src/statequant/kernels/slots.py:180-186
+ *   sqb_mamba2_step  `_m2_step[(rows * HV,)](...)`                  src/statequant/kernels/mamba2.py:232-240
+ *   sqb_kda_step     `_kda_step[(rows * HV,)](...)`                 src/statequant/kernels/kda.py:199-204
+ *
+ * Return value: 0 on success, a negative SQB_E* code otherwise; sqb_last_error() gives the message of the
+ * last failure on the calling thread.  Nothing is launched when an error is returned.
+ */
+#ifndef STATEQUANT_B200_H
+#define STATEQUANT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of activation tensors */
+enum { SQB_F32 = 0, SQB_BF16 = 1, SQB_F16 = 2 };
+
+/* error codes */
+enum {
+  SQB_OK = 0,
+  SQB_EINVAL = -1,      /* a shape, stride, alignment or format the kernels do not support */
+  SQB_ECUDA = -2,       /* the CUDA runtime refused the launch */
+  SQB_ENOTBUILT = -3    /* this build has no kernel for the requested (kind, bits, axis) */
+};
+
+/*
+ * The packed state of one layer, as per-sequence tables.  Sequence (slot) s of table X lives at
+ * X + s * sX (bytes).  Field meaning and element layout are the reference's
+ * (src/statequant/kernels/slots.py:9-28, kda.py:291-295):
+ *
+ *   S     codes  bits 4: uint8 [HV, DV, DK/2], byte j = (c[2j]+8) | (c[2j+1]+8) << 4
+ *                bits 8: int8 [HV, DV, DK];  bits 16: bf16 [HV, DV, DK];  bits 32: fp32 [HV, DV, DK]
+ *   SC    fp16 scales  axis k: [HV, DV, DK/group];  axis v: [HV, DV/group, DK]   (unused for bits 16 / 32)
+ *   KB    buffered keys  int8 or bf16 [HK, m, DK]       KBS fp16 [HK, m]  (int8 buffer only)
+ *   UB    buffered values int8 or bf16 [HV, m, DV]      UBS fp16 [HV, m]  (int8 buffer only)
+ *   GB    fp32 [HV, m]  cumulative log decay of each buffered token   (KDA: [HV, m, DK])
+ *   GCUR  fp32 [HV]     running log decay since the last fold          (KDA: [HV, DK])
+ *   NPTR  int32 [>= HV] buffer fill counter, one copy per value head
+ */
+typedef struct sqb_state {
+  void *S;      int64_t sS;
+  void *SC;     int64_t sSC;
+  void *KB;     int64_t sKB;
+  void *KBS;    int64_t sKBS;
+  void *UB;     int64_t sUB;
+  void *UBS;    int64_t sUBS;
+  void *GB;     int64_t sGB;
+  void *GCUR;   int64_t sGC;
+  void *NPTR;   int64_t sN;
+  int32_t bits;          /* 4, 8, 16 (bf16 state) or 32 (fp32 state) */
+  int32_t axis_k;        /* 1: scale groups run along d_k; 0: along d_v */
+  int32_t group;         /* scale group length */
+  int32_t buffer_bits;   /* 8: int8 + fp16 absmax scale per vector; 16: bf16 */
+  int32_t m;             /* buffer length, a power of two <= 32 */
+  int32_t hv, hk;        /* value heads, key heads (Mamba2: heads, groups); hv % hk == 0 */
+  int32_t dk, dv;        /* head dims */
+  int32_t reserved;
+} sqb_state_t;
+
+/*
+ * Inputs of one Gated DeltaNet decode token for `rows` batch rows.
+ *   idx       int32 [rows] slot of each row, or NULL: row b is sequence b (lockstep).  idx <= 0 marks a padding
+ *             row: its output row is zeroed and nothing else is touched.
+ *   q, k      [rows, hk, dk] (qk_per_key_head = 1) or [rows, hv, dk] (0); raw, l2-normalised in the kernel,
+ *             q scaled by `scale`; unit inner stride, row strides sq / sk
+ *   v         [rows, hv, dv]
+ *   g, beta   [rows, hv] log decay and beta (after the sigmoid)               when gate == 0
+ *   a, b      [rows, hv]; A_log fp32 [hv]; dt_bias [hv]                         when gate == 1:
+ *             g = -exp(A_log) * softplus(a + dt_bias), beta = sigmoid(b)
+ *   out       [rows, hv, dv], row stride so
+ */
+typedef struct sqb_gdn_inputs {
+  const int32_t *idx;
+  const void *q;      int64_t sq;
+  const void *k;      int64_t sk;
+  const void *v;      int64_t sv;
+  const void *g;      int64_t sg;
+  const void *beta;   int64_t sbeta;
+  const void *a;      int64_t sa;
+  const void *b;      int64_t sb;
+  const void *A_log;
+  const void *dt_bias;
+  void *out;          int64_t so;
+  float scale;
+  int32_t rows;
+  int32_t qk_per_key_head;
+  int32_t gate;
+  int32_t qk_dtype, v_dtype, gb_dtype, ab_dtype, alog_dtype, dtb_dtype, out_dtype;
+  int32_t reserved;
+} sqb_gdn_inputs_t;
+
+/*
+ * Inputs of one Mamba2 / SSD decode token.
+ *   x [rows, hv, dv], dt [rows, hv] raw, B / C [rows, hk, dk], A / D / dt_bias [hv] (D, dt_bias may be NULL);
+ *   dt = softplus(dt + dt_bias) if dt_softplus, clamped to [dt_min, dt_max] if dt_clamp; out [rows, hv, dv].
+ */
+typedef struct sqb_mamba2_inputs {
+  const int32_t *idx;
+  const void *x;      int64_t sx;
+  const void *dt;     int64_t sdt;
+  const void *B;      int64_t sB;
+  const void *C;      int64_t sC;
+  const void *A;
+  const void *D;
+  const void *dt_bias;
+  void *out;          int64_t so;
+  float dt_min, dt_max;
+  int32_t rows;
+  int32_t dt_softplus, dt_clamp;
+  int32_t x_dtype, dt_dtype, bc_dtype, a_dtype, d_dtype, dtb_dtype, out_dtype;
+} sqb_mamba2_inputs_t;
+
+/*
+ * Inputs of one KDA decode token.
+ *   q, k, g [rows, hv, dk] (g: log decay per key channel), v [rows, hv, dv], beta [rows, hv], out [rows, hv, dv].
+ */
+typedef struct sqb_kda_inputs {
+  const int32_t *idx;
+  const void *q;      int64_t sq;
+  const void *k;      int64_t sk;
+  const void *v;      int64_t sv;
+  const void *g;      int64_t sg;
+  const void *beta;   int64_t sbeta;
+  void *out;          int64_t so;
+  float scale;
+  int32_t rows;
+  int32_t qk_dtype, v_dtype, g_dtype, beta_dtype, out_dtype;
+  int32_t reserved;
+} sqb_kda_inputs_t;
+
+/* replaces `_fused_step[(BH,)]`, src/statequant/kernels/fold.py:401-407 and slots.py:180-186 */
+int sqb_gdn_step(const sqb_state_t *st, const sqb_gdn_inputs_t *in, void *cuda_stream);
+/* replaces `_m2_step[(rows * HV,)]`, src/statequant/kernels/mamba2.py:232-240 */
+int sqb_mamba2_step(const sqb_state_t *st, const sqb_mamba2_inputs_t *in, void *cuda_stream);
+/* replaces `_kda_step[(rows * HV,)]`, src/statequant/kernels/kda.py:199-204 */
+int sqb_kda_step(const sqb_state_t *st, const sqb_kda_inputs_t *in, void *cuda_stream);
+
+/* message of the last error returned on this thread ("" if none) */
+const char *sqb_last_error(void);
+/* ABI version of this header; bumped whenever a struct changes */
+int sqb_abi_version(void);
+/* number of kernel launches issued by this library in this process (all threads) */
+int64_t sqb_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

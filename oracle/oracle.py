@@ -1,0 +1,127 @@
+"""Python handle on the CPU oracle (``oracle/sq_oracle.c``).  TEST INFRASTRUCTURE: only tests/, the smoke check
+and the benchmark's CPU legs may import this module; the package ``statequant_b200`` never does.
+
+The oracle takes the same argument structs as the C ABI, with host pointers, so a test steps the very same blob
+bytes through the CUDA kernels and through the oracle and compares the results byte for byte.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import torch
+
+from statequant_b200 import _cabi
+from statequant_b200.kernels import kda as _kda
+from statequant_b200.kernels import mamba2 as _m2
+from statequant_b200.kernels.slots import _gdn_inputs
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB = os.path.join(HERE, 'liboracle.so')
+_lib = None
+
+
+def build(force=False):
+    srcs = [os.path.join(HERE, f) for f in ('sq_oracle.c', 'sq_oracle_gga.c', 'Makefile')]
+    srcs.append(os.path.join(HERE, '..', 'include', 'statequant_b200.h'))
+    if force or not os.path.exists(LIB) or any(os.path.getmtime(s) > os.path.getmtime(LIB) for s in srcs):
+        subprocess.run(['make', '-C', HERE, '-B', 'liboracle.so'], check=True, capture_output=True)
+    return LIB
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB):
+            build()
+        L = C.CDLL(LIB)
+        for n in ('sqo_gdn_step', 'sqo_mamba2_step', 'sqo_kda_step'):
+            getattr(L, n).restype = C.c_int
+            getattr(L, n).argtypes = [C.c_void_p, C.c_void_p]
+        L.sqo_num_threads.restype = C.c_int
+        _lib = L
+    return _lib
+
+
+def _cpu(*ts):
+    for t in ts:
+        assert t is None or t.device.type == 'cpu', 'the oracle works on host memory'
+
+
+def num_threads():
+    return int(lib().sqo_num_threads())
+
+
+def pack_vk(x, bits, axis_k, group):
+    """fp32 [n, dv, dk] -> (codes, scales) with the oracle's packer."""
+    x = x.float().contiguous()
+    n, dv, dk = x.shape
+    if bits == 4:
+        codes = torch.empty(n, dv, dk // 2, dtype=torch.uint8)
+    elif bits == 8:
+        codes = torch.empty(n, dv, dk, dtype=torch.int8)
+    else:
+        codes = torch.empty(n, dv, dk, dtype=torch.bfloat16 if bits == 16 else torch.float32)
+    ns = (dv * -(-dk // group) if axis_k else (dv // group) * dk) if bits <= 8 else 1
+    scales = torch.ones(n, ns, dtype=torch.float16)
+    lib().sqo_pack_vk(C.c_void_p(x.data_ptr()), C.c_int64(n), dv, dk, bits, int(axis_k), group,
+                      C.c_void_p(codes.data_ptr()), C.c_void_p(scales.data_ptr()))
+    if bits <= 8:
+        scales = scales.view(n, dv, -1) if axis_k else scales.view(n, dv // group, dk)
+    return codes, scales
+
+
+def unpack_vk(codes, scales, bits, axis_k, group, dk):
+    n, dv = codes.shape[:2]
+    x = torch.empty(n, dv, dk, dtype=torch.float32)
+    codes, scales = codes.contiguous(), scales.contiguous()
+    lib().sqo_unpack_vk(C.c_void_p(codes.data_ptr()), C.c_void_p(scales.data_ptr()), C.c_int64(n), dv, dk, bits,
+                        int(axis_k), group, C.c_void_p(x.data_ptr()))
+    return x
+
+
+def gdn_step(lay, views, idx, q, k, v, out, scale, *, g=None, beta=None, gate=None, per_key_head=True):
+    """``SlotLayout.step`` on host memory through the oracle."""
+    _cpu(views['S'], idx, q, k, v, out)
+    a = _gdn_inputs(idx, q, k, v, out, scale, g, beta, gate, per_key_head)
+    st = lay._struct(views)
+    rc = lib().sqo_gdn_step(C.byref(st), C.byref(a))
+    assert rc == 0
+    return out
+
+
+def mamba2_step(lay, views, idx, x, dt, B, Cm, out, A, D=None, dt_bias=None, dt_softplus=True,
+                dt_limit=(0., float('inf'))):
+    _cpu(views['S'], idx, x, dt, B, Cm, out)
+    a = _m2._inputs(lay, idx, x, dt, B, Cm, out, A, D, dt_bias, dt_softplus, dt_limit)
+    rc = lib().sqo_mamba2_step(C.byref(lay._struct(views)), C.byref(a))
+    assert rc == 0
+    return out
+
+
+def kda_step(lay, views, idx, q, k, v, g, beta, out, scale=None):
+    _cpu(views['S'], idx, q, k, v, g, beta, out)
+    a = _kda._inputs(lay, idx, q, k, v, g, beta, out, lay.DK ** -0.5 if scale is None else scale)
+    rc = lib().sqo_kda_step(C.byref(lay._struct(views)), C.byref(a))
+    assert rc == 0
+    return out
+
+
+def slot_read(lay, views, slots):
+    """``layout.read`` through the oracle: fp32 [P, HV, DV, DK]."""
+    slots = slots.to(torch.int64).contiguous()
+    P = slots.shape[0]
+    out = torch.empty(P, lay.HV, lay.DV, lay.DK, dtype=torch.float32)
+    rc = lib().sqo_slot_read(C.byref(lay._struct(views)), int(lay.kind), C.c_void_p(slots.data_ptr()), C.c_int64(P),
+                             C.c_void_p(out.data_ptr()))
+    assert rc == 0
+    return out
+
+
+def slot_write(lay, views, slots, S):
+    slots = slots.to(torch.int64).contiguous()
+    S = S.float().contiguous()
+    rc = lib().sqo_slot_write(C.byref(lay._struct(views)), int(lay.kind), C.c_void_p(slots.data_ptr()),
+                              C.c_int64(slots.shape[0]), C.c_void_p(S.data_ptr()))
+    assert rc == 0

@@ -1,0 +1,99 @@
+// Shared device helpers of the packed-state decode kernels (sm_100a).
+//
+// Numerics contract (what "the same bytes as the reference" rests on):
+//   * scales:   s = fp16_rn(max(amax, 1e-8) / qmax) clamped below at 2^-24, IEEE division
+//   * payloads: code = clamp(rint(x / s)), IEEE division, round half to even
+//   * no fast-math; this file is compiled with --fmad=false, so every fused multiply-add below is written
+//     explicitly (fmaf / __ffma2_rn) and every separately rounded product stays separate.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace sqb {
+
+constexpr int NT = 128;  // threads per CTA
+constexpr int NW = 4;    // warps per CTA
+constexpr float FP16_TINY = 5.960464477539063e-08f;   // 2^-24
+constexpr float FP16_MIN_NORMAL = 6.103515625e-05f;   // 2^-14
+constexpr float MAGIC = 12582912.0f;                  // 1.5 * 2^23: adding it rounds to an integer (half-even)
+
+enum { DT_F32 = 0, DT_BF16 = 1, DT_F16 = 2 };
+enum { K_GDN = 0, K_M2 = 1, K_KDA = 2 };
+
+__device__ __forceinline__ float ldf(const void* p, int dt, long long i) {
+  if (dt == DT_F32) return reinterpret_cast<const float*>(p)[i];
+  if (dt == DT_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+  return __half2float(reinterpret_cast<const __half*>(p)[i]);
+}
+__device__ __forceinline__ void stf(void* p, int dt, long long i, float v) {
+  if (dt == DT_F32) reinterpret_cast<float*>(p)[i] = v;
+  else if (dt == DT_BF16) reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+  else reinterpret_cast<__half*>(p)[i] = __float2half_rn(v);
+}
+__device__ __forceinline__ int dt_size(int dt) { return dt == DT_F32 ? 4 : 2; }
+
+__device__ __forceinline__ float h2f(unsigned short h) { return __half2float(__ushort_as_half(h)); }
+__device__ __forceinline__ unsigned short f2h(float f) { return __half_as_ushort(__float2half_rn(f)); }
+__device__ __forceinline__ float bf2f(unsigned short b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
+__device__ __forceinline__ unsigned short f2bf(float f) { return __bfloat16_as_ushort(__float2bfloat16_rn(f)); }
+
+// Quantizer scale of a group with absolute maximum amax (see the contract above).
+__device__ __forceinline__ float fp16_scale(float amax, float qmax) {
+  float s = __fdiv_rn(fmaxf(amax, 1e-8f), qmax);
+  s = h2f(f2h(s));
+  return fmaxf(s, FP16_TINY);
+}
+// clamp(rint(x / s), +-qmax), exact
+__device__ __forceinline__ float rq_exact(float x, float s, float qmax) {
+  return fminf(fmaxf(rintf(__fdiv_rn(x, s)), -qmax), qmax);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---- int8 -> fp32 through the mantissa (no integer->float conversion instruction) --------------------------------
+// wx = word ^ 0x80808080 holds the four codes as unsigned bytes c + 128; byte i lands in the mantissa of 2^23.
+template <int I>
+__device__ __forceinline__ float byte_to_f(uint32_t wx) {
+  return __uint_as_float(__byte_perm(wx, 0x4B000000u, 0x7540 | I)) - 8388736.0f;   // 2^23 + 128
+}
+
+// ---- int4 -> fp32, eight codes of one 32-bit word ----------------------------------------------------------------
+// Nibble i (bits 4i..4i+3, key column i of the word) is masked in place into the mantissa of 2^23, which yields
+// (u - 8) * 16^e exactly after the bias is subtracted, with e = i for i <= 4 and e = i - 5 for i = 5, 6, 7 (those
+// three come from the word shifted down by 20).  The factor 16^-e is a power of two, so it is folded exactly into
+// whatever the code is multiplied with (the read-out vector, or the scale).  Pair p holds columns 2p, 2p+1.
+__device__ __forceinline__ void unpack_nib8(uint32_t w, float2 f[4]) {
+  const uint32_t w2 = w >> 20;
+  const uint32_t K = 0x4B000000u;
+  float2 t;
+  t.x = __uint_as_float((w & 0x0000000Fu) | K);
+  t.y = __uint_as_float((w & 0x000000F0u) | K);
+  f[0] = __fadd2_rn(t, make_float2(-8388616.0f, -8388736.0f));     // 2^23 + 8, 2^23 + 8*16
+  t.x = __uint_as_float((w & 0x00000F00u) | K);
+  t.y = __uint_as_float((w & 0x0000F000u) | K);
+  f[1] = __fadd2_rn(t, make_float2(-8390656.0f, -8421376.0f));     // + 8*16^2, + 8*16^3
+  t.x = __uint_as_float((w & 0x000F0000u) | K);
+  t.y = __uint_as_float((w2 & 0x0000000Fu) | K);
+  f[2] = __fadd2_rn(t, make_float2(-8912896.0f, -8388616.0f));     // + 8*16^4, + 8
+  t.x = __uint_as_float((w2 & 0x000000F0u) | K);
+  t.y = __uint_as_float((w2 & 0x00000F00u) | K);
+  f[3] = __fadd2_rn(t, make_float2(-8388736.0f, -8390656.0f));
+}
+// 16^-e of column j (0..7) of a word, matching unpack_nib8
+__device__ __forceinline__ float nib_prescale(int j) {
+  const int e = j <= 4 ? j : j - 5;
+  return __uint_as_float(static_cast<uint32_t>(127 - 4 * e) << 23);
+}
+
+}  // namespace sqb

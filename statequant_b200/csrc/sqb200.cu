@@ -1,0 +1,198 @@
+// C ABI of statequant_b200 (see include/statequant_b200.h): argument checks, kernel selection, launch.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/statequant_b200.h"
+#include "delta_step.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+std::atomic<long long> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof g_err, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+bool pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
+int ilog2(int x) { int l = 0; while ((1 << l) < x) l++; return l; }
+bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// What the kernels support; everything else is refused before any launch.
+int check_state(const sqb_state_t* st, int kind, int* lpr_log2) {
+  if (!st) return fail(SQB_EINVAL, "state is NULL");
+  const int bits = st->bits, dk = st->dk, dv = st->dv, m = st->m, g = st->group;
+  if (bits != 4 && bits != 8 && bits != 16 && bits != 32) return fail(SQB_EINVAL, "bits %d: expected 4, 8, 16 or 32", bits);
+  if (st->buffer_bits != 8 && st->buffer_bits != 16) return fail(SQB_EINVAL, "buffer_bits %d: expected 8 or 16", st->buffer_bits);
+  if (!pow2(m) || m > 32) return fail(SQB_EINVAL, "m %d: expected a power of two <= 32", m);
+  if (st->hv <= 0 || st->hk <= 0 || st->hv % st->hk) return fail(SQB_EINVAL, "heads hv %d, hk %d: hv must be a multiple of hk", st->hv, st->hk);
+  if (kind == sqb::K_KDA && st->hv != st->hk) return fail(SQB_EINVAL, "KDA: key heads must equal value heads");
+  const int cpl = 128 / bits;
+  if (dk % cpl || !pow2(dk / cpl) || dk / cpl > 32)
+    return fail(SQB_EINVAL, "d_k %d with %d-bit codes: d_k * bits / 128 must be a power of two <= 32", dk, bits);
+  const int lpr = dk / cpl, rpp = 32 / lpr;
+  if (dv % 4 || dv <= 0) return fail(SQB_EINVAL, "d_v %d: expected a positive multiple of 4", dv);
+  if (bits <= 8) {
+    if (!pow2(g)) return fail(SQB_EINVAL, "group %d: expected a power of two", g);
+    if (st->axis_k) {
+      if (g % cpl || dk % g) return fail(SQB_EINVAL, "key-axis group %d on d_k %d with %d-bit codes: the group must be a multiple of %d and divide d_k", g, dk, bits, cpl);
+    } else {
+      if (dv % g) return fail(SQB_EINVAL, "value-axis group %d must divide d_v %d", g, dv);
+      if (g % rpp || dv % (sqb::NW * rpp)) return fail(SQB_EINVAL, "value-axis group %d, d_v %d: both must be multiples of %d rows", g, dv, rpp);
+      const int wpg = g / rpp < sqb::NW ? g / rpp : sqb::NW;
+      if (g / (rpp * wpg) > 64 / cpl) return fail(SQB_EINVAL, "value-axis group %d on d_k %d: at most %d rows per group", g, dk, (64 / cpl) * rpp * sqb::NW);
+    }
+    if (!st->SC) return fail(SQB_EINVAL, "SC is NULL for an integer state");
+  }
+  if (!st->S || !st->KB || !st->UB || !st->GB || !st->GCUR || !st->NPTR) return fail(SQB_EINVAL, "a state table pointer is NULL");
+  if (st->buffer_bits == 8 && (!st->KBS || !st->UBS)) return fail(SQB_EINVAL, "KBS / UBS are NULL for an int8 buffer");
+  if (!al16(st->S) || st->sS % 16) return fail(SQB_EINVAL, "codes table: base and per-sequence stride must be multiples of 16 bytes");
+  if ((reinterpret_cast<uintptr_t>(st->KB) & 7) || st->sKB % 8 || (reinterpret_cast<uintptr_t>(st->UB) & 7) || st->sUB % 8)
+    return fail(SQB_EINVAL, "buffer tables: base and stride must be multiples of 8 bytes");
+  if ((static_cast<long long>(m) * dk) % 8 || (static_cast<long long>(m) * dv) % 8 || (static_cast<long long>(dv) * dk * bits / 8) % 16)
+    return fail(SQB_EINVAL, "per-head sizes are not 16-byte multiples (m %d, d_k %d, d_v %d)", m, dk, dv);
+  *lpr_log2 = ilog2(lpr);
+  return 0;
+}
+
+void fill_state(sqb::StepArgs& a, const sqb_state_t* st, int lpr_log2) {
+  a.S = static_cast<uint8_t*>(st->S); a.SC = static_cast<uint8_t*>(st->SC);
+  a.KB = static_cast<uint8_t*>(st->KB); a.KBS = static_cast<uint8_t*>(st->KBS);
+  a.UB = static_cast<uint8_t*>(st->UB); a.UBS = static_cast<uint8_t*>(st->UBS);
+  a.GB = static_cast<uint8_t*>(st->GB); a.GCUR = static_cast<uint8_t*>(st->GCUR);
+  a.NPTR = static_cast<uint8_t*>(st->NPTR);
+  a.sS = st->sS; a.sSC = st->sSC; a.sKB = st->sKB; a.sKBS = st->sKBS; a.sUB = st->sUB; a.sUBS = st->sUBS;
+  a.sGB = st->sGB; a.sGC = st->sGC; a.sN = st->sN;
+  a.group = st->group; a.qbuf = st->buffer_bits == 8; a.M = st->m; a.HV = st->hv; a.HK = st->hk;
+  a.DK = st->dk; a.DV = st->dv; a.lpr_log2 = lpr_log2; a.state_f32 = 0;
+}
+
+template <int KIND, int BITS, bool AXK>
+int launch_one(const sqb::StepArgs& a, cudaStream_t stream) {
+  auto kern = sqb::delta_step_kernel<KIND, BITS, AXK>;
+  const sqb::Smem plan = sqb::smem_plan(KIND, a.DK, a.DV, a.M, 128 / BITS, 1 << a.lpr_log2);
+  const size_t smem = static_cast<size_t>(plan.total) * sizeof(float);
+  static std::atomic<size_t> configured{0};       // per instantiation
+  if (smem > 48 * 1024 && smem > configured.load()) {
+    if (smem > 200 * 1024) return fail(SQB_EINVAL, "shape needs %zu bytes of shared memory per CTA", smem);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return fail(SQB_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    configured.store(smem);
+  }
+  const long long ctas = static_cast<long long>(a.rows) * a.HV;
+  if (ctas > 2147483647LL) return fail(SQB_EINVAL, "rows * hv = %lld exceeds the grid limit", ctas);
+  kern<<<static_cast<unsigned>(ctas), sqb::NT, smem, stream>>>(a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(SQB_ECUDA, "kernel launch: %s", cudaGetErrorString(e));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return 0;
+}
+
+template <int KIND>
+int launch(const sqb::StepArgs& a, int bits, bool axk, cudaStream_t stream) {
+  switch (bits) {
+    case 4: return axk ? launch_one<KIND, 4, true>(a, stream) : launch_one<KIND, 4, false>(a, stream);
+    case 8: return axk ? launch_one<KIND, 8, true>(a, stream) : launch_one<KIND, 8, false>(a, stream);
+    case 16: return launch_one<KIND, 16, true>(a, stream);
+    case 32: return launch_one<KIND, 32, true>(a, stream);
+  }
+  return fail(SQB_ENOTBUILT, "no kernel for %d-bit states", bits);
+}
+
+int check_dtype(int dt, const char* what) {
+  if (dt < 0 || dt > 2) return fail(SQB_EINVAL, "%s: element type %d is not fp32 / bf16 / fp16", what, dt);
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* sqb_last_error(void) { return g_err; }
+int sqb_abi_version(void) { return 1; }
+int64_t sqb_launch_count(void) { return g_launches.load(); }
+
+int sqb_gdn_step(const sqb_state_t* st, const sqb_gdn_inputs_t* in, void* stream) {
+  int lpr_log2 = 0;
+  if (int rc = check_state(st, sqb::K_GDN, &lpr_log2)) return rc;
+  if (!in) return fail(SQB_EINVAL, "inputs are NULL");
+  if (in->rows <= 0) return in->rows == 0 ? 0 : fail(SQB_EINVAL, "rows %d < 0", in->rows);
+  if (!in->q || !in->k || !in->v || !in->out) return fail(SQB_EINVAL, "q, k, v or out is NULL");
+  if (in->gate ? (!in->a || !in->b || !in->A_log || !in->dt_bias) : (!in->g || !in->beta))
+    return fail(SQB_EINVAL, in->gate ? "gate inputs (a, b, A_log, dt_bias) missing" : "g / beta missing");
+  if (check_dtype(in->qk_dtype, "q/k") || check_dtype(in->v_dtype, "v") || check_dtype(in->out_dtype, "out")) return SQB_EINVAL;
+  sqb::StepArgs a;
+  memset(&a, 0, sizeof a);
+  fill_state(a, st, lpr_log2);
+  a.rows = in->rows; a.idx = in->idx;
+  a.q = static_cast<const uint8_t*>(in->q); a.sq = in->sq;
+  a.k = static_cast<const uint8_t*>(in->k); a.sk = in->sk;
+  a.v = static_cast<const uint8_t*>(in->v); a.sv = in->sv;
+  a.g = static_cast<const uint8_t*>(in->g); a.sg = in->sg;
+  a.beta = static_cast<const uint8_t*>(in->beta); a.sbeta = in->sbeta;
+  a.a = static_cast<const uint8_t*>(in->a); a.sa = in->sa;
+  a.b = static_cast<const uint8_t*>(in->b); a.sb = in->sb;
+  a.A_log = static_cast<const uint8_t*>(in->A_log); a.dt_bias = static_cast<const uint8_t*>(in->dt_bias);
+  a.out = static_cast<uint8_t*>(in->out); a.so = in->so;
+  a.dt_qk = in->qk_dtype; a.dt_v = in->v_dtype; a.dt_g = in->gb_dtype; a.dt_beta = in->gb_dtype;
+  a.dt_ab = in->ab_dtype; a.dt_alog = in->alog_dtype; a.dt_dtb = in->dtb_dtype; a.dt_out = in->out_dtype;
+  a.per_key_head = in->qk_per_key_head; a.gate = in->gate; a.scale = in->scale;
+  return launch<sqb::K_GDN>(a, st->bits, st->bits > 8 || st->axis_k, static_cast<cudaStream_t>(stream));
+}
+
+int sqb_mamba2_step(const sqb_state_t* st, const sqb_mamba2_inputs_t* in, void* stream) {
+  int lpr_log2 = 0;
+  if (int rc = check_state(st, sqb::K_M2, &lpr_log2)) return rc;
+  if (!in) return fail(SQB_EINVAL, "inputs are NULL");
+  if (in->rows <= 0) return in->rows == 0 ? 0 : fail(SQB_EINVAL, "rows %d < 0", in->rows);
+  if (!in->x || !in->dt || !in->B || !in->C || !in->A || !in->out) return fail(SQB_EINVAL, "x, dt, B, C, A or out is NULL");
+  if (check_dtype(in->x_dtype, "x") || check_dtype(in->bc_dtype, "B/C") || check_dtype(in->out_dtype, "out")) return SQB_EINVAL;
+  sqb::StepArgs a;
+  memset(&a, 0, sizeof a);
+  fill_state(a, st, lpr_log2);
+  a.rows = in->rows; a.idx = in->idx;
+  a.q = static_cast<const uint8_t*>(in->C); a.sq = in->sC;
+  a.k = static_cast<const uint8_t*>(in->B); a.sk = in->sB;
+  a.v = static_cast<const uint8_t*>(in->x); a.sv = in->sx;
+  a.g = static_cast<const uint8_t*>(in->dt); a.sg = in->sdt;
+  a.A_log = static_cast<const uint8_t*>(in->A);
+  a.beta = static_cast<const uint8_t*>(in->D);
+  a.dt_bias = static_cast<const uint8_t*>(in->dt_bias);
+  a.out = static_cast<uint8_t*>(in->out); a.so = in->so;
+  a.dt_qk = in->bc_dtype; a.dt_v = in->x_dtype; a.dt_g = in->dt_dtype; a.dt_beta = in->d_dtype;
+  a.dt_alog = in->a_dtype; a.dt_dtb = in->dtb_dtype; a.dt_out = in->out_dtype;
+  a.per_key_head = 1; a.dt_softplus = in->dt_softplus; a.dt_clamp = in->dt_clamp;
+  a.dt_min = in->dt_min; a.dt_max = in->dt_max; a.scale = 1.0f;
+  return launch<sqb::K_M2>(a, st->bits, st->bits > 8 || st->axis_k, static_cast<cudaStream_t>(stream));
+}
+
+int sqb_kda_step(const sqb_state_t* st, const sqb_kda_inputs_t* in, void* stream) {
+  int lpr_log2 = 0;
+  if (int rc = check_state(st, sqb::K_KDA, &lpr_log2)) return rc;
+  if (!in) return fail(SQB_EINVAL, "inputs are NULL");
+  if (in->rows <= 0) return in->rows == 0 ? 0 : fail(SQB_EINVAL, "rows %d < 0", in->rows);
+  if (!in->q || !in->k || !in->v || !in->g || !in->beta || !in->out) return fail(SQB_EINVAL, "q, k, v, g, beta or out is NULL");
+  if (check_dtype(in->qk_dtype, "q/k") || check_dtype(in->v_dtype, "v") || check_dtype(in->g_dtype, "g") ||
+      check_dtype(in->out_dtype, "out")) return SQB_EINVAL;
+  sqb::StepArgs a;
+  memset(&a, 0, sizeof a);
+  fill_state(a, st, lpr_log2);
+  a.rows = in->rows; a.idx = in->idx;
+  a.q = static_cast<const uint8_t*>(in->q); a.sq = in->sq;
+  a.k = static_cast<const uint8_t*>(in->k); a.sk = in->sk;
+  a.v = static_cast<const uint8_t*>(in->v); a.sv = in->sv;
+  a.g = static_cast<const uint8_t*>(in->g); a.sg = in->sg;
+  a.beta = static_cast<const uint8_t*>(in->beta); a.sbeta = in->sbeta;
+  a.out = static_cast<uint8_t*>(in->out); a.so = in->so;
+  a.dt_qk = in->qk_dtype; a.dt_v = in->v_dtype; a.dt_g = in->g_dtype; a.dt_beta = in->beta_dtype;
+  a.dt_out = in->out_dtype; a.per_key_head = 1; a.scale = in->scale;
+  return launch<sqb::K_KDA>(a, st->bits, st->bits > 8 || st->axis_k, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
