@@ -1,0 +1,340 @@
+#!/usr/bin/env python
+"""Benchmark of the fused packed-state decode step.
+
+Workload (the configuration the metric is quoted on): the 24-layer Gated DeltaNet decode stack at Qwen3.5-4B
+shapes -- 32 value heads, 16 key heads, d_k = d_v = 128, buffer length 8 with an int8 buffer -- batch 256 slots per
+GPU, bf16 activations with in-kernel gating, the state stored int8 (preset int8k: key-axis groups of 32); int4v and
+pace4 are timed as secondary variants.  Every slot is pre-warmed by random steps drawn from the same distributions.
+A "step" is one decode token for the whole batch through all 24 layers (24 launches); the metric counts
+layer-steps (one layer advancing one token for the batch) per second.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Prints one JSON line (rank 0).  With N > 1 it is launched under torchrun, one process per GPU: slots are
+independent, so each rank owns its own 256 slots and there is no data-path collective (weak scaling).
+``--impl reference`` times the CPU restatement of the reference's torch path (the oracle) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, 'tests')):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch  # noqa: E402
+
+HV, HK, DK, DV, M = 32, 16, 128, 128, 8
+LAYERS = 24
+PRESETS = {'int8k': (8, 'k', 32), 'int4v': (4, 'v', 32), 'pace4': (4, 'k', 64)}
+METRIC = 'decode layer-steps/s (24-layer GDN stack, batch 256 slots per GPU)'
+UNIT = 'layer-steps/s'
+
+
+def algorithmic_bytes(lay):
+    """Bytes one (slot, layer, step) must move, averaged over a fold period of m steps: the stored state read every
+    step and rewritten once per m, the live half of the buffer, the appended entry, counters, bf16 inputs and
+    output."""
+    b = lay.breakdown()
+    m = lay.m
+    state = (b['S'] + b.get('SC', 0)) * (1 + 1 / m)
+    buf = b['KB'] + b['UB'] + b.get('KBS', 0) + b.get('UBS', 0) + b['GB']
+    io = 2 * (2 * lay.HK * lay.DK + lay.HV * lay.DV + 2 * lay.HV) + 2 * lay.HV * lay.DV
+    total = state + buf * (m - 1) / (2 * m) + buf / m + 2 * (b['GCUR'] + b['NPTR']) + io
+    return total, state
+
+
+def make_inputs(batch, gen, device, pinned=False):
+    """One layer's activations, bf16: q, k l2-normalised N(0,1) per key head, v ~ N(0,1), gate inputs a, b."""
+    f = lambda *s: torch.randn(*s, generator=gen)                                        # noqa: E731
+    q, k = f(batch, HK, DK), f(batch, HK, DK)
+    q = q / q.norm(dim=-1, keepdim=True)
+    k = k / k.norm(dim=-1, keepdim=True)
+    t = [q.bfloat16(), k.bfloat16(), f(batch, HV, DV).bfloat16(), (f(batch, HV) + 2.0).bfloat16(), f(batch, HV).bfloat16()]
+    if pinned:
+        return [x.pin_memory() for x in t]
+    return [x.to(device) for x in t]
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while the timed region runs."""
+    Q = ('clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,'
+         'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
+         'clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.Q}', '--format=csv,noheader,nounits',
+                                          '-lms', '200', '-i', str(index)], stdout=subprocess.PIPE, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [x.strip() for x in line.split(',')]))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        time.sleep(0.25)
+        self.proc.terminate()
+        rows = [r for ts, r in self.rows if t0 <= ts <= t1 + 0.2 and len(r) >= 7] or [r for _, r in self.rows if len(r) >= 7]
+        if not rows:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['no samples']}
+        sm = sorted(float(r[0]) for r in rows)
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith('active') for r in rows)]
+        return {'sm_mhz': sm[len(sm) // 2], 'sm_max_mhz': float(rows[0][1]), 'reasons': reasons,
+                'samples': len(rows), 'power_w_max': max(float(r[2]) for r in rows)}
+
+
+def measured_peak_gbs():
+    try:
+        return float(json.load(open(os.path.join(ROOT, 'MEASURED_PEAKS.json')))['hbm_gbs']), 'measured'
+    except Exception:
+        return 6650.0, 'fallback'
+
+
+class Stack:
+    """The 24-layer stack of one preset on one GPU: blobs, resident inputs, a CUDA graph of one decode step."""
+
+    def __init__(self, preset, batch, device, seed):
+        import statequant_b200 as sq
+        from statequant_b200.kernels import SlotLayout
+        self.lay = SlotLayout(sq.Quantizer(*PRESETS[preset]), HV, HK, DK, DV, m=M, buffer_bits=8)
+        self.batch, self.device = batch, device
+        gen = torch.Generator().manual_seed(seed)
+        self.blobs = [self.lay.alloc(batch + 1, device) for _ in range(LAYERS)]
+        self.views = [self.lay.views(b) for b in self.blobs]
+        self.idx = (torch.randperm(batch, generator=gen) + 1).to(torch.int32).to(device)     # slot 0 is padding
+        self.inputs = [make_inputs(batch, gen, device) for _ in range(LAYERS)]
+        self.A_log = (torch.randn(HV, generator=gen) * 0.3).to(device)
+        self.dt_bias = torch.randn(HV, generator=gen).to(device)
+        self.outs = [torch.empty(batch, HV, DV, dtype=torch.bfloat16, device=device) for _ in range(LAYERS)]
+        self.graph = None
+
+    def step(self):
+        for l in range(LAYERS):
+            q, k, v, a, b = self.inputs[l]
+            self.lay.step(self.views[l], self.idx, q, k, v, self.outs[l], DK ** -0.5,
+                          gate=(a, b, self.A_log, self.dt_bias))
+
+    def prewarm(self, steps, gen):
+        """Random steps from the input distributions so that codes, scales and buffers hold realistic values."""
+        for t in range(steps):
+            if t % 64 == 0:                      # refresh the activations now and then
+                self.inputs = [make_inputs(self.batch, gen, self.device) for _ in range(LAYERS)]
+            self.step()
+        torch.cuda.synchronize()
+
+    def capture(self):
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self.step()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.step()
+
+    def timed(self, steps):
+        """ms for `steps` graph replays, CUDA events on the launching stream."""
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            self.graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+
+def run_e2e(stack, steps, warmup):
+    """The same stack driven through the public API from HOST buffers: every step copies that step's activations for
+    all layers from pinned host memory, launches the 24 layer steps, and reads the last layer's output back."""
+    gen = torch.Generator().manual_seed(99)
+    host = [make_inputs(stack.batch, gen, None, pinned=True) for _ in range(LAYERS)]
+    out_h = torch.empty(stack.batch, HV, DV, dtype=torch.bfloat16).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for lay_in in host for t in lay_in)
+    d2h = out_h.numel() * out_h.element_size()
+
+    def one():
+        for l in range(LAYERS):
+            for dst, src in zip(stack.inputs[l], host[l]):
+                dst.copy_(src, non_blocking=True)
+        stack.graph.replay()
+        out_h.copy_(stack.outs[-1], non_blocking=True)
+
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        one()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1), h2d, d2h
+
+
+def cpu_baseline(batch, steps, warmup, preset='int8k'):
+    """The oracle (CPU restatement of the reference's torch path) on one layer, all host threads: layer-steps/s."""
+    import statequant_b200 as sq
+    from oracle import oracle
+    from statequant_b200.kernels import SlotLayout
+    lay = SlotLayout(sq.Quantizer(*PRESETS[preset]), HV, HK, DK, DV, m=M, buffer_bits=8)
+    gen = torch.Generator().manual_seed(7)
+    blob = lay.alloc(batch + 1, 'cpu')
+    V = lay.views(blob)
+    lay.write(V, torch.arange(1, batch + 1), torch.randn(batch, HV, DV, DK, generator=gen) * 0.3)
+    idx = torch.arange(1, batch + 1, dtype=torch.int32)
+    q, k, v, a, b = make_inputs(batch, gen, 'cpu')
+    A_log, dtb = torch.randn(HV, generator=gen) * 0.3, torch.randn(HV, generator=gen)
+    out = torch.empty(batch, HV, DV, dtype=torch.bfloat16)
+    for _ in range(warmup):
+        oracle.gdn_step(lay, V, idx, q, k, v, out, DK ** -0.5, gate=(a, b, A_log, dtb))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.gdn_step(lay, V, idx, q, k, v, out, DK ** -0.5, gate=(a, b, A_log, dtb))
+    dt = time.perf_counter() - t0
+    return steps / dt, oracle.num_threads(), dt
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=128)
+    ap.add_argument('--warmup', type=int, default=8)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--batch', type=int, default=256)
+    ap.add_argument('--prewarm', type=int, default=512)
+    ap.add_argument('--preset', default='int8k', choices=list(PRESETS))
+    ap.add_argument('--no-variants', action='store_true', help='time the headline preset only')
+    args = ap.parse_args()
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    config = {'workload': f'24-layer GDN decode stack, Qwen3.5-4B shapes (HV 32, HK 16, d 128, m 8, int8 buffer), '
+                          f'state preset {args.preset}, batch {args.batch} slots per GPU, bf16 activations, in-kernel gate',
+              'layers': LAYERS, 'batch_per_gpu': args.batch, 'preset': args.preset, 'prewarm_steps': args.prewarm,
+              'l2': 'working set per step (all layers) far exceeds L2; no flush needed',
+              'sharding': 'slots sharded across GPUs, no collective'}
+
+    if args.impl == 'reference':
+        if rank != 0:
+            return
+        import __graft_entry__ as ge
+        ge.build()
+        steps = max(1, args.steps)
+        val, cores, dt = cpu_baseline(args.batch, steps, max(1, min(args.warmup, 8)), args.preset)
+        sample = f'one layer of the stack, batch {args.batch}, {steps} layer-steps, {dt:.1f} s wall'
+        print(json.dumps({
+            'impl': 'reference', 'metric': METRIC, 'value': val, 'unit': UNIT, 'n_gpus': args.gpus, 'steps': steps,
+            'warmup': args.warmup, 'ms_per_step': 1e3 / val, 'higher_is_better': True, 'scaling': 'weak',
+            'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic', 'config': config,
+            'cpu_baseline': {'value': val, 'unit': UNIT, 'cores': cores, 'kind': 'port', 'sample': sample},
+            'e2e': {'value': val, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}}))
+        return
+
+    from statequant_b200 import _cabi
+    assert torch.cuda.is_available(), 'bench.py needs a GPU (there is no CPU fallback)'
+    torch.cuda.set_device(local)
+    device = f'cuda:{local}'
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group('nccl', device_id=torch.device(device))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    results = {}
+    presets = [args.preset] + ([] if args.no_variants else [p for p in PRESETS if p != args.preset])
+    clocks = None
+    launches = 0
+    e2e = None
+    for pi, preset in enumerate(presets):
+        stack = Stack(preset, args.batch, device, seed=1234 + rank)
+        stack.prewarm(args.prewarm, torch.Generator().manual_seed(4321 + rank))
+        stack.capture()
+        for _ in range(max(3, args.warmup)):
+            stack.graph.replay()
+        barrier()
+        sampler = ClockSampler(local) if (pi == 0 and rank == 0) else None
+        t0 = time.time()
+        l0 = _cabi.launch_count()
+        ms = stack.timed(args.steps)
+        barrier()
+        t1 = time.time()
+        ms = max_over_ranks(ms)
+        if sampler is not None:
+            clocks = sampler.stop(t0, t1)
+        total, state = algorithmic_bytes(stack.lay)
+        lsteps = args.steps * LAYERS
+        per_launch_s = ms * 1e-3 / lsteps
+        results[preset] = {'layer_steps_per_s': world * lsteps / (ms * 1e-3), 'us_per_layer_step': per_launch_s * 1e6,
+                           'ms_per_step': ms / args.steps,
+                           'total_gbs_per_gpu': args.batch * total / per_launch_s / 1e9,
+                           'state_gbs_per_gpu': args.batch * state / per_launch_s / 1e9,
+                           'bytes_per_slot_layer_step': total}
+        if pi == 0:
+            launches = args.steps * LAYERS
+            barrier()
+            ems, h2d, d2h = run_e2e(stack, max(1, min(args.steps, 32)), 3)
+            esteps = max(1, min(args.steps, 32))
+            ems = max_over_ranks(ems)
+            e2e = {'value': world * esteps * LAYERS / (ems * 1e-3), 'unit': UNIT, 'h2d_bytes_per_step': h2d,
+                   'd2h_bytes_per_step': d2h, 'steps': esteps,
+                   'note': 'per step: all 24 layers\' activations copied from pinned host memory, last layer\'s output read back'}
+        del stack
+        torch.cuda.empty_cache()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    head = results[args.preset]
+    peak, which = measured_peak_gbs()
+    line = {
+        'metric': METRIC, 'value': head['layer_steps_per_s'], 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
+        'warmup': max(3, args.warmup), 'ms_per_step': head['ms_per_step'], 'higher_is_better': True, 'scaling': 'weak',
+        'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic', 'config': config,
+        'us_per_layer_step': head['us_per_layer_step'],
+        'state_gbs_per_gpu': head['state_gbs_per_gpu'], 'state_frac_of_8tbs': head['state_gbs_per_gpu'] / 8000.0,
+        'total_frac_of_8tbs': head['total_gbs_per_gpu'] / 8000.0,
+        'roofline': {'bound': 'hbm', 'achieved': head['total_gbs_per_gpu'], 'peak': peak, 'unit': 'GB/s',
+                     'frac': head['total_gbs_per_gpu'] / peak, 'traffic': None, 'peak_source': which,
+                     'kernel': 'delta_step_kernel<GDN>', 'algorithmic_bytes_per_launch': args.batch * head['bytes_per_slot_layer_step']},
+        'variants': results, 'clocks': clocks, 'e2e': e2e, 'gpu_launches': launches,
+    }
+    if world == 1:
+        import __graft_entry__ as ge
+        ge.build()
+        v, cores, dt = cpu_baseline(args.batch, 16, 4, args.preset)
+        line['cpu_baseline'] = {'value': v, 'unit': UNIT, 'cores': cores, 'kind': 'port',
+                                'sample': f'one layer of the stack, batch {args.batch}, 16 layer-steps after 4 warm-up, {dt:.1f} s wall'}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

@@ -80,3 +80,94 @@ def nibble_steps(a, b):
 
 def load_golden(name):
     return dict(np.load(os.path.join(GOLDEN, name + '.npz')))
+
+
+def _tt(a, dev):
+    t = torch.from_numpy(a)
+    return t.to(dev)
+
+
+def replay_vs_golden(name, c, oracle=None, device='cpu', act_dtype=torch.float32):
+    """Step a blob through the oracle (``oracle`` given) or the CUDA kernels (``oracle=None``) and compare every
+    step with the reference's golden record, adopting the golden buffer entry / folded codes after each comparison
+    (so a rounding flip is counted once).  Returns the statistics dict; structural properties are asserted here."""
+    from cases import make_inputs
+    G = load_golden(name)
+    inp = make_inputs(c)
+    lay = layout_of(c)
+    B, hv, hk, dk, dv, m, T = c['B'], c['hv'], c['hk'], c['dk'], c['dv'], c['m'], c['T']
+    raw, blob = fresh_blob(lay, B + 2, seed=c['seed'], pad=64)
+    raw = raw.to(device)
+    blob = raw[:, 64:64 + lay.nbytes]
+    V = lay.views(blob)
+    sl = torch.arange(1, B + 1, device=device)
+    lay.write(V, sl, inp['S0'].view(B, hv, dv, dk).to(device))
+    codes0 = torch.from_numpy(G['codes0'])
+    if codes0.dtype == torch.int16:
+        codes0 = codes0.view(torch.bfloat16)
+    assert torch.equal(V['S'][sl].reshape(codes0.shape).cpu(), codes0)
+    idx = torch.arange(1, B + 1, dtype=torch.int32, device=device)
+    before = raw.clone()
+    st = dict(worst=0., flips=0, nbuf=0, cflips=0, ncodes=0, sflips=0)
+    folds = list(G['fold_t'])
+    soft = c['kind'] == 'm2' and c.get('softplus', True)
+    for t in range(T):
+        n = int(V['NPTR'][1, 0])
+        out = torch.full((B, hv, dv), 7., device=device)
+        a = {k: v.to(device) for k, v in step_args(c, inp, t, act_dtype).items()}
+        run_step(c, lay, V, idx, a, out, inp, oracle=oracle)
+        want = _tt(G['o'][t], device).view(B, hv, dv)
+        st['worst'] = max(st['worst'], ((out - want).abs().max() / want.abs().max()).item())
+        kc, uc = _tt(G['Kc'][t], device), _tt(G['Uc'][t], device)
+        if c['bb'] == 16:
+            kc, uc = kc.view(torch.bfloat16), uc.view(torch.bfloat16)
+        st['flips'] += int((V['KB'][sl, :, n].reshape(kc.shape) != kc).sum()) + \
+            int((V['UB'][sl, :, n].reshape(uc.shape) != uc).sum())
+        st['nbuf'] += kc.numel() + uc.numel()
+        if c['bb'] == 8:
+            st['sflips'] += int((V['KBS'][sl, :, n].reshape(-1) != _tt(G['Ks'][t], device).reshape(-1)).sum())
+            st['sflips'] += int((V['UBS'][sl, :, n].reshape(-1) != _tt(G['Us'][t], device).reshape(-1)).sum())
+        gb, gw = V['GB'][sl, :, n].reshape(-1), _tt(G['G'][t], device).reshape(-1)
+        if soft or oracle is None:
+            # a decay that comes out of exp / log (in-kernel softplus) or is read back from the device differs from
+            # torch's in the last place at most; the additions themselves are the same
+            assert torch.allclose(gb, gw, rtol=2e-6, atol=1e-12), (gb - gw).abs().max()
+        if not soft:
+            assert torch.equal(gb, gw)
+        V['GB'][sl, :, n] = gw.view(V['GB'][sl, :, n].shape)
+        if soft and t not in folds:
+            V['GCUR'][sl] = gw.view(V['GCUR'][sl].shape)
+        V['KB'][sl, :, n] = kc.view(B, hk, dk)
+        V['UB'][sl, :, n] = uc.view(B, hv, dv)
+        if c['bb'] == 8:
+            V['KBS'][sl, :, n] = _tt(G['Ks'][t], device).view(B, hk)
+            V['UBS'][sl, :, n] = _tt(G['Us'][t], device).view(B, hv)
+        if t in folds:
+            fi = folds.index(t)
+            assert int(V['NPTR'][1, 0]) == 0 and float(V['GCUR'][sl].abs().max()) == 0.
+            gc = torch.from_numpy(G['codes'][fi])
+            if gc.dtype == torch.int16:
+                gc = gc.view(torch.bfloat16)
+            gc = gc.to(device)
+            st['cflips'] += int((V['S'][sl].reshape(gc.shape) != gc).sum())
+            st['ncodes'] += gc.numel()
+            V['S'][sl] = gc.view(V['S'][sl].shape)
+            if 'SC' in V:
+                gs = _tt(G['scales'][fi], device)
+                st['sflips'] += int((V['SC'][sl].reshape(gs.shape) != gs).sum())
+                V['SC'][sl] = gs.view(V['SC'][sl].shape)
+        assert torch.equal(V['NPTR'][sl, :hv].cpu(), torch.full((B, hv), (n + 1) % m, dtype=torch.int32))
+    assert len(folds) == T // m
+    keep = torch.ones_like(raw, dtype=torch.bool)
+    keep[1:B + 1, 64:64 + lay.nbytes] = False
+    assert torch.equal(raw[keep], before[keep]), 'bytes outside the live slots were written'
+    return st
+
+
+def check_stats(name, st, o_tol=2e-5):
+    print(f"\n[{name}] max rel |o - o_ref| {st['worst']:.2e}; buffer entries flipped {st['flips']}/{st['nbuf']}; "
+          f"codes differing after folds {st['cflips']}/{st['ncodes']}; scales differing {st['sflips']}")
+    assert st['worst'] < o_tol, st['worst']
+    assert st['flips'] <= max(1, 1e-4 * st['nbuf']), st['flips']
+    assert st['cflips'] <= max(1, 1e-4 * st['ncodes']), st['cflips']
+    assert st['sflips'] <= max(1, 1e-4 * max(st['ncodes'], 1)), st['sflips']

@@ -6,12 +6,11 @@ appended to the buffer and the codes / scales it wrote at a fold are compared by
 against the reference's thresholds (<= 1e-4 of entries: fp32 sums that associate differently can move a value
 across a rounding boundary), and the golden entry is adopted so that one flip is counted once.
 """
-import numpy as np
 import pytest
 import torch
 
-from cases import CASES, PACK_CASES, make_inputs, pack_input
-from harness import field_diff, fresh_blob, layout_of, load_golden, run_step, step_args
+from cases import CASES, PACK_CASES, pack_input
+from harness import check_stats, field_diff, fresh_blob, layout_of, load_golden, replay_vs_golden
 from oracle import oracle
 
 import statequant_b200 as sq
@@ -35,90 +34,9 @@ def test_pack_matches_reference(bits, axis, group, dk, dv):
     assert torch.equal(x.transpose(1, 2), sq.Quantizer(bits, axis, group, scale_dtype='fp16').fake(S.transpose(1, 2)))
 
 
-def _adopt_entry(c, lay, V, sl, n, G, t):
-    B, hv, hk, dk, dv = c['B'], c['hv'], c['hk'], c['dk'], c['dv']
-    kc, uc = torch.from_numpy(G['Kc'][t]), torch.from_numpy(G['Uc'][t])
-    if c['bb'] == 16:
-        kc, uc = kc.view(torch.bfloat16), uc.view(torch.bfloat16)
-    V['KB'][sl, :, n] = kc.view(B, hk, dk)
-    V['UB'][sl, :, n] = uc.view(B, hv, dv)
-    if c['bb'] == 8:
-        V['KBS'][sl, :, n] = torch.from_numpy(G['Ks'][t]).view(B, hk)
-        V['UBS'][sl, :, n] = torch.from_numpy(G['Us'][t]).view(B, hv)
-
-
 @pytest.mark.parametrize('name', list(CASES))
 def test_decode_matches_reference(name):
-    c = CASES[name]
-    G = load_golden(name)
-    inp = make_inputs(c)
-    lay = layout_of(c)
-    B, hv, hk, dk, dv, m, T = c['B'], c['hv'], c['hk'], c['dk'], c['dv'], c['m'], c['T']
-    raw, blob = fresh_blob(lay, B + 2, seed=c['seed'], pad=64)
-    V = lay.views(blob)
-    sl = torch.arange(1, B + 1)
-    lay.write(V, sl, inp['S0'].view(B, hv, dv, dk))
-    codes0 = torch.from_numpy(G['codes0'])
-    if codes0.dtype == torch.int16:
-        codes0 = codes0.view(torch.bfloat16)
-    assert torch.equal(V['S'][sl].reshape(codes0.shape), codes0)
-    idx = torch.arange(1, B + 1, dtype=torch.int32)
-    before = raw.clone()
-    worst, flips, nbuf, cflips, ncodes, sflips = 0., 0, 0, 0, 0, 0
-    folds = list(G['fold_t'])
-    for t in range(T):
-        n = int(V['NPTR'][1, 0])
-        out = torch.full((B, hv, dv), 7.)
-        run_step(c, lay, V, idx, step_args(c, inp, t), out, inp, oracle=oracle)
-        want = torch.from_numpy(G['o'][t]).view(B, hv, dv)
-        worst = max(worst, ((out - want).abs().max() / want.abs().max()).item())
-        # the appended entry, as stored
-        kc, uc = torch.from_numpy(G['Kc'][t]), torch.from_numpy(G['Uc'][t])
-        if c['bb'] == 16:
-            kc, uc = kc.view(torch.bfloat16), uc.view(torch.bfloat16)
-        flips += int((V['KB'][sl, :, n].reshape(kc.shape) != kc).sum()) + int((V['UB'][sl, :, n].reshape(uc.shape) != uc).sum())
-        nbuf += kc.numel() + uc.numel()
-        if c['bb'] == 8:
-            assert torch.equal(V['KBS'][sl, :, n].reshape(-1), torch.from_numpy(G['Ks'][t]).reshape(-1))
-            sflips += int((V['UBS'][sl, :, n].reshape(-1) != torch.from_numpy(G['Us'][t]).reshape(-1)).sum())
-        # cumulative decay: the same fp32 additions, bit for bit, unless the decay itself comes out of an in-kernel
-        # softplus (libm's and torch's exp / log differ in the last place)
-        gb, gw = V['GB'][sl, :, n].reshape(-1), torch.from_numpy(G['G'][t]).reshape(-1)
-        if c['kind'] == 'm2' and c.get('softplus', True):
-            assert torch.allclose(gb, gw, rtol=2e-6, atol=0), (gb - gw).abs().max()
-            V['GB'][sl, :, n] = gw.view(V['GB'][sl, :, n].shape)
-            if t not in folds:
-                V['GCUR'][sl] = gw.view(V['GCUR'][sl].shape)
-        else:
-            assert torch.equal(gb, gw)
-        _adopt_entry(c, lay, V, sl, n, G, t)
-        if t in folds:
-            fi = folds.index(t)
-            assert int(V['NPTR'][1, 0]) == 0 and float(V['GCUR'][sl].abs().max()) == 0.
-            gc = torch.from_numpy(G['codes'][fi])
-            if gc.dtype == torch.int16:
-                gc = gc.view(torch.bfloat16)
-            cflips += int((V['S'][sl].reshape(gc.shape) != gc).sum())
-            ncodes += gc.numel()
-            V['S'][sl] = gc.view(V['S'][sl].shape)
-            if 'SC' in V:
-                gs = torch.from_numpy(G['scales'][fi])
-                sflips += int((V['SC'][sl].reshape(gs.shape) != gs).sum())
-                V['SC'][sl] = gs.view(V['SC'][sl].shape)
-        else:
-            assert int(V['NPTR'][1, 0]) == (n + 1) % m
-        assert torch.equal(V['NPTR'][sl, :hv], torch.full((B, hv), (n + 1) % m, dtype=torch.int32))
-    print(f'\n[{name}] max rel |o - o_ref| {worst:.2e}; buffer entries flipped {flips}/{nbuf}; codes differing after '
-          f'folds {cflips}/{ncodes}; scales differing {sflips}')
-    assert len(folds) == T // m
-    assert worst < 2e-5, worst
-    assert flips <= max(1, 1e-4 * nbuf), flips
-    assert cflips <= max(1, 1e-4 * ncodes), cflips
-    assert sflips <= max(1, 1e-4 * ncodes), sflips
-    # nothing outside the live slots was written (slot 0, the spare slot, the padding around each slot)
-    keep = torch.ones_like(raw, dtype=torch.bool)
-    keep[1:B + 1, 64:64 + lay.nbytes] = False
-    assert torch.equal(raw[keep], before[keep])
+    check_stats(name, replay_vs_golden(name, CASES[name], oracle=oracle))
 
 
 @pytest.mark.parametrize('name', ['gdn_int4k32_m8_b8', 'kda_int4k32_m8_b8', 'm2_int8k32_m8_b8'])

@@ -1,0 +1,365 @@
+"""Parity of the sm_100a decode step with the reference, on a B200: against the reference's golden vectors and
+against the CPU oracle on the same blob bytes, through the C ABI (``layout.step`` -> ``sqb_*_step``)."""
+import pytest
+import torch
+
+from cases import CASES, make_inputs
+from harness import (check_stats, field_diff, fresh_blob, layout_of, replay_vs_golden, run_step, step_args)
+from oracle import oracle
+
+import statequant_b200 as sq
+from statequant_b200.kernels import (KDASlotLayout, Mamba2SlotLayout, PackedGDNState, PackedKDAState,
+                                     PackedMamba2State, SlotLayout)
+
+pytestmark = pytest.mark.gpu
+DEV = 'cuda'
+
+
+@pytest.mark.parametrize('name', list(CASES))
+def test_decode_matches_reference_golden(name):
+    """The CUDA step against the reference's golden record (re-sync protocol of the reference's own tests)."""
+    check_stats(name, replay_vs_golden(name, CASES[name], oracle=None, device=DEV))
+
+
+def _oracle_lockstep(c, T, act_dtype, seed_slots=7, gate=False):
+    """Step the same blob through CUDA and through the oracle from identical pre-step bytes, every step; compare
+    outputs and every blob field; continue from the CUDA blob.  Slots are a random subset with padding rows."""
+    inp = make_inputs(dict(c, T=T))
+    lay = layout_of(c)
+    B, hv, hk, dk, dv, m = c['B'], c['hv'], c['hk'], c['dk'], c['dv'], c['m']
+    n_slots = 9
+    raw, blob = fresh_blob(lay, n_slots, seed=seed_slots, pad=32)
+    Vh = lay.views(blob)
+    gen = torch.Generator().manual_seed(seed_slots)
+    live = (torch.randperm(n_slots - 1, generator=gen)[:B] + 1)
+    lay.write(Vh, live, inp['S0'].view(B, hv, dv, dk))
+    for s in live.tolist():                                   # sequences at different buffer positions
+        Vh['NPTR'][s] = int(torch.randint(0, m, (1,), generator=gen))
+        # their live buffer entries must be sane numbers (garbage may hold NaN patterns); dead ones stay garbage
+        n = int(Vh['NPTR'][s, 0])
+        Vh['GB'][s][:, :n] = -torch.rand(Vh['GB'][s][:, :n].shape, generator=gen) * 0.3
+        Vh['GCUR'][s] = -torch.rand(Vh['GCUR'][s].shape, generator=gen) * 0.1 - 0.3
+        if c['bb'] == 8:
+            Vh['KBS'][s][:, :n] = (torch.rand(Vh['KBS'][s][:, :n].shape, generator=gen) * 0.01 + 1e-3).half()
+            Vh['UBS'][s][:, :n] = (torch.rand(Vh['UBS'][s][:, :n].shape, generator=gen) * 0.02 + 1e-3).half()
+        else:
+            Vh['KB'][s][:, :n] = (torch.randn(Vh['KB'][s][:, :n].shape, generator=gen) * 0.1).bfloat16()
+            Vh['UB'][s][:, :n] = (torch.randn(Vh['UB'][s][:, :n].shape, generator=gen)).bfloat16()
+    rawd = raw.to(DEV)
+    blobd = rawd[:, 32:32 + lay.nbytes]
+    Vd = lay.views(blobd)
+    rows = B + 2
+    st = dict(worst=0., buf=0, nbuf=0, codes=0, ncodes=0, scal=0)
+    for t in range(T):
+        perm = torch.randperm(rows, generator=gen)
+        idx_l = [0] * rows
+        src = [None] * rows
+        order = live[torch.randperm(B, generator=gen)].tolist()
+        for j, r in enumerate(perm.tolist()):
+            if j < B:
+                idx_l[r], src[r] = order[j], j
+            else:
+                idx_l[r] = 0 if j == B else -1
+        idx = torch.tensor(idx_l, dtype=torch.int32)
+        a = step_args(c, inp, t, act_dtype)
+        # scatter the B activations into the padded batch
+        ap = {}
+        for k_, v_ in a.items():
+            full = torch.zeros(rows, *v_.shape[1:], dtype=v_.dtype)
+            for r in range(rows):
+                if src[r] is not None:
+                    full[r] = v_[src[r]]
+            ap[k_] = full
+        odt = torch.float32 if act_dtype == torch.float32 else act_dtype
+        out_h = torch.full((rows, hv, dv), 7., dtype=odt)
+        out_d = torch.full((rows, hv, dv), 7., dtype=odt, device=DEV)
+        pre = raw.clone()
+        run_step(c, lay, Vh, idx, ap, out_h, inp, oracle=oracle)
+        run_step(c, lay, Vd, idx.to(DEV), {k_: v_.to(DEV) for k_, v_ in ap.items()}, out_d, inp)
+        got = rawd.cpu()
+        o_d, o_h = out_d.cpu().float(), out_h.float()
+        for r in range(rows):
+            if src[r] is None:
+                assert torch.equal(o_d[r], torch.zeros_like(o_d[r]))
+        den = o_h.abs().max()
+        st['worst'] = max(st['worst'], ((o_d - o_h).abs().max() / den).item())
+        d = field_diff(lay, got[:, 32:32 + lay.nbytes], blob, live.tolist())
+        st['buf'] += d['KB'] + d['UB']
+        st['nbuf'] += B * (hk * dk + hv * dv)
+        st['scal'] += d.get('KBS', 0) + d.get('UBS', 0) + d.get('SC', 0)
+        st['codes'] += d['S']
+        st['ncodes'] += B * hv * dv * dk
+        assert d['NPTR'] == 0, d
+        if not (c['kind'] == 'm2' and c.get('softplus', True)) and not gate:
+            assert d['GB'] == 0 and d['GCUR'] == 0, d
+        # everything outside the live slots is untouched on the device
+        keep = torch.ones_like(raw, dtype=torch.bool)
+        for s in live.tolist():
+            keep[s, 32:32 + lay.nbytes] = False
+        assert torch.equal(got[keep], pre[keep]), 'bytes outside live slots changed'
+        raw.copy_(got)                                          # re-sync: continue from the device's bytes
+    return st
+
+
+@pytest.mark.parametrize('name', list(CASES))
+@pytest.mark.parametrize('act', ['fp32', 'bf16'])
+def test_step_matches_oracle_on_slots(name, act):
+    c = CASES[name]
+    act_dtype = torch.float32 if act == 'fp32' else torch.bfloat16
+    st = _oracle_lockstep(c, T=2 * c['m'] + 3, act_dtype=act_dtype)
+    print(f"\n[{name} {act}] max rel |o - o_oracle| {st['worst']:.2e}; buffer bytes differing {st['buf']}/{st['nbuf']}; "
+          f"code bytes differing {st['codes']}/{st['ncodes']}; scales differing {st['scal']}")
+    # bf16 outputs: both sides round the same fp32 value to bf16, so a last-place difference shows as one bf16 ulp
+    assert st['worst'] < (2e-5 if act == 'fp32' else 1e-2), st['worst']
+    assert st['buf'] <= max(1, 1e-4 * st['nbuf']), st
+    assert st['codes'] <= max(1, 1e-4 * st['ncodes']), st
+    assert st['scal'] <= max(1, 1e-4 * st['ncodes']), st
+
+
+def test_gdn_in_kernel_gate_matches_oracle():
+    c = dict(CASES['gdn_pace4_qwen'])
+    inp = make_inputs(c)
+    lay = layout_of(c)
+    B, hv, hk, dk, dv = c['B'], c['hv'], c['hk'], c['dk'], c['dv']
+    raw, blob = fresh_blob(lay, 4, seed=5)
+    Vh = lay.views(blob)
+    sl = torch.tensor([2])
+    lay.write(Vh, sl, inp['S0'].view(B, hv, dv, dk))
+    blobd = blob.to(DEV)
+    Vd = lay.views(blobd)
+    g = torch.Generator().manual_seed(9)
+    A_log = torch.randn(hv, generator=g) * 0.5
+    dt_bias = torch.randn(hv, generator=g).bfloat16()
+    idx = torch.tensor([2], dtype=torch.int32)
+    for t in range(10):
+        a = torch.randn(B, hv, generator=g).bfloat16()
+        bb = torch.randn(B, hv, generator=g).bfloat16()
+        q, k, v = inp['q'][t].bfloat16(), inp['k'][t].bfloat16(), inp['v'][t].bfloat16()
+        oh = torch.empty(B, hv, dv)
+        od = torch.empty(B, hv, dv, device=DEV)
+        oracle.gdn_step(lay, Vh, idx, q, k, v, oh, dk ** -0.5, gate=(a, bb, A_log, dt_bias))
+        lay.step(Vd, idx.to(DEV), q.to(DEV), k.to(DEV), v.to(DEV), od, dk ** -0.5,
+                 gate=(a.to(DEV), bb.to(DEV), A_log.to(DEV), dt_bias.to(DEV)))
+        assert ((od.cpu() - oh).abs().max() / oh.abs().max()).item() < 2e-5
+        d = field_diff(lay, blobd.cpu(), blob, [2])
+        assert d['S'] + d['KB'] + d['UB'] <= 2, d
+        blob.copy_(blobd.cpu())
+    # and the gate path agrees with passing g, beta computed in torch (reference: tests/test_slots.py:153-171)
+    gt = -A_log.exp() * torch.nn.functional.softplus(a.float() + dt_bias.float())
+    bt = bb.float().sigmoid()
+    b1, b2 = blobd.clone(), blobd.clone()
+    o1, o2 = torch.empty(B, hv, dv, device=DEV), torch.empty(B, hv, dv, device=DEV)
+    lay.step(lay.views(b1), idx.to(DEV), q.to(DEV), k.to(DEV), v.to(DEV), o1, dk ** -0.5, g=gt.to(DEV), beta=bt.to(DEV))
+    lay.step(lay.views(b2), idx.to(DEV), q.to(DEV), k.to(DEV), v.to(DEV), o2, dk ** -0.5,
+             gate=(a.to(DEV), bb.to(DEV), A_log.to(DEV), dt_bias.to(DEV)))
+    assert torch.allclose(o1, o2, rtol=1e-5, atol=1e-5), (o1 - o2).abs().max()
+
+
+@pytest.mark.parametrize('name', ['gdn_pace4_qwen', 'gdn_int4v32_m8_b8', 'm2_int8k32_m8_b8', 'kda_pace4'])
+def test_lockstep_container_equals_slot_path(name):
+    """PackedGDNState / PackedMamba2State / PackedKDAState (contiguous tables, identity slot map) give the same
+    bytes as the slot layout stepping the same sequences."""
+    c = CASES[name]
+    inp = make_inputs(c)
+    lay = layout_of(c)
+    B, hv, hk, dk, dv, m = c['B'], c['hv'], c['hk'], c['dk'], c['dv'], c['m']
+    fmt = sq.Quantizer(*c['fmt'])
+    blob = lay.alloc(B + 1, DEV)
+    V = lay.views(blob)
+    sl = torch.arange(1, B + 1, device=DEV)
+    S0 = inp['S0'].to(DEV)
+    lay.write(V, sl, S0.view(B, hv, dv, dk))
+    if c['kind'] == 'gdn':
+        ker = PackedGDNState(S0.transpose(1, 2), fmt, m=m, hv=hv, hk=hk, buffer_bits=c['bb'], out_dtype=torch.float32)
+    elif c['kind'] == 'm2':
+        ker = PackedMamba2State(S0, fmt, m=m, hv=hv, hk=hk, buffer_bits=c['bb'], out_dtype=torch.float32)
+    else:
+        ker = PackedKDAState(S0, fmt, m=m, hv=hv, buffer_bits=c['bb'], out_dtype=torch.float32)
+    assert torch.equal(ker.codes.view(B, *V['S'].shape[1:]), V['S'][sl])
+    idx = torch.arange(1, B + 1, dtype=torch.int32, device=DEV)
+    for t in range(c['T']):
+        a = {k_: v_.to(DEV) for k_, v_ in step_args(c, inp, t).items()}
+        out = torch.empty(B, hv, dv, device=DEV)
+        run_step(c, lay, V, idx, a, out, inp)
+        if c['kind'] == 'gdn':
+            o = ker.step(a['q'].reshape(B * hk, dk), a['k'].reshape(B * hk, dk), a['v'].reshape(B * hv, dv),
+                         a['g'].reshape(-1), a['beta'].reshape(-1), dk ** -0.5)
+        elif c['kind'] == 'm2':
+            o = ker.step(a['x'], a['dt'], a['B'], a['C'], inp['A'].to(DEV), inp['D'].to(DEV), inp['dt_bias'].to(DEV),
+                         dt_softplus=True)
+        else:
+            o = ker.step(a['q'], a['k'], a['v'], a['g'], a['beta'], dk ** -0.5)
+        assert torch.equal(o.reshape(B, hv, dv), out), t
+        assert ker.n == int(V['NPTR'][1, 0]) == (t + 1) % m
+    assert torch.equal(ker.codes.view(B, *V['S'].shape[1:]), V['S'][sl])
+    assert torch.equal(ker.scales.view(B, *V['SC'].shape[1:]), V['SC'][sl])
+    assert torch.equal(ker.UB.view(B, *V['UB'].shape[1:]), V['UB'][sl])
+    assert torch.equal(ker.KB.view(B, *V['KB'].shape[1:]), V['KB'][sl])
+
+
+def test_gdn_q_k_per_value_head():
+    """q, k handed per value head [B * hv, d_k] (the lockstep container's other input form) equal the per-key-head
+    form when the value heads of a group share them (reference: tests/test_kernels.py:137-150)."""
+    c = CASES['gdn_pace4_qwen']
+    inp = make_inputs(c)
+    B, hv, hk, dk, dv = c['B'], c['hv'], c['hk'], c['dk'], c['dv']
+    S0 = inp['S0'].to(DEV).transpose(1, 2)
+    fmt = sq.Quantizer(*c['fmt'])
+    a = PackedGDNState(S0, fmt, m=8, hv=hv, hk=hk, out_dtype=torch.float32)
+    b = PackedGDNState(S0, fmt, m=8, hv=hv, hk=hk, out_dtype=torch.float32)
+    for t in range(10):
+        qh, kh = inp['q'][t].to(DEV).reshape(B * hk, dk), inp['k'][t].to(DEV).reshape(B * hk, dk)
+        qf = qh.reshape(B, hk, 1, dk).expand(-1, -1, hv // hk, -1).reshape(B * hv, dk).contiguous()
+        kf = kh.reshape(B, hk, 1, dk).expand(-1, -1, hv // hk, -1).reshape(B * hv, dk).contiguous()
+        v, g, be = inp['v'][t].to(DEV).reshape(B * hv, dv), inp['g'][t].to(DEV).reshape(-1), inp['beta'][t].to(DEV).reshape(-1)
+        oa = a.step(qf, kf, v, g, be, dk ** -0.5).clone()
+        ob = b.step(qh, kh, v, g, be, dk ** -0.5).clone()
+        assert torch.equal(oa, ob)
+    assert torch.equal(a.codes, b.codes) and torch.equal(a.KB, b.KB)
+
+
+@pytest.mark.parametrize('name', ['gdn_pace4_qwen', 'm2_int8k32_m8_b8', 'kda_pace4'])
+def test_cuda_graph_replay_equals_eager(name):
+    """One captured padded batch replayed with changing slot tables and inputs gives the bytes of eager launches
+    (reference: tests/test_slots.py:174-207)."""
+    c = CASES[name]
+    inp = make_inputs(dict(c, T=24))
+    lay = layout_of(c)
+    B, hv, hk, dk, dv = c['B'], c['hv'], c['hk'], c['dk'], c['dv']
+    n_slots, rows = 6, 4
+    blob = lay.alloc(n_slots, DEV)
+    V = lay.views(blob)
+    g = torch.Generator().manual_seed(4)
+    S = torch.randn(n_slots - 1, hv, dv, dk, generator=g).to(DEV) * 0.5
+    lay.write(V, torch.arange(1, n_slots, device=DEV), S)
+    blob_e = blob.clone()
+    Ve = lay.views(blob_e)
+    idx = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    a0 = step_args(c, inp, 0)
+    stat = {k_: torch.zeros(rows, *v_.shape[1:], dtype=v_.dtype, device=DEV) for k_, v_ in a0.items()}
+    out = torch.zeros(rows, hv, dv, device=DEV)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        run_step(c, lay, V, idx, stat, out, inp)               # all rows padding: nothing touched
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    assert torch.equal(blob, blob_e)
+    G = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(G):
+        run_step(c, lay, V, idx, stat, out, inp)
+    tables = [[5, 2, 3, 0], [2, 0, 0, -1], [3, 5, 0, 0], [5, 3, 2, 1], [0, 0, 0, 0]] * 4
+    for t, tab in enumerate(tables):
+        idx.copy_(torch.tensor(tab, dtype=torch.int32))
+        a = step_args(c, inp, t)
+        for k_, v_ in a.items():
+            reps = -(-rows // v_.shape[0])
+            stat[k_].copy_(v_.repeat(reps, *([1] * (v_.dim() - 1)))[:rows])
+        G.replay()
+        oe = torch.zeros_like(out)
+        run_step(c, lay, Ve, idx, stat, oe, inp)
+        torch.cuda.synchronize()
+        assert torch.equal(out, oe), t
+    assert torch.equal(blob, blob_e)
+    assert len({int(V['NPTR'][s_, 0]) for s_ in (1, 2, 3, 5)}) > 1        # counters diverged
+
+
+def test_fp32_state_slot():
+    """The unpacked fp32 slot ('fp32' format): write stores S exactly, the step folds in fp32, read() predicts the
+    step after a fold (reference: tests/test_slots.py:219-251)."""
+    hv, hk, D, m = 4, 2, 128, 4
+    lay = SlotLayout('fp32', hv, hk, D, D, m=m, buffer_bits=8)
+    blob = torch.randint(0, 256, (8, lay.nbytes), dtype=torch.uint8).to(DEV)
+    V = lay.views(blob)
+    idx = torch.tensor([5, 2], dtype=torch.int32, device=DEV)
+    g0 = torch.Generator().manual_seed(2)
+    S = (torch.randn(2, hv, D, D, generator=g0) * 0.5).to(DEV)
+    lay.write(V, idx, S)
+    assert torch.equal(V['S'][idx.long()], S)
+    for t in range(2 * m + 1):
+        q, k = (torch.randn(2, hk, D, generator=g0).to(DEV) for _ in range(2))
+        v = torch.randn(2, hv, D, generator=g0).to(DEV)
+        gg = (-torch.rand(2, hv, generator=g0) * 0.08).to(DEV)
+        beta = torch.rand(2, hv, generator=g0).sigmoid().to(DEV)
+        out = torch.empty(2, hv, D, device=DEV)
+        if t == 2 * m:
+            St = lay.read(V, idx)
+            qn = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * D ** -0.5
+            kn = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+            qx, kx = qn.repeat_interleave(hv // hk, 1), kn.repeat_interleave(hv // hk, 1)
+            a = gg.exp()[..., None]
+            u = beta[..., None] * (v - a * torch.einsum('phvk,phk->phv', St, kx))
+            o_pred = a * torch.einsum('phvk,phk->phv', St, qx) + (qx * kx).sum(-1, keepdim=True) * u
+        lay.step(V, idx, q, k, v, out, D ** -0.5, g=gg, beta=beta)
+        if t == 2 * m - 1:
+            Sf = V['S'][idx.long()]
+            assert int(V['NPTR'][5, 0]) == 0
+            assert not torch.equal(Sf, Sf.bfloat16().float())
+    assert ((out - o_pred).norm() / o_pred.norm()).item() < 1e-5
+
+
+def test_full_batch_properties_qwen_shapes():
+    """BASELINE-size batch (256 rows x 32 value heads, pace4): determinism, padding rows, a sample of rows against
+    the oracle, and the fold period (all counters wrap together)."""
+    hv, hk, D, m, B = 32, 16, 128, 8, 256
+    lay = SlotLayout(sq.Quantizer(4, 'k', 64), hv, hk, D, D, m=m)
+    g0 = torch.Generator().manual_seed(1)
+    blob = lay.alloc(B + 1, DEV)
+    V = lay.views(blob)
+    S = torch.randn(B, hv, D, D, generator=g0) * 0.3
+    lay.write(V, torch.arange(1, B + 1, device=DEV), S.to(DEV))
+    idx = (torch.randperm(B, generator=g0) + 1).to(torch.int32)
+    idx[::17] = 0
+    idxd = idx.to(DEV)
+    blob2 = blob.clone()
+    V2 = lay.views(blob2)
+    sample = [int(s) for s in idx[1:6] if s > 0]
+    for t in range(m + 1):
+        q, k = (torch.randn(B, hk, D, generator=g0).bfloat16() for _ in range(2))
+        v = torch.randn(B, hv, D, generator=g0).bfloat16()
+        a, b = (torch.randn(B, hv, generator=g0).bfloat16() for _ in range(2))
+        A_log, dtb = torch.randn(hv, generator=g0) * 0.3, torch.randn(hv, generator=g0)
+        out = torch.empty(B, hv, D, dtype=torch.bfloat16, device=DEV)
+        out2 = torch.empty_like(out)
+        args = [x.to(DEV) for x in (q, k, v)]
+        gate = tuple(x.to(DEV) for x in (a, b, A_log, dtb))
+        pre = blob[torch.tensor(sample, device=DEV)].cpu()
+        lay.step(V, idxd, *args, out, D ** -0.5, gate=gate)
+        lay.step(V2, idxd, *args, out2, D ** -0.5, gate=gate)
+        assert torch.equal(out, out2) and torch.equal(blob, blob2)         # deterministic
+        assert torch.equal(out[idxd <= 0], torch.zeros_like(out[idxd <= 0]))
+        # oracle on the sampled slots from their pre-step bytes
+        hb = torch.zeros(B + 1, lay.nbytes, dtype=torch.uint8)
+        hb[torch.tensor(sample)] = pre
+        rows = [int((idx == s).nonzero()[0]) for s in sample]
+        oh = torch.empty(len(rows), hv, D, dtype=torch.bfloat16)
+        oracle.gdn_step(lay, lay.views(hb), idx[rows].contiguous(), q[rows].contiguous(), k[rows].contiguous(),
+                        v[rows].contiguous(), oh, D ** -0.5,
+                        gate=(a[rows].contiguous(), b[rows].contiguous(), A_log, dtb))
+        assert torch.allclose(out[rows].cpu().float(), oh.float(), rtol=1e-2, atol=1e-3)
+        d = field_diff(lay, blob.cpu(), hb, sample)
+        assert d['S'] <= 1e-4 * len(sample) * hv * D * D // 2 + 1 and d['UB'] + d['KB'] <= 2, d
+    n = V['NPTR'][idxd[idxd > 0].long(), 0]
+    assert int(n.min()) == int(n.max()) == (m + 1) % m
+
+
+def test_bad_tensors_raise():
+    lay = SlotLayout(sq.Quantizer(4, 'k', 64), 4, 2, 128, 128)
+    blob = lay.alloc(3, DEV)
+    V = lay.views(blob)
+    q = torch.zeros(2, 2, 128, device=DEV)
+    v = torch.zeros(2, 4, 128, device=DEV)
+    out = torch.zeros(2, 4, 128, device=DEV)
+    gb = torch.zeros(2, 4, device=DEV)
+    with pytest.raises(AssertionError):
+        lay.step(V, torch.tensor([1, 2], device=DEV), q, q, v, out, 1.0, g=gb, beta=gb)          # int64 idx
+    with pytest.raises(TypeError):
+        lay.step(V, torch.tensor([1, 2], dtype=torch.int32, device=DEV), q.double(), q.double(), v, out, 1.0, g=gb, beta=gb)
+    with pytest.raises(AssertionError):
+        lay.step(V, torch.tensor([1, 2], dtype=torch.int32, device=DEV), q, q, v, out.transpose(1, 2), 1.0, g=gb, beta=gb)
+    with pytest.raises(RuntimeError, match='d_k 96'):
+        l2 = SlotLayout(sq.Quantizer(4, 'k', 64), 4, 2, 96, 128)
+        b2 = l2.alloc(2, DEV)
+        l2.step(l2.views(b2), torch.tensor([1], dtype=torch.int32, device=DEV), torch.zeros(1, 2, 96, device=DEV),
+                torch.zeros(1, 2, 96, device=DEV), torch.zeros(1, 4, 128, device=DEV), torch.zeros(1, 4, 128, device=DEV),
+                1.0, g=torch.zeros(1, 4, device=DEV), beta=torch.zeros(1, 4, device=DEV))
