@@ -32,7 +32,7 @@ for p in (ROOT, os.path.join(ROOT, 'tests')):
 import torch  # noqa: E402
 
 HV, HK, DK, DV, M = 32, 16, 128, 128, 8
-LAYERS = 24
+LAYERS = 24          # overridden by --layers (profiling runs use fewer)
 PRESETS = {'int8k': (8, 'k', 32), 'int4v': (4, 'v', 32), 'pace4': (4, 'k', 64)}
 METRIC = 'decode layer-steps/s (24-layer GDN stack, batch 256 slots per GPU)'
 UNIT = 'layer-steps/s'
@@ -153,7 +153,10 @@ class Stack:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
-            self.graph.replay()
+            if self.graph is not None:
+                self.graph.replay()
+            else:
+                self.step()
         e1.record()
         torch.cuda.synchronize()
         return e0.elapsed_time(e1)
@@ -220,7 +223,13 @@ def main():
     ap.add_argument('--prewarm', type=int, default=512)
     ap.add_argument('--preset', default='int8k', choices=list(PRESETS))
     ap.add_argument('--no-variants', action='store_true', help='time the headline preset only')
+    ap.add_argument('--layers', type=int, default=24, help='layers of the stack (24 = the benchmark; fewer for ncu captures)')
+    ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer leg')
+    ap.add_argument('--no-cpu', action='store_true', help='skip the CPU-baseline leg')
+    ap.add_argument('--eager', action='store_true', help='launch eagerly instead of replaying a CUDA graph')
     args = ap.parse_args()
+    global LAYERS
+    LAYERS = args.layers
     rank = int(os.environ.get('RANK', '0'))
     world = int(os.environ.get('WORLD_SIZE', '1'))
     local = int(os.environ.get('LOCAL_RANK', '0'))
@@ -274,9 +283,9 @@ def main():
     for pi, preset in enumerate(presets):
         stack = Stack(preset, args.batch, device, seed=1234 + rank)
         stack.prewarm(args.prewarm, torch.Generator().manual_seed(4321 + rank))
-        stack.capture()
-        for _ in range(max(3, args.warmup)):
-            stack.graph.replay()
+        if not args.eager:
+            stack.capture()
+        stack.timed(max(3, args.warmup))
         barrier()
         sampler = ClockSampler(local) if (pi == 0 and rank == 0) else None
         t0 = time.time()
@@ -297,6 +306,7 @@ def main():
                            'bytes_per_slot_layer_step': total}
         if pi == 0:
             launches = args.steps * LAYERS
+        if pi == 0 and not args.no_e2e and not args.eager:
             barrier()
             ems, h2d, d2h = run_e2e(stack, max(1, min(args.steps, 32)), 3)
             esteps = max(1, min(args.steps, 32))
@@ -325,7 +335,7 @@ def main():
                      'kernel': 'delta_step_kernel<GDN>', 'algorithmic_bytes_per_launch': args.batch * head['bytes_per_slot_layer_step']},
         'variants': results, 'clocks': clocks, 'e2e': e2e, 'gpu_launches': launches,
     }
-    if world == 1:
+    if world == 1 and not args.no_cpu:
         import __graft_entry__ as ge
         ge.build()
         v, cores, dt = cpu_baseline(args.batch, 16, 4, args.preset)

@@ -50,6 +50,7 @@ def build(force=False, verbose=False):
     cmd = [_nvcc(), '-gencode', 'arch=compute_100a,code=sm_100a', '-O3', '-lineinfo', '-std=c++17',
            '--fmad=false', '-Xcompiler', '-fPIC', '-shared', '-cudart', 'static',
            '-o', OUT] + [os.path.join(SRC, u) for u in UNITS]
+    cmd += os.environ.get('SQB_NVCC_EXTRA', '').split()
     if verbose:
         cmd.insert(1, '-Xptxas')
         cmd.insert(2, '-v')

@@ -220,7 +220,6 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
   // ---- read pass: rows of this lane, first batch of code chunks in flight before anything else -----------------
   const int RW = DV / NW;                      // rows per warp
   const int npass = (RW + RPP - 1) / RPP;
-  const int row0 = warp * RW + rl;
   uint4 cw[NPF];
   unsigned short scw[NPF];
 #pragma unroll
@@ -627,26 +626,26 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
       }
     }
     // ---- re-round and store ----
-    if (!QUANT) {
+    if constexpr (!QUANT) {
 #pragma unroll
       for (int pp = 0; pp < PPW; pp++) {
         if (!rv[pp]) continue;
         uint4 o;
-        if (BITS == 16) {
+        if constexpr (BITS == 16) {
           o.x = f2bf(acc[pp][0].x) | (static_cast<uint32_t>(f2bf(acc[pp][0].y)) << 16);
           o.y = f2bf(acc[pp][1].x) | (static_cast<uint32_t>(f2bf(acc[pp][1].y)) << 16);
-          o.z = f2bf(acc[pp][2 % NP].x) | (static_cast<uint32_t>(f2bf(acc[pp][2 % NP].y)) << 16);
-          o.w = f2bf(acc[pp][3 % NP].x) | (static_cast<uint32_t>(f2bf(acc[pp][3 % NP].y)) << 16);
+          o.z = f2bf(acc[pp][2].x) | (static_cast<uint32_t>(f2bf(acc[pp][2].y)) << 16);
+          o.w = f2bf(acc[pp][3].x) | (static_cast<uint32_t>(f2bf(acc[pp][3].y)) << 16);
         } else {
           o.x = __float_as_uint(acc[pp][0].x); o.y = __float_as_uint(acc[pp][0].y);
-          o.z = __float_as_uint(acc[pp][1 % NP].x); o.w = __float_as_uint(acc[pp][1 % NP].y);
+          o.z = __float_as_uint(acc[pp][1].x); o.w = __float_as_uint(acc[pp][1].y);
         }
         *reinterpret_cast<uint4*>(Sh + (long long)rows[pp] * rowbytes + c * 16) = o;
       }
     } else {
       // scales
       float sc[AXK ? PPW : CPL];
-      if (AXK) {
+      if constexpr (AXK) {
         const int lpg = G / CPL;                 // lanes per key group
 #pragma unroll
         for (int pp = 0; pp < PPW; pp++) {
@@ -696,7 +695,7 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
         float2 t[NP];
         constexpr float MB = BITS == 4 ? MAGIC + 8.0f : MAGIC;
         bool ok;
-        if (AXK) {
+        if constexpr (AXK) {
           const float s = sc[pp];
           ok = s >= FP16_MIN_NORMAL && round_fast<NP>(acc[pp], s, __fdiv_rn(1.0f, s), MB, t);
           if (!ok) {
@@ -715,7 +714,7 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
         }
         uint4 o;
         uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
-        if (BITS == 4) {
+        if constexpr (BITS == 4) {
 #pragma unroll
           for (int w = 0; w < 4; w++) {
             uint32_t x = 0;
@@ -729,8 +728,8 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
         } else {
 #pragma unroll
           for (int w = 0; w < 4; w++) {
-            const uint32_t lo = __byte_perm(__float_as_uint(t[(2 * w) % NP].x), __float_as_uint(t[(2 * w) % NP].y), 0x0040);
-            const uint32_t hi = __byte_perm(__float_as_uint(t[(2 * w + 1) % NP].x), __float_as_uint(t[(2 * w + 1) % NP].y), 0x0040);
+            const uint32_t lo = __byte_perm(__float_as_uint(t[2 * w].x), __float_as_uint(t[2 * w].y), 0x0040);
+            const uint32_t hi = __byte_perm(__float_as_uint(t[2 * w + 1].x), __float_as_uint(t[2 * w + 1].y), 0x0040);
             ow[w] = __byte_perm(lo, hi, 0x5410);
           }
         }

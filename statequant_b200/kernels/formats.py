@@ -59,7 +59,10 @@ def check_dims(fmt, dk, dv):
 
 
 def _scale_of(amax, qmax):
-    s = (amax.clamp_min(1e-8) / qmax).to(torch.float16).float()
+    # tensor / tensor: an IEEE division on every device (torch's CUDA kernels turn tensor / python-scalar into a
+    # multiplication by the reciprocal, which moves about one scale in a thousand by an fp16 ulp)
+    q = torch.full((), qmax, dtype=torch.float32, device=amax.device)
+    s = torch.div(amax.clamp_min(1e-8), q).to(torch.float16).float()
     return s.clamp_min(FP16_TINY)
 
 

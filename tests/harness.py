@@ -42,6 +42,9 @@ def step_args(c, inp, t, dtype=torch.float32):
                 beta=inp['beta'][t].contiguous())
 
 
+_DEVCONST = {}
+
+
 def run_step(c, lay, views, idx, a, out, inp, oracle=None):
     """One step through the CUDA kernels (oracle=None) or the oracle module."""
     dev = out.device
@@ -49,7 +52,10 @@ def run_step(c, lay, views, idx, a, out, inp, oracle=None):
         f = lay.step if oracle is None else (lambda *x, **kw: oracle.gdn_step(lay, *x, **kw))
         return f(views, idx, a['q'], a['k'], a['v'], out, c['dk'] ** -0.5, g=a['g'], beta=a['beta'])
     if c['kind'] == 'm2':
-        A, D, dtb = inp['A'].to(dev), inp['D'].to(dev), inp['dt_bias'].to(dev)
+        key = (id(inp['A']), str(dev))
+        if key not in _DEVCONST:                       # per-layer constants live on the device once (graph capture)
+            _DEVCONST[key] = (inp['A'].to(dev), inp['D'].to(dev), inp['dt_bias'].to(dev), inp['A'])
+        A, D, dtb = _DEVCONST[key][:3]
         f = lay.step if oracle is None else (lambda *x, **kw: oracle.mamba2_step(lay, *x, **kw))
         sp = c.get('softplus', True)
         return f(views, idx, a['x'], a['dt'], a['B'], a['C'], out, A, D, dtb if sp else None, dt_softplus=sp)
