@@ -153,6 +153,12 @@ const char *sqb_last_error(void);
 int sqb_abi_version(void);
 /* number of kernel launches issued by this library in this process (all threads) */
 int64_t sqb_launch_count(void);
+/* tuning / test switches.  "force_generic_kernel" = 1 routes every step through the generic kernel instead of the
+   one that stages the state through shared memory with bulk async copies (both give the same bytes). */
+int sqb_set_option(const char *name, int value);
+/* Device-side health word of the current device (synchronises): the number of CTAs whose wait for a bulk copy ran
+   out of its iteration budget since the library was loaded.  0 in a healthy run. */
+int sqb_device_status(int *wait_timeouts);
 
 #ifdef __cplusplus
 }

@@ -91,6 +91,10 @@ def lib():
             f = getattr(L, name)
             f.restype = C.c_int
             f.argtypes = [vp, vp, vp]
+        L.sqb_set_option.restype = C.c_int
+        L.sqb_set_option.argtypes = [C.c_char_p, C.c_int]
+        L.sqb_device_status.restype = C.c_int
+        L.sqb_device_status.argtypes = [C.POINTER(C.c_int)]
         if L.sqb_abi_version() != ABI_VERSION:
             raise RuntimeError(f'{LIB_PATH} has ABI {L.sqb_abi_version()}, this package expects {ABI_VERSION}: rebuild')
         _lib = L
@@ -108,3 +112,14 @@ def current_stream(device):
 
 def launch_count():
     return int(lib().sqb_launch_count())
+
+
+def set_option(name, value):
+    check(lib().sqb_set_option(name.encode(), int(value)), 'sqb_set_option')
+
+
+def device_status():
+    """Number of CTAs whose bounded wait for a bulk copy ran out (0 in a healthy run); synchronises the device."""
+    n = C.c_int(0)
+    check(lib().sqb_device_status(C.byref(n)), 'sqb_device_status')
+    return n.value

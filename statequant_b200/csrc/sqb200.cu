@@ -6,6 +6,7 @@
 
 #include "../../include/statequant_b200.h"
 #include "delta_step.cuh"
+#include "step_tma.cuh"
 
 namespace {
 
@@ -94,8 +95,73 @@ int launch_one(const sqb::StepArgs& a, cudaStream_t stream) {
   return 0;
 }
 
+// ---- the staged kernel (integer states, d_k 64 or 128, everything 16-byte aligned) -----------------------------------
+bool tma_ok(const sqb::StepArgs& a, int bits, bool axk) {
+  if (bits != 4 && bits != 8) return false;
+  if (a.DK != 64 && a.DK != 128) return false;
+  const int lpr = a.DK / 16, rpp = 32 / lpr, bsz = a.qbuf ? 1 : 2, g = a.group;
+  if (a.DV % (sqb::NW * rpp)) return false;
+  if (axk) {
+    if (g % 16 || a.DK % g) return false;
+  } else {
+    if (g % rpp || a.DV % g) return false;
+    const int wpg = g / rpp < sqb::NW ? g / rpp : sqb::NW;
+    if (g / (rpp * wpg) > 2) return false;
+  }
+  const long long codes_b = static_cast<long long>(a.DV) * a.DK * bits / 8;
+  const long long scales_b = (axk ? static_cast<long long>(a.DV) * (a.DK / g) : static_cast<long long>(a.DV / g) * a.DK) * 2;
+  const long long ub_b = static_cast<long long>(a.M) * a.DV * bsz, kb_b = static_cast<long long>(a.M) * a.DK * bsz;
+  if (codes_b % 16 || scales_b % 16 || ub_b % 16 || kb_b % 16) return false;
+  auto a16 = [](const void* p, long long s) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && s % 16 == 0; };
+  if (!a16(a.S, a.sS) || !a16(a.SC, a.sSC) || !a16(a.UB, a.sUB) || !a16(a.KB, a.sKB)) return false;
+  return true;
+}
+
+template <int KIND, int BITS, bool AXK, int LPR>
+int launch_tma_one(const sqb::StepArgs& a, cudaStream_t stream) {
+  auto kern = sqb::step_tma_kernel<KIND, BITS, AXK, LPR>;
+  const int gqa = a.HV / a.HK;
+  int nst = gqa < 2 ? gqa : (KIND == sqb::K_M2 && gqa >= 3 ? 3 : 2);
+  sqb::Smem2 plan = sqb::smem2_plan(KIND, BITS, AXK, a.group, a.DK, a.DV, a.M, a.qbuf, nst);
+  while (nst > 1 && plan.total > 100 * 1024) {
+    nst--;
+    plan = sqb::smem2_plan(KIND, BITS, AXK, a.group, a.DK, a.DV, a.M, a.qbuf, nst);
+  }
+  if (plan.total > 220 * 1024) return 1;    // does not fit: the caller falls back to the generic kernel
+  static std::atomic<int> configured{0};
+  if (plan.total > configured.load()) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.total);
+    if (e != cudaSuccess) return fail(SQB_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    configured.store(plan.total);
+  }
+  const long long ctas = static_cast<long long>(a.rows) * a.HK;
+  if (ctas > 2147483647LL) return fail(SQB_EINVAL, "rows * hk = %lld exceeds the grid limit", ctas);
+  kern<<<static_cast<unsigned>(ctas), sqb::NT, plan.total, stream>>>(a, nst);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(SQB_ECUDA, "kernel launch: %s", cudaGetErrorString(e));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return 0;
+}
+
+template <int KIND>
+int launch_tma(const sqb::StepArgs& a, int bits, bool axk, cudaStream_t stream) {
+  const bool d128 = a.DK == 128;
+  if (bits == 4) {
+    if (axk) return d128 ? launch_tma_one<KIND, 4, true, 8>(a, stream) : launch_tma_one<KIND, 4, true, 4>(a, stream);
+    return d128 ? launch_tma_one<KIND, 4, false, 8>(a, stream) : launch_tma_one<KIND, 4, false, 4>(a, stream);
+  }
+  if (axk) return d128 ? launch_tma_one<KIND, 8, true, 8>(a, stream) : launch_tma_one<KIND, 8, true, 4>(a, stream);
+  return d128 ? launch_tma_one<KIND, 8, false, 8>(a, stream) : launch_tma_one<KIND, 8, false, 4>(a, stream);
+}
+
+int g_force_generic = 0;     // set through sqb_set_option (tests time and check both kernels)
+
 template <int KIND>
 int launch(const sqb::StepArgs& a, int bits, bool axk, cudaStream_t stream) {
+  if (!g_force_generic && tma_ok(a, bits, axk)) {
+    const int rc = launch_tma<KIND>(a, bits, axk, stream);
+    if (rc <= 0) return rc;
+  }
   switch (bits) {
     case 4: return axk ? launch_one<KIND, 4, true>(a, stream) : launch_one<KIND, 4, false>(a, stream);
     case 8: return axk ? launch_one<KIND, 8, true>(a, stream) : launch_one<KIND, 8, false>(a, stream);
@@ -117,6 +183,19 @@ extern "C" {
 const char* sqb_last_error(void) { return g_err; }
 int sqb_abi_version(void) { return 1; }
 int64_t sqb_launch_count(void) { return g_launches.load(); }
+
+int sqb_set_option(const char* name, int value) {
+  if (name && !strcmp(name, "force_generic_kernel")) { g_force_generic = value; return 0; }
+  return fail(SQB_EINVAL, "unknown option");
+}
+
+int sqb_device_status(int* wait_timeouts) {
+  int st[4] = {0, 0, 0, 0};
+  cudaError_t e = cudaMemcpyFromSymbol(st, sqb::g_step_status, sizeof st);
+  if (e != cudaSuccess) return fail(SQB_ECUDA, "cudaMemcpyFromSymbol: %s", cudaGetErrorString(e));
+  if (wait_timeouts) *wait_timeouts = st[0];
+  return 0;
+}
 
 int sqb_gdn_step(const sqb_state_t* st, const sqb_gdn_inputs_t* in, void* stream) {
   int lpr_log2 = 0;

@@ -15,8 +15,19 @@ pytestmark = pytest.mark.gpu
 DEV = 'cuda'
 
 
+@pytest.fixture(params=['staged', 'generic'])
+def kernel_path(request):
+    """Both device code paths: the kernel that stages the state through shared memory with bulk async copies
+    (default wherever its alignment and shape conditions hold) and the generic one."""
+    from statequant_b200 import _cabi
+    _cabi.set_option('force_generic_kernel', request.param == 'generic')
+    yield request.param
+    _cabi.set_option('force_generic_kernel', 0)
+    assert _cabi.device_status() == 0, 'a bulk-copy wait timed out on the device'
+
+
 @pytest.mark.parametrize('name', list(CASES))
-def test_decode_matches_reference_golden(name):
+def test_decode_matches_reference_golden(name, kernel_path):
     """The CUDA step against the reference's golden record (re-sync protocol of the reference's own tests)."""
     check_stats(name, replay_vs_golden(name, CASES[name], oracle=None, device=DEV))
 
@@ -103,7 +114,7 @@ def _oracle_lockstep(c, T, act_dtype, seed_slots=7, gate=False):
 
 @pytest.mark.parametrize('name', list(CASES))
 @pytest.mark.parametrize('act', ['fp32', 'bf16'])
-def test_step_matches_oracle_on_slots(name, act):
+def test_step_matches_oracle_on_slots(name, act, kernel_path):
     c = CASES[name]
     act_dtype = torch.float32 if act == 'fp32' else torch.bfloat16
     st = _oracle_lockstep(c, T=2 * c['m'] + 3, act_dtype=act_dtype)
