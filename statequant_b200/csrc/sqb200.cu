@@ -99,6 +99,7 @@ int launch_one(const sqb::StepArgs& a, cudaStream_t stream) {
 bool tma_ok(const sqb::StepArgs& a, int bits, bool axk) {
   if (bits != 4 && bits != 8) return false;
   if (a.DK != 64 && a.DK != 128) return false;
+  if (!a.per_key_head && a.HV != a.HK) return false;      // q, k per value head: generic kernel
   const int lpr = a.DK / 16, rpp = 32 / lpr, bsz = a.qbuf ? 1 : 2, g = a.group;
   if (a.DV % (sqb::NW * rpp)) return false;
   if (axk) {
@@ -122,10 +123,10 @@ int launch_tma_one(const sqb::StepArgs& a, cudaStream_t stream) {
   auto kern = sqb::step_tma_kernel<KIND, BITS, AXK, LPR>;
   const int gqa = a.HV / a.HK;
   int nst = gqa < 2 ? gqa : (KIND == sqb::K_M2 && gqa >= 3 ? 3 : 2);
-  sqb::Smem2 plan = sqb::smem2_plan(KIND, BITS, AXK, a.group, a.DK, a.DV, a.M, a.qbuf, nst);
+  sqb::Smem2 plan = sqb::smem2_plan(KIND, BITS, AXK, a.group, a.DK, a.DV, a.M, a.qbuf, nst, gqa);
   while (nst > 1 && plan.total > 100 * 1024) {
     nst--;
-    plan = sqb::smem2_plan(KIND, BITS, AXK, a.group, a.DK, a.DV, a.M, a.qbuf, nst);
+    plan = sqb::smem2_plan(KIND, BITS, AXK, a.group, a.DK, a.DV, a.M, a.qbuf, nst, gqa);
   }
   if (plan.total > 220 * 1024) return 1;    // does not fit: the caller falls back to the generic kernel
   static std::atomic<int> configured{0};

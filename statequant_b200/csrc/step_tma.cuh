@@ -53,13 +53,15 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
-// shared-memory plan of the staged kernel (byte offsets)
+// shared-memory plan of the staged kernel (byte offsets; float offsets from f0)
 struct Smem2 {
   int bars, stage0, stage_bytes, codes_b, scales_b, ub_b, kb, gbt, f0, total;
-  int xq, xk, ga, ae, us, R, L, Dq, Dk, cq, ck, dec, red, ubs, cmax, rdk, ldv;   // float offsets from f0
+  int xq, xk, ga, ae, krnd, us, R, L, Dq, Dk, hd, decf, ubs, red, misc, cmax, rdk, ldv;
 };
+constexpr int HD_W = 8;     // per-head scalars: g, beta | dt, gcur, alpha, a, gnew, D, n
 __host__ __device__ inline int al16i(int x) { return (x + 15) & ~15; }
-__host__ __device__ inline Smem2 smem2_plan(int kind, int bits, int axk, int group, int DK, int DV, int M, int qbuf, int nst) {
+__host__ __device__ inline Smem2 smem2_plan(int kind, int bits, int axk, int group, int DK, int DV, int M, int qbuf,
+                                            int nst, int gqa) {
   Smem2 s;
   const int bsz = qbuf ? 1 : 2;
   s.codes_b = DV * DK * bits / 8;
@@ -80,18 +82,19 @@ __host__ __device__ inline Smem2 smem2_plan(int kind, int bits, int axk, int gro
   s.xk = f; f += DK;
   s.ga = f; f += (kind == K_KDA ? DK : 0);
   s.ae = f; f += (kind == K_KDA ? DK : 0);
-  s.us = f; f += DV;
+  s.krnd = f; f += DK;
+  s.us = f; f += 2 * DV;
   s.R = f; f += M * s.rdk;
   s.L = f; f += M * s.ldv;
   s.Dq = f; f += 32;
   s.Dk = f; f += 32;
-  s.cq = f; f += 32;
-  s.ck = f; f += 32;
-  s.dec = f; f += 32;
-  s.ubs = f; f += 32;
-  s.red = f; f += 16;
+  s.hd = f; f += gqa * HD_W;
+  s.decf = f; f += gqa * M;
+  s.ubs = f; f += gqa * M;
+  s.red = f; f += 8;
+  s.misc = f; f += 8;
   s.cmax = f; f += (axk ? 0 : 2 * NW * DK);
-  s.total = s.f0 + f * 4;
+  s.total = s.f0 + ((f + 3) & ~3) * 4;
   return s;
 }
 
@@ -173,8 +176,29 @@ __device__ __forceinline__ float transpose_reduce(float (&v)[LPR], int c) {
   return v[0];
 }
 
+// Rounds DV/4-word chunks of a value vector against scale s: code = clamp(rint(div_rn(x, s)), +-127), by a
+// reciprocal multiply checked with an exact residual (see round_fast); returns the four codes as bytes of a word
+// and their dequantised values.
+__device__ __forceinline__ uint32_t round4_i8(const float* x, float s, float r, bool fast_ok, float (&deq)[4]) {
+  float2 t[2];
+  const float2 xv[2] = {make_float2(x[0], x[1]), make_float2(x[2], x[3])};
+  bool ok = fast_ok && round_fast<2>(xv, s, r, MAGIC, t);
+  if (!ok) {
+    t[0].x = rq_exact(x[0], s, 127.0f) + MAGIC; t[0].y = rq_exact(x[1], s, 127.0f) + MAGIC;
+    t[1].x = rq_exact(x[2], s, 127.0f) + MAGIC; t[1].y = rq_exact(x[3], s, 127.0f) + MAGIC;
+  }
+  deq[0] = (t[0].x - MAGIC) * s; deq[1] = (t[0].y - MAGIC) * s;
+  deq[2] = (t[1].x - MAGIC) * s; deq[3] = (t[1].y - MAGIC) * s;
+  const uint32_t lo = __byte_perm(__float_as_uint(t[0].x), __float_as_uint(t[0].y), 0x0040);
+  const uint32_t hi = __byte_perm(__float_as_uint(t[1].x), __float_as_uint(t[1].y), 0x0040);
+  return __byte_perm(lo, hi, 0x5410);
+}
+
+#ifndef SQB_MINB
+#define SQB_MINB 4
+#endif
 template <int KIND, int BITS, bool AXK, int LPR>
-__global__ void __launch_bounds__(NT) step_tma_kernel(const __grid_constant__ StepArgs A, const int nst) {
+__global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_constant__ StepArgs A, const int nst) {
   constexpr int DK = LPR * 16;
   constexpr int RPP = 32 / LPR;                  // rows per warp pass
   constexpr int CB = 16 * BITS / 8;              // bytes of a lane chunk
@@ -202,13 +226,13 @@ __global__ void __launch_bounds__(NT) step_tma_kernel(const __grid_constant__ St
       return;
     }
   }
-  const Smem2 P = smem2_plan(KIND, BITS, AXK, G, DK, DV, M, A.qbuf, nst);
+  const Smem2 P = smem2_plan(KIND, BITS, AXK, G, DK, DV, M, A.qbuf, nst, gqa);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smraw + P.bars);
   uint8_t* kbt = smraw + P.kb;
   float* fsm = reinterpret_cast<float*>(smraw + P.f0);
-  float *xq = fsm + P.xq, *xk = fsm + P.xk, *ga = fsm + P.ga, *ae = fsm + P.ae, *us = fsm + P.us, *R = fsm + P.R,
-        *L = fsm + P.L, *Dq = fsm + P.Dq, *Dk = fsm + P.Dk, *cq = fsm + P.cq, *ck = fsm + P.ck, *dec = fsm + P.dec,
-        *red = fsm + P.red, *ubsf = fsm + P.ubs, *cmax = fsm + P.cmax;
+  float *xq = fsm + P.xq, *xk = fsm + P.xk, *ga = fsm + P.ga, *ae = fsm + P.ae, *krnd = fsm + P.krnd, *us = fsm + P.us,
+        *R = fsm + P.R, *L = fsm + P.L, *Dq = fsm + P.Dq, *Dk = fsm + P.Dk, *hd = fsm + P.hd, *decf = fsm + P.decf,
+        *ubsf = fsm + P.ubs, *red = fsm + P.red, *misc = fsm + P.misc, *cmax = fsm + P.cmax;
   const float* gbt = reinterpret_cast<const float*>(smraw + P.gbt);
   const int RDK = P.rdk, LDV = P.ldv;
   const int bsz = A.qbuf ? 1 : 2;
@@ -244,21 +268,27 @@ __global__ void __launch_bounds__(NT) step_tma_kernel(const __grid_constant__ St
     bulk_g2s(kbt, KBh, M * DK * bsz, &bars[nst]);
     if (VDEC) bulk_g2s(smraw + P.gbt, GBseq + (long long)h0 * M * DK, M * DK * 4, &bars[nst]);
     for (int s = 0; s < nst && s < gqa; s++) issue_stage(s, h0 + s);
+    misc[2] = 0.f;                                      // "a copy never arrived" flag
   }
   __syncthreads();     // barriers initialised before anyone polls them
 
-  // ---- key-head prologue: each warp normalises q and k redundantly (shuffles only); lane holds CW columns -------
-  const bool per_head_qk = KIND == K_GDN && !A.per_key_head;     // q, k given per value head: prologue per head
-  float qr[CW], kr[CW], gnr[CW];     // normalised q (scaled), normalised k (Mamba2: C, B), KDA: running decay incl. this token
-  float kq = 0.f, kmax = 0.f;
-  auto prologue = [&](int hq) {
+  // ---- prologue, by role ----------------------------------------------------------------------------------------
+  if (warp == 0) {
+    // the key head: normalise q and k (lane holds CW columns), k.q, the key appended to the buffer, and the dot
+    // products of the buffered keys with q and k
+    const int n0 = NPseq[h0] & (M - 1);       // the heads of a slot advance together
+    float ksv = 0.f;                          // scale of buffered key `lane`
+    if (A.qbuf && lane < M) ksv = h2f(KBSh[lane]);
+    float qr[CW], kr[CW], gnr[CW];
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (int j = 0; j < CW; j++) {
-      qr[j] = ldf(A.q + (long long)b * A.sq, A.dt_qk, (long long)hq * DK + lane * CW + j);
-      kr[j] = ldf(A.k + (long long)b * A.sk, A.dt_qk, (long long)hq * DK + lane * CW + j);
+      qr[j] = ldf(A.q + (long long)b * A.sq, A.dt_qk, (long long)hk * DK + lane * CW + j);
+      kr[j] = ldf(A.k + (long long)b * A.sk, A.dt_qk, (long long)hk * DK + lane * CW + j);
       s0 += qr[j] * qr[j];
       s1 += kr[j] * kr[j];
+      if (VDEC) gnr[j] = GCseq[(long long)h0 * DK + lane * CW + j] +
+                         ldf(A.g + (long long)b * A.sg, A.dt_g, (long long)h0 * DK + lane * CW + j);
     }
     if (KIND != K_M2) {
       s0 = warp_sum(s0);
@@ -275,166 +305,146 @@ __global__ void __launch_bounds__(NT) step_tma_kernel(const __grid_constant__ St
     for (int j = 0; j < CW; j++) {
       d += kr[j] * qr[j];
       mx = fmaxf(mx, fabsf(kr[j]));
+      xq[lane * CW + j] = qr[j];
+      xk[lane * CW + j] = kr[j];
+      if (VDEC) { ga[lane * CW + j] = gnr[j]; ae[lane * CW + j] = expf(gnr[j]); }
     }
-    kq = warp_sum(d);
-    kmax = warp_max(mx);
-  };
-  prologue(per_head_qk ? h0 : hk);
-  // the key that goes into the buffer is the group's first head's (identical to every head's when q, k are per key head)
-  float kxr[CW];
-#pragma unroll
-  for (int j = 0; j < CW; j++) kxr[j] = kr[j];
-  const float ksc = A.qbuf ? fp16_scale(kmax, 127.0f) : 1.0f;
-  if (VDEC) {
-#pragma unroll
-    for (int j = 0; j < CW; j++) {
-      const int k = lane * CW + j;
-      gnr[j] = GCseq[(long long)h0 * DK + k] + ldf(A.g + (long long)b * A.sg, A.dt_g, (long long)h0 * DK + k);
-    }
-  }
-  auto publish_qk = [&]() {     // warp 0's copy goes to shared memory for the lane slices of the state pass
-    if (warp == 0) {
+    d = warp_sum(d);
+    mx = warp_max(mx);
+    if (lane == 0) misc[0] = d;
+    // append the key at slot n0; its rounded value is what the fold uses for slot M-1
+    if (A.qbuf) {
+      const float ksc = fp16_scale(mx, 127.0f);
+      uint32_t w = 0;
 #pragma unroll
       for (int j = 0; j < CW; j++) {
-        xq[lane * CW + j] = qr[j];
-        xk[lane * CW + j] = kr[j];
-        if (VDEC) { ga[lane * CW + j] = gnr[j]; ae[lane * CW + j] = expf(gnr[j]); }
+        const float cc = rq_exact(kr[j], ksc, 127.0f);
+        w |= (static_cast<uint32_t>(static_cast<int>(cc)) & 0xFFu) << (8 * j);
+        krnd[lane * CW + j] = cc * ksc;
+      }
+      if (CW == 4) *reinterpret_cast<uint32_t*>(KBh + (long long)n0 * DK + lane * 4) = w;
+      else *reinterpret_cast<unsigned short*>(KBh + (long long)n0 * DK + lane * 2) = static_cast<unsigned short>(w);
+      if (lane == 0) KBSh[n0] = f2h(ksc);
+    } else {
+#pragma unroll
+      for (int j = 0; j < CW; j++) {
+        const unsigned short bb = f2bf(kr[j]);
+        reinterpret_cast<unsigned short*>(KBh)[(long long)n0 * DK + lane * CW + j] = bb;
+        krnd[lane * CW + j] = bf2f(bb);
       }
     }
-  };
-  publish_qk();
-
-  // ---- buffered keys: dot products with q and k per slot (warp w: slots w, w + 4, ...) --------------------------
-  bool alive = mbar_wait(&bars[nst], 0);
-  const int n0 = NPseq[h0] & (M - 1);       // the heads of a slot advance together; each still reads its own copy below
-  auto key_of = [&](int i, int j) -> float {        // buffered key i, column lane*CW + j, dequantised
-    const int k = lane * CW + j;
-    if (A.qbuf) return static_cast<float>(reinterpret_cast<const int8_t*>(kbt)[i * DK + k]) * h2f(KBSh[i]);
-    return bf2f(reinterpret_cast<const unsigned short*>(kbt)[i * DK + k]);
-  };
-  auto key_dots = [&]() {
-    for (int i = warp; i < M; i += NW) {
+    if (!mbar_wait(&bars[nst], 0) && lane == 0) misc[2] = 1.f;
+    for (int i = 0; i < M; i++) {
       float dq = 0.f, dk = 0.f;
+      const float ks_i = __shfl_sync(0xffffffffu, ksv, i);
       if (i < n0) {
 #pragma unroll
         for (int j = 0; j < CW; j++) {
-          float kv = key_of(i, j);
-          if (VDEC) kv = kv * expf(gnr[j] - gbt[i * DK + lane * CW + j]);
+          const int k = lane * CW + j;
+          float kv;
+          if (A.qbuf) kv = static_cast<float>(reinterpret_cast<const int8_t*>(kbt)[i * DK + k]) * ks_i;
+          else kv = bf2f(reinterpret_cast<const unsigned short*>(kbt)[i * DK + k]);
+          if (VDEC) kv = kv * expf(gnr[j] - gbt[i * DK + k]);
           dq = fmaf(kv, qr[j], dq);
           if (TWO) dk = fmaf(kv, kr[j], dk);
         }
+        dq = warp_sum(dq);
+        dk = warp_sum(dk);
       }
-      dq = warp_sum(dq);
-      dk = warp_sum(dk);
       if (lane == 0) { Dq[i] = dq; Dk[i] = dk; }
     }
-  };
-  key_dots();
-  // append the key at slot n (first head's counter); int8: one fp16 absmax scale per vector
-  if (warp == 0) {
-    const int n = n0;
-    if (A.qbuf) {
-      uint32_t w = 0;
-#pragma unroll
-      for (int j = 0; j < CW; j++) w |= (static_cast<uint32_t>(static_cast<int>(rq_exact(kxr[j], ksc, 127.0f))) & 0xFFu) << (8 * j);
-      if (CW == 4) *reinterpret_cast<uint32_t*>(KBh + (long long)n * DK + lane * 4) = w;
-      else *reinterpret_cast<unsigned short*>(KBh + (long long)n * DK + lane * 2) = static_cast<unsigned short>(w);
-      if (lane == 0) KBSh[n] = f2h(ksc);
-    } else {
-#pragma unroll
-      for (int j = 0; j < CW; j++)
-        reinterpret_cast<unsigned short*>(KBh)[(long long)n * DK + lane * CW + j] = f2bf(kxr[j]);
+  } else if (warp == 1) {
+    // per value head: gates, counters, decay factors of the live buffer slots and their value scales
+    for (int hi = lane; hi < gqa; hi += 32) {
+      const int h = h0 + hi;
+      float g = 0.f, bt = 0.f, Dv = 0.f, gcur = 0.f;
+      if (KIND == K_GDN) {
+        if (A.gate) {
+          const float x = ldf(A.a + (long long)b * A.sa, A.dt_ab, h) + ldf(A.dt_bias, A.dt_dtb, h);
+          const float sp = x <= 20.0f ? logf(1.0f + expf(x)) : x;
+          g = -expf(ldf(A.A_log, A.dt_alog, h)) * sp;
+          bt = __fdiv_rn(1.0f, 1.0f + expf(-ldf(A.b + (long long)b * A.sb, A.dt_ab, h)));
+        } else {
+          g = ldf(A.g + (long long)b * A.sg, A.dt_g, h);
+          bt = ldf(A.beta + (long long)b * A.sbeta, A.dt_g, h);
+        }
+      } else if (KIND == K_M2) {
+        float dtv = ldf(A.g + (long long)b * A.sg, A.dt_g, h);
+        if (A.dt_bias) dtv = dtv + ldf(A.dt_bias, A.dt_dtb, h);
+        if (A.dt_softplus) dtv = dtv <= 20.0f ? logf(1.0f + expf(dtv)) : dtv;
+        if (A.dt_clamp) dtv = fminf(fmaxf(dtv, A.dt_min), A.dt_max);
+        g = __fmul_rn(ldf(A.A_log, A.dt_alog, h), dtv);
+        bt = dtv;
+        if (A.beta) Dv = ldf(A.beta, A.dt_beta, h);
+      } else {
+        bt = ldf(A.beta + (long long)b * A.sbeta, A.dt_beta, h);
+      }
+      if (!VDEC) gcur = GCseq[h];
+      float* o = hd + hi * HD_W;
+      o[0] = g; o[1] = bt; o[2] = gcur; o[3] = VDEC ? 1.0f : expf(gcur); o[4] = VDEC ? 1.0f : expf(g);
+      o[5] = gcur + g; o[6] = Dv; o[7] = __int_as_float(NPseq[h] & (M - 1));
+    }
+    for (int e = lane; e < gqa * M; e += 32) {
+      const int hi = e / M, i = e - hi * M, h = h0 + hi;
+      const bool live = i < (NPseq[h] & (M - 1));
+      float dcy = 0.f, us_i = 0.f;
+      if (live) {
+        dcy = VDEC ? 1.0f : expf(GCseq[h] - GBseq[(long long)h * M + i]);
+        us_i = A.qbuf ? h2f(UBSseq[h * M + i]) : 1.0f;
+      }
+      decf[e] = dcy;
+      ubsf[e] = us_i;
     }
   }
-  alive = __syncthreads_and(alive) != 0;    // xq, xk, Dq, Dk visible; the decision to go on is CTA-wide
-  if (!alive) {
+  __syncthreads();
+  if (misc[2] != 0.f) {
     if (tid == 0) atomicAdd(&g_step_status[0], 1);
     return;
   }
+  const float kq = misc[0];
 
   // ---- the value heads of this key head ---------------------------------------------------------------------------
+  const int RW = DV / NW;
+  const int npass = RW / RPP;
+  float2 vq[8], vk[8];
+  auto load_slice = [&](const unsigned short* scrow) {
+#pragma unroll
+    for (int p = 0; p < 8; p++) {
+      const int k0 = c * 16 + 2 * p;
+      float q0 = xq[k0], q1 = xq[k0 + 1], k0v = 0.f, k1v = 0.f;
+      if (TWO) { k0v = xk[k0]; k1v = xk[k0 + 1]; }
+      if (VDEC) { q0 = ae[k0] * q0; q1 = ae[k0 + 1] * q1; k0v = ae[k0] * k0v; k1v = ae[k0 + 1] * k1v; }
+      if (!AXK) {
+        const float s0 = h2f(scrow[k0]), s1 = h2f(scrow[k0 + 1]);
+        q0 = q0 * s0; q1 = q1 * s1; k0v = k0v * s0; k1v = k1v * s1;
+      }
+      const float p0 = presc<BITS>(2 * p), p1 = presc<BITS>(2 * p + 1);
+      vq[p] = make_float2(q0 * p0, q1 * p1);
+      vk[p] = make_float2(k0v * p0, k1v * p1);
+    }
+  };
+  if (AXK) load_slice(nullptr);
   bool r_built = false;
   for (int hi = 0; hi < gqa; hi++) {
     const int h = h0 + hi;
     const int s = hi % nst;
     const uint32_t parity = (hi / nst) & 1;
+    const int par = hi & 1;
     uint8_t* st = smraw + P.stage0 + s * P.stage_bytes;
     const uint8_t* codes = st;
     const unsigned short* scs = reinterpret_cast<const unsigned short*>(st + P.codes_b);
     const uint8_t* ubt = st + P.codes_b + P.scales_b;
     uint8_t* orow = A.out + (long long)b * A.so + (long long)h * DV * osz;
-    unsigned short* UBSh = A.qbuf ? UBSseq + h * M : nullptr;
-    float* GBh = GBseq + (long long)h * M * (VDEC ? DK : 1);
-    float* GCh = GCseq + (long long)h * (VDEC ? DK : 1);
-    int* NPh = NPseq + h;
-    const int n = *NPh & (M - 1);
+    const float* hdv = hd + hi * HD_W;
+    const float beta = hdv[1], alpha = hdv[3], a = hdv[4], gnew = hdv[5], Dv = hdv[6];
+    const int n = __float_as_int(hdv[7]);
+    const float* dcf = decf + hi * M;
+    const float* usf = ubsf + hi * M;
+    float* usb = us + par * DV;
 
-    if (per_head_qk && hi > 0) {       // q, k of this value head
-      __syncthreads();
-      prologue(h);
-      publish_qk();
-      key_dots();
-      __syncthreads();
-    }
-    // gates
-    float g = 0.f, beta = 0.f, dtv = 0.f, Dv = 0.f, gcur = 0.f;
-    if (KIND == K_GDN) {
-      if (A.gate) {
-        const float x = ldf(A.a + (long long)b * A.sa, A.dt_ab, h) + ldf(A.dt_bias, A.dt_dtb, h);
-        const float sp = x <= 20.0f ? logf(1.0f + expf(x)) : x;
-        g = -expf(ldf(A.A_log, A.dt_alog, h)) * sp;
-        beta = __fdiv_rn(1.0f, 1.0f + expf(-ldf(A.b + (long long)b * A.sb, A.dt_ab, h)));
-      } else {
-        g = ldf(A.g + (long long)b * A.sg, A.dt_g, h);
-        beta = ldf(A.beta + (long long)b * A.sbeta, A.dt_g, h);
-      }
-    } else if (KIND == K_M2) {
-      dtv = ldf(A.g + (long long)b * A.sg, A.dt_g, h);
-      if (A.dt_bias) dtv = dtv + ldf(A.dt_bias, A.dt_dtb, h);
-      if (A.dt_softplus) dtv = dtv <= 20.0f ? logf(1.0f + expf(dtv)) : dtv;
-      if (A.dt_clamp) dtv = fminf(fmaxf(dtv, A.dt_min), A.dt_max);
-      g = __fmul_rn(ldf(A.A_log, A.dt_alog, h), dtv);
-      if (A.beta) Dv = ldf(A.beta, A.dt_beta, h);
-    } else {
-      beta = ldf(A.beta + (long long)b * A.sbeta, A.dt_beta, h);
-    }
-    if (!VDEC) gcur = *GCh;
-    const float alpha = VDEC ? 1.0f : expf(gcur);
-    const float a = VDEC ? 1.0f : expf(g);
-    const float gnew = gcur + g;
-    // buffer coefficients of this head: c_q[i] = (a_n / a_i) (k_i . q) for live slots; buffered value scales
-    if (tid < M) {
-      const bool live = tid < n;
-      float d = 1.0f;
-      if (!VDEC && live) d = expf(gcur - GBh[tid]);
-      cq[tid] = live ? d * Dq[tid] : 0.f;
-      ck[tid] = live ? d * Dk[tid] : 0.f;
-      ubsf[tid] = (live && A.qbuf) ? h2f(UBSh[tid]) : (live ? 1.0f : 0.f);
-    }
-    alive = __syncthreads_and(mbar_wait(&bars[s], parity)) != 0;
-    if (!alive) break;
+    if (!mbar_wait(&bars[s], parity)) misc[2] = 1.f;      // checked CTA-wide after the pass
 
     // ---- state pass ----
-    const int RW = DV / NW;
-    const int npass = RW / RPP;
-    float2 vq[8], vk[8];
-    auto load_slice = [&](const unsigned short* scrow) {
-#pragma unroll
-      for (int p = 0; p < 8; p++) {
-        const int k0 = c * 16 + 2 * p;
-        float q0 = xq[k0], q1 = xq[k0 + 1], k0v = 0.f, k1v = 0.f;
-        if (TWO) { k0v = xk[k0]; k1v = xk[k0 + 1]; }
-        if (VDEC) { q0 = ae[k0] * q0; q1 = ae[k0 + 1] * q1; k0v = ae[k0] * k0v; k1v = ae[k0 + 1] * k1v; }
-        if (!AXK) {
-          const float s0 = h2f(scrow[k0]), s1 = h2f(scrow[k0 + 1]);
-          q0 = q0 * s0; q1 = q1 * s1; k0v = k0v * s0; k1v = k1v * s1;
-        }
-        const float p0 = presc<BITS>(2 * p), p1 = presc<BITS>(2 * p + 1);
-        vq[p] = make_float2(q0 * p0, q1 * p1);
-        vk[p] = make_float2(k0v * p0, k1v * p1);
-      }
-    };
-    if (AXK) load_slice(nullptr);
     int cur_gv = -1;
     float umax = 0.f;
     for (int p0 = 0; p0 < npass; p0 += LPR) {
@@ -480,13 +490,12 @@ __global__ void __launch_bounds__(NT) step_tma_kernel(const __grid_constant__ St
       if (own) {
         const int row = orow_i;
         if (!VDEC) { tq = alpha * tq; tk = alpha * tk; }
-        for (int i = 0; i < M; i++) {
+        for (int i = 0; i < n; i++) {                          // live slots only; dead ones may hold garbage
           float ub;
-          if (A.qbuf) ub = static_cast<float>(reinterpret_cast<const int8_t*>(ubt)[i * DV + row]) * ubsf[i];
+          if (A.qbuf) ub = static_cast<float>(reinterpret_cast<const int8_t*>(ubt)[i * DV + row]) * usf[i];
           else ub = bf2f(reinterpret_cast<const unsigned short*>(ubt)[i * DV + row]);
-          ub = i < n ? ub : 0.f;
-          tq = fmaf(ub, cq[i], tq);
-          if (TWO) tk = fmaf(ub, ck[i], tk);
+          tq = fmaf(ub, dcf[i] * Dq[i], tq);
+          if (TWO) tk = fmaf(ub, dcf[i] * Dk[i], tk);
         }
         float u, o;
         if (KIND == K_GDN) {
@@ -496,227 +505,227 @@ __global__ void __launch_bounds__(NT) step_tma_kernel(const __grid_constant__ St
           u = beta * (vt - tk);
           o = fmaf(kq, u, tq);
         } else {
-          u = dtv * vt;
+          u = beta * vt;                                       // beta holds dt
           o = fmaf(kq, u, a * tq);
           if (A.beta) o = fmaf(Dv, vt, o);
         }
-        us[row] = u;
+        usb[row] = u;
         umax = fmaxf(umax, fabsf(u));
         stf(orow, A.dt_out, row, o);
       }
     }
-    // ---- append the value at slot n: one absmax scale over the whole row ----
     umax = warp_max(umax);
-    if (lane == 0) red[warp] = umax;
-    __syncthreads();
+    if (lane == 0) red[par * 4 + warp] = umax;
+    __syncthreads();                                           // u of this head complete; the stage is read out
+    if (misc[2] != 0.f) break;
     const bool full = n == M - 1;
-    float usc = 1.0f;
-    if (A.qbuf) usc = fp16_scale(fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])), 127.0f);
+    if (!full && tid == 0 && hi + nst < gqa) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      issue_stage(s, h + nst);
+    }
+
+    // ---- append the value at slot n (warp 0; the others go on): one absmax scale over the whole row ----
     uint8_t* UBh = UBseq + (long long)h * M * DV * bsz;
-    if (A.qbuf) {
-      for (int e = tid; e < DV / 4; e += NT) {
-        uint32_t w = 0;
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-          const float cc = rq_exact(us[4 * e + j], usc, 127.0f);
-          w |= (static_cast<uint32_t>(static_cast<int>(cc)) & 0xFFu) << (8 * j);
-          if (full) L[n * LDV + 4 * e + j] = cc * usc;
+    float* GBh = GBseq + (long long)h * M * (VDEC ? DK : 1);
+    float* GCh = GCseq + (long long)h * (VDEC ? DK : 1);
+    if (warp == 0) {
+      if (A.qbuf) {
+        const float usc = fp16_scale(fmaxf(fmaxf(red[par * 4], red[par * 4 + 1]), fmaxf(red[par * 4 + 2], red[par * 4 + 3])), 127.0f);
+        const bool fast_ok = usc >= FP16_MIN_NORMAL;
+        const float r = __fdiv_rn(1.0f, usc);
+        for (int e = lane; e < DV / 4; e += 32) {
+          float dq4[4];
+          const uint32_t w = round4_i8(usb + 4 * e, usc, r, fast_ok, dq4);
+          *reinterpret_cast<uint32_t*>(UBh + (long long)n * DV + 4 * e) = w;
+          if (full) { L[n * LDV + 4 * e] = dq4[0]; L[n * LDV + 4 * e + 1] = dq4[1]; L[n * LDV + 4 * e + 2] = dq4[2]; L[n * LDV + 4 * e + 3] = dq4[3]; }
         }
-        *reinterpret_cast<uint32_t*>(UBh + (long long)n * DV + 4 * e) = w;
+        if (lane == 0) UBSseq[h * M + n] = f2h(usc);
+      } else {
+        for (int e = lane; e < DV / 2; e += 32) {
+          const unsigned short b0 = f2bf(usb[2 * e]), b1 = f2bf(usb[2 * e + 1]);
+          if (full) { L[n * LDV + 2 * e] = bf2f(b0); L[n * LDV + 2 * e + 1] = bf2f(b1); }
+          *reinterpret_cast<uint32_t*>(UBh + ((long long)n * DV + 2 * e) * 2) = b0 | (static_cast<uint32_t>(b1) << 16);
+        }
       }
-      if (tid == 0) UBSh[n] = f2h(usc);
-    } else {
-      for (int e = tid; e < DV / 2; e += NT) {
-        const unsigned short b0 = f2bf(us[2 * e]), b1 = f2bf(us[2 * e + 1]);
-        if (full) { L[n * LDV + 2 * e] = bf2f(b0); L[n * LDV + 2 * e + 1] = bf2f(b1); }
-        *reinterpret_cast<uint32_t*>(UBh + ((long long)n * DV + 2 * e) * 2) = b0 | (static_cast<uint32_t>(b1) << 16);
+      if (VDEC) {
+        for (int t = lane; t < DK; t += 32) {
+          GBh[(long long)n * DK + t] = ga[t];
+          GCh[t] = full ? 0.f : ga[t];
+        }
+      } else if (lane == 0) {
+        GBh[n] = gnew;
+        *GCh = full ? 0.f : gnew;
       }
+      if (lane == 0) NPseq[h] = full ? 0 : n + 1;
     }
-    if (VDEC) {
-      for (int t = tid; t < DK; t += NT) {
-        GBh[(long long)n * DK + t] = ga[t];
-        GCh[t] = full ? 0.f : ga[t];
+    if (!full) continue;
+
+    // ---- fold: S = decay * S_0 + sum_i L_i R_i^T in slot order, re-rounded in place ----
+    const float alphan = VDEC ? 1.0f : expf(gnew);
+    // R: the keys of all slots (KDA: times their decay ratio), once per key head; slot M-1 is the new key
+    if (!r_built) {
+      for (int e = tid; e < M * DK; e += NT) {
+        const int i = e / DK, k = e - i * DK;
+        float kv;
+        if (i == M - 1) {
+          kv = krnd[k];
+        } else {
+          if (A.qbuf) kv = static_cast<float>(reinterpret_cast<const int8_t*>(kbt)[e]) * h2f(KBSh[i]);
+          else kv = bf2f(reinterpret_cast<const unsigned short*>(kbt)[e]);
+          if (VDEC) kv = kv * expf(ga[k] - gbt[e]);
+        }
+        R[i * RDK + (k / 16) * 20 + (k % 16)] = kv;
       }
-    } else if (tid == 0) {
-      GBh[n] = gnew;
-      *GCh = full ? 0.f : gnew;
+      r_built = true;
     }
-    if (tid == 0) *NPh = full ? 0 : n + 1;
+    // L: the buffered values of slots 0..M-2, times their decay (GDN, Mamba2); slot M-1 is written by warp 0 above
+    for (int e = tid; e < (M - 1) * DV; e += NT) {
+      const int i = e / DV, v = e - i * DV;
+      float ub;
+      if (A.qbuf) ub = static_cast<float>(reinterpret_cast<const int8_t*>(ubt)[e]) * usf[i];
+      else ub = bf2f(reinterpret_cast<const unsigned short*>(ubt)[e]);
+      if (!VDEC) ub = expf(gnew - GBh[i]) * ub;
+      L[i * LDV + v] = ub;
+    }
+    __syncthreads();
 
-    // ---- fold ----
-    if (full) {
-      const float alphan = VDEC ? 1.0f : expf(gnew);
-      // R: the keys of all slots (KDA: times their decay ratio), once per key head; slot M-1 from registers
-      if (!r_built) {
-        for (int i = warp; i < M - 1; i += NW) {
+    int wpg = NW, ppw = PPW, gpi = 1;
+    if (!AXK) {
+      wpg = min(NW, G / RPP);
+      ppw = G / (RPP * wpg);
+      gpi = NW / wpg;
+    }
+    const int BR = AXK ? NW * PPW * RPP : gpi * G;
+    const int niter = (DV + BR - 1) / BR;
+    unsigned short* SCh = SCseq + (long long)h * scn;
+    uint8_t* Sh = Sseq + (long long)h * P.codes_b;
+    for (int it = 0; it < niter; it++) {
+      int rows[PPW];
+      bool rv[PPW];
+      float2 acc[PPW][8];
+      const int gvrow = AXK ? 0 : it * gpi + warp / wpg;
 #pragma unroll
-          for (int j = 0; j < CW; j++) {
-            const int k = lane * CW + j;
-            float kv = key_of(i, j);
-            if (VDEC) kv = kv * expf(gnr[j] - gbt[i * DK + k]);
-            R[i * RDK + (k / 16) * 20 + (k % 16)] = kv;
-          }
-        }
-        if (warp == 0) {
+      for (int pp = 0; pp < PPW; pp++) {
+        int row;
+        if (AXK) row = it * BR + warp * (PPW * RPP) + pp * RPP + rl;
+        else row = gvrow * G + (warp % wpg) * (ppw * RPP) + pp * RPP + rl;
+        rv[pp] = pp < ppw && row < DV;
+        rows[pp] = rv[pp] ? row : 0;
+        decode16<BITS>(codes + rows[pp] * ROWB + c * CB, acc[pp]);
+        if (AXK) {
+          const float sc = h2f(scs[rows[pp] * NG + gl]);
 #pragma unroll
-          for (int j = 0; j < CW; j++) {
-            const int k = lane * CW + j;
-            const float kv = A.qbuf ? rq_exact(kxr[j], ksc, 127.0f) * ksc : bf2f(f2bf(kxr[j]));
-            R[(M - 1) * RDK + (k / 16) * 20 + (k % 16)] = kv;
-          }
+          for (int p = 0; p < 8; p++)
+            acc[pp][p] = __fmul2_rn(acc[pp][p], make_float2(sc * presc<BITS>(2 * p), sc * presc<BITS>(2 * p + 1)));
         }
-        r_built = true;
       }
-      // L: the buffered values of slots 0..M-2 times their decay (GDN, Mamba2); slot M-1 was written above
-      if (!VDEC && tid < M - 1) dec[tid] = expf(gnew - GBh[tid]);
-      __syncthreads();
-      for (int e = tid; e < (M - 1) * DV; e += NT) {
-        const int i = e / DV, v = e - i * DV;
-        float ub;
-        if (A.qbuf) ub = static_cast<float>(reinterpret_cast<const int8_t*>(ubt)[i * DV + v]) * ubsf[i];
-        else ub = bf2f(reinterpret_cast<const unsigned short*>(ubt)[i * DV + v]);
-        L[i * LDV + v] = VDEC ? ub : dec[i] * ub;
-      }
-      __syncthreads();
-
-      int wpg = NW, ppw = PPW, gpi = 1;
       if (!AXK) {
-        wpg = min(NW, G / RPP);
-        ppw = G / (RPP * wpg);
-        gpi = NW / wpg;
-      }
-      const int BR = AXK ? NW * PPW * RPP : gpi * G;
-      const int niter = (DV + BR - 1) / BR;
-      unsigned short* SCh = SCseq + (long long)h * scn;
-      uint8_t* Sh = Sseq + (long long)h * P.codes_b;
-      for (int it = 0; it < niter; it++) {
-        int rows[PPW];
-        bool rv[PPW];
-        float2 acc[PPW][8];
-        const int gvrow = AXK ? 0 : it * gpi + warp / wpg;
-#pragma unroll
-        for (int pp = 0; pp < PPW; pp++) {
-          int row;
-          if (AXK) row = it * BR + warp * (PPW * RPP) + pp * RPP + rl;
-          else row = gvrow * G + (warp % wpg) * (ppw * RPP) + pp * RPP + rl;
-          rv[pp] = pp < ppw && row < DV;
-          rows[pp] = rv[pp] ? row : 0;
-          decode16<BITS>(codes + rows[pp] * ROWB + c * CB, acc[pp]);
-          if (AXK) {
-            const float sc = h2f(scs[rows[pp] * NG + gl]);
-#pragma unroll
-            for (int p = 0; p < 8; p++)
-              acc[pp][p] = __fmul2_rn(acc[pp][p], make_float2(sc * presc<BITS>(2 * p), sc * presc<BITS>(2 * p + 1)));
-          }
-        }
-        if (!AXK) {
-          const bool gvalid = gvrow * G < DV;
-#pragma unroll
-          for (int p = 0; p < 8; p++) {
-            const int k0 = c * 16 + 2 * p;
-            const float s0 = gvalid ? h2f(scs[gvrow * DK + k0]) : 0.f, s1 = gvalid ? h2f(scs[gvrow * DK + k0 + 1]) : 0.f;
-            const float2 s2 = make_float2(s0 * presc<BITS>(2 * p), s1 * presc<BITS>(2 * p + 1));
-#pragma unroll
-            for (int pp = 0; pp < PPW; pp++) acc[pp][p] = __fmul2_rn(acc[pp][p], s2);
-          }
-        }
+        const bool gvalid = gvrow * G < DV;
 #pragma unroll
         for (int p = 0; p < 8; p++) {
-          float2 d2 = make_float2(alphan, alphan);
-          if (VDEC) d2 = make_float2(ae[c * 16 + 2 * p], ae[c * 16 + 2 * p + 1]);
+          const int k0 = c * 16 + 2 * p;
+          const float s0 = gvalid ? h2f(scs[gvrow * DK + k0]) : 0.f, s1 = gvalid ? h2f(scs[gvrow * DK + k0 + 1]) : 0.f;
+          const float2 s2 = make_float2(s0 * presc<BITS>(2 * p), s1 * presc<BITS>(2 * p + 1));
 #pragma unroll
-          for (int pp = 0; pp < PPW; pp++) acc[pp][p] = __fmul2_rn(acc[pp][p], d2);
+          for (int pp = 0; pp < PPW; pp++) acc[pp][p] = __fmul2_rn(acc[pp][p], s2);
         }
-        for (int i = 0; i < M; i++) {
-          float2 l2[PPW];
+      }
+#pragma unroll
+      for (int p = 0; p < 8; p++) {
+        float2 d2 = make_float2(alphan, alphan);
+        if (VDEC) d2 = make_float2(ae[c * 16 + 2 * p], ae[c * 16 + 2 * p + 1]);
+#pragma unroll
+        for (int pp = 0; pp < PPW; pp++) acc[pp][p] = __fmul2_rn(acc[pp][p], d2);
+      }
+      for (int i = 0; i < M; i++) {
+        float2 l2[PPW];
+#pragma unroll
+        for (int pp = 0; pp < PPW; pp++) {
+          const float l = L[i * LDV + rows[pp]];
+          l2[pp] = make_float2(l, l);
+        }
+        const float4* rrow = reinterpret_cast<const float4*>(R + i * RDK + c * 20);
+#pragma unroll
+        for (int j4 = 0; j4 < 4; j4++) {
+          const float4 kr4 = rrow[j4];
+          const float2 ka = make_float2(kr4.x, kr4.y), kb2 = make_float2(kr4.z, kr4.w);
 #pragma unroll
           for (int pp = 0; pp < PPW; pp++) {
-            const float l = L[i * LDV + rows[pp]];
-            l2[pp] = make_float2(l, l);
-          }
-          const float4* rrow = reinterpret_cast<const float4*>(R + i * RDK + c * 20);
-#pragma unroll
-          for (int j4 = 0; j4 < 4; j4++) {
-            const float4 kr4 = rrow[j4];
-            const float2 ka = make_float2(kr4.x, kr4.y), kb2 = make_float2(kr4.z, kr4.w);
-#pragma unroll
-            for (int pp = 0; pp < PPW; pp++) {
-              acc[pp][2 * j4] = __ffma2_rn(l2[pp], ka, acc[pp][2 * j4]);
-              acc[pp][2 * j4 + 1] = __ffma2_rn(l2[pp], kb2, acc[pp][2 * j4 + 1]);
-            }
+            acc[pp][2 * j4] = __ffma2_rn(l2[pp], ka, acc[pp][2 * j4]);
+            acc[pp][2 * j4 + 1] = __ffma2_rn(l2[pp], kb2, acc[pp][2 * j4 + 1]);
           }
         }
-        // re-round
-        constexpr float MB = BITS == 4 ? MAGIC + 8.0f : MAGIC;
-        if constexpr (AXK) {
-          const int lpg = G / 16;
+      }
+      // re-round
+      constexpr float MB = BITS == 4 ? MAGIC + 8.0f : MAGIC;
+      if constexpr (AXK) {
+        const int lpg = G / 16;
 #pragma unroll
-          for (int pp = 0; pp < PPW; pp++) {
-            float am = 0.f;
+        for (int pp = 0; pp < PPW; pp++) {
+          float am = 0.f;
 #pragma unroll
-            for (int p = 0; p < 8; p++) am = fmaxf(am, fmaxf(fabsf(acc[pp][p].x), fabsf(acc[pp][p].y)));
-            for (int o = 1; o < lpg; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-            const float sc = fp16_scale(am, QMAX);
-            if (!rv[pp]) continue;
-            if ((c & (lpg - 1)) == 0) SCh[rows[pp] * NG + gl] = f2h(sc);
-            float2 t[8];
-            bool ok = sc >= FP16_MIN_NORMAL && round_fast<8>(acc[pp], sc, __fdiv_rn(1.0f, sc), MB, t);
-            if (!ok) {
-#pragma unroll
-              for (int p = 0; p < 8; p++) {
-                t[p].x = rq_exact(acc[pp][p].x, sc, QMAX) + MB;
-                t[p].y = rq_exact(acc[pp][p].y, sc, QMAX) + MB;
-              }
-            }
-            store_codes16<BITS>(Sh + (long long)rows[pp] * ROWB + c * CB, t);
-          }
-        } else {
-          // column maxima over the group's rows: this lane's passes, the lanes of other rows, the other warps
-          float cm[16];
-#pragma unroll
-          for (int p = 0; p < 8; p++) {
-            float m0 = 0.f, m1 = 0.f;
-#pragma unroll
-            for (int pp = 0; pp < PPW; pp++) {
-              if (rv[pp]) { m0 = fmaxf(m0, fabsf(acc[pp][p].x)); m1 = fmaxf(m1, fabsf(acc[pp][p].y)); }
-            }
-            for (int o = LPR; o < 32; o <<= 1) {
-              m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
-              m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, o));
-            }
-            cm[2 * p] = m0;
-            cm[2 * p + 1] = m1;
-          }
-          __syncthreads();
-          if (rl == 0) {
-#pragma unroll
-            for (int j = 0; j < 16; j++) cmax[warp * DK + c * 16 + j] = cm[j];
-          }
-          __syncthreads();
-          // scale and reciprocal of every column of every group in flight, one column per thread
-          float* ssc = cmax + NW * DK;          // [gpi][DK] scales, reciprocal flag packed alongside
-          for (int e = tid; e < gpi * DK; e += NT) {
-            const int gi = e / DK, k = e - gi * DK;
-            float am = 0.f;
-            for (int w = 0; w < wpg; w++) am = fmaxf(am, cmax[(gi * wpg + w) * DK + k]);
-            const float sc = fp16_scale(am, QMAX);
-            ssc[gi * DK + k] = sc;
-            const int gvr = it * gpi + gi;
-            if (gvr * G < DV) SCh[gvr * DK + k] = f2h(sc);
-          }
-          __syncthreads();
-          const float* myssc = ssc + (warp / wpg) * DK + c * 16;
-#pragma unroll
-          for (int pp = 0; pp < PPW; pp++) {
-            if (!rv[pp]) continue;
-            float2 t[8];
+          for (int p = 0; p < 8; p++) am = fmaxf(am, fmaxf(fabsf(acc[pp][p].x), fabsf(acc[pp][p].y)));
+          for (int o = 1; o < lpg; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+          const float sc = fp16_scale(am, QMAX);
+          if (!rv[pp]) continue;
+          if ((c & (lpg - 1)) == 0) SCh[rows[pp] * NG + gl] = f2h(sc);
+          float2 t[8];
+          bool ok = sc >= FP16_MIN_NORMAL && round_fast<8>(acc[pp], sc, __fdiv_rn(1.0f, sc), MB, t);
+          if (!ok) {
 #pragma unroll
             for (int p = 0; p < 8; p++) {
-              t[p].x = rq_exact(acc[pp][p].x, myssc[2 * p], QMAX) + MB;
-              t[p].y = rq_exact(acc[pp][p].y, myssc[2 * p + 1], QMAX) + MB;
+              t[p].x = rq_exact(acc[pp][p].x, sc, QMAX) + MB;
+              t[p].y = rq_exact(acc[pp][p].y, sc, QMAX) + MB;
             }
-            store_codes16<BITS>(Sh + (long long)rows[pp] * ROWB + c * CB, t);
           }
+          store_codes16<BITS>(Sh + (long long)rows[pp] * ROWB + c * CB, t);
+        }
+      } else {
+        // column maxima over the group's rows: this lane's passes, the lanes of other rows, the other warps
+        float cm[16];
+#pragma unroll
+        for (int p = 0; p < 8; p++) {
+          float m0 = 0.f, m1 = 0.f;
+#pragma unroll
+          for (int pp = 0; pp < PPW; pp++) {
+            if (rv[pp]) { m0 = fmaxf(m0, fabsf(acc[pp][p].x)); m1 = fmaxf(m1, fabsf(acc[pp][p].y)); }
+          }
+          for (int o = LPR; o < 32; o <<= 1) {
+            m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
+            m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, o));
+          }
+          cm[2 * p] = m0;
+          cm[2 * p + 1] = m1;
+        }
+        __syncthreads();
+        if (rl == 0) {
+#pragma unroll
+          for (int j = 0; j < 16; j++) cmax[warp * DK + c * 16 + j] = cm[j];
+        }
+        __syncthreads();
+        // scale (and its reciprocal) of every column of every group in flight, one column per thread
+        float* ssc = cmax + NW * DK;
+        for (int e = tid; e < gpi * DK; e += NT) {
+          const int gi = e / DK, k = e - gi * DK;
+          float am = 0.f;
+          for (int w = 0; w < wpg; w++) am = fmaxf(am, cmax[(gi * wpg + w) * DK + k]);
+          const float sc = fp16_scale(am, QMAX);
+          ssc[gi * DK + k] = sc;
+          const int gvr = it * gpi + gi;
+          if (gvr * G < DV) SCh[gvr * DK + k] = f2h(sc);
+        }
+        __syncthreads();
+        const float* myssc = ssc + (warp / wpg) * DK + c * 16;
+#pragma unroll
+        for (int pp = 0; pp < PPW; pp++) {
+          if (!rv[pp]) continue;
+          float2 t[8];
+#pragma unroll
+          for (int p = 0; p < 8; p++) {
+            t[p].x = rq_exact(acc[pp][p].x, myssc[2 * p], QMAX) + MB;
+            t[p].y = rq_exact(acc[pp][p].y, myssc[2 * p + 1], QMAX) + MB;
+          }
+          store_codes16<BITS>(Sh + (long long)rows[pp] * ROWB + c * CB, t);
         }
       }
     }
@@ -727,11 +736,7 @@ __global__ void __launch_bounds__(NT) step_tma_kernel(const __grid_constant__ St
       issue_stage(s, h + nst);
     }
   }
-  if (!alive) {
-    // a copy never completed: record it and leave without touching the state further.  Nothing else of this CTA is
-    // in flight except copies into its own shared memory, which the hardware retires with the CTA.
-    if (tid == 0) atomicAdd(&g_step_status[0], 1);
-  }
+  if (misc[2] != 0.f && tid == 0) atomicAdd(&g_step_status[0], 1);   // a copy never completed (see mbar_wait)
 }
 
 }  // namespace sqb
