@@ -55,8 +55,8 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 
 // shared-memory plan of the staged kernel (byte offsets; float offsets from f0)
 struct Smem2 {
-  int bars, stage0, stage_bytes, codes_b, scales_b, ub_b, kb, gbt, f0, total;
-  int xq, xk, ga, ae, krnd, us, R, L, Dq, Dk, hd, decf, ubs, red, misc, cmax, rdk, ldv;
+  int bars, stage0, stage_bytes, codes_b, scales_b, ub_b, kb, gbt, rl, f0, total;
+  int xq, xk, ga, ae, krnd, us, Dq, Dk, hd, decf, ubs, red, misc, cmax, rdk, ldv;
 };
 constexpr int HD_W = 8;     // per-head scalars: g, beta | dt, gcur, alpha, a, gnew, D, n
 __host__ __device__ inline int al16i(int x) { return (x + 15) & ~15; }
@@ -64,34 +64,39 @@ __host__ __device__ inline Smem2 smem2_plan(int kind, int bits, int axk, int gro
                                             int nst, int gqa) {
   Smem2 s;
   const int bsz = qbuf ? 1 : 2;
+  const int lpr = DK / 16;
+  s.rdk = lpr * 20;                 // 16 columns + 4 floats of padding per lane chunk
+  s.ldv = DV + 32 / lpr;
   s.codes_b = DV * DK * bits / 8;
   s.scales_b = al16i((axk ? DV * (DK / group) : (DV / group) * DK) * 2);
   s.ub_b = al16i(M * DV * bsz);
   s.stage_bytes = s.codes_b + s.scales_b + s.ub_b;
+  const int rl_bytes = al16i((M * s.rdk + M * s.ldv) * 4);     // fold tiles R [M][rdk], L [M][ldv]
   int o = 0;
   s.bars = o; o += 64;
   s.stage0 = o; o += nst * s.stage_bytes;
+  // a fold step keeps a single stage in flight, so its R / L tiles can live in the last stage's buffer
+  if (nst >= 2 && rl_bytes <= s.stage_bytes) {
+    s.rl = s.stage0 + (nst - 1) * s.stage_bytes;
+  } else {
+    s.rl = o; o += rl_bytes;
+  }
   s.kb = o; o += al16i(M * DK * bsz);
   s.gbt = o; o += (kind == K_KDA ? M * DK * 4 : 0);
   s.f0 = o;
-  const int lpr = DK / 16;
-  s.rdk = lpr * 20;                 // 16 columns + 4 floats of padding per lane chunk
-  s.ldv = DV + 32 / lpr;
   int f = 0;
   s.xq = f; f += DK;
   s.xk = f; f += DK;
   s.ga = f; f += (kind == K_KDA ? DK : 0);
   s.ae = f; f += (kind == K_KDA ? DK : 0);
   s.krnd = f; f += DK;
-  s.us = f; f += 2 * DV;
-  s.R = f; f += M * s.rdk;
-  s.L = f; f += M * s.ldv;
+  s.us = f; f += gqa * DV;
   s.Dq = f; f += 32;
   s.Dk = f; f += 32;
   s.hd = f; f += gqa * HD_W;
   s.decf = f; f += gqa * M;
   s.ubs = f; f += gqa * M;
-  s.red = f; f += 8;
+  s.red = f; f += gqa * NW;
   s.misc = f; f += 8;
   s.cmax = f; f += (axk ? 0 : 2 * NW * DK);
   s.total = s.f0 + ((f + 3) & ~3) * 4;
@@ -176,9 +181,9 @@ __device__ __forceinline__ float transpose_reduce(float (&v)[LPR], int c) {
   return v[0];
 }
 
-// Rounds DV/4-word chunks of a value vector against scale s: code = clamp(rint(div_rn(x, s)), +-127), by a
-// reciprocal multiply checked with an exact residual (see round_fast); returns the four codes as bytes of a word
-// and their dequantised values.
+// Rounds four entries of a value vector against scale s: code = clamp(rint(div_rn(x, s)), +-127), by a reciprocal
+// multiply checked with an exact residual (see round_fast); returns the four codes as bytes of a word and their
+// dequantised values.
 __device__ __forceinline__ uint32_t round4_i8(const float* x, float s, float r, bool fast_ok, float (&deq)[4]) {
   float2 t[2];
   const float2 xv[2] = {make_float2(x[0], x[1]), make_float2(x[2], x[3])};
@@ -204,6 +209,7 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
   constexpr int CB = 16 * BITS / 8;              // bytes of a lane chunk
   constexpr int ROWB = DK * BITS / 8;
   constexpr int CW = DK / 32;                    // columns per lane in the prologue
+  constexpr int QD = DK / 4;                     // columns per lane in the buffered-key dot products
   constexpr bool TWO = KIND != K_M2;
   constexpr bool VDEC = KIND == K_KDA;
   constexpr float QMAX = BITS == 4 ? 7.0f : 127.0f;
@@ -216,6 +222,36 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
   const int b = blockIdx.x / A.HK, hk = blockIdx.x - b * A.HK;
   const int h0 = hk * gqa;
   const int osz = dt_size(A.dt_out);
+
+  // ---- activation loads that do not depend on the slot: issued before anything else ----------------------------
+  float qr[CW], kr[CW], g4[4];
+  if (warp == 0) {
+#pragma unroll
+    for (int j = 0; j < CW; j++) {
+      qr[j] = ldf(A.q + (long long)b * A.sq, A.dt_qk, (long long)hk * DK + lane * CW + j);
+      kr[j] = ldf(A.k + (long long)b * A.sk, A.dt_qk, (long long)hk * DK + lane * CW + j);
+    }
+  } else if (warp == 1) {
+    g4[0] = g4[1] = g4[2] = g4[3] = 0.f;
+    if (lane < gqa) {                                  // heads beyond 32 per key head are loaded in the loop below
+      const int h = h0 + lane;
+      if (KIND == K_GDN) {
+        if (A.gate) {
+          g4[0] = ldf(A.a + (long long)b * A.sa, A.dt_ab, h); g4[1] = ldf(A.dt_bias, A.dt_dtb, h);
+          g4[2] = ldf(A.A_log, A.dt_alog, h);                 g4[3] = ldf(A.b + (long long)b * A.sb, A.dt_ab, h);
+        } else {
+          g4[0] = ldf(A.g + (long long)b * A.sg, A.dt_g, h);  g4[1] = ldf(A.beta + (long long)b * A.sbeta, A.dt_g, h);
+        }
+      } else if (KIND == K_M2) {
+        g4[0] = ldf(A.g + (long long)b * A.sg, A.dt_g, h);
+        if (A.dt_bias) g4[1] = ldf(A.dt_bias, A.dt_dtb, h);
+        g4[2] = ldf(A.A_log, A.dt_alog, h);
+        if (A.beta) g4[3] = ldf(A.beta, A.dt_beta, h);
+      } else {
+        g4[0] = ldf(A.beta + (long long)b * A.sbeta, A.dt_beta, h);
+      }
+    }
+  }
 
   long long seq = b;
   if (A.idx != nullptr) {
@@ -231,10 +267,12 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
   uint8_t* kbt = smraw + P.kb;
   float* fsm = reinterpret_cast<float*>(smraw + P.f0);
   float *xq = fsm + P.xq, *xk = fsm + P.xk, *ga = fsm + P.ga, *ae = fsm + P.ae, *krnd = fsm + P.krnd, *us = fsm + P.us,
-        *R = fsm + P.R, *L = fsm + P.L, *Dq = fsm + P.Dq, *Dk = fsm + P.Dk, *hd = fsm + P.hd, *decf = fsm + P.decf,
-        *ubsf = fsm + P.ubs, *red = fsm + P.red, *misc = fsm + P.misc, *cmax = fsm + P.cmax;
-  const float* gbt = reinterpret_cast<const float*>(smraw + P.gbt);
+        *Dq = fsm + P.Dq, *Dk = fsm + P.Dk, *hd = fsm + P.hd, *decf = fsm + P.decf, *ubsf = fsm + P.ubs,
+        *red = fsm + P.red, *misc = fsm + P.misc, *cmax = fsm + P.cmax;
+  float* R = reinterpret_cast<float*>(smraw + P.rl);
   const int RDK = P.rdk, LDV = P.ldv;
+  float* L = R + M * RDK;
+  const float* gbt = reinterpret_cast<const float*>(smraw + P.gbt);
   const int bsz = A.qbuf ? 1 : 2;
   const int NG = AXK ? DK / G : 1;
   const int scn = AXK ? DV * NG : (DV / G) * DK;         // scales per head
@@ -250,41 +288,46 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
   float* GBseq = reinterpret_cast<float*>(A.GB + seq * A.sGB);
   float* GCseq = reinterpret_cast<float*>(A.GCUR + seq * A.sGC);
   int* NPseq = reinterpret_cast<int*>(A.NPTR + seq * A.sN);
+  const uint32_t stage_tx = P.codes_b + scn * 2 + M * DV * bsz;
 
-  // ---- producer: barriers, the key tile, the first stages ------------------------------------------------------
-  auto issue_stage = [&](int s, int h) {
+  auto issue_stage = [&](int s, int h) {                 // one thread issues a whole stage (refills)
     uint8_t* st = smraw + P.stage0 + s * P.stage_bytes;
-    mbar_expect_tx(&bars[s], P.codes_b + scn * 2 + M * DV * bsz);
+    mbar_expect_tx(&bars[s], stage_tx);
     bulk_g2s(st, Sseq + (long long)h * P.codes_b, P.codes_b, &bars[s]);
     bulk_g2s(st + P.codes_b, SCseq + (long long)h * scn, scn * 2, &bars[s]);
     bulk_g2s(st + P.codes_b + P.scales_b, UBseq + (long long)h * M * DV * bsz, M * DV * bsz, &bars[s]);
   };
-  if (tid == 0) {
-    for (int s = 0; s <= nst; s++) mbar_init(&bars[s], 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    uint32_t kbytes = M * DK * bsz + (VDEC ? M * DK * 4 : 0);
-    mbar_expect_tx(&bars[nst], kbytes);
-    bulk_g2s(kbt, KBh, M * DK * bsz, &bars[nst]);
-    if (VDEC) bulk_g2s(smraw + P.gbt, GBseq + (long long)h0 * M * DK, M * DK * 4, &bars[nst]);
-    for (int s = 0; s < nst && s < gqa; s++) issue_stage(s, h0 + s);
-    misc[2] = 0.f;                                      // "a copy never arrived" flag
-  }
-  __syncthreads();     // barriers initialised before anyone polls them
 
   // ---- prologue, by role ----------------------------------------------------------------------------------------
   if (warp == 0) {
-    // the key head: normalise q and k (lane holds CW columns), k.q, the key appended to the buffer, and the dot
-    // products of the buffered keys with q and k
+    // producer: barriers, then the key tile and stage 0, one copy per lane
+    if (lane == 0) {
+      for (int s = 0; s <= nst; s++) mbar_init(&bars[s], 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      misc[2] = 0.f;                                      // "a copy never arrived" flag
+    }
+    __syncwarp();
+    if (lane == 0) {
+      mbar_expect_tx(&bars[nst], M * DK * bsz + (VDEC ? M * DK * 4 : 0));
+      bulk_g2s(kbt, KBh, M * DK * bsz, &bars[nst]);
+    } else if (lane == 1) {
+      if (VDEC) bulk_g2s(smraw + P.gbt, GBseq + (long long)h0 * M * DK, M * DK * 4, &bars[nst]);
+    } else if (lane == 2) {
+      mbar_expect_tx(&bars[0], stage_tx);
+      bulk_g2s(smraw + P.stage0, Sseq + (long long)h0 * P.codes_b, P.codes_b, &bars[0]);
+    } else if (lane == 3) {
+      bulk_g2s(smraw + P.stage0 + P.codes_b, SCseq + (long long)h0 * scn, scn * 2, &bars[0]);
+    } else if (lane == 4) {
+      bulk_g2s(smraw + P.stage0 + P.codes_b + P.scales_b, UBseq + (long long)h0 * M * DV * bsz, M * DV * bsz, &bars[0]);
+    }
+    // the key head: counters and buffered-key scales first (their latency overlaps the normalisation)
     const int n0 = NPseq[h0] & (M - 1);       // the heads of a slot advance together
     float ksv = 0.f;                          // scale of buffered key `lane`
     if (A.qbuf && lane < M) ksv = h2f(KBSh[lane]);
-    float qr[CW], kr[CW], gnr[CW];
+    float gnr[CW];
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (int j = 0; j < CW; j++) {
-      qr[j] = ldf(A.q + (long long)b * A.sq, A.dt_qk, (long long)hk * DK + lane * CW + j);
-      kr[j] = ldf(A.k + (long long)b * A.sk, A.dt_qk, (long long)hk * DK + lane * CW + j);
       s0 += qr[j] * qr[j];
       s1 += kr[j] * kr[j];
       if (VDEC) gnr[j] = GCseq[(long long)h0 * DK + lane * CW + j] +
@@ -309,9 +352,13 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
       xk[lane * CW + j] = kr[j];
       if (VDEC) { ga[lane * CW + j] = gnr[j]; ae[lane * CW + j] = expf(gnr[j]); }
     }
+    // the remaining stages: a fold step keeps only one in flight (the last stage's buffer holds the fold tiles)
+    if (lane == 0 && n0 != M - 1) {
+      for (int s = 1; s < nst && s < gqa; s++) issue_stage(s, h0 + s);
+    }
     d = warp_sum(d);
     mx = warp_max(mx);
-    if (lane == 0) misc[0] = d;
+    if (lane == 0) { misc[0] = d; misc[1] = __int_as_float(n0); }
     // append the key at slot n0; its rounded value is what the fold uses for slot M-1
     if (A.qbuf) {
       const float ksc = fp16_scale(mx, 127.0f);
@@ -333,60 +380,98 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
         krnd[lane * CW + j] = bf2f(bb);
       }
     }
+    __syncwarp();                              // xq, xk (ga) written by this warp are read below
     if (!mbar_wait(&bars[nst], 0) && lane == 0) misc[2] = 1.f;
-    for (int i = 0; i < M; i++) {
+    // dot products of the buffered keys with q and k: lane = (slot, quarter of d_k), 8 slots per round
+    for (int i0 = 0; i0 < M; i0 += 8) {
+      const int i = i0 + (lane >> 2), part = lane & 3;
+      const float ks_i = __shfl_sync(0xffffffffu, ksv, i & 31);
       float dq = 0.f, dk = 0.f;
-      const float ks_i = __shfl_sync(0xffffffffu, ksv, i);
       if (i < n0) {
 #pragma unroll
-        for (int j = 0; j < CW; j++) {
-          const int k = lane * CW + j;
-          float kv;
-          if (A.qbuf) kv = static_cast<float>(reinterpret_cast<const int8_t*>(kbt)[i * DK + k]) * ks_i;
-          else kv = bf2f(reinterpret_cast<const unsigned short*>(kbt)[i * DK + k]);
-          if (VDEC) kv = kv * expf(gnr[j] - gbt[i * DK + k]);
-          dq = fmaf(kv, qr[j], dq);
-          if (TWO) dk = fmaf(kv, kr[j], dk);
+        for (int j0 = 0; j0 < QD; j0 += 4) {
+          const int k = part * QD + j0;
+          float kv[4];
+          if (A.qbuf) {
+            const uint32_t wx = *reinterpret_cast<const uint32_t*>(kbt + i * DK + k) ^ 0x80808080u;
+            kv[0] = byte_to_f<0>(wx) * ks_i; kv[1] = byte_to_f<1>(wx) * ks_i;
+            kv[2] = byte_to_f<2>(wx) * ks_i; kv[3] = byte_to_f<3>(wx) * ks_i;
+          } else {
+            const uint2 w2 = *reinterpret_cast<const uint2*>(kbt + (i * DK + k) * 2);
+            kv[0] = __uint_as_float(w2.x << 16); kv[1] = __uint_as_float(w2.x & 0xFFFF0000u);
+            kv[2] = __uint_as_float(w2.y << 16); kv[3] = __uint_as_float(w2.y & 0xFFFF0000u);
+          }
+          const float4 q4 = *reinterpret_cast<const float4*>(xq + k);
+          const float4 k4 = *reinterpret_cast<const float4*>(xk + k);
+          if (VDEC) {
+            const float4 g4v = *reinterpret_cast<const float4*>(ga + k);
+            const float4 b4 = *reinterpret_cast<const float4*>(gbt + i * DK + k);
+            kv[0] = kv[0] * expf(g4v.x - b4.x); kv[1] = kv[1] * expf(g4v.y - b4.y);
+            kv[2] = kv[2] * expf(g4v.z - b4.z); kv[3] = kv[3] * expf(g4v.w - b4.w);
+          }
+          dq = fmaf(kv[0], q4.x, dq); dq = fmaf(kv[1], q4.y, dq); dq = fmaf(kv[2], q4.z, dq); dq = fmaf(kv[3], q4.w, dq);
+          if (TWO) { dk = fmaf(kv[0], k4.x, dk); dk = fmaf(kv[1], k4.y, dk); dk = fmaf(kv[2], k4.z, dk); dk = fmaf(kv[3], k4.w, dk); }
         }
-        dq = warp_sum(dq);
-        dk = warp_sum(dk);
       }
-      if (lane == 0) { Dq[i] = dq; Dk[i] = dk; }
+      dq += __shfl_xor_sync(0xffffffffu, dq, 1); dq += __shfl_xor_sync(0xffffffffu, dq, 2);
+      dk += __shfl_xor_sync(0xffffffffu, dk, 1); dk += __shfl_xor_sync(0xffffffffu, dk, 2);
+      if (part == 0 && i < M) { Dq[i] = dq; Dk[i] = dk; }
     }
   } else if (warp == 1) {
-    // per value head: gates, counters, decay factors of the live buffer slots and their value scales
+    // per value head: gates and the scalars derived from them
     for (int hi = lane; hi < gqa; hi += 32) {
       const int h = h0 + hi;
-      float g = 0.f, bt = 0.f, Dv = 0.f, gcur = 0.f;
+      if (hi >= 32) {                                    // more than 32 heads per key head: load here
+        g4[0] = g4[1] = g4[2] = g4[3] = 0.f;
+        if (KIND == K_GDN) {
+          if (A.gate) {
+            g4[0] = ldf(A.a + (long long)b * A.sa, A.dt_ab, h); g4[1] = ldf(A.dt_bias, A.dt_dtb, h);
+            g4[2] = ldf(A.A_log, A.dt_alog, h);                 g4[3] = ldf(A.b + (long long)b * A.sb, A.dt_ab, h);
+          } else {
+            g4[0] = ldf(A.g + (long long)b * A.sg, A.dt_g, h);  g4[1] = ldf(A.beta + (long long)b * A.sbeta, A.dt_g, h);
+          }
+        } else if (KIND == K_M2) {
+          g4[0] = ldf(A.g + (long long)b * A.sg, A.dt_g, h);
+          if (A.dt_bias) g4[1] = ldf(A.dt_bias, A.dt_dtb, h);
+          g4[2] = ldf(A.A_log, A.dt_alog, h);
+          if (A.beta) g4[3] = ldf(A.beta, A.dt_beta, h);
+        } else {
+          g4[0] = ldf(A.beta + (long long)b * A.sbeta, A.dt_beta, h);
+        }
+      }
+      const float gcur = VDEC ? 0.f : GCseq[h];
+      float g = 0.f, bt = 0.f, Dv = 0.f;
       if (KIND == K_GDN) {
         if (A.gate) {
-          const float x = ldf(A.a + (long long)b * A.sa, A.dt_ab, h) + ldf(A.dt_bias, A.dt_dtb, h);
+          const float x = g4[0] + g4[1];
           const float sp = x <= 20.0f ? logf(1.0f + expf(x)) : x;
-          g = -expf(ldf(A.A_log, A.dt_alog, h)) * sp;
-          bt = __fdiv_rn(1.0f, 1.0f + expf(-ldf(A.b + (long long)b * A.sb, A.dt_ab, h)));
+          g = -expf(g4[2]) * sp;
+          bt = __fdiv_rn(1.0f, 1.0f + expf(-g4[3]));
         } else {
-          g = ldf(A.g + (long long)b * A.sg, A.dt_g, h);
-          bt = ldf(A.beta + (long long)b * A.sbeta, A.dt_g, h);
+          g = g4[0];
+          bt = g4[1];
         }
       } else if (KIND == K_M2) {
-        float dtv = ldf(A.g + (long long)b * A.sg, A.dt_g, h);
-        if (A.dt_bias) dtv = dtv + ldf(A.dt_bias, A.dt_dtb, h);
+        float dtv = g4[0];
+        if (A.dt_bias) dtv = dtv + g4[1];
         if (A.dt_softplus) dtv = dtv <= 20.0f ? logf(1.0f + expf(dtv)) : dtv;
         if (A.dt_clamp) dtv = fminf(fmaxf(dtv, A.dt_min), A.dt_max);
-        g = __fmul_rn(ldf(A.A_log, A.dt_alog, h), dtv);
+        g = __fmul_rn(g4[2], dtv);
         bt = dtv;
-        if (A.beta) Dv = ldf(A.beta, A.dt_beta, h);
+        Dv = g4[3];
       } else {
-        bt = ldf(A.beta + (long long)b * A.sbeta, A.dt_beta, h);
+        bt = g4[0];
       }
-      if (!VDEC) gcur = GCseq[h];
       float* o = hd + hi * HD_W;
       o[0] = g; o[1] = bt; o[2] = gcur; o[3] = VDEC ? 1.0f : expf(gcur); o[4] = VDEC ? 1.0f : expf(g);
-      o[5] = gcur + g; o[6] = Dv; o[7] = __int_as_float(NPseq[h] & (M - 1));
+      o[5] = gcur + g; o[6] = Dv;
     }
+  } else if (warp == 2) {
+    // per (value head, buffer slot): counters, decay factors of the live slots and their value scales
     for (int e = lane; e < gqa * M; e += 32) {
       const int hi = e / M, i = e - hi * M, h = h0 + hi;
-      const bool live = i < (NPseq[h] & (M - 1));
+      const int n = NPseq[h] & (M - 1);
+      const bool live = i < n;
       float dcy = 0.f, us_i = 0.f;
       if (live) {
         dcy = VDEC ? 1.0f : expf(GCseq[h] - GBseq[(long long)h * M + i]);
@@ -394,6 +479,7 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
       }
       decf[e] = dcy;
       ubsf[e] = us_i;
+      if (i == 0) hd[hi * HD_W + 7] = __int_as_float(n);
     }
   }
   __syncthreads();
@@ -402,6 +488,8 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
     return;
   }
   const float kq = misc[0];
+  const bool fold_step = __float_as_int(misc[1]) == M - 1;
+  const int nsteff = fold_step ? 1 : nst;                // stages actually in flight
 
   // ---- the value heads of this key head ---------------------------------------------------------------------------
   const int RW = DV / NW;
@@ -427,9 +515,8 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
   bool r_built = false;
   for (int hi = 0; hi < gqa; hi++) {
     const int h = h0 + hi;
-    const int s = hi % nst;
-    const uint32_t parity = (hi / nst) & 1;
-    const int par = hi & 1;
+    const int s = hi % nsteff;
+    const uint32_t parity = (hi / nsteff) & 1;
     uint8_t* st = smraw + P.stage0 + s * P.stage_bytes;
     const uint8_t* codes = st;
     const unsigned short* scs = reinterpret_cast<const unsigned short*>(st + P.codes_b);
@@ -440,7 +527,7 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
     const int n = __float_as_int(hdv[7]);
     const float* dcf = decf + hi * M;
     const float* usf = ubsf + hi * M;
-    float* usb = us + par * DV;
+    float* usb = us + hi * DV;
 
     if (!mbar_wait(&bars[s], parity)) misc[2] = 1.f;      // checked CTA-wide after the pass
 
@@ -515,22 +602,29 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
       }
     }
     umax = warp_max(umax);
-    if (lane == 0) red[par * 4 + warp] = umax;
-    __syncthreads();                                           // u of this head complete; the stage is read out
-    if (misc[2] != 0.f) break;
-    const bool full = n == M - 1;
-    if (!full && tid == 0 && hi + nst < gqa) {
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      issue_stage(s, h + nst);
+    if (lane == 0) red[hi * NW + warp] = umax;
+    if (!fold_step) {
+      // appends are done after the last head; a stage that is needed again is refilled once every warp has read it
+      if (hi + nst < gqa) {
+        __syncthreads();
+        if (tid == 0) {
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          issue_stage(s, h + nst);
+        }
+      }
+      continue;
     }
 
-    // ---- append the value at slot n (warp 0; the others go on): one absmax scale over the whole row ----
+    // ================= fold step: append and fold this head before going on =======================================
+    __syncthreads();                                           // u of this head complete
+    if (misc[2] != 0.f) break;
+    const bool full = n == M - 1;
     uint8_t* UBh = UBseq + (long long)h * M * DV * bsz;
     float* GBh = GBseq + (long long)h * M * (VDEC ? DK : 1);
     float* GCh = GCseq + (long long)h * (VDEC ? DK : 1);
     if (warp == 0) {
       if (A.qbuf) {
-        const float usc = fp16_scale(fmaxf(fmaxf(red[par * 4], red[par * 4 + 1]), fmaxf(red[par * 4 + 2], red[par * 4 + 3])), 127.0f);
+        const float usc = fp16_scale(fmaxf(fmaxf(red[hi * NW], red[hi * NW + 1]), fmaxf(red[hi * NW + 2], red[hi * NW + 3])), 127.0f);
         const bool fast_ok = usc >= FP16_MIN_NORMAL;
         const float r = __fdiv_rn(1.0f, usc);
         for (int e = lane; e < DV / 4; e += 32) {
@@ -558,182 +652,221 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
       }
       if (lane == 0) NPseq[h] = full ? 0 : n + 1;
     }
-    if (!full) continue;
-
-    // ---- fold: S = decay * S_0 + sum_i L_i R_i^T in slot order, re-rounded in place ----
-    const float alphan = VDEC ? 1.0f : expf(gnew);
-    // R: the keys of all slots (KDA: times their decay ratio), once per key head; slot M-1 is the new key
-    if (!r_built) {
-      for (int e = tid; e < M * DK; e += NT) {
-        const int i = e / DK, k = e - i * DK;
-        float kv;
-        if (i == M - 1) {
-          kv = krnd[k];
-        } else {
-          if (A.qbuf) kv = static_cast<float>(reinterpret_cast<const int8_t*>(kbt)[e]) * h2f(KBSh[i]);
-          else kv = bf2f(reinterpret_cast<const unsigned short*>(kbt)[e]);
-          if (VDEC) kv = kv * expf(ga[k] - gbt[e]);
+    if (full) {
+      // ---- fold: S = decay * S_0 + sum_i L_i R_i^T in slot order, re-rounded in place ----
+      const float alphan = VDEC ? 1.0f : expf(gnew);
+      // R: the keys of all slots (KDA: times their decay ratio), once per key head; slot M-1 is the new key
+      if (!r_built) {
+        for (int e = tid; e < M * DK; e += NT) {
+          const int i = e / DK, k = e - i * DK;
+          float kv;
+          if (i == M - 1) {
+            kv = krnd[k];
+          } else {
+            if (A.qbuf) kv = static_cast<float>(reinterpret_cast<const int8_t*>(kbt)[e]) * h2f(KBSh[i]);
+            else kv = bf2f(reinterpret_cast<const unsigned short*>(kbt)[e]);
+            if (VDEC) kv = kv * expf(ga[k] - gbt[e]);
+          }
+          R[i * RDK + (k / 16) * 20 + (k % 16)] = kv;
         }
-        R[i * RDK + (k / 16) * 20 + (k % 16)] = kv;
+        r_built = true;
       }
-      r_built = true;
-    }
-    // L: the buffered values of slots 0..M-2, times their decay (GDN, Mamba2); slot M-1 is written by warp 0 above
-    for (int e = tid; e < (M - 1) * DV; e += NT) {
-      const int i = e / DV, v = e - i * DV;
-      float ub;
-      if (A.qbuf) ub = static_cast<float>(reinterpret_cast<const int8_t*>(ubt)[e]) * usf[i];
-      else ub = bf2f(reinterpret_cast<const unsigned short*>(ubt)[e]);
-      if (!VDEC) ub = expf(gnew - GBh[i]) * ub;
-      L[i * LDV + v] = ub;
-    }
-    __syncthreads();
+      // L: the buffered values of slots 0..M-2, times their decay (GDN, Mamba2); slot M-1 is written by warp 0 above
+      for (int e = tid; e < (M - 1) * DV; e += NT) {
+        const int i = e / DV, v = e - i * DV;
+        float ub;
+        if (A.qbuf) ub = static_cast<float>(reinterpret_cast<const int8_t*>(ubt)[e]) * usf[i];
+        else ub = bf2f(reinterpret_cast<const unsigned short*>(ubt)[e]);
+        if (!VDEC) ub = expf(gnew - GBh[i]) * ub;
+        L[i * LDV + v] = ub;
+      }
+      __syncthreads();
 
-    int wpg = NW, ppw = PPW, gpi = 1;
-    if (!AXK) {
-      wpg = min(NW, G / RPP);
-      ppw = G / (RPP * wpg);
-      gpi = NW / wpg;
-    }
-    const int BR = AXK ? NW * PPW * RPP : gpi * G;
-    const int niter = (DV + BR - 1) / BR;
-    unsigned short* SCh = SCseq + (long long)h * scn;
-    uint8_t* Sh = Sseq + (long long)h * P.codes_b;
-    for (int it = 0; it < niter; it++) {
-      int rows[PPW];
-      bool rv[PPW];
-      float2 acc[PPW][8];
-      const int gvrow = AXK ? 0 : it * gpi + warp / wpg;
-#pragma unroll
-      for (int pp = 0; pp < PPW; pp++) {
-        int row;
-        if (AXK) row = it * BR + warp * (PPW * RPP) + pp * RPP + rl;
-        else row = gvrow * G + (warp % wpg) * (ppw * RPP) + pp * RPP + rl;
-        rv[pp] = pp < ppw && row < DV;
-        rows[pp] = rv[pp] ? row : 0;
-        decode16<BITS>(codes + rows[pp] * ROWB + c * CB, acc[pp]);
-        if (AXK) {
-          const float sc = h2f(scs[rows[pp] * NG + gl]);
-#pragma unroll
-          for (int p = 0; p < 8; p++)
-            acc[pp][p] = __fmul2_rn(acc[pp][p], make_float2(sc * presc<BITS>(2 * p), sc * presc<BITS>(2 * p + 1)));
-        }
-      }
+      int wpg = NW, ppw = PPW, gpi = 1;
       if (!AXK) {
-        const bool gvalid = gvrow * G < DV;
-#pragma unroll
-        for (int p = 0; p < 8; p++) {
-          const int k0 = c * 16 + 2 * p;
-          const float s0 = gvalid ? h2f(scs[gvrow * DK + k0]) : 0.f, s1 = gvalid ? h2f(scs[gvrow * DK + k0 + 1]) : 0.f;
-          const float2 s2 = make_float2(s0 * presc<BITS>(2 * p), s1 * presc<BITS>(2 * p + 1));
-#pragma unroll
-          for (int pp = 0; pp < PPW; pp++) acc[pp][p] = __fmul2_rn(acc[pp][p], s2);
-        }
+        wpg = min(NW, G / RPP);
+        ppw = G / (RPP * wpg);
+        gpi = NW / wpg;
       }
-#pragma unroll
-      for (int p = 0; p < 8; p++) {
-        float2 d2 = make_float2(alphan, alphan);
-        if (VDEC) d2 = make_float2(ae[c * 16 + 2 * p], ae[c * 16 + 2 * p + 1]);
-#pragma unroll
-        for (int pp = 0; pp < PPW; pp++) acc[pp][p] = __fmul2_rn(acc[pp][p], d2);
-      }
-      for (int i = 0; i < M; i++) {
-        float2 l2[PPW];
+      const int BR = AXK ? NW * PPW * RPP : gpi * G;
+      const int niter = (DV + BR - 1) / BR;
+      unsigned short* SCh = SCseq + (long long)h * scn;
+      uint8_t* Sh = Sseq + (long long)h * P.codes_b;
+      for (int it = 0; it < niter; it++) {
+        int rows[PPW];
+        bool rv[PPW];
+        float2 acc[PPW][8];
+        const int gvrow = AXK ? 0 : it * gpi + warp / wpg;
 #pragma unroll
         for (int pp = 0; pp < PPW; pp++) {
-          const float l = L[i * LDV + rows[pp]];
-          l2[pp] = make_float2(l, l);
-        }
-        const float4* rrow = reinterpret_cast<const float4*>(R + i * RDK + c * 20);
+          int row;
+          if (AXK) row = it * BR + warp * (PPW * RPP) + pp * RPP + rl;
+          else row = gvrow * G + (warp % wpg) * (ppw * RPP) + pp * RPP + rl;
+          rv[pp] = pp < ppw && row < DV;
+          rows[pp] = rv[pp] ? row : 0;
+          decode16<BITS>(codes + rows[pp] * ROWB + c * CB, acc[pp]);
+          if (AXK) {
+            const float sc = h2f(scs[rows[pp] * NG + gl]);
 #pragma unroll
-        for (int j4 = 0; j4 < 4; j4++) {
-          const float4 kr4 = rrow[j4];
-          const float2 ka = make_float2(kr4.x, kr4.y), kb2 = make_float2(kr4.z, kr4.w);
-#pragma unroll
-          for (int pp = 0; pp < PPW; pp++) {
-            acc[pp][2 * j4] = __ffma2_rn(l2[pp], ka, acc[pp][2 * j4]);
-            acc[pp][2 * j4 + 1] = __ffma2_rn(l2[pp], kb2, acc[pp][2 * j4 + 1]);
+            for (int p = 0; p < 8; p++)
+              acc[pp][p] = __fmul2_rn(acc[pp][p], make_float2(sc * presc<BITS>(2 * p), sc * presc<BITS>(2 * p + 1)));
           }
         }
-      }
-      // re-round
-      constexpr float MB = BITS == 4 ? MAGIC + 8.0f : MAGIC;
-      if constexpr (AXK) {
-        const int lpg = G / 16;
-#pragma unroll
-        for (int pp = 0; pp < PPW; pp++) {
-          float am = 0.f;
-#pragma unroll
-          for (int p = 0; p < 8; p++) am = fmaxf(am, fmaxf(fabsf(acc[pp][p].x), fabsf(acc[pp][p].y)));
-          for (int o = 1; o < lpg; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-          const float sc = fp16_scale(am, QMAX);
-          if (!rv[pp]) continue;
-          if ((c & (lpg - 1)) == 0) SCh[rows[pp] * NG + gl] = f2h(sc);
-          float2 t[8];
-          bool ok = sc >= FP16_MIN_NORMAL && round_fast<8>(acc[pp], sc, __fdiv_rn(1.0f, sc), MB, t);
-          if (!ok) {
-#pragma unroll
-            for (int p = 0; p < 8; p++) {
-              t[p].x = rq_exact(acc[pp][p].x, sc, QMAX) + MB;
-              t[p].y = rq_exact(acc[pp][p].y, sc, QMAX) + MB;
-            }
-          }
-          store_codes16<BITS>(Sh + (long long)rows[pp] * ROWB + c * CB, t);
-        }
-      } else {
-        // column maxima over the group's rows: this lane's passes, the lanes of other rows, the other warps
-        float cm[16];
-#pragma unroll
-        for (int p = 0; p < 8; p++) {
-          float m0 = 0.f, m1 = 0.f;
-#pragma unroll
-          for (int pp = 0; pp < PPW; pp++) {
-            if (rv[pp]) { m0 = fmaxf(m0, fabsf(acc[pp][p].x)); m1 = fmaxf(m1, fabsf(acc[pp][p].y)); }
-          }
-          for (int o = LPR; o < 32; o <<= 1) {
-            m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
-            m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, o));
-          }
-          cm[2 * p] = m0;
-          cm[2 * p + 1] = m1;
-        }
-        __syncthreads();
-        if (rl == 0) {
-#pragma unroll
-          for (int j = 0; j < 16; j++) cmax[warp * DK + c * 16 + j] = cm[j];
-        }
-        __syncthreads();
-        // scale (and its reciprocal) of every column of every group in flight, one column per thread
-        float* ssc = cmax + NW * DK;
-        for (int e = tid; e < gpi * DK; e += NT) {
-          const int gi = e / DK, k = e - gi * DK;
-          float am = 0.f;
-          for (int w = 0; w < wpg; w++) am = fmaxf(am, cmax[(gi * wpg + w) * DK + k]);
-          const float sc = fp16_scale(am, QMAX);
-          ssc[gi * DK + k] = sc;
-          const int gvr = it * gpi + gi;
-          if (gvr * G < DV) SCh[gvr * DK + k] = f2h(sc);
-        }
-        __syncthreads();
-        const float* myssc = ssc + (warp / wpg) * DK + c * 16;
-#pragma unroll
-        for (int pp = 0; pp < PPW; pp++) {
-          if (!rv[pp]) continue;
-          float2 t[8];
+        if (!AXK) {
+          const bool gvalid = gvrow * G < DV;
 #pragma unroll
           for (int p = 0; p < 8; p++) {
-            t[p].x = rq_exact(acc[pp][p].x, myssc[2 * p], QMAX) + MB;
-            t[p].y = rq_exact(acc[pp][p].y, myssc[2 * p + 1], QMAX) + MB;
+            const int k0 = c * 16 + 2 * p;
+            const float s0 = gvalid ? h2f(scs[gvrow * DK + k0]) : 0.f, s1 = gvalid ? h2f(scs[gvrow * DK + k0 + 1]) : 0.f;
+            const float2 s2 = make_float2(s0 * presc<BITS>(2 * p), s1 * presc<BITS>(2 * p + 1));
+#pragma unroll
+            for (int pp = 0; pp < PPW; pp++) acc[pp][p] = __fmul2_rn(acc[pp][p], s2);
           }
-          store_codes16<BITS>(Sh + (long long)rows[pp] * ROWB + c * CB, t);
+        }
+#pragma unroll
+        for (int p = 0; p < 8; p++) {
+          float2 d2 = make_float2(alphan, alphan);
+          if (VDEC) d2 = make_float2(ae[c * 16 + 2 * p], ae[c * 16 + 2 * p + 1]);
+#pragma unroll
+          for (int pp = 0; pp < PPW; pp++) acc[pp][p] = __fmul2_rn(acc[pp][p], d2);
+        }
+        for (int i = 0; i < M; i++) {
+          float2 l2[PPW];
+#pragma unroll
+          for (int pp = 0; pp < PPW; pp++) {
+            const float l = L[i * LDV + rows[pp]];
+            l2[pp] = make_float2(l, l);
+          }
+          const float4* rrow = reinterpret_cast<const float4*>(R + i * RDK + c * 20);
+#pragma unroll
+          for (int j4 = 0; j4 < 4; j4++) {
+            const float4 kr4 = rrow[j4];
+            const float2 ka = make_float2(kr4.x, kr4.y), kb2 = make_float2(kr4.z, kr4.w);
+#pragma unroll
+            for (int pp = 0; pp < PPW; pp++) {
+              acc[pp][2 * j4] = __ffma2_rn(l2[pp], ka, acc[pp][2 * j4]);
+              acc[pp][2 * j4 + 1] = __ffma2_rn(l2[pp], kb2, acc[pp][2 * j4 + 1]);
+            }
+          }
+        }
+        // re-round
+        constexpr float MB = BITS == 4 ? MAGIC + 8.0f : MAGIC;
+        if constexpr (AXK) {
+          const int lpg = G / 16;
+#pragma unroll
+          for (int pp = 0; pp < PPW; pp++) {
+            float am = 0.f;
+#pragma unroll
+            for (int p = 0; p < 8; p++) am = fmaxf(am, fmaxf(fabsf(acc[pp][p].x), fabsf(acc[pp][p].y)));
+            for (int o = 1; o < lpg; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+            const float sc = fp16_scale(am, QMAX);
+            if (!rv[pp]) continue;
+            if ((c & (lpg - 1)) == 0) SCh[rows[pp] * NG + gl] = f2h(sc);
+            float2 t[8];
+            bool ok = sc >= FP16_MIN_NORMAL && round_fast<8>(acc[pp], sc, __fdiv_rn(1.0f, sc), MB, t);
+            if (!ok) {
+#pragma unroll
+              for (int p = 0; p < 8; p++) {
+                t[p].x = rq_exact(acc[pp][p].x, sc, QMAX) + MB;
+                t[p].y = rq_exact(acc[pp][p].y, sc, QMAX) + MB;
+              }
+            }
+            store_codes16<BITS>(Sh + (long long)rows[pp] * ROWB + c * CB, t);
+          }
+        } else {
+          // column maxima over the group's rows: this lane's passes, the lanes of other rows, the other warps
+          float cm[16];
+#pragma unroll
+          for (int p = 0; p < 8; p++) {
+            float m0 = 0.f, m1 = 0.f;
+#pragma unroll
+            for (int pp = 0; pp < PPW; pp++) {
+              if (rv[pp]) { m0 = fmaxf(m0, fabsf(acc[pp][p].x)); m1 = fmaxf(m1, fabsf(acc[pp][p].y)); }
+            }
+            for (int o = LPR; o < 32; o <<= 1) {
+              m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
+              m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, o));
+            }
+            cm[2 * p] = m0;
+            cm[2 * p + 1] = m1;
+          }
+          __syncthreads();
+          if (rl == 0) {
+#pragma unroll
+            for (int j = 0; j < 16; j++) cmax[warp * DK + c * 16 + j] = cm[j];
+          }
+          __syncthreads();
+          // scale of every column of every group in flight, one column per thread
+          float* ssc = cmax + NW * DK;
+          for (int e = tid; e < gpi * DK; e += NT) {
+            const int gi = e / DK, k = e - gi * DK;
+            float am = 0.f;
+            for (int w = 0; w < wpg; w++) am = fmaxf(am, cmax[(gi * wpg + w) * DK + k]);
+            const float sc = fp16_scale(am, QMAX);
+            ssc[gi * DK + k] = sc;
+            const int gvr = it * gpi + gi;
+            if (gvr * G < DV) SCh[gvr * DK + k] = f2h(sc);
+          }
+          __syncthreads();
+          const float* myssc = ssc + (warp / wpg) * DK + c * 16;
+#pragma unroll
+          for (int pp = 0; pp < PPW; pp++) {
+            if (!rv[pp]) continue;
+            float2 t[8];
+#pragma unroll
+            for (int p = 0; p < 8; p++) {
+              t[p].x = rq_exact(acc[pp][p].x, myssc[2 * p], QMAX) + MB;
+              t[p].y = rq_exact(acc[pp][p].y, myssc[2 * p + 1], QMAX) + MB;
+            }
+            store_codes16<BITS>(Sh + (long long)rows[pp] * ROWB + c * CB, t);
+          }
         }
       }
     }
-    // ---- this stage is free: refill it with the head nst further on ----
+    // ---- the stage is free: refill it with the next head (a fold step keeps one stage in flight) ----
     __syncthreads();
-    if (tid == 0 && hi + nst < gqa) {
+    if (tid == 0 && hi + 1 < gqa) {
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      issue_stage(s, h + nst);
+      issue_stage(0, h + 1);
+    }
+  }
+  if (!fold_step) {
+    // ---- append the values of all heads at their slot n: warp w takes heads w, w + 4, ... ----
+    __syncthreads();
+    if (misc[2] == 0.f) {
+      for (int hi = warp; hi < gqa; hi += NW) {
+        const int h = h0 + hi;
+        const int n = __float_as_int(hd[hi * HD_W + 7]);
+        const float gnew = hd[hi * HD_W + 5];
+        const float* usb = us + hi * DV;
+        uint8_t* UBh = UBseq + (long long)h * M * DV * bsz;
+        if (A.qbuf) {
+          const float usc = fp16_scale(fmaxf(fmaxf(red[hi * NW], red[hi * NW + 1]), fmaxf(red[hi * NW + 2], red[hi * NW + 3])), 127.0f);
+          const bool fast_ok = usc >= FP16_MIN_NORMAL;
+          const float r = __fdiv_rn(1.0f, usc);
+          for (int e = lane; e < DV / 4; e += 32) {
+            float dq4[4];
+            *reinterpret_cast<uint32_t*>(UBh + (long long)n * DV + 4 * e) = round4_i8(usb + 4 * e, usc, r, fast_ok, dq4);
+          }
+          if (lane == 0) UBSseq[h * M + n] = f2h(usc);
+        } else {
+          for (int e = lane; e < DV / 2; e += 32)
+            *reinterpret_cast<uint32_t*>(UBh + ((long long)n * DV + 2 * e) * 2) =
+                f2bf(usb[2 * e]) | (static_cast<uint32_t>(f2bf(usb[2 * e + 1])) << 16);
+        }
+        if (VDEC) {
+          float* GBh = GBseq + (long long)h * M * DK;
+          float* GCh = GCseq + (long long)h * DK;
+          for (int t = lane; t < DK; t += 32) {
+            GBh[(long long)n * DK + t] = ga[t];
+            GCh[t] = ga[t];
+          }
+        } else if (lane == 0) {
+          GBseq[(long long)h * M + n] = gnew;
+          GCseq[h] = gnew;
+        }
+        if (lane == 0) NPseq[h] = n + 1;
+      }
     }
   }
   if (misc[2] != 0.f && tid == 0) atomicAdd(&g_step_status[0], 1);   // a copy never completed (see mbar_wait)
