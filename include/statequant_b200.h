@@ -140,12 +140,49 @@ typedef struct sqb_kda_inputs {
   int32_t reserved;
 } sqb_kda_inputs_t;
 
+/*
+ * The packed GGA / STEP slot table of one layer (mixed per-head widths, optional pure-write window).
+ * Slot s lives at blob + s * stride.  Inside a slot (reference: src/statequant/kernels/_gga_triton.py:3-13,
+ * src/statequant/integrations/vllm_gga.py:182-205):
+ *   0            int32 [4]: n (queued pairs), head (ring index of the oldest pair)
+ *   offs[h]      head h at its width bits[h]: 16 -> fp16 [dk, dv]; 4 / 6 / 8 -> codes [dk, dv * b / 8] (u = z + qmax,
+ *                little-endian along dv; 6 bit: four codes per three bytes), r fp16 [dk], c fp16 [dv];
+ *                2 -> codes [dk, dv / 4] (u = (z + 3) / 2), r fp16 [dk, dv / group], c fp16 [dv].  State = r c z.
+ *   qoff + h qsz the window of head h (pw only): P e4m3 [m, dk], V e4m3 [m, dv], PS fp32 [m], VS fp32 [m]
+ * offs, bits (int32 [hv]) and w (fp32 [hv, dk], STEP's impact factors) are device arrays of the layer's plan.
+ */
+typedef struct sqb_gga_layout {
+  void *blob;          int64_t stride;
+  const int32_t *offs; const int32_t *bits; const float *w;
+  int64_t qoff;
+  int32_t qsz;
+  int32_t hv, hk, dk, dv;
+  int32_t m;           /* window length */
+  int32_t pw;          /* 1: pure-write window on */
+  int32_t group;       /* column group of 2-bit row factors (32) */
+  int32_t reserved;
+} sqb_gga_layout_t;
+
 /* replaces `_fused_step[(BH,)]`, src/statequant/kernels/fold.py:401-407 and slots.py:180-186 */
 int sqb_gdn_step(const sqb_state_t *st, const sqb_gdn_inputs_t *in, void *cuda_stream);
 /* replaces `_m2_step[(rows * HV,)]`, src/statequant/kernels/mamba2.py:232-240 */
 int sqb_mamba2_step(const sqb_state_t *st, const sqb_mamba2_inputs_t *in, void *cuda_stream);
 /* replaces `_kda_step[(rows * HV,)]`, src/statequant/kernels/kda.py:199-204 */
 int sqb_kda_step(const sqb_state_t *st, const sqb_kda_inputs_t *in, void *cuda_stream);
+
+/* One GGA decode token: replaces `_gga_step[(B * HV,)]` + `_gga_advance[(B,)]`,
+   src/statequant/integrations/vllm_gga.py:252-257.  Takes the gate form of the GDN inputs (gate must be 1). */
+int sqb_gga_step(const sqb_gga_layout_t *lay, const sqb_gdn_inputs_t *in, void *cuda_stream);
+/* Fit + pack canonical states X fp32 [P, hv, dk, dv] into slots idx [P] and zero their counters: replaces
+   `_gga_store[(P * HV,)]`, src/statequant/integrations/vllm_gga.py:317-318 */
+int sqb_gga_store(const sqb_gga_layout_t *lay, const int32_t *idx, int64_t P, const float *X, void *cuda_stream);
+/* Unpack slots idx [P] into Y fp32 [P, hv, dk, dv] (stored state without the window): replaces
+   `_gga_load[(P * HV,)]`, src/statequant/integrations/vllm_gga.py:270-271 */
+int sqb_gga_load(const sqb_gga_layout_t *lay, const int32_t *idx, int64_t P, float *Y, void *cuda_stream);
+/* STEP's dual-axis fit as a fake-quant pass, x -> y fp32 [B, H, dk, dv], bits int32 [H], w fp32 [H, dk]: replaces
+   `_stepquant_fit[(B * H,)]`, src/statequant/kernels/_stepquant_triton.py:86-99 */
+int sqb_stepquant_fit(const float *x, float *y, const int32_t *bits, const float *w, int64_t B, int32_t H,
+                      int32_t dk, int32_t dv, int32_t group, void *cuda_stream);
 
 /* message of the last error returned on this thread ("" if none) */
 const char *sqb_last_error(void);

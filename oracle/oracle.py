@@ -40,6 +40,7 @@ def lib():
             getattr(L, n).restype = C.c_int
             getattr(L, n).argtypes = [C.c_void_p, C.c_void_p]
         L.sqo_num_threads.restype = C.c_int
+        L.sqo_gga_step.restype = L.sqo_gga_store.restype = L.sqo_gga_load.restype = C.c_int
         _lib = L
     return _lib
 
@@ -125,3 +126,44 @@ def slot_write(lay, views, slots, S):
     rc = lib().sqo_slot_write(C.byref(lay._struct(views)), int(lay.kind), C.c_void_p(slots.data_ptr()),
                               C.c_int64(slots.shape[0]), C.c_void_p(S.data_ptr()))
     assert rc == 0
+
+
+# ---- GGA / STEP ---------------------------------------------------------------------------------------------------
+def stepquant_fit(x, bits, w, group=32):
+    """step_quant.fit through the oracle: x [B, H, dk, dv] fp32 (host)."""
+    x = x.float().contiguous()
+    y = torch.empty_like(x)
+    bits = bits.to(torch.int32).contiguous()
+    w = w.float().contiguous()
+    B, H, dk, dv = x.shape
+    lib().sqo_stepquant_fit(C.c_void_p(x.data_ptr()), C.c_void_p(y.data_ptr()), C.c_void_p(bits.data_ptr()),
+                            C.c_void_p(w.data_ptr()), C.c_int64(B), H, dk, dv, group)
+    return y
+
+
+def gga_step(pk, views, idx, q, k, v, out, scale, gate, layer):
+    """``GGAPacked.step`` (step + counter advance) on host memory through the oracle."""
+    _cpu(views['blob'], idx, q, k, v, out)
+    a = _gdn_inputs(idx, q, k, v, out, scale, None, None, gate, True)
+    rc = lib().sqo_gga_step(C.byref(pk._struct(views, layer)), C.byref(a))
+    assert rc == 0
+    return out
+
+
+def gga_store(pk, views, idx, S, layer):
+    """``GGAPacked.write``: S value-major [P, HV, dv, dk]."""
+    idx32 = idx.to(torch.int32).contiguous()
+    X = S.float().transpose(-1, -2).contiguous()
+    rc = lib().sqo_gga_store(C.byref(pk._struct(views, layer)), C.c_void_p(idx32.data_ptr()), C.c_int64(idx32.shape[0]),
+                             C.c_void_p(X.data_ptr()))
+    assert rc == 0
+
+
+def gga_load(pk, views, idx, layer):
+    """``GGAPacked.stored``: canonical fp32 [P, HV, dk, dv]."""
+    idx32 = idx.to(torch.int32).contiguous()
+    Y = torch.empty(idx32.shape[0], pk.HV, pk.DK, pk.DV)
+    rc = lib().sqo_gga_load(C.byref(pk._struct(views, layer)), C.c_void_p(idx32.data_ptr()), C.c_int64(idx32.shape[0]),
+                            C.c_void_p(Y.data_ptr()))
+    assert rc == 0
+    return Y

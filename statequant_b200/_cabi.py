@@ -87,10 +87,14 @@ def lib():
         L.sqb_last_error.restype = C.c_char_p
         L.sqb_abi_version.restype = C.c_int
         L.sqb_launch_count.restype = C.c_int64
-        for name in ('sqb_gdn_step', 'sqb_mamba2_step', 'sqb_kda_step'):
+        for name in ('sqb_gdn_step', 'sqb_mamba2_step', 'sqb_kda_step', 'sqb_gga_step'):
             f = getattr(L, name)
             f.restype = C.c_int
             f.argtypes = [vp, vp, vp]
+        L.sqb_gga_store.restype = L.sqb_gga_load.restype = L.sqb_stepquant_fit.restype = C.c_int
+        L.sqb_gga_store.argtypes = [vp, vp, i64, vp, vp]
+        L.sqb_gga_load.argtypes = [vp, vp, i64, vp, vp]
+        L.sqb_stepquant_fit.argtypes = [vp, vp, vp, vp, i64, i32, i32, i32, i32, vp]
         L.sqb_set_option.restype = C.c_int
         L.sqb_set_option.argtypes = [C.c_char_p, C.c_int]
         L.sqb_device_status.restype = C.c_int

@@ -1,0 +1,443 @@
+// GGA / STEP mixed-bit state with the pure-write window (PW-S m): the fused decode step, the prefill-side
+// store / load, and STEP's dual-axis fit as a stand-alone pass.
+//
+// One CTA (256 threads) per (batch row, value head) holds the head's whole [d_k, d_v] tile in shared memory
+// (fp32, rows padded by one float so that row-wise and column-wise sweeps are both free of bank conflicts):
+//   decode codes -> O;  A O = a (O - beta k (k^T O));  the queued left factors are propagated and re-encoded in FP8,
+//   one warp per window row;  o = (A O)^T q + sum_i (R(A p_i) . q) v_i + (beta k . q) v;  the evicted pair is merged;
+//   the tile is re-fitted (row factors, column factors, one weighted least-squares refit of the column factors)
+//   and re-packed in place;  (R(beta k), R(v)) is enqueued.  A second, tiny kernel moves the window counters.
+// Every token reads and rewrites the whole head: 2 x state bytes of HBM traffic per step, no dense contraction.
+//
+// Arithmetic follows the reference's device statement (src/statequant/kernels/_gga_triton.py:207-308 and
+// _stepquant_triton.py:37-60): IEEE division and square root, round half to even, fp16 factors clamped to
+// [2^-24, 65504], E4M3 nearest-even with saturation at 448; only the order of fp32 reductions differs.
+#pragma once
+#include "common.cuh"
+
+namespace sqb {
+
+constexpr int GNT = 256;   // threads per CTA of the GGA kernels
+constexpr int GNW = 8;
+
+struct GgaArgs {
+  uint8_t* blob; long long stride;
+  const int* offs; const int* bits; const float* w;
+  long long qoff; int qsz;
+  int HV, HK, DK, DV, M, pw, group, rows;
+  const int* idx;
+  const uint8_t *q, *k, *v, *a, *b, *A_log, *dt_bias;
+  long long sq, sk, sv, sa, sb;
+  uint8_t* out; long long so;
+  int dt_qk, dt_v, dt_ab, dt_alog, dt_dtb, dt_out;
+  float scale;
+  // store / load / fit
+  const float* X; float* Y; long long P;
+};
+
+__device__ __forceinline__ float halfc(float x) { return h2f(f2h(fminf(fmaxf(x, FP16_TINY), 65504.0f))); }
+
+// |y| <= 448 rounded to the E4M3 grid, nearest even (spacing 2^(e-3) for exponent e >= -6)
+__device__ __forceinline__ float e4m3_round(float y) {
+  int e = static_cast<int>((__float_as_uint(y) >> 23) & 255u) - 127;
+  e = max(e, -6);
+  const float ulp = __uint_as_float(static_cast<uint32_t>(e - 3 + 127) << 23);
+  return rintf(__fdiv_rn(y, ulp)) * ulp;
+}
+__device__ __forceinline__ uint8_t e4m3_byte(float y) {          // y on the grid, |y| <= 448
+  const uint32_t u = __float_as_uint(y);
+  const uint8_t s = static_cast<uint8_t>((u >> 24) & 0x80u);
+  const float a = fabsf(y);
+  if (a == 0.f) return s;
+  const int e = static_cast<int>((u >> 23) & 255u) - 127;
+  if (e < -6) return s | static_cast<uint8_t>(__float2int_rn(a * 512.0f));
+  return s | static_cast<uint8_t>(((e + 7) << 3) | ((u >> 20) & 7u));
+}
+__device__ __forceinline__ float e4m3_val(uint8_t b) {
+  const int e = (b >> 3) & 15, m = b & 7;
+  const float v = e == 0 ? static_cast<float>(m) * 0.001953125f
+                         : __uint_as_float((static_cast<uint32_t>(e - 7 + 127) << 23) | (static_cast<uint32_t>(m) << 20));
+  return (b & 0x80) ? -v : v;
+}
+
+template <bool MAX>
+__device__ __forceinline__ float block_reduce256(float v, float* red) {
+  v = MAX ? warp_max(v) : warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = red[0];
+#pragma unroll
+  for (int w = 1; w < GNW; w++) r = MAX ? fmaxf(r, red[w]) : r + red[w];
+  return r;
+}
+
+__device__ __forceinline__ float enc_level(float y, float qmax, bool two) {
+  if (two) return (y >= 0.f ? 1.0f : -1.0f) * (fabsf(y) >= 2.0f ? 3.0f : 1.0f);
+  return fminf(fmaxf(rintf(y), -qmax), qmax);
+}
+
+// ---- head codes -> fp32 tile T[k * LD + v] ------------------------------------------------------------------------
+__device__ void gga_decode_head(const uint8_t* S, int b, int dk, int dv, int group, float* T, int LD) {
+  const int tid = threadIdx.x;
+  if (b == 16) {
+    const unsigned short* p = reinterpret_cast<const unsigned short*>(S);
+    for (int e = tid; e < dk * dv; e += GNT) T[(e / dv) * LD + (e % dv)] = h2f(p[e]);
+    return;
+  }
+  const int ng = dv / group, nr = b == 2 ? dk * ng : dk, qmax = (1 << (b - 1)) - 1;
+  const unsigned short* R = reinterpret_cast<const unsigned short*>(S + static_cast<size_t>(dk) * dv * b / 8);
+  const unsigned short* C = R + nr;
+  const int rowb = dv * b / 8;
+  for (int e = tid; e < dk * dv; e += GNT) {
+    const int k = e / dv, v = e - k * dv;
+    const uint8_t* row = S + static_cast<size_t>(k) * rowb;
+    float z;
+    if (b == 8) z = static_cast<float>(static_cast<int>(row[v]) - qmax);
+    else if (b == 4) z = static_cast<float>(static_cast<int>((row[v >> 1] >> (4 * (v & 1))) & 15) - qmax);
+    else if (b == 2) z = static_cast<float>((row[v >> 2] >> (2 * (v & 3))) & 3) * 2.0f - 3.0f;
+    else {
+      const uint8_t* t = row + 3 * (v >> 2);
+      const uint32_t wd = t[0] | (static_cast<uint32_t>(t[1]) << 8) | (static_cast<uint32_t>(t[2]) << 16);
+      z = static_cast<float>(static_cast<int>((wd >> (6 * (v & 3))) & 63) - qmax);
+    }
+    const float rf = h2f(b == 2 ? R[k * ng + v / group] : R[k]);
+    T[k * LD + v] = (rf * h2f(C[v])) * z;
+  }
+}
+
+// ---- STEP dual-axis fit of the tile T (values x), then either pack it at S or write r c z to Yout -----------------
+// scratch: rs[dk * ng] row factors, cs[dv] column factors, ps[2 * dv] partial sums, red[8]
+__device__ void gga_fit_store(float* T, int LD, const float* w, int b, int dk, int dv, int group, uint8_t* S,
+                              float* Yout, float* rs, float* cs, float* ps, float* wsm) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (b == 16) {
+    for (int e = tid; e < dk * dv; e += GNT) {
+      const int k = e / dv, v = e - k * dv;
+      const unsigned short hbits = f2h(T[k * LD + v]);
+      if (S) reinterpret_cast<unsigned short*>(S)[e] = hbits;
+      else Yout[e] = h2f(hbits);
+    }
+    return;
+  }
+  const bool two = b == 2;
+  const float qmax = two ? 3.0f : static_cast<float>((1 << (b - 1)) - 1);
+  const int ng = dv / group, nrg = two ? ng : 1;
+  for (int k = tid; k < dk; k += GNT) wsm[k] = w[k];
+  __syncthreads();
+  // row factors: r = half(sqrt(max(mean |x|, 1e-20) / w)), per row or per (row, 32-column group)
+  for (int k = warp; k < dk; k += GNW) {
+    if (two) {
+      for (int g = 0; g < ng; g++) {
+        float s = 0.f;
+        for (int v = g * group + lane; v < (g + 1) * group; v += 32) s += fabsf(T[k * LD + v]);
+        s = warp_sum(s);
+        if (lane == 0) rs[k * ng + g] = halfc(__fsqrt_rn(__fdiv_rn(fmaxf(s * (1.0f / group), 1e-20f), wsm[k])));
+      }
+    } else {
+      float s = 0.f;
+      for (int v = lane; v < dv; v += 32) s += fabsf(T[k * LD + v]);
+      s = warp_sum(s);
+      if (lane == 0) rs[k] = halfc(__fsqrt_rn(__fdiv_rn(fmaxf(s * (1.0f / dv), 1e-20f), wsm[k])));
+    }
+  }
+  __syncthreads();
+  // column factors: c = half(max_k |x / r| / qmax); two threads per column, each half of the rows
+  const int half_id = tid / dv, col = tid - half_id * dv;      // dv <= 128: half_id in {0, 1}
+  const int k0 = half_id * (dk / 2), k1 = k0 + dk / 2;
+  const bool act = tid < 2 * dv;
+  if (act) {
+    float m = 0.f;
+    for (int k = k0; k < k1; k++) {
+      const float y0 = __fdiv_rn(T[k * LD + col], rs[k * nrg + (two ? col / group : 0)]);
+      m = fmaxf(m, __fdiv_rn(fabsf(y0), qmax));
+    }
+    ps[half_id * dv + col] = m;
+  }
+  __syncthreads();
+  if (tid < dv) cs[tid] = halfc(fmaxf(ps[tid], ps[dv + tid]));
+  __syncthreads();
+  // weighted least-squares refit of c with the codes fixed
+  if (act) {
+    const float c0 = cs[col];
+    float num = 0.f, den = 0.f;
+    for (int k = k0; k < k1; k++) {
+      const float x = T[k * LD + col], rf = rs[k * nrg + (two ? col / group : 0)];
+      const float z = enc_level(__fdiv_rn(__fdiv_rn(x, rf), c0), qmax, two);
+      const float vv = rf * z, ww = wsm[k] * wsm[k];
+      num += (ww * vv) * x;
+      den += ww * (vv * vv);
+    }
+    ps[half_id * dv + col] = num;
+    ps[2 * dv + half_id * dv + col] = den;
+  }
+  __syncthreads();
+  if (tid < dv) {
+    const float num = ps[tid] + ps[dv + tid], den = ps[2 * dv + tid] + ps[3 * dv + tid];
+    cs[tid] = halfc(den > 0.f ? __fdiv_rn(num, fmaxf(den, 1e-30f)) : cs[tid]);
+  }
+  __syncthreads();
+  // codes with the refitted c
+  if (!S) {
+    for (int e = tid; e < dk * dv; e += GNT) {
+      const int k = e / dv, v = e - k * dv;
+      const float rf = rs[k * nrg + (two ? v / group : 0)];
+      const float z = enc_level(__fdiv_rn(__fdiv_rn(T[k * LD + v], rf), cs[v]), qmax, two);
+      Yout[e] = (rf * cs[v]) * z;
+    }
+    return;
+  }
+  const int iq = static_cast<int>(qmax);
+  const int rowb = dv * b / 8;
+  const int per = b == 8 ? 1 : (b == 4 ? 2 : 4);                 // codes per packing unit
+  const int ub = b == 6 ? 3 : 1;                                 // bytes per packing unit
+  const int units = dv / per;
+  for (int e = tid; e < dk * units; e += GNT) {
+    const int k = e / units, j = e - k * units;
+    uint32_t wd = 0;
+    for (int t = 0; t < per; t++) {
+      const int v = j * per + t;
+      const float rf = rs[k * nrg + (two ? v / group : 0)];
+      const float z = enc_level(__fdiv_rn(__fdiv_rn(T[k * LD + v], rf), cs[v]), qmax, two);
+      const int u = two ? static_cast<int>((z + 3.0f) * 0.5f) : static_cast<int>(z) + iq;
+      wd |= static_cast<uint32_t>(u) << (b * t);
+    }
+    uint8_t* p = S + static_cast<size_t>(k) * rowb + j * ub;
+    p[0] = static_cast<uint8_t>(wd & 255u);
+    if (b == 6) { p[1] = static_cast<uint8_t>((wd >> 8) & 255u); p[2] = static_cast<uint8_t>(wd >> 16); }
+  }
+  unsigned short* R = reinterpret_cast<unsigned short*>(S + static_cast<size_t>(dk) * dv * b / 8);
+  for (int i = tid; i < dk * nrg; i += GNT) R[i] = f2h(rs[i]);
+  unsigned short* C = R + dk * nrg;
+  for (int v = tid; v < dv; v += GNT) C[v] = f2h(cs[v]);
+}
+
+// shared-memory plan (floats) of the GGA kernels
+struct GgaSmem { int T, q, k, bk, v, o, kO, rs, cs, ps, wsm, Pw, Vw, r0, coef, red, total, LD; };
+__host__ __device__ inline GgaSmem gga_smem(int dk, int dv, int M, int group) {
+  GgaSmem s;
+  int o = 0;
+  s.LD = dv + 1;
+  s.T = o; o += dk * s.LD;
+  s.q = o; o += dk; s.k = o; o += dk; s.bk = o; o += dk;
+  s.v = o; o += dv; s.o = o; o += dv; s.kO = o; o += 2 * dv;
+  s.rs = o; o += dk * (dv / group > 0 ? dv / group : 1);
+  s.cs = o; o += dv; s.ps = o; o += 4 * dv; s.wsm = o; o += dk;
+  s.Pw = o; o += M * dk; s.Vw = o; o += M * dv; s.r0 = o; o += dk; s.coef = o; o += 32; s.red = o; o += 16;
+  s.total = o;
+  return s;
+}
+
+
+// ---- the decode step ----------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(GNT) gga_step_kernel(const __grid_constant__ GgaArgs A) {
+  extern __shared__ __align__(16) float gsm[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int dk = A.DK, dv = A.DV, M = A.M, HV = A.HV;
+  const int bh = blockIdx.x, b = bh / HV, h = bh - b * HV, hk = h / (HV / A.HK);
+  uint8_t* orow = A.out + (long long)b * A.so + (long long)h * dv * dt_size(A.dt_out);
+  const long long seq = A.idx[b];
+  if (seq <= 0) {
+    for (int v = tid; v < dv; v += GNT) stf(orow, A.dt_out, v, 0.0f);
+    return;
+  }
+  const GgaSmem P = gga_smem(dk, dv, M, A.group);
+  const int LD = P.LD;
+  float *T = gsm + P.T, *q = gsm + P.q, *k = gsm + P.k, *bk = gsm + P.bk, *v = gsm + P.v, *o = gsm + P.o,
+        *kO = gsm + P.kO, *Pw = gsm + P.Pw, *Vw = gsm + P.Vw, *r0 = gsm + P.r0, *coef = gsm + P.coef, *red = gsm + P.red;
+  uint8_t* base = A.blob + seq * A.stride;
+  const int bits = A.bits[h];
+  uint8_t* S = base + A.offs[h];
+
+  // q, k (fla's normalisation), gates
+  float sq = 0.f, sk = 0.f;
+  for (int i = tid; i < dk; i += GNT) {
+    const float qv = ldf(A.q + (long long)b * A.sq, A.dt_qk, (long long)hk * dk + i);
+    const float kv = ldf(A.k + (long long)b * A.sk, A.dt_qk, (long long)hk * dk + i);
+    q[i] = qv; k[i] = kv;
+    sq += qv * qv; sk += kv * kv;
+  }
+  for (int i = tid; i < dv; i += GNT) v[i] = ldf(A.v + (long long)b * A.sv, A.dt_v, (long long)h * dv + i);
+  sq = block_reduce256<false>(sq, red);
+  sk = block_reduce256<false>(sk, red);
+  const float nq = __fsqrt_rn(sq + 1e-6f), nk = __fsqrt_rn(sk + 1e-6f);
+  const float x = ldf(A.a + (long long)b * A.sa, A.dt_ab, h) + ldf(A.dt_bias, A.dt_dtb, h);
+  const float sp = x <= 20.0f ? logf(1.0f + expf(x)) : x;
+  const float a = expf(-expf(ldf(A.A_log, A.dt_alog, h)) * sp);
+  const float beta = __fdiv_rn(1.0f, 1.0f + expf(-ldf(A.b + (long long)b * A.sb, A.dt_ab, h)));
+  float bqp = 0.f;
+  for (int i = tid; i < dk; i += GNT) {
+    const float qn = __fdiv_rn(q[i], nq) * A.scale, kn = __fdiv_rn(k[i], nk);
+    q[i] = qn; k[i] = kn; bk[i] = beta * kn;
+    bqp += (beta * kn) * qn;
+  }
+  gga_decode_head(S, bits, dk, dv, A.group, T, LD);
+  const float bq = block_reduce256<false>(bqp, red);            // (beta k) . q; also orders the tile writes
+  // kO = k^T O, two threads per column
+  const int half_id = tid / dv, col = tid - half_id * dv;
+  const bool act = tid < 2 * dv;
+  const int k0 = half_id * (dk / 2), k1 = k0 + dk / 2;
+  if (act) {
+    float s = 0.f;
+    for (int i = k0; i < k1; i++) s = fmaf(k[i], T[i * LD + col], s);
+    kO[half_id * dv + col] = s;
+  }
+  __syncthreads();
+  if (tid < dv) kO[tid] = kO[tid] + kO[dv + tid];
+  __syncthreads();
+  // A O in place
+  for (int e = tid; e < dk * dv; e += GNT) {
+    const int i = e / dv, j = e - i * dv;
+    T[i * LD + j] = a * (T[i * LD + j] - bk[i] * kO[j]);
+  }
+  __syncthreads();
+  if (act) {
+    float s = 0.f;
+    for (int i = k0; i < k1; i++) s = fmaf(T[i * LD + col], q[i], s);
+    kO[half_id * dv + col] = s;
+  }
+  __syncthreads();
+  if (tid < dv) o[tid] = (kO[tid] + kO[dv + tid]) + bq * v[tid];
+  __syncthreads();
+
+  const bool window = A.pw && bits != 16;
+  if (window) {
+    const int* ct = reinterpret_cast<const int*>(base);
+    const int n = ct[0], hd = ct[1];
+    uint8_t* qb = base + A.qoff + (long long)h * A.qsz;
+    uint8_t *PP = qb, *VP = qb + (long long)M * dk;
+    float *PS = reinterpret_cast<float*>(qb + (long long)M * (dk + dv)), *VS = PS + M;
+    // one warp per window row, in age order: propagate, re-encode, read out
+    for (int i = warp; i < M; i += GNW) {
+      const bool live = i < n;
+      float cf = 0.f;
+      if (live) {
+        const int jj = (hd + i) % M;
+        const float ps_ = PS[jj], vs_ = VS[jj];
+        float kp = 0.f;
+        for (int t = lane; t < dk; t += 32) {
+          const float pv = e4m3_val(PP[jj * dk + t]) * ps_;
+          Pw[i * dk + t] = pv;
+          kp = fmaf(k[t], pv, kp);
+        }
+        for (int t = lane; t < dv; t += 32) Vw[i * dv + t] = e4m3_val(VP[jj * dv + t]) * vs_;
+        kp = warp_sum(kp);
+        float am = 0.f;
+        for (int t = lane; t < dk; t += 32) {
+          const float ap = a * (Pw[i * dk + t] - bk[t] * kp);
+          Pw[i * dk + t] = ap;
+          am = fmaxf(am, fabsf(ap));
+        }
+        am = warp_max(am);
+        const float sc = __fdiv_rn(am, 448.0f), safe = sc > 0.f ? sc : 1.0f;
+        for (int t = lane; t < dk; t += 32) {
+          const float y = e4m3_round(fminf(fmaxf(__fdiv_rn(Pw[i * dk + t], safe), -448.0f), 448.0f));
+          PP[jj * dk + t] = e4m3_byte(y);
+          const float r = sc > 0.f ? y * safe : 0.f;
+          Pw[i * dk + t] = r;
+          cf = fmaf(r, q[t], cf);
+        }
+        if (lane == 0) PS[jj] = sc;
+        cf = warp_sum(cf);
+      }
+      if (lane == 0) coef[i] = live ? cf : 0.f;
+    }
+    __syncthreads();
+    if (tid < dv) {
+      float acc = o[tid];
+      for (int i = 0; i < M && i < n; i++) acc = fmaf(coef[i], Vw[i * dv + tid], acc);
+      o[tid] = acc;
+    }
+    if (n == M) {                                               // merge the evicted (oldest) pair into the state
+      for (int e = tid; e < dk * dv; e += GNT) {
+        const int i = e / dv, j = e - i * dv;
+        T[i * LD + j] = T[i * LD + j] + Pw[i] * Vw[j];
+      }
+    }
+    // enqueue (R(beta k), R(v)) at the slot after the youngest pair (the evicted one's when the window is full)
+    const int jn = n < M ? (hd + n) % M : hd;
+    if (warp < 2) {
+      const float* src = warp == 0 ? bk : v;
+      const int len = warp == 0 ? dk : dv;
+      float am = 0.f;
+      for (int t = lane; t < len; t += 32) am = fmaxf(am, fabsf(src[t]));
+      am = warp_max(am);
+      const float sc = __fdiv_rn(am, 448.0f), safe = sc > 0.f ? sc : 1.0f;
+      uint8_t* dst = warp == 0 ? PP + jn * dk : VP + jn * dv;
+      for (int t = lane; t < len; t += 32)
+        dst[t] = e4m3_byte(e4m3_round(fminf(fmaxf(__fdiv_rn(src[t], safe), -448.0f), 448.0f)));
+      if (lane == 0) (warp == 0 ? PS : VS)[jn] = sc;
+    }
+  } else {
+    for (int e = tid; e < dk * dv; e += GNT) {
+      const int i = e / dv, j = e - i * dv;
+      T[i * LD + j] = T[i * LD + j] + bk[i] * v[j];
+    }
+  }
+  __syncthreads();
+  for (int j = tid; j < dv; j += GNT) stf(orow, A.dt_out, j, o[j]);
+  gga_fit_store(T, LD, A.w + (long long)h * dk, bits, dk, dv, A.group, S, nullptr, gsm + P.rs, gsm + P.cs, gsm + P.ps,
+                gsm + P.wsm);
+}
+
+// window counters, after every head of the slot has read them
+__global__ void gga_advance_kernel(uint8_t* blob, long long stride, const int* idx, int rows, int M) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= rows) return;
+  const long long seq = idx[b];
+  if (seq <= 0) return;
+  int* ct = reinterpret_cast<int*>(blob + seq * stride);
+  const int n = ct[0], hd = ct[1];
+  ct[0] = min(n + 1, M);
+  ct[1] = n == M ? (hd + 1) % M : hd;
+}
+
+// fit + pack canonical states X [P, HV, dk, dv] into slots; zero the counters
+__global__ void __launch_bounds__(GNT) gga_store_kernel(const __grid_constant__ GgaArgs A) {
+  extern __shared__ __align__(16) float gsm[];
+  const int tid = threadIdx.x;
+  const int dk = A.DK, dv = A.DV, HV = A.HV;
+  const int ph = blockIdx.x, p = ph / HV, h = ph - p * HV;
+  const long long seq = A.idx[p];
+  const GgaSmem P = gga_smem(dk, dv, A.M, A.group);
+  float* T = gsm + P.T;
+  const float* x = A.X + (long long)ph * dk * dv;
+  for (int e = tid; e < dk * dv; e += GNT) T[(e / dv) * P.LD + (e % dv)] = x[e];
+  __syncthreads();
+  uint8_t* base = A.blob + seq * A.stride;
+  gga_fit_store(T, P.LD, A.w + (long long)h * dk, A.bits[h], dk, dv, A.group, base + A.offs[h], nullptr, gsm + P.rs,
+                gsm + P.cs, gsm + P.ps, gsm + P.wsm);
+  if (h == 0 && tid < 2) reinterpret_cast<int*>(base)[tid] = 0;
+}
+
+// unpack slots into canonical fp32 Y [P, HV, dk, dv] (the stored state, without the window)
+__global__ void __launch_bounds__(GNT) gga_load_kernel(const __grid_constant__ GgaArgs A) {
+  extern __shared__ __align__(16) float gsm[];
+  const int tid = threadIdx.x;
+  const int dk = A.DK, dv = A.DV, HV = A.HV;
+  const int ph = blockIdx.x, p = ph / HV, h = ph - p * HV;
+  const long long seq = A.idx[p];
+  const GgaSmem P = gga_smem(dk, dv, A.M, A.group);
+  float* T = gsm + P.T;
+  gga_decode_head(A.blob + seq * A.stride + A.offs[h], A.bits[h], dk, dv, A.group, T, P.LD);
+  __syncthreads();
+  float* y = A.Y + (long long)ph * dk * dv;
+  for (int e = tid; e < dk * dv; e += GNT) y[e] = T[(e / dv) * P.LD + (e % dv)];
+}
+
+// STEP's dual-axis fit as a fake-quant pass: Y = fit(X), X / Y [B, H, dk, dv]
+__global__ void __launch_bounds__(GNT) stepquant_fit_kernel(const __grid_constant__ GgaArgs A) {
+  extern __shared__ __align__(16) float gsm[];
+  const int tid = threadIdx.x;
+  const int dk = A.DK, dv = A.DV, HV = A.HV;
+  const int ph = blockIdx.x, h = ph % HV;
+  const GgaSmem P = gga_smem(dk, dv, 1, A.group);
+  float* T = gsm + P.T;
+  const float* x = A.X + (long long)ph * dk * dv;
+  for (int e = tid; e < dk * dv; e += GNT) T[(e / dv) * P.LD + (e % dv)] = x[e];
+  __syncthreads();
+  gga_fit_store(T, P.LD, A.w + (long long)h * dk, A.bits[h], dk, dv, A.group, nullptr, A.Y + (long long)ph * dk * dv,
+                gsm + P.rs, gsm + P.cs, gsm + P.ps, gsm + P.wsm);
+}
+
+}  // namespace sqb

@@ -7,6 +7,7 @@
 #include "../../include/statequant_b200.h"
 #include "delta_step.cuh"
 #include "step_tma.cuh"
+#include "gga.cuh"
 
 namespace {
 
@@ -273,6 +274,108 @@ int sqb_kda_step(const sqb_state_t* st, const sqb_kda_inputs_t* in, void* stream
   a.dt_qk = in->qk_dtype; a.dt_v = in->v_dtype; a.dt_g = in->g_dtype; a.dt_beta = in->beta_dtype;
   a.dt_out = in->out_dtype; a.per_key_head = 1; a.scale = in->scale;
   return launch<sqb::K_KDA>(a, st->bits, st->bits > 8 || st->axis_k, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
+
+// ---- GGA / STEP -----------------------------------------------------------------------------------------------------
+namespace {
+
+int check_gga(const sqb_gga_layout_t* L, bool need_plan) {
+  if (!L || !L->blob) return fail(SQB_EINVAL, "GGA layout or blob is NULL");
+  if (need_plan && (!L->offs || !L->bits || !L->w)) return fail(SQB_EINVAL, "GGA plan arrays (offs, bits, w) are NULL");
+  if (L->dk <= 0 || L->dv <= 0 || L->dk % 2 || L->dv % 32 || L->dv > 128 || L->dk > 256)
+    return fail(SQB_EINVAL, "GGA head dims d_k %d, d_v %d: d_k even <= 256, d_v a multiple of 32 <= 128", L->dk, L->dv);
+  if (L->hv <= 0 || L->hk <= 0 || L->hv % L->hk) return fail(SQB_EINVAL, "heads hv %d, hk %d", L->hv, L->hk);
+  if (L->group != 32) return fail(SQB_EINVAL, "GGA column group %d: expected 32", L->group);
+  if (L->pw && (L->m < 1 || L->m > 64)) return fail(SQB_EINVAL, "window length %d", L->m);
+  if (L->stride % 16 || (reinterpret_cast<uintptr_t>(L->blob) & 15)) return fail(SQB_EINVAL, "GGA blob: base and slot stride must be multiples of 16 bytes");
+  return 0;
+}
+
+void fill_gga(sqb::GgaArgs& a, const sqb_gga_layout_t* L) {
+  memset(&a, 0, sizeof a);
+  a.blob = static_cast<uint8_t*>(L->blob); a.stride = L->stride;
+  a.offs = L->offs; a.bits = L->bits; a.w = L->w; a.qoff = L->qoff; a.qsz = L->qsz;
+  a.HV = L->hv; a.HK = L->hk; a.DK = L->dk; a.DV = L->dv; a.M = L->pw ? L->m : 1; a.pw = L->pw; a.group = L->group;
+}
+
+template <typename K>
+int launch_gga(K kern, const sqb::GgaArgs& a, long long ctas, cudaStream_t stream) {
+  const sqb::GgaSmem plan = sqb::gga_smem(a.DK, a.DV, a.M, a.group);
+  const int smem = plan.total * static_cast<int>(sizeof(float));
+  if (smem > 200 * 1024) return fail(SQB_EINVAL, "GGA tile needs %d bytes of shared memory", smem);
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return fail(SQB_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  if (ctas <= 0) return 0;
+  kern<<<static_cast<unsigned>(ctas), sqb::GNT, smem, stream>>>(a);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(SQB_ECUDA, "kernel launch: %s", cudaGetErrorString(e));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int sqb_gga_step(const sqb_gga_layout_t* L, const sqb_gdn_inputs_t* in, void* stream) {
+  if (int rc = check_gga(L, true)) return rc;
+  if (!in) return fail(SQB_EINVAL, "inputs are NULL");
+  if (in->rows <= 0) return in->rows == 0 ? 0 : fail(SQB_EINVAL, "rows %d < 0", in->rows);
+  if (!in->gate || !in->a || !in->b || !in->A_log || !in->dt_bias) return fail(SQB_EINVAL, "the GGA step takes the gate inputs (a, b, A_log, dt_bias)");
+  if (!in->idx || !in->q || !in->k || !in->v || !in->out) return fail(SQB_EINVAL, "idx, q, k, v or out is NULL");
+  sqb::GgaArgs a;
+  fill_gga(a, L);
+  a.rows = in->rows; a.idx = in->idx;
+  a.q = static_cast<const uint8_t*>(in->q); a.sq = in->sq; a.k = static_cast<const uint8_t*>(in->k); a.sk = in->sk;
+  a.v = static_cast<const uint8_t*>(in->v); a.sv = in->sv;
+  a.a = static_cast<const uint8_t*>(in->a); a.sa = in->sa; a.b = static_cast<const uint8_t*>(in->b); a.sb = in->sb;
+  a.A_log = static_cast<const uint8_t*>(in->A_log); a.dt_bias = static_cast<const uint8_t*>(in->dt_bias);
+  a.out = static_cast<uint8_t*>(in->out); a.so = in->so;
+  a.dt_qk = in->qk_dtype; a.dt_v = in->v_dtype; a.dt_ab = in->ab_dtype; a.dt_alog = in->alog_dtype;
+  a.dt_dtb = in->dtb_dtype; a.dt_out = in->out_dtype; a.scale = in->scale;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (int rc = launch_gga(sqb::gga_step_kernel, a, static_cast<long long>(in->rows) * L->hv, st)) return rc;
+  if (L->pw) {
+    sqb::gga_advance_kernel<<<(in->rows + 127) / 128, 128, 0, st>>>(a.blob, a.stride, a.idx, in->rows, L->m);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(SQB_ECUDA, "kernel launch: %s", cudaGetErrorString(e));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  }
+  return 0;
+}
+
+int sqb_gga_store(const sqb_gga_layout_t* L, const int32_t* idx, int64_t P, const float* X, void* stream) {
+  if (int rc = check_gga(L, true)) return rc;
+  if (P <= 0) return P == 0 ? 0 : fail(SQB_EINVAL, "P < 0");
+  if (!idx || !X) return fail(SQB_EINVAL, "idx or X is NULL");
+  sqb::GgaArgs a;
+  fill_gga(a, L);
+  a.idx = idx; a.X = X; a.P = P;
+  return launch_gga(sqb::gga_store_kernel, a, P * L->hv, static_cast<cudaStream_t>(stream));
+}
+
+int sqb_gga_load(const sqb_gga_layout_t* L, const int32_t* idx, int64_t P, float* Y, void* stream) {
+  if (int rc = check_gga(L, true)) return rc;
+  if (P <= 0) return P == 0 ? 0 : fail(SQB_EINVAL, "P < 0");
+  if (!idx || !Y) return fail(SQB_EINVAL, "idx or Y is NULL");
+  sqb::GgaArgs a;
+  fill_gga(a, L);
+  a.idx = idx; a.Y = Y; a.P = P;
+  return launch_gga(sqb::gga_load_kernel, a, P * L->hv, static_cast<cudaStream_t>(stream));
+}
+
+int sqb_stepquant_fit(const float* x, float* y, const int32_t* bits, const float* w, int64_t B, int32_t H, int32_t dk,
+                      int32_t dv, int32_t group, void* stream) {
+  if (!x || !y || !bits || !w) return fail(SQB_EINVAL, "x, y, bits or w is NULL");
+  if (dk <= 0 || dv <= 0 || dk % 2 || dv % 32 || dv > 128 || dk > 256 || group != 32)
+    return fail(SQB_EINVAL, "fit: d_k %d even <= 256, d_v %d a multiple of 32 <= 128, group %d = 32", dk, dv, group);
+  if (B <= 0) return B == 0 ? 0 : fail(SQB_EINVAL, "B < 0");
+  sqb::GgaArgs a;
+  memset(&a, 0, sizeof a);
+  a.bits = bits; a.w = w; a.HV = H; a.HK = H; a.DK = dk; a.DV = dv; a.M = 1; a.group = group; a.X = x; a.Y = y;
+  return launch_gga(sqb::stepquant_fit_kernel, a, B * H, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -80,3 +80,36 @@ def pack_input(bits, axis, group, dk, dv):
     S[0, :, :dk // 2] = 0
     S[1] *= 1e-6
     return S
+
+
+# ---- GGA / STEP cases: per-head widths of one layer, window on / off; idx has a padding row -------------------
+GGA_CASES = {
+    'gga_step_pw':   dict(hv=4, hk=2, d=64, m=8, pw=True, T=11, B=2, idx=[0, 3], widths=[2, 4, 16, 8], seed=51,
+                          keep=[0, 8, 10]),
+    'gga_step_nopw': dict(hv=4, hk=2, d=64, m=8, pw=False, T=4, B=2, idx=[-1, 1], widths=[6, 4, 16, 2], seed=52,
+                          keep=[0, 3]),
+    'gga_step_128':  dict(hv=2, hk=2, d=128, m=4, pw=True, T=6, B=1, idx=[1], widths=[4, 6], seed=53, keep=[5]),
+}
+
+
+def gga_plan(hv, d, seed, widths):
+    r = np.random.RandomState(seed)
+    return torch.tensor(widths, dtype=torch.int64), torch.from_numpy((r.rand(hv, d) + 0.5).astype(np.float32))
+
+
+def gga_inputs(c):
+    r = np.random.RandomState(c['seed'] + 100)
+    B, hv, hk, D, T = c['B'], c['hv'], c['hk'], c['d'], c['T']
+    live = sum(1 for i in c['idx'] if i > 0)
+    f = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32))      # noqa: E731
+    return dict(S0=f(r.standard_normal((live, hv, D, D)) * 0.3),                    # value-major [P, HV, dv, dk]
+                q=f(r.standard_normal((T, B, hk, D))), k=f(r.standard_normal((T, B, hk, D))),
+                v=f(r.standard_normal((T, B, hv, D))), a=f(r.standard_normal((T, B, hv)) * 0.5 - 2),
+                b=f(r.standard_normal((T, B, hv))), A_log=f(r.standard_normal(hv) * 0.3),
+                dt_bias=f(r.standard_normal(hv) * 0.3))
+
+
+def fit_input(D):
+    """States for the stand-alone fit: [2, 5, D, D] with columns spanning three decades."""
+    r = np.random.RandomState(40 + D)
+    return torch.from_numpy((r.standard_normal((2, 5, D, D)) * np.logspace(-3, 0, D)).astype(np.float32))
