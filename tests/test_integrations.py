@@ -1,0 +1,102 @@
+"""Host-side bindings (CPU): the STATEQUANT_VLLM surface, the slot sizes handed to vLLM's memory planner, and the
+rebinding of an installed reference package onto this package's classes."""
+import os
+
+import pytest
+import torch
+
+import statequant_b200 as sq
+from statequant_b200.integrations import vllm_plugin as P
+from statequant_b200.kernels import GGAPacked, KDASlotLayout, Mamba2SlotLayout, SlotLayout
+
+
+@pytest.fixture
+def env(monkeypatch):
+    def set_(**kw):
+        for k in list(os.environ):
+            if k.startswith('STATEQUANT_'):
+                monkeypatch.delenv(k)
+        for k, v in kw.items():
+            monkeypatch.setenv(k, v)
+        P._STATE.clear()
+    yield set_
+    P._STATE.clear()
+
+
+def test_config_parsing(env):
+    env()
+    assert P.config() is None
+    env(STATEQUANT_VLLM='pace4')
+    fmt, m, bb, fused = P.config()
+    assert (fmt.bits, fmt.axis, fmt.group, m, bb, fused) == (4, 'k', 64, 8, 8, None)
+    env(STATEQUANT_VLLM='int8vg64', STATEQUANT_VLLM_M='4', STATEQUANT_VLLM_BUFFER_BITS='16', STATEQUANT_VLLM_FUSED='1')
+    fmt, m, bb, fused = P.config()
+    assert (fmt.bits, fmt.axis, fmt.group, m, bb, fused) == (8, 'v', 64, 4, 16, True)
+    env(STATEQUANT_VLLM='bf16')
+    assert P.config()[0] == 'bf16'
+    env(STATEQUANT_VLLM='int5k')
+    with pytest.raises(AssertionError):
+        P.config()
+    env(STATEQUANT_VLLM='pace4', STATEQUANT_VLLM_LAYERS='gdn,mamba2')
+    assert P.layer_kinds() == ('gdn', 'mamba2')
+    env(STATEQUANT_VLLM='pace4', STATEQUANT_VLLM_LAYERS='rwkv')
+    with pytest.raises(AssertionError):
+        P.layer_kinds()
+
+
+def test_layout_factories(env, tmp_path):
+    env(STATEQUANT_VLLM='pace4')
+    lay = P.layout(32, 16, 128, 128)
+    assert isinstance(lay, SlotLayout) and lay.nbytes == 329728 and P.layout(32, 16, 128, 128) is lay
+    assert isinstance(P.mamba2_layout(128, 8, 128, 64), Mamba2SlotLayout)
+    assert isinstance(P.kda_layout(32, 128, 128), KDASlotLayout)
+    plan = {'plan': {l: (torch.tensor([[4, 6, 4, 4, 6, 4][l % 6]] * 32), torch.ones(32, 128)) for l in range(24)},
+            'group': 32}
+    path = str(tmp_path / 'plan.pt')
+    torch.save(plan, path)
+    env(STATEQUANT_VLLM=f'gga:{path}:pw')
+    lay = P.layout(32, 16, 128, 128)
+    assert isinstance(lay, GGAPacked) and lay.pw and lay.nbytes == 477200
+
+
+def test_vllm_calculators_see_packed_slot_size(env):
+    """vLLM's own calculators, patched, hand the packed slot size to the memory planner (reference:
+    tests/test_vllm_plugin.py)."""
+    mu = pytest.importorskip('vllm.model_executor.layers.mamba.mamba_utils')
+    if not hasattr(mu.MambaStateShapeCalculator, 'gated_delta_net_state_shape'):
+        pytest.skip('this vLLM has no GDN state calculators')
+    env(STATEQUANT_VLLM='int8k')
+    shape0, dtype0 = P.patch_calculators()
+    try:
+        conv, ssm = mu.MambaStateShapeCalculator.gated_delta_net_state_shape(1, 16, 32, 128, 128, 4)
+        assert ssm == (608256,)
+        assert conv == shape0(1, 16, 32, 128, 128, 4)[0]
+        conv2, ssm2 = mu.MambaStateShapeCalculator.gated_delta_net_state_shape(2, 16, 32, 128, 128, 4)
+        assert ssm2 == (SlotLayout(sq.Quantizer(8, 'k', 32), 16, 8, 128, 128).nbytes,)
+        dts = mu.MambaStateDtypeCalculator.gated_delta_net_state_dtype(torch.bfloat16, 'auto')
+        assert dts[1] == torch.uint8
+    finally:
+        P.unpatch_calculators()
+    assert mu.MambaStateShapeCalculator.gated_delta_net_state_shape(1, 16, 32, 128, 128, 4)[1] != (608256,)
+
+
+def test_bind_reference_rebinds_a_package(tmp_path, monkeypatch):
+    """A stand-in package with the reference's module layout is rebound onto this package's classes."""
+    root = tmp_path / 'fakeref'
+    for d in ('', 'kernels', 'integrations'):
+        (root / d).mkdir(parents=True, exist_ok=True)
+        (root / d / '__init__.py').write_text('')
+    for m in ('fold', 'slots', 'mamba2', 'kda'):
+        (root / 'kernels' / f'{m}.py').write_text('PackedGDNState = SlotLayout = None\n')
+    (root / 'integrations' / 'vllm_gga.py').write_text('GGAPacked = None\n')
+    monkeypatch.syspath_prepend(str(tmp_path))
+    from statequant_b200.integrations import binding
+    done = binding.bind_reference('fakeref')
+    import fakeref.kernels as FK
+    import fakeref.kernels.slots as FS
+    import fakeref.integrations.vllm_gga as FG
+    from fakeref.kernels._stepquant_triton import fit
+    from statequant_b200.kernels.gga import fit as our_fit
+    assert FK.PackedGDNState is sq.kernels.PackedGDNState and FS.SlotLayout is SlotLayout
+    assert FG.GGAPacked is GGAPacked and fit is our_fit
+    assert ('fakeref.kernels', 'pack_vk') in done and binding.bind_reference('fakeref') is done
