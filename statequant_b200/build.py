@@ -2,7 +2,7 @@
 
     python -m statequant_b200.build [--force] [--verbose]
 
-nvcc cross-compiles without a GPU.  ``--fmad=false`` stops the compiler from contracting separately rounded
+nvcc cross-compiles without a GPU; the translation units compile in parallel and are linked into one library.  ``--fmad=false`` stops the compiler from contracting separately rounded
 products into FMAs (every FMA the kernels want is written explicitly), and there is no fast-math flag: the stored
 codes depend on IEEE division, square root and round-half-even.
 """
@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, 'csrc')
 OUT_DIR = os.path.join(HERE, 'lib')
 OUT = os.path.join(OUT_DIR, 'libstatequant_b200.so')
-UNITS = ['sqb200.cu']
+UNITS = ['sqb200.cu', 'staged_gdn.cu', 'staged_m2.cu', 'staged_kda.cu', 'pipe_gdn.cu', 'pipe_m2.cu', 'pipe_kda.cu', 'fold_launch.cu']
 
 
 def _nvcc():
@@ -47,18 +47,35 @@ def build(force=False, verbose=False):
     if not force and up_to_date():
         return OUT
     os.makedirs(OUT_DIR, exist_ok=True)
-    cmd = [_nvcc(), '-gencode', 'arch=compute_100a,code=sm_100a', '-O3', '-lineinfo', '-std=c++17',
-           '--fmad=false', '-Xcompiler', '-fPIC', '-shared', '-cudart', 'static',
-           '-o', OUT] + [os.path.join(SRC, u) for u in UNITS]
-    cmd += os.environ.get('SQB_NVCC_EXTRA', '').split()
+    obj_dir = os.path.join(OUT_DIR, 'obj')
+    os.makedirs(obj_dir, exist_ok=True)
+    flags = ['-gencode', 'arch=compute_100a,code=sm_100a', '-O3', '-lineinfo', '-std=c++17', '--fmad=false',
+             '-Xcompiler', '-fPIC'] + os.environ.get('SQB_NVCC_EXTRA', '').split()
     if verbose:
-        cmd.insert(1, '-Xptxas')
-        cmd.insert(2, '-v')
+        flags += ['-Xptxas', '-v']
+    units = os.environ.get('SQB_UNITS', '').split() or UNITS     # a subset recompiles only those objects
+
+    def compile_unit(u):
+        obj = os.path.join(obj_dir, u[:-3] + '.o')
+        cmd = [_nvcc()] + flags + ['-c', os.path.join(SRC, u), '-o', obj]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        return u, cmd, r
+
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(max_workers=min(len(units), os.cpu_count() or 1)) as pool:
+        for u, cmd, r in pool.map(compile_unit, units):
+            if r.returncode != 0:
+                raise RuntimeError('nvcc failed:\n' + ' '.join(cmd) + '\n' + r.stdout + r.stderr)
+            if verbose:
+                print(f'==== {u}\n' + r.stdout + r.stderr)
+    objs = [os.path.join(obj_dir, u[:-3] + '.o') for u in UNITS]
+    missing = [o for o in objs if not os.path.exists(o)]
+    if missing:
+        raise RuntimeError('objects missing (build all units first): ' + ' '.join(missing))
+    cmd = [_nvcc(), '-gencode', 'arch=compute_100a,code=sm_100a', '-shared', '-cudart', 'static', '-o', OUT] + objs
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
-        raise RuntimeError('nvcc failed:\n' + ' '.join(cmd) + '\n' + r.stdout + r.stderr)
-    if verbose:
-        print(r.stdout + r.stderr)
+        raise RuntimeError('link failed:\n' + ' '.join(cmd) + '\n' + r.stdout + r.stderr)
     return OUT
 
 

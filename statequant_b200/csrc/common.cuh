@@ -32,7 +32,7 @@ __device__ __forceinline__ void stf(void* p, int dt, long long i, float v) {
   else if (dt == DT_BF16) reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
   else reinterpret_cast<__half*>(p)[i] = __float2half_rn(v);
 }
-__device__ __forceinline__ int dt_size(int dt) { return dt == DT_F32 ? 4 : 2; }
+__host__ __device__ __forceinline__ int dt_size(int dt) { return dt == DT_F32 ? 4 : 2; }
 
 __device__ __forceinline__ float h2f(unsigned short h) { return __half2float(__ushort_as_half(h)); }
 __device__ __forceinline__ unsigned short f2h(float f) { return __half_as_ushort(__float2half_rn(f)); }
@@ -95,5 +95,8 @@ __device__ __forceinline__ float nib_prescale(int j) {
   const int e = j <= 4 ? j : j - 5;
   return __uint_as_float(static_cast<uint32_t>(127 - 4 * e) << 23);
 }
+
+// floats per row of the fold's value-major L tile (M coefficients, padded so that rows fall on distinct banks)
+__host__ __device__ inline int fold_lm(int M) { return (M < 4 ? 4 : M) + 4; }
 
 }  // namespace sqb

@@ -48,6 +48,7 @@ struct StepArgs {
   int dt_qk, dt_v, dt_g, dt_beta, dt_ab, dt_alog, dt_dtb, dt_out;
   int per_key_head, gate, dt_softplus, dt_clamp;
   float scale, dt_min, dt_max;
+  int* status;               // device health word: [0] counts CTAs whose bounded wait ran out
 };
 
 // shared-memory plan (floats)

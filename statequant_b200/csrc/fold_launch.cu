@@ -1,0 +1,60 @@
+// Host side of the fold launch (see fold_kernel.cuh and launchers.h for the return convention).
+#include <atomic>
+#include "launchers.h"
+#include "fold_kernel.cuh"
+
+namespace sqb {
+namespace {
+
+template <bool VDEC, int BITS, bool AXK, int LPR>
+int launch_fold_one(const StepArgs& a, cudaStream_t stream) {
+  auto kern = fold_kernel<VDEC, BITS, AXK, LPR>;
+  const SmemF plan = smemf_plan(VDEC, BITS, AXK, a.group, a.DK, a.DV, a.M, a.qbuf);
+  if (plan.total > 220 * 1024) return 1;
+  static std::atomic<int> configured{0};
+  if (plan.total > configured.load()) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.total);
+    if (e != cudaSuccess) return -1000 - static_cast<int>(e);
+    configured.store(plan.total);
+  }
+  static thread_local int sms[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int& nsm = sms[dev & 63];
+  if (!nsm) cudaDeviceGetAttribute(&nsm, cudaDevAttrMultiProcessorCount, dev);
+  if (!nsm) return 1;
+  FoldArgs f;
+  f.S = a.S; f.SC = a.SC; f.KB = a.KB; f.KBS = a.KBS; f.UB = a.UB; f.UBS = a.UBS; f.GB = a.GB; f.GCUR = a.GCUR; f.NPTR = a.NPTR;
+  f.sS = a.sS; f.sSC = a.sSC; f.sKB = a.sKB; f.sKBS = a.sKBS; f.sUB = a.sUB; f.sUBS = a.sUBS; f.sGB = a.sGB; f.sGC = a.sGC; f.sN = a.sN;
+  f.idx = a.idx; f.group = a.group; f.qbuf = a.qbuf; f.M = a.M; f.HV = a.HV; f.HK = a.HK; f.DV = a.DV; f.rows = a.rows;
+  f.status = a.status;
+  const long long pairs = static_cast<long long>(a.rows) * a.HV;
+  int per_sm = (220 * 1024) / (plan.total + 1024);
+  if (per_sm > 4) per_sm = 4;
+  if (per_sm < 1) per_sm = 1;
+  long long grid = static_cast<long long>(nsm) * per_sm;
+  if (grid > pairs) grid = pairs;
+  kern<<<static_cast<unsigned>(grid), NT, plan.total, stream>>>(f, plan);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return -1000 - static_cast<int>(e);
+  return 0;
+}
+
+template <bool VDEC>
+int launch_fold_kind(const StepArgs& a, int bits, bool axk, cudaStream_t stream) {
+  const bool d128 = a.DK == 128;
+  if (bits == 4) {
+    if (axk) return d128 ? launch_fold_one<VDEC, 4, true, 8>(a, stream) : launch_fold_one<VDEC, 4, true, 4>(a, stream);
+    return d128 ? launch_fold_one<VDEC, 4, false, 8>(a, stream) : launch_fold_one<VDEC, 4, false, 4>(a, stream);
+  }
+  if (axk) return d128 ? launch_fold_one<VDEC, 8, true, 8>(a, stream) : launch_fold_one<VDEC, 8, true, 4>(a, stream);
+  return d128 ? launch_fold_one<VDEC, 8, false, 8>(a, stream) : launch_fold_one<VDEC, 8, false, 4>(a, stream);
+}
+
+}  // namespace
+
+int launch_fold(int kind, const StepArgs& a, int bits, bool axk, cudaStream_t stream) {
+  return kind == K_KDA ? launch_fold_kind<true>(a, bits, axk, stream) : launch_fold_kind<false>(a, bits, axk, stream);
+}
+
+}  // namespace sqb

@@ -1,0 +1,209 @@
+// The fold of one value head, shared by the staged and the pipelined kernel:
+//     S[v][k] = decay * (code[v][k] * scale) + sum_i L[v][i] * R[i][k]      (slot order, one fma.rn per term)
+// re-rounded to codes with fresh scales and written back in place.
+//
+// Shared-memory operands: codes / scs are the head's stored state (a stage buffer); R[i][.] is slot i's key in the
+// lane-chunk layout (16 columns + 4 floats of padding per lane, so 128-bit reads of the LPR chunks of a row hit
+// distinct banks); L is value-major, L[v * LM + i] = decayed buffered value of slot i at row v, LM = fold_lm(M), so
+// a row's M coefficients are one or two 128-bit reads.  A lane owns 16 columns of two rows at a time; the slot
+// loop is unrolled for the usual buffer length 8 (immediate offsets, no loop control in the hot part).
+#pragma once
+#include "common.cuh"
+
+namespace sqb {
+
+#ifndef SQB_FOLD_UNROLL8
+#define SQB_FOLD_UNROLL8 1
+#endif
+
+template <int LPR, int MC>
+__device__ __forceinline__ void fold_mac(float2 (&a0)[8], float2 (&a1)[8], const float* Rc, const float* l0p,
+                                         const float* l1p, int M) {
+  constexpr int RDK = LPR * 20;
+  if constexpr (MC == 8) {
+    const float4 x0 = *reinterpret_cast<const float4*>(l0p), x1 = *reinterpret_cast<const float4*>(l0p + 4);
+    const float4 y0 = *reinterpret_cast<const float4*>(l1p), y1 = *reinterpret_cast<const float4*>(l1p + 4);
+    const float l0[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    const float l1[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const float4* rrow = reinterpret_cast<const float4*>(Rc + i * RDK);
+      const float2 la = make_float2(l0[i], l0[i]), lb = make_float2(l1[i], l1[i]);
+#pragma unroll
+      for (int j4 = 0; j4 < 4; j4++) {
+        const float4 k4 = rrow[j4];
+        const float2 ka = make_float2(k4.x, k4.y), kb = make_float2(k4.z, k4.w);
+        a0[2 * j4] = __ffma2_rn(la, ka, a0[2 * j4]);
+        a0[2 * j4 + 1] = __ffma2_rn(la, kb, a0[2 * j4 + 1]);
+        a1[2 * j4] = __ffma2_rn(lb, ka, a1[2 * j4]);
+        a1[2 * j4 + 1] = __ffma2_rn(lb, kb, a1[2 * j4 + 1]);
+      }
+    }
+  } else {
+    for (int i = 0; i < M; i++) {
+      const float4* rrow = reinterpret_cast<const float4*>(Rc + i * RDK);
+      const float2 la = make_float2(l0p[i], l0p[i]), lb = make_float2(l1p[i], l1p[i]);
+#pragma unroll
+      for (int j4 = 0; j4 < 4; j4++) {
+        const float4 k4 = rrow[j4];
+        const float2 ka = make_float2(k4.x, k4.y), kb = make_float2(k4.z, k4.w);
+        a0[2 * j4] = __ffma2_rn(la, ka, a0[2 * j4]);
+        a0[2 * j4 + 1] = __ffma2_rn(la, kb, a0[2 * j4 + 1]);
+        a1[2 * j4] = __ffma2_rn(lb, ka, a1[2 * j4]);
+        a1[2 * j4 + 1] = __ffma2_rn(lb, kb, a1[2 * j4 + 1]);
+      }
+    }
+  }
+}
+
+// code * scale (* 16^-e of the 4-bit unpacking), then * decay: two roundings, as the reference does them
+template <int BITS, bool VDEC>
+__device__ __forceinline__ void fold_dequant(float2 (&a)[8], float sc, float alphan, const float* aec) {
+#pragma unroll
+  for (int p = 0; p < 8; p++) {
+    float2 s2;
+    if constexpr (BITS == 4) s2 = make_float2(sc * nib_prescale((2 * p) & 7), sc * nib_prescale((2 * p + 1) & 7));
+    else s2 = make_float2(sc, sc);
+    a[p] = __fmul2_rn(a[p], s2);
+    float2 d2 = make_float2(alphan, alphan);
+    if constexpr (VDEC) d2 = make_float2(aec[2 * p], aec[2 * p + 1]);
+    a[p] = __fmul2_rn(a[p], d2);
+  }
+}
+
+// sync(): barrier among the 128 threads that fold (returns false if the CTA is aborting).  Returns false on abort.
+template <int BITS, bool AXK, int LPR, bool VDEC, class Sync>
+__device__ __forceinline__ bool fold_rows(const uint8_t* codes, const unsigned short* scs, const float* R,
+                                          const float* L, const float* ae, float alphan, int DV, int G, int M,
+                                          float* cmax, uint8_t* Sh, unsigned short* SCh, int warp, int lane, int tid,
+                                          Sync sync) {
+  constexpr int DK = LPR * 16;
+  constexpr int RPP = 32 / LPR;
+  constexpr int CB = 16 * BITS / 8;
+  constexpr int ROWB = DK * BITS / 8;
+  constexpr int PPW = 2;
+  constexpr float QMAX = BITS == 4 ? 7.0f : 127.0f;
+  [[maybe_unused]] constexpr float MB = BITS == 4 ? MAGIC + 8.0f : MAGIC;
+  const int c = lane & (LPR - 1), rl = lane / LPR;
+  const int LM = fold_lm(M);
+  const float* Rc = R + c * 20;
+  const float* aec = VDEC ? ae + c * 16 : nullptr;
+
+  if constexpr (AXK) {
+    const int NG = DK / G;
+    const int gl = (c * 16) / G;
+    const int lpg = G / 16;
+    constexpr int BR = NW * PPW * RPP;
+    const int niter = (DV + BR - 1) / BR;
+    for (int it = 0; it < niter; it++) {
+      const int row0 = it * BR + warp * (PPW * RPP) + rl, row1 = row0 + RPP;
+      const bool v0 = row0 < DV, v1 = row1 < DV;
+      const int r0 = v0 ? row0 : 0, r1 = v1 ? row1 : 0;
+      float2 a0[8], a1[8];
+      decode16<BITS>(codes + r0 * ROWB + c * CB, a0);
+      decode16<BITS>(codes + r1 * ROWB + c * CB, a1);
+      fold_dequant<BITS, VDEC>(a0, h2f(scs[r0 * NG + gl]), alphan, aec);
+      fold_dequant<BITS, VDEC>(a1, h2f(scs[r1 * NG + gl]), alphan, aec);
+      if (SQB_FOLD_UNROLL8 && M == 8) fold_mac<LPR, 8>(a0, a1, Rc, L + r0 * LM, L + r1 * LM, M);
+      else fold_mac<LPR, 0>(a0, a1, Rc, L + r0 * LM, L + r1 * LM, M);
+      // fresh scales: absmax over the group's lanes
+      float am0 = 0.f, am1 = 0.f;
+#pragma unroll
+      for (int p = 0; p < 8; p++) {
+        am0 = fmaxf(am0, fmaxf(fabsf(a0[p].x), fabsf(a0[p].y)));
+        am1 = fmaxf(am1, fmaxf(fabsf(a1[p].x), fabsf(a1[p].y)));
+      }
+      for (int o = 1; o < lpg; o <<= 1) {
+        am0 = fmaxf(am0, __shfl_xor_sync(0xffffffffu, am0, o));
+        am1 = fmaxf(am1, __shfl_xor_sync(0xffffffffu, am1, o));
+      }
+      const float sc0 = fp16_scale(am0, QMAX), sc1 = fp16_scale(am1, QMAX);
+      const bool lead = (c & (lpg - 1)) == 0;
+      float2 tt[8];
+      if (v0) {
+        if (lead) SCh[r0 * NG + gl] = f2h(sc0);
+        uint4 pk;
+        if (sc0 >= FP16_MIN_NORMAL && round_fast<8>(a0, sc0, __fdiv_rn(1.0f, sc0), MB, tt)) pk = pack_codes16<BITS>(tt);
+        else pk = round_exact_pack<BITS>(a0[0], a0[1], a0[2], a0[3], a0[4], a0[5], a0[6], a0[7], sc0);
+        store_packed16<BITS>(Sh + (long long)r0 * ROWB + c * CB, pk);
+      }
+      if (v1) {
+        if (lead) SCh[r1 * NG + gl] = f2h(sc1);
+        uint4 pk;
+        if (sc1 >= FP16_MIN_NORMAL && round_fast<8>(a1, sc1, __fdiv_rn(1.0f, sc1), MB, tt)) pk = pack_codes16<BITS>(tt);
+        else pk = round_exact_pack<BITS>(a1[0], a1[1], a1[2], a1[3], a1[4], a1[5], a1[6], a1[7], sc1);
+        store_packed16<BITS>(Sh + (long long)r1 * ROWB + c * CB, pk);
+      }
+    }
+    return true;
+  } else {
+    // scale groups run along d_v: a group of G rows shares one scale per column
+    const int wpg = min(NW, G / RPP);               // warps that share a group
+    const int ppw = G / (RPP * wpg);                // rows per lane (1 or 2)
+    const int gpi = NW / wpg;                       // groups in flight
+    const int BR = gpi * G;
+    const int niter = (DV + BR - 1) / BR;
+    for (int it = 0; it < niter; it++) {
+      const int gvrow = it * gpi + warp / wpg;
+      const bool gvalid = gvrow * G < DV;
+      const int row0 = gvrow * G + (warp % wpg) * (ppw * RPP) + rl, row1 = row0 + RPP;
+      const bool v0 = row0 < DV, v1 = ppw > 1 && row1 < DV;
+      const int r0 = v0 ? row0 : 0, r1 = v1 ? row1 : 0;
+      float2 a0[8], a1[8];
+      decode16<BITS>(codes + r0 * ROWB + c * CB, a0);
+      decode16<BITS>(codes + r1 * ROWB + c * CB, a1);
+#pragma unroll
+      for (int p = 0; p < 8; p++) {
+        const int k0 = c * 16 + 2 * p;
+        const float s0 = gvalid ? h2f(scs[gvrow * DK + k0]) : 0.f, s1 = gvalid ? h2f(scs[gvrow * DK + k0 + 1]) : 0.f;
+        float2 s2 = make_float2(s0, s1);
+        if constexpr (BITS == 4) s2 = make_float2(s0 * nib_prescale((2 * p) & 7), s1 * nib_prescale((2 * p + 1) & 7));
+        float2 d2 = make_float2(alphan, alphan);
+        if constexpr (VDEC) d2 = make_float2(aec[2 * p], aec[2 * p + 1]);
+        a0[p] = __fmul2_rn(__fmul2_rn(a0[p], s2), d2);
+        a1[p] = __fmul2_rn(__fmul2_rn(a1[p], s2), d2);
+      }
+      if (SQB_FOLD_UNROLL8 && M == 8) fold_mac<LPR, 8>(a0, a1, Rc, L + r0 * LM, L + r1 * LM, M);
+      else fold_mac<LPR, 0>(a0, a1, Rc, L + r0 * LM, L + r1 * LM, M);
+      // column maxima over the group's rows: this lane's rows, the lanes of other rows, the other warps
+      float cm[16];
+#pragma unroll
+      for (int p = 0; p < 8; p++) {
+        float m0 = 0.f, m1 = 0.f;
+        if (v0) { m0 = fabsf(a0[p].x); m1 = fabsf(a0[p].y); }
+        if (v1) { m0 = fmaxf(m0, fabsf(a1[p].x)); m1 = fmaxf(m1, fabsf(a1[p].y)); }
+        for (int o = LPR; o < 32; o <<= 1) {
+          m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
+          m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, o));
+        }
+        cm[2 * p] = m0;
+        cm[2 * p + 1] = m1;
+      }
+      if (!sync()) return false;                      // cmax free (the previous iteration's readers are done)
+      if (rl == 0) {
+#pragma unroll
+        for (int j = 0; j < 16; j++) cmax[warp * DK + c * 16 + j] = cm[j];
+      }
+      if (!sync()) return false;
+      float* ssc = cmax + NW * DK;                    // scale of every column of every group in flight
+      for (int e = tid; e < gpi * DK; e += NT) {
+        const int gi = e / DK, k = e - gi * DK;
+        float am = 0.f;
+        for (int w = 0; w < wpg; w++) am = fmaxf(am, cmax[(gi * wpg + w) * DK + k]);
+        const float sc = fp16_scale(am, QMAX);
+        ssc[gi * DK + k] = sc;
+        const int gvr = it * gpi + gi;
+        if (gvr * G < DV) SCh[gvr * DK + k] = f2h(sc);
+      }
+      if (!sync()) return false;
+      const float* myssc = ssc + (warp / wpg) * DK + c * 16;
+      if (v0) store_packed16<BITS>(Sh + (long long)r0 * ROWB + c * CB,
+                                   round_exact_pack_cols<BITS>(a0[0], a0[1], a0[2], a0[3], a0[4], a0[5], a0[6], a0[7], myssc));
+      if (v1) store_packed16<BITS>(Sh + (long long)r1 * ROWB + c * CB,
+                                   round_exact_pack_cols<BITS>(a1[0], a1[1], a1[2], a1[3], a1[4], a1[5], a1[6], a1[7], myssc));
+    }
+    return true;
+  }
+}
+
+}  // namespace sqb

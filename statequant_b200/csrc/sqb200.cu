@@ -6,8 +6,12 @@
 
 #include "../../include/statequant_b200.h"
 #include "delta_step.cuh"
-#include "step_tma.cuh"
+#include "launchers.h"
 #include "gga.cuh"
+
+namespace sqb {
+__device__ int g_step_status[4];   // [0]: number of CTAs whose bounded wait ran out (0 in a healthy run)
+}
 
 namespace {
 
@@ -63,7 +67,20 @@ int check_state(const sqb_state_t* st, int kind, int* lpr_log2) {
   return 0;
 }
 
+int* status_ptr() {
+  static thread_local int* ptr[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int*& p = ptr[dev & 63];
+  if (!p) {
+    void* q = nullptr;
+    if (cudaGetSymbolAddress(&q, sqb::g_step_status) == cudaSuccess) p = static_cast<int*>(q);
+  }
+  return p;
+}
+
 void fill_state(sqb::StepArgs& a, const sqb_state_t* st, int lpr_log2) {
+  a.status = status_ptr();
   a.S = static_cast<uint8_t*>(st->S); a.SC = static_cast<uint8_t*>(st->SC);
   a.KB = static_cast<uint8_t*>(st->KB); a.KBS = static_cast<uint8_t*>(st->KBS);
   a.UB = static_cast<uint8_t*>(st->UB); a.UBS = static_cast<uint8_t*>(st->UBS);
@@ -97,7 +114,7 @@ int launch_one(const sqb::StepArgs& a, cudaStream_t stream) {
 }
 
 // ---- the staged kernel (integer states, d_k 64 or 128, everything 16-byte aligned) -----------------------------------
-bool tma_ok(const sqb::StepArgs& a, int bits, bool axk) {
+bool tma_ok(const sqb::StepArgs& a, int bits, bool axk, bool kda) {
   if (bits != 4 && bits != 8) return false;
   if (a.DK != 64 && a.DK != 128) return false;
   if (!a.per_key_head && a.HV != a.HK) return false;      // q, k per value head: generic kernel
@@ -116,53 +133,45 @@ bool tma_ok(const sqb::StepArgs& a, int bits, bool axk) {
   if (codes_b % 16 || scales_b % 16 || ub_b % 16 || kb_b % 16) return false;
   auto a16 = [](const void* p, long long s) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && s % 16 == 0; };
   if (!a16(a.S, a.sS) || !a16(a.SC, a.sSC) || !a16(a.UB, a.sUB) || !a16(a.KB, a.sKB)) return false;
+  if (kda && (!a16(a.GB, a.sGB) || !a16(a.GCUR, a.sGC))) return false;
   return true;
 }
 
-template <int KIND, int BITS, bool AXK, int LPR>
-int launch_tma_one(const sqb::StepArgs& a, cudaStream_t stream) {
-  auto kern = sqb::step_tma_kernel<KIND, BITS, AXK, LPR>;
-  const int gqa = a.HV / a.HK;
-  int nst = gqa < 2 ? gqa : (KIND == sqb::K_M2 && gqa >= 3 ? 3 : 2);
-  sqb::Smem2 plan = sqb::smem2_plan(KIND, BITS, AXK, a.group, a.DK, a.DV, a.M, a.qbuf, nst, gqa);
-  while (nst > 1 && plan.total > 100 * 1024) {
-    nst--;
-    plan = sqb::smem2_plan(KIND, BITS, AXK, a.group, a.DK, a.DV, a.M, a.qbuf, nst, gqa);
-  }
-  if (plan.total > 220 * 1024) return 1;    // does not fit: the caller falls back to the generic kernel
-  static std::atomic<int> configured{0};
-  if (plan.total > configured.load()) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.total);
-    if (e != cudaSuccess) return fail(SQB_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    configured.store(plan.total);
-  }
-  const long long ctas = static_cast<long long>(a.rows) * a.HK;
-  if (ctas > 2147483647LL) return fail(SQB_EINVAL, "rows * hk = %lld exceeds the grid limit", ctas);
-  kern<<<static_cast<unsigned>(ctas), sqb::NT, plan.total, stream>>>(a, nst);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return fail(SQB_ECUDA, "kernel launch: %s", cudaGetErrorString(e));
-  g_launches.fetch_add(1, std::memory_order_relaxed);
-  return 0;
-}
+int g_force_generic = 0;     // set through sqb_set_option (tests time and check every kernel)
+int g_kernel_path = 0;       // 0: best available; 1: generic; 2: staged (one CTA per tile); 3: persistent pipeline
 
+// launchers of the staged and pipelined kernels live in their own translation units (launchers.h)
+int sub_rc(int rc) {
+  if (rc >= 0) {
+    if (rc == 0) g_launches.fetch_add(1, std::memory_order_relaxed);
+    return rc;
+  }
+  return fail(SQB_ECUDA, "kernel launch: %s", cudaGetErrorString(static_cast<cudaError_t>(-rc - 1000)));
+}
 template <int KIND>
 int launch_tma(const sqb::StepArgs& a, int bits, bool axk, cudaStream_t stream) {
-  const bool d128 = a.DK == 128;
-  if (bits == 4) {
-    if (axk) return d128 ? launch_tma_one<KIND, 4, true, 8>(a, stream) : launch_tma_one<KIND, 4, true, 4>(a, stream);
-    return d128 ? launch_tma_one<KIND, 4, false, 8>(a, stream) : launch_tma_one<KIND, 4, false, 4>(a, stream);
-  }
-  if (axk) return d128 ? launch_tma_one<KIND, 8, true, 8>(a, stream) : launch_tma_one<KIND, 8, true, 4>(a, stream);
-  return d128 ? launch_tma_one<KIND, 8, false, 8>(a, stream) : launch_tma_one<KIND, 8, false, 4>(a, stream);
+  if (KIND == sqb::K_GDN) return sub_rc(sqb::launch_staged_gdn(a, bits, axk, stream));
+  if (KIND == sqb::K_M2) return sub_rc(sqb::launch_staged_m2(a, bits, axk, stream));
+  return sub_rc(sqb::launch_staged_kda(a, bits, axk, stream));
 }
-
-int g_force_generic = 0;     // set through sqb_set_option (tests time and check both kernels)
+template <int KIND>
+int launch_pipe(const sqb::StepArgs& a, int bits, bool axk, cudaStream_t stream) {
+  if (KIND == sqb::K_GDN) return sub_rc(sqb::launch_pipe_gdn(a, bits, axk, stream));
+  if (KIND == sqb::K_M2) return sub_rc(sqb::launch_pipe_m2(a, bits, axk, stream));
+  return sub_rc(sqb::launch_pipe_kda(a, bits, axk, stream));
+}
 
 template <int KIND>
 int launch(const sqb::StepArgs& a, int bits, bool axk, cudaStream_t stream) {
-  if (!g_force_generic && tma_ok(a, bits, axk)) {
-    const int rc = launch_tma<KIND>(a, bits, axk, stream);
-    if (rc <= 0) return rc;
+  const int path = g_force_generic ? 1 : g_kernel_path;
+  if (path != 1 && tma_ok(a, bits, axk, KIND == sqb::K_KDA)) {
+    // the staged and the pipelined kernel only append on a slot's m-th token; the fold launch that follows them
+    // rewrites the state of the heads whose buffer is full (the generic kernel folds inside its own launch)
+    int rc = 1;
+    if (path == 0 || path == 3) rc = launch_pipe<KIND>(a, bits, axk, stream);
+    if (rc > 0) rc = launch_tma<KIND>(a, bits, axk, stream);
+    if (rc < 0) return rc;
+    if (rc == 0) return sub_rc(sqb::launch_fold(KIND, a, bits, axk, stream));
   }
   switch (bits) {
     case 4: return axk ? launch_one<KIND, 4, true>(a, stream) : launch_one<KIND, 4, false>(a, stream);
@@ -188,6 +197,7 @@ int64_t sqb_launch_count(void) { return g_launches.load(); }
 
 int sqb_set_option(const char* name, int value) {
   if (name && !strcmp(name, "force_generic_kernel")) { g_force_generic = value; return 0; }
+  if (name && !strcmp(name, "kernel_path") && value >= 0 && value <= 3) { g_kernel_path = value; return 0; }
   return fail(SQB_EINVAL, "unknown option");
 }
 

@@ -21,8 +21,6 @@
 
 namespace sqb {
 
-__device__ int g_step_status[4];   // [0]: number of CTAs whose copy-completion wait ran out (0 in a healthy run)
-
 // ---- mbarrier / bulk-copy wrappers ---------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
@@ -40,13 +38,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after about a second, records it and lets the caller bail out.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {       // never blocks
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;     // a wait gives up after one second
+// Bounded wait: gives up after WAIT_LIMIT_NS (try_wait itself may block for a hardware-defined time, so the bound is
+// on the clock, not on the iteration count), records nothing itself and lets the caller bail out.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (int it = 0; it < (1 << 22); it++) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (int it = 0;; it++) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (it > 64) __nanosleep(200);
+    if (it > 64) __nanosleep(100);
+    if ((it & 15) == 15 && global_ns() - t0 > WAIT_LIMIT_NS) return false;
   }
-  return false;
 }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -66,21 +82,15 @@ __host__ __device__ inline Smem2 smem2_plan(int kind, int bits, int axk, int gro
   const int bsz = qbuf ? 1 : 2;
   const int lpr = DK / 16;
   s.rdk = lpr * 20;                 // 16 columns + 4 floats of padding per lane chunk
-  s.ldv = DV + 32 / lpr;
+  s.ldv = fold_lm(M);               // floats per row of the value-major L tile
   s.codes_b = DV * DK * bits / 8;
   s.scales_b = al16i((axk ? DV * (DK / group) : (DV / group) * DK) * 2);
   s.ub_b = al16i(M * DV * bsz);
   s.stage_bytes = s.codes_b + s.scales_b + s.ub_b;
-  const int rl_bytes = al16i((M * s.rdk + M * s.ldv) * 4);     // fold tiles R [M][rdk], L [M][ldv]
   int o = 0;
   s.bars = o; o += 64;
   s.stage0 = o; o += nst * s.stage_bytes;
-  // a fold step keeps a single stage in flight, so its R / L tiles can live in the last stage's buffer
-  if (nst >= 2 && rl_bytes <= s.stage_bytes) {
-    s.rl = s.stage0 + (nst - 1) * s.stage_bytes;
-  } else {
-    s.rl = o; o += rl_bytes;
-  }
+  s.rl = 0;
   s.kb = o; o += al16i(M * DK * bsz);
   s.gbt = o; o += (kind == K_KDA ? M * DK * 4 : 0);
   s.f0 = o;
@@ -89,7 +99,7 @@ __host__ __device__ inline Smem2 smem2_plan(int kind, int bits, int axk, int gro
   s.xk = f; f += DK;
   s.ga = f; f += (kind == K_KDA ? DK : 0);
   s.ae = f; f += (kind == K_KDA ? DK : 0);
-  s.krnd = f; f += DK;
+  s.krnd = f;
   s.us = f; f += gqa * DV;
   s.Dq = f; f += 32;
   s.Dk = f; f += 32;
@@ -98,7 +108,7 @@ __host__ __device__ inline Smem2 smem2_plan(int kind, int bits, int axk, int gro
   s.ubs = f; f += gqa * M;
   s.red = f; f += gqa * NW;
   s.misc = f; f += 8;
-  s.cmax = f; f += (axk ? 0 : 2 * NW * DK);
+  s.cmax = f;
   s.total = s.f0 + ((f + 3) & ~3) * 4;
   return s;
 }
@@ -133,13 +143,13 @@ __device__ __forceinline__ float presc(int j) {
   return 1.0f;
 }
 
-// 16 rounded codes, held as the low mantissa bits of t (see round_fast), packed and stored: 8 bytes of int4 or 16
-// bytes of int8.
+// 16 rounded codes, held as the low mantissa bits of t (see round_fast), packed: 8 bytes of int4 (x, y of the result)
+// or 16 bytes of int8.
 template <int BITS>
-__device__ __forceinline__ void store_codes16(uint8_t* p, const float2 (&t)[8]) {
+__device__ __forceinline__ uint4 pack_codes16(const float2 (&t)[8]) {
+  uint4 o = make_uint4(0u, 0u, 0u, 0u);
+  uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
   if constexpr (BITS == 4) {
-    uint2 o;
-    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
     for (int w = 0; w < 2; w++) {
       uint32_t x = 0;
@@ -150,18 +160,54 @@ __device__ __forceinline__ void store_codes16(uint8_t* p, const float2 (&t)[8]) 
       }
       ow[w] = x;
     }
-    *reinterpret_cast<uint2*>(p) = o;
   } else {
-    uint4 o;
-    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
     for (int w = 0; w < 4; w++) {
       const uint32_t lo = __byte_perm(__float_as_uint(t[2 * w].x), __float_as_uint(t[2 * w].y), 0x0040);
       const uint32_t hi = __byte_perm(__float_as_uint(t[2 * w + 1].x), __float_as_uint(t[2 * w + 1].y), 0x0040);
       ow[w] = __byte_perm(lo, hi, 0x5410);
     }
-    *reinterpret_cast<uint4*>(p) = o;
   }
+  return o;
+}
+template <int BITS>
+__device__ __forceinline__ void store_packed16(uint8_t* p, const uint4& o) {
+  if constexpr (BITS == 4) *reinterpret_cast<uint2*>(p) = make_uint2(o.x, o.y);
+  else *reinterpret_cast<uint4*>(p) = o;
+}
+template <int BITS>
+__device__ __forceinline__ void store_codes16(uint8_t* p, const float2 (&t)[8]) {
+  store_packed16<BITS>(p, pack_codes16<BITS>(t));
+}
+// The exact path of the rounding, out of line (it is rare where round_fast applies, and long): sixteen values against
+// one scale, or against sixteen scales in shared memory.
+template <int BITS>
+__device__ __noinline__ uint4 round_exact_pack(float2 a0, float2 a1, float2 a2, float2 a3, float2 a4, float2 a5,
+                                               float2 a6, float2 a7, float sc) {
+  constexpr float QMAX = BITS == 4 ? 7.0f : 127.0f;
+  constexpr float MB = BITS == 4 ? MAGIC + 8.0f : MAGIC;
+  const float2 a[8] = {a0, a1, a2, a3, a4, a5, a6, a7};
+  float2 t[8];
+#pragma unroll
+  for (int p = 0; p < 8; p++) {
+    t[p].x = rq_exact(a[p].x, sc, QMAX) + MB;
+    t[p].y = rq_exact(a[p].y, sc, QMAX) + MB;
+  }
+  return pack_codes16<BITS>(t);
+}
+template <int BITS>
+__device__ __noinline__ uint4 round_exact_pack_cols(float2 a0, float2 a1, float2 a2, float2 a3, float2 a4, float2 a5,
+                                                    float2 a6, float2 a7, const float* sc) {
+  constexpr float QMAX = BITS == 4 ? 7.0f : 127.0f;
+  constexpr float MB = BITS == 4 ? MAGIC + 8.0f : MAGIC;
+  const float2 a[8] = {a0, a1, a2, a3, a4, a5, a6, a7};
+  float2 t[8];
+#pragma unroll
+  for (int p = 0; p < 8; p++) {
+    t[p].x = rq_exact(a[p].x, sc[2 * p], QMAX) + MB;
+    t[p].y = rq_exact(a[p].y, sc[2 * p + 1], QMAX) + MB;
+  }
+  return pack_codes16<BITS>(t);
 }
 
 // Transposing butterfly over the LPR lanes of a row group: in v[j] = this lane's partial for pass j; out: the full
@@ -199,6 +245,11 @@ __device__ __forceinline__ uint32_t round4_i8(const float* x, float s, float r, 
   return __byte_perm(lo, hi, 0x5410);
 }
 
+}  // namespace sqb
+#include "fold_rows.cuh"
+#include "pass_rows.cuh"
+namespace sqb {
+
 #ifndef SQB_MINB
 #define SQB_MINB 4
 #endif
@@ -213,7 +264,6 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
   constexpr bool TWO = KIND != K_M2;
   constexpr bool VDEC = KIND == K_KDA;
   constexpr float QMAX = BITS == 4 ? 7.0f : 127.0f;
-  constexpr int PPW = 2;                         // fold: rows a lane accumulates at a time
 
   extern __shared__ __align__(128) uint8_t smraw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -266,12 +316,9 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
   uint64_t* bars = reinterpret_cast<uint64_t*>(smraw + P.bars);
   uint8_t* kbt = smraw + P.kb;
   float* fsm = reinterpret_cast<float*>(smraw + P.f0);
-  float *xq = fsm + P.xq, *xk = fsm + P.xk, *ga = fsm + P.ga, *ae = fsm + P.ae, *krnd = fsm + P.krnd, *us = fsm + P.us,
+  float *xq = fsm + P.xq, *xk = fsm + P.xk, *ga = fsm + P.ga, *ae = fsm + P.ae, *us = fsm + P.us,
         *Dq = fsm + P.Dq, *Dk = fsm + P.Dk, *hd = fsm + P.hd, *decf = fsm + P.decf, *ubsf = fsm + P.ubs,
-        *red = fsm + P.red, *misc = fsm + P.misc, *cmax = fsm + P.cmax;
-  float* R = reinterpret_cast<float*>(smraw + P.rl);
-  const int RDK = P.rdk, LDV = P.ldv;
-  float* L = R + M * RDK;
+        *red = fsm + P.red, *misc = fsm + P.misc;
   const float* gbt = reinterpret_cast<const float*>(smraw + P.gbt);
   const int bsz = A.qbuf ? 1 : 2;
   const int NG = AXK ? DK / G : 1;
@@ -352,8 +399,8 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
       xk[lane * CW + j] = kr[j];
       if (VDEC) { ga[lane * CW + j] = gnr[j]; ae[lane * CW + j] = expf(gnr[j]); }
     }
-    // the remaining stages: a fold step keeps only one in flight (the last stage's buffer holds the fold tiles)
-    if (lane == 0 && n0 != M - 1) {
+    // the remaining stages
+    if (lane == 0) {
       for (int s = 1; s < nst && s < gqa; s++) issue_stage(s, h0 + s);
     }
     d = warp_sum(d);
@@ -367,7 +414,6 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
       for (int j = 0; j < CW; j++) {
         const float cc = rq_exact(kr[j], ksc, 127.0f);
         w |= (static_cast<uint32_t>(static_cast<int>(cc)) & 0xFFu) << (8 * j);
-        krnd[lane * CW + j] = cc * ksc;
       }
       if (CW == 4) *reinterpret_cast<uint32_t*>(KBh + (long long)n0 * DK + lane * 4) = w;
       else *reinterpret_cast<unsigned short*>(KBh + (long long)n0 * DK + lane * 2) = static_cast<unsigned short>(w);
@@ -377,7 +423,6 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
       for (int j = 0; j < CW; j++) {
         const unsigned short bb = f2bf(kr[j]);
         reinterpret_cast<unsigned short*>(KBh)[(long long)n0 * DK + lane * CW + j] = bb;
-        krnd[lane * CW + j] = bf2f(bb);
       }
     }
     __syncwarp();                              // xq, xk (ga) written by this warp are read below
@@ -484,12 +529,10 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
   }
   __syncthreads();
   if (misc[2] != 0.f) {
-    if (tid == 0) atomicAdd(&g_step_status[0], 1);
+    if (tid == 0) atomicAdd(&A.status[0], 1);
     return;
   }
   const float kq = misc[0];
-  const bool fold_step = __float_as_int(misc[1]) == M - 1;
-  const int nsteff = fold_step ? 1 : nst;                // stages actually in flight
 
   // ---- the value heads of this key head ---------------------------------------------------------------------------
   const int RW = DV / NW;
@@ -512,11 +555,10 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
     }
   };
   if (AXK) load_slice(nullptr);
-  bool r_built = false;
   for (int hi = 0; hi < gqa; hi++) {
     const int h = h0 + hi;
-    const int s = hi % nsteff;
-    const uint32_t parity = (hi / nsteff) & 1;
+    const int s = hi % nst;
+    const uint32_t parity = (hi / nst) & 1;
     uint8_t* st = smraw + P.stage0 + s * P.stage_bytes;
     const uint8_t* codes = st;
     const unsigned short* scs = reinterpret_cast<const unsigned short*>(st + P.codes_b);
@@ -535,45 +577,12 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
     int cur_gv = -1;
     float umax = 0.f;
     for (int p0 = 0; p0 < npass; p0 += LPR) {
-      float pq[LPR], pk[LPR];
       const bool own = p0 + c < npass;                         // this lane finishes the row of pass p0 + c
       const int orow_i = warp * RW + (own ? p0 + c : 0) * RPP + rl;
       const float vt = ldf(A.v + (long long)b * A.sv, A.dt_v, (long long)h * DV + orow_i);
-#pragma unroll
-      for (int p = 0; p < LPR; p++) {
-        pq[p] = 0.f;
-        pk[p] = 0.f;
-        if (p0 + p < npass) {                                  // uniform
-          const int row = warp * RW + (p0 + p) * RPP + rl;
-          if (!AXK) {
-            const int gv = (warp * RW + (p0 + p) * RPP) / G;   // uniform over the warp: G is a multiple of RPP
-            if (gv != cur_gv) { cur_gv = gv; load_slice(scs + gv * DK); }
-          }
-          float2 f[8];
-          decode16<BITS>(codes + row * ROWB + c * CB, f);
-          float2 aq0 = make_float2(0.f, 0.f), aq1 = aq0, ak0 = aq0, ak1 = aq0;
-#pragma unroll
-          for (int j = 0; j < 8; j += 2) {
-            aq0 = __ffma2_rn(f[j], vq[j], aq0);
-            aq1 = __ffma2_rn(f[j + 1], vq[j + 1], aq1);
-            if (TWO) {
-              ak0 = __ffma2_rn(f[j], vk[j], ak0);
-              ak1 = __ffma2_rn(f[j + 1], vk[j + 1], ak1);
-            }
-          }
-          float sq_ = (aq0.x + aq0.y) + (aq1.x + aq1.y);
-          float sk_ = (ak0.x + ak0.y) + (ak1.x + ak1.y);
-          if (AXK) {
-            const float sc = h2f(scs[row * NG + gl]);
-            sq_ = sq_ * sc;
-            sk_ = sk_ * sc;
-          }
-          pq[p] = sq_;
-          pk[p] = sk_;
-        }
-      }
-      float tq = transpose_reduce<LPR>(pq, c);
-      float tk = TWO ? transpose_reduce<LPR>(pk, c) : 0.f;
+      float tq, tk;
+      pass_rows<BITS, AXK, TWO, LPR>(codes, scs, vq, vk, p0, npass, warp * RW, G, NG, gl, c, rl, cur_gv,
+                                     [&](int gv) { load_slice(scs + gv * DK); }, tq, tk);
       if (own) {
         const int row = orow_i;
         if (!VDEC) { tq = alpha * tq; tk = alpha * tk; }
@@ -603,234 +612,16 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
     }
     umax = warp_max(umax);
     if (lane == 0) red[hi * NW + warp] = umax;
-    if (!fold_step) {
-      // appends are done after the last head; a stage that is needed again is refilled once every warp has read it
-      if (hi + nst < gqa) {
-        __syncthreads();
-        if (tid == 0) {
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          issue_stage(s, h + nst);
-        }
-      }
-      continue;
-    }
-
-    // ================= fold step: append and fold this head before going on =======================================
-    __syncthreads();                                           // u of this head complete
-    if (misc[2] != 0.f) break;
-    const bool full = n == M - 1;
-    uint8_t* UBh = UBseq + (long long)h * M * DV * bsz;
-    float* GBh = GBseq + (long long)h * M * (VDEC ? DK : 1);
-    float* GCh = GCseq + (long long)h * (VDEC ? DK : 1);
-    if (warp == 0) {
-      if (A.qbuf) {
-        const float usc = fp16_scale(fmaxf(fmaxf(red[hi * NW], red[hi * NW + 1]), fmaxf(red[hi * NW + 2], red[hi * NW + 3])), 127.0f);
-        const bool fast_ok = usc >= FP16_MIN_NORMAL;
-        const float r = __fdiv_rn(1.0f, usc);
-        for (int e = lane; e < DV / 4; e += 32) {
-          float dq4[4];
-          const uint32_t w = round4_i8(usb + 4 * e, usc, r, fast_ok, dq4);
-          *reinterpret_cast<uint32_t*>(UBh + (long long)n * DV + 4 * e) = w;
-          if (full) { L[n * LDV + 4 * e] = dq4[0]; L[n * LDV + 4 * e + 1] = dq4[1]; L[n * LDV + 4 * e + 2] = dq4[2]; L[n * LDV + 4 * e + 3] = dq4[3]; }
-        }
-        if (lane == 0) UBSseq[h * M + n] = f2h(usc);
-      } else {
-        for (int e = lane; e < DV / 2; e += 32) {
-          const unsigned short b0 = f2bf(usb[2 * e]), b1 = f2bf(usb[2 * e + 1]);
-          if (full) { L[n * LDV + 2 * e] = bf2f(b0); L[n * LDV + 2 * e + 1] = bf2f(b1); }
-          *reinterpret_cast<uint32_t*>(UBh + ((long long)n * DV + 2 * e) * 2) = b0 | (static_cast<uint32_t>(b1) << 16);
-        }
-      }
-      if (VDEC) {
-        for (int t = lane; t < DK; t += 32) {
-          GBh[(long long)n * DK + t] = ga[t];
-          GCh[t] = full ? 0.f : ga[t];
-        }
-      } else if (lane == 0) {
-        GBh[n] = gnew;
-        *GCh = full ? 0.f : gnew;
-      }
-      if (lane == 0) NPseq[h] = full ? 0 : n + 1;
-    }
-    if (full) {
-      // ---- fold: S = decay * S_0 + sum_i L_i R_i^T in slot order, re-rounded in place ----
-      const float alphan = VDEC ? 1.0f : expf(gnew);
-      // R: the keys of all slots (KDA: times their decay ratio), once per key head; slot M-1 is the new key
-      if (!r_built) {
-        for (int e = tid; e < M * DK; e += NT) {
-          const int i = e / DK, k = e - i * DK;
-          float kv;
-          if (i == M - 1) {
-            kv = krnd[k];
-          } else {
-            if (A.qbuf) kv = static_cast<float>(reinterpret_cast<const int8_t*>(kbt)[e]) * h2f(KBSh[i]);
-            else kv = bf2f(reinterpret_cast<const unsigned short*>(kbt)[e]);
-            if (VDEC) kv = kv * expf(ga[k] - gbt[e]);
-          }
-          R[i * RDK + (k / 16) * 20 + (k % 16)] = kv;
-        }
-        r_built = true;
-      }
-      // L: the buffered values of slots 0..M-2, times their decay (GDN, Mamba2); slot M-1 is written by warp 0 above
-      for (int e = tid; e < (M - 1) * DV; e += NT) {
-        const int i = e / DV, v = e - i * DV;
-        float ub;
-        if (A.qbuf) ub = static_cast<float>(reinterpret_cast<const int8_t*>(ubt)[e]) * usf[i];
-        else ub = bf2f(reinterpret_cast<const unsigned short*>(ubt)[e]);
-        if (!VDEC) ub = expf(gnew - GBh[i]) * ub;
-        L[i * LDV + v] = ub;
-      }
+    // appends are done after the last head; a stage that is needed again is refilled once every warp has read it
+    if (hi + nst < gqa) {
       __syncthreads();
-
-      int wpg = NW, ppw = PPW, gpi = 1;
-      if (!AXK) {
-        wpg = min(NW, G / RPP);
-        ppw = G / (RPP * wpg);
-        gpi = NW / wpg;
+      if (tid == 0) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        issue_stage(s, h + nst);
       }
-      const int BR = AXK ? NW * PPW * RPP : gpi * G;
-      const int niter = (DV + BR - 1) / BR;
-      unsigned short* SCh = SCseq + (long long)h * scn;
-      uint8_t* Sh = Sseq + (long long)h * P.codes_b;
-      for (int it = 0; it < niter; it++) {
-        int rows[PPW];
-        bool rv[PPW];
-        float2 acc[PPW][8];
-        const int gvrow = AXK ? 0 : it * gpi + warp / wpg;
-#pragma unroll
-        for (int pp = 0; pp < PPW; pp++) {
-          int row;
-          if (AXK) row = it * BR + warp * (PPW * RPP) + pp * RPP + rl;
-          else row = gvrow * G + (warp % wpg) * (ppw * RPP) + pp * RPP + rl;
-          rv[pp] = pp < ppw && row < DV;
-          rows[pp] = rv[pp] ? row : 0;
-          decode16<BITS>(codes + rows[pp] * ROWB + c * CB, acc[pp]);
-          if (AXK) {
-            const float sc = h2f(scs[rows[pp] * NG + gl]);
-#pragma unroll
-            for (int p = 0; p < 8; p++)
-              acc[pp][p] = __fmul2_rn(acc[pp][p], make_float2(sc * presc<BITS>(2 * p), sc * presc<BITS>(2 * p + 1)));
-          }
-        }
-        if (!AXK) {
-          const bool gvalid = gvrow * G < DV;
-#pragma unroll
-          for (int p = 0; p < 8; p++) {
-            const int k0 = c * 16 + 2 * p;
-            const float s0 = gvalid ? h2f(scs[gvrow * DK + k0]) : 0.f, s1 = gvalid ? h2f(scs[gvrow * DK + k0 + 1]) : 0.f;
-            const float2 s2 = make_float2(s0 * presc<BITS>(2 * p), s1 * presc<BITS>(2 * p + 1));
-#pragma unroll
-            for (int pp = 0; pp < PPW; pp++) acc[pp][p] = __fmul2_rn(acc[pp][p], s2);
-          }
-        }
-#pragma unroll
-        for (int p = 0; p < 8; p++) {
-          float2 d2 = make_float2(alphan, alphan);
-          if (VDEC) d2 = make_float2(ae[c * 16 + 2 * p], ae[c * 16 + 2 * p + 1]);
-#pragma unroll
-          for (int pp = 0; pp < PPW; pp++) acc[pp][p] = __fmul2_rn(acc[pp][p], d2);
-        }
-        for (int i = 0; i < M; i++) {
-          float2 l2[PPW];
-#pragma unroll
-          for (int pp = 0; pp < PPW; pp++) {
-            const float l = L[i * LDV + rows[pp]];
-            l2[pp] = make_float2(l, l);
-          }
-          const float4* rrow = reinterpret_cast<const float4*>(R + i * RDK + c * 20);
-#pragma unroll
-          for (int j4 = 0; j4 < 4; j4++) {
-            const float4 kr4 = rrow[j4];
-            const float2 ka = make_float2(kr4.x, kr4.y), kb2 = make_float2(kr4.z, kr4.w);
-#pragma unroll
-            for (int pp = 0; pp < PPW; pp++) {
-              acc[pp][2 * j4] = __ffma2_rn(l2[pp], ka, acc[pp][2 * j4]);
-              acc[pp][2 * j4 + 1] = __ffma2_rn(l2[pp], kb2, acc[pp][2 * j4 + 1]);
-            }
-          }
-        }
-        // re-round
-        constexpr float MB = BITS == 4 ? MAGIC + 8.0f : MAGIC;
-        if constexpr (AXK) {
-          const int lpg = G / 16;
-#pragma unroll
-          for (int pp = 0; pp < PPW; pp++) {
-            float am = 0.f;
-#pragma unroll
-            for (int p = 0; p < 8; p++) am = fmaxf(am, fmaxf(fabsf(acc[pp][p].x), fabsf(acc[pp][p].y)));
-            for (int o = 1; o < lpg; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-            const float sc = fp16_scale(am, QMAX);
-            if (!rv[pp]) continue;
-            if ((c & (lpg - 1)) == 0) SCh[rows[pp] * NG + gl] = f2h(sc);
-            float2 t[8];
-            bool ok = sc >= FP16_MIN_NORMAL && round_fast<8>(acc[pp], sc, __fdiv_rn(1.0f, sc), MB, t);
-            if (!ok) {
-#pragma unroll
-              for (int p = 0; p < 8; p++) {
-                t[p].x = rq_exact(acc[pp][p].x, sc, QMAX) + MB;
-                t[p].y = rq_exact(acc[pp][p].y, sc, QMAX) + MB;
-              }
-            }
-            store_codes16<BITS>(Sh + (long long)rows[pp] * ROWB + c * CB, t);
-          }
-        } else {
-          // column maxima over the group's rows: this lane's passes, the lanes of other rows, the other warps
-          float cm[16];
-#pragma unroll
-          for (int p = 0; p < 8; p++) {
-            float m0 = 0.f, m1 = 0.f;
-#pragma unroll
-            for (int pp = 0; pp < PPW; pp++) {
-              if (rv[pp]) { m0 = fmaxf(m0, fabsf(acc[pp][p].x)); m1 = fmaxf(m1, fabsf(acc[pp][p].y)); }
-            }
-            for (int o = LPR; o < 32; o <<= 1) {
-              m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
-              m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, o));
-            }
-            cm[2 * p] = m0;
-            cm[2 * p + 1] = m1;
-          }
-          __syncthreads();
-          if (rl == 0) {
-#pragma unroll
-            for (int j = 0; j < 16; j++) cmax[warp * DK + c * 16 + j] = cm[j];
-          }
-          __syncthreads();
-          // scale of every column of every group in flight, one column per thread
-          float* ssc = cmax + NW * DK;
-          for (int e = tid; e < gpi * DK; e += NT) {
-            const int gi = e / DK, k = e - gi * DK;
-            float am = 0.f;
-            for (int w = 0; w < wpg; w++) am = fmaxf(am, cmax[(gi * wpg + w) * DK + k]);
-            const float sc = fp16_scale(am, QMAX);
-            ssc[gi * DK + k] = sc;
-            const int gvr = it * gpi + gi;
-            if (gvr * G < DV) SCh[gvr * DK + k] = f2h(sc);
-          }
-          __syncthreads();
-          const float* myssc = ssc + (warp / wpg) * DK + c * 16;
-#pragma unroll
-          for (int pp = 0; pp < PPW; pp++) {
-            if (!rv[pp]) continue;
-            float2 t[8];
-#pragma unroll
-            for (int p = 0; p < 8; p++) {
-              t[p].x = rq_exact(acc[pp][p].x, myssc[2 * p], QMAX) + MB;
-              t[p].y = rq_exact(acc[pp][p].y, myssc[2 * p + 1], QMAX) + MB;
-            }
-            store_codes16<BITS>(Sh + (long long)rows[pp] * ROWB + c * CB, t);
-          }
-        }
-      }
-    }
-    // ---- the stage is free: refill it with the next head (a fold step keeps one stage in flight) ----
-    __syncthreads();
-    if (tid == 0 && hi + 1 < gqa) {
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      issue_stage(0, h + 1);
     }
   }
-  if (!fold_step) {
+  {
     // ---- append the values of all heads at their slot n: warp w takes heads w, w + 4, ... ----
     __syncthreads();
     if (misc[2] == 0.f) {
@@ -869,7 +660,7 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
       }
     }
   }
-  if (misc[2] != 0.f && tid == 0) atomicAdd(&g_step_status[0], 1);   // a copy never completed (see mbar_wait)
+  if (misc[2] != 0.f && tid == 0) atomicAdd(&A.status[0], 1);   // a copy never completed (see mbar_wait)
 }
 
 }  // namespace sqb

@@ -15,15 +15,16 @@ pytestmark = pytest.mark.gpu
 DEV = 'cuda'
 
 
-@pytest.fixture(params=['staged', 'generic'])
+@pytest.fixture(params=['pipeline', 'staged', 'generic'])
 def kernel_path(request):
-    """Both device code paths: the kernel that stages the state through shared memory with bulk async copies
-    (default wherever its alignment and shape conditions hold) and the generic one."""
+    """Every device code path: the persistent producer / consumer pipeline (default wherever its alignment and
+    shape conditions hold), the kernel with one CTA per tile that stages the state through shared memory, and the
+    generic one."""
     from statequant_b200 import _cabi
-    _cabi.set_option('force_generic_kernel', request.param == 'generic')
+    _cabi.set_option('kernel_path', {'generic': 1, 'staged': 2, 'pipeline': 3}[request.param])
     yield request.param
-    _cabi.set_option('force_generic_kernel', 0)
-    assert _cabi.device_status() == 0, 'a bulk-copy wait timed out on the device'
+    _cabi.set_option('kernel_path', 0)
+    assert _cabi.device_status() == 0, 'a bounded wait ran out on the device'
 
 
 @pytest.mark.parametrize('name', list(CASES))
