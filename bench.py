@@ -227,8 +227,8 @@ def main():
     ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer leg')
     ap.add_argument('--no-cpu', action='store_true', help='skip the CPU-baseline leg')
     ap.add_argument('--eager', action='store_true', help='launch eagerly instead of replaying a CUDA graph')
-    ap.add_argument('--kernel-path', type=int, default=0, choices=[0, 1, 2, 3],
-                    help='0 best kernel for the shape; 1 generic; 2 staged; 3 persistent pipeline (profiling / comparison)')
+    ap.add_argument('--kernel-path', type=int, default=0, choices=[0, 1, 2],
+                    help='0 best kernel for the shape; 1 generic; 2 staged + fold launch (profiling / comparison)')
     args = ap.parse_args()
     global LAYERS
     LAYERS = args.layers

@@ -191,10 +191,10 @@ int sqb_abi_version(void);
 /* number of kernel launches issued by this library in this process (all threads) */
 int64_t sqb_launch_count(void);
 /* tuning / test switches.  "kernel_path" selects the kernel of the decode steps: 0 the best one for the shape
-   (default), 1 the generic kernel (direct loads; any supported shape), 2 the staged kernel (one CTA per batch row and
-   key head, the state staged through shared memory by bulk async copies), 3 the persistent pipeline (a producer warp
-   runs copies and the key-head prologue ahead of four consumer warps).  2 and 3 fall back to 1 for shapes they do not
-   take.  "force_generic_kernel" = 1 is the same as kernel_path 1.  All give the same bytes. */
+   (default), 1 the generic kernel (direct loads, folds inside its own launch; any supported shape), 2 the staged
+   kernel (one CTA per batch row and key head, the state staged through shared memory by bulk async copies) followed
+   by the fold launch, falling back to 1 for shapes it does not take.  "force_generic_kernel" = 1 is the same as
+   kernel_path 1.  All give the same bytes. */
 int sqb_set_option(const char *name, int value);
 /* Device-side health word of the current device (synchronises): the number of CTAs whose wait for a bulk copy ran
    out of its iteration budget since the library was loaded.  0 in a healthy run. */

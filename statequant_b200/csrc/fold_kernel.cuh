@@ -1,6 +1,6 @@
 // The fold as its own launch, right after the step kernel of the same call.
 //
-// On a slot's m-th token the step kernels (staged / pipelined) only append: they leave the head's counter at m
+// On a slot's m-th token the staged step kernel only appends: it leaves the head's counter at m
 // (a value that never survives the call), the running log decay in GCUR and the buffer complete.  This kernel then
 // rewrites the stored state of exactly those heads,
 //     S = exp(gcur) S_0 + sum_i (exp(gcur - G_i) u_i) k_i^T      (KDA: the decay ratio sits on the key, per channel)

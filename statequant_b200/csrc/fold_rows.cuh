@@ -1,4 +1,4 @@
-// The fold of one value head, shared by the staged and the pipelined kernel:
+// The fold of one value head (used by the fold kernel):
 //     S[v][k] = decay * (code[v][k] * scale) + sum_i L[v][i] * R[i][k]      (slot order, one fma.rn per term)
 // re-rounded to codes with fresh scales and written back in place.
 //

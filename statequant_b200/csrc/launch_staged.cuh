@@ -41,4 +41,5 @@ int launch_staged(const StepArgs& a, int bits, bool axk, cudaStream_t stream) {
   return d128 ? launch_staged_one<KIND, 8, false, 8>(a, stream) : launch_staged_one<KIND, 8, false, 4>(a, stream);
 }
 
+
 }  // namespace sqb

@@ -1,5 +1,5 @@
-// Launchers of the staged and the pipelined decode-step kernels, one translation unit per recurrence kind so that
-// they compile in parallel.  Return 0: launched; 1: the kernel does not take this shape (the caller falls back);
+// Launchers of the staged decode-step kernels (one translation unit per recurrence kind, so that they compile in
+// parallel) and of the fold kernel.  Return 0: launched; 1: the kernel does not take this shape (the caller falls back);
 // < 0: -(1000 + cudaError_t).
 #pragma once
 #include <cuda_runtime.h>
@@ -9,9 +9,6 @@ namespace sqb {
 int launch_staged_gdn(const StepArgs& a, int bits, bool axk, cudaStream_t stream);
 int launch_staged_m2(const StepArgs& a, int bits, bool axk, cudaStream_t stream);
 int launch_staged_kda(const StepArgs& a, int bits, bool axk, cudaStream_t stream);
-int launch_pipe_gdn(const StepArgs& a, int bits, bool axk, cudaStream_t stream);
-int launch_pipe_m2(const StepArgs& a, int bits, bool axk, cudaStream_t stream);
-int launch_pipe_kda(const StepArgs& a, int bits, bool axk, cudaStream_t stream);
-// the fold launch that follows a staged / pipelined step (those kernels only append on a slot's m-th token)
+// the fold launch that follows a staged step (that kernel only appends on a slot's m-th token)
 int launch_fold(int kind, const StepArgs& a, int bits, bool axk, cudaStream_t stream);
 }  // namespace sqb

@@ -1,4 +1,4 @@
-// The state pass of one value head, shared by the staged and the pipelined kernel: the dot products of LPR row
+// The state pass of one value head of the staged kernel: the dot products of LPR row
 // passes with the read-out vectors, reduced so that lane c of a row group ends up with the finished sums of pass
 // p0 + c (the row it then owns in the epilogue).
 //

@@ -138,9 +138,9 @@ bool tma_ok(const sqb::StepArgs& a, int bits, bool axk, bool kda) {
 }
 
 int g_force_generic = 0;     // set through sqb_set_option (tests time and check every kernel)
-int g_kernel_path = 0;       // 0: best available; 1: generic; 2: staged (one CTA per tile); 3: persistent pipeline
+int g_kernel_path = 0;       // 0: best available; 1: generic; 2: staged + fold launch
 
-// launchers of the staged and pipelined kernels live in their own translation units (launchers.h)
+// launchers of the staged kernels and of the fold kernel live in their own translation units (launchers.h)
 int sub_rc(int rc) {
   if (rc >= 0) {
     if (rc == 0) g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -154,22 +154,14 @@ int launch_tma(const sqb::StepArgs& a, int bits, bool axk, cudaStream_t stream) 
   if (KIND == sqb::K_M2) return sub_rc(sqb::launch_staged_m2(a, bits, axk, stream));
   return sub_rc(sqb::launch_staged_kda(a, bits, axk, stream));
 }
-template <int KIND>
-int launch_pipe(const sqb::StepArgs& a, int bits, bool axk, cudaStream_t stream) {
-  if (KIND == sqb::K_GDN) return sub_rc(sqb::launch_pipe_gdn(a, bits, axk, stream));
-  if (KIND == sqb::K_M2) return sub_rc(sqb::launch_pipe_m2(a, bits, axk, stream));
-  return sub_rc(sqb::launch_pipe_kda(a, bits, axk, stream));
-}
 
 template <int KIND>
 int launch(const sqb::StepArgs& a, int bits, bool axk, cudaStream_t stream) {
   const int path = g_force_generic ? 1 : g_kernel_path;
   if (path != 1 && tma_ok(a, bits, axk, KIND == sqb::K_KDA)) {
-    // the staged and the pipelined kernel only append on a slot's m-th token; the fold launch that follows them
-    // rewrites the state of the heads whose buffer is full (the generic kernel folds inside its own launch)
-    int rc = 1;
-    if (path == 0 || path == 3) rc = launch_pipe<KIND>(a, bits, axk, stream);
-    if (rc > 0) rc = launch_tma<KIND>(a, bits, axk, stream);
+    // the staged kernel only appends on a slot's m-th token; the fold launch that follows it rewrites the state of
+    // the heads whose buffer is full (the generic kernel folds inside its own launch)
+    const int rc = launch_tma<KIND>(a, bits, axk, stream);
     if (rc < 0) return rc;
     if (rc == 0) return sub_rc(sqb::launch_fold(KIND, a, bits, axk, stream));
   }
@@ -197,7 +189,7 @@ int64_t sqb_launch_count(void) { return g_launches.load(); }
 
 int sqb_set_option(const char* name, int value) {
   if (name && !strcmp(name, "force_generic_kernel")) { g_force_generic = value; return 0; }
-  if (name && !strcmp(name, "kernel_path") && value >= 0 && value <= 3) { g_kernel_path = value; return 0; }
+  if (name && !strcmp(name, "kernel_path") && value >= 0 && value <= 2) { g_kernel_path = value; return 0; }
   return fail(SQB_EINVAL, "unknown option");
 }
 

@@ -4,8 +4,9 @@
 // 16 for Nemotron-H Mamba2, 1 for KDA).  What depends on the key head only -- normalising q and k, the buffered
 // keys and their dot products with q and k, the key appended to the buffer -- is done once per CTA; the heads'
 // codes, scales and buffered values arrive through a ring of shared-memory stages filled by cp.async.bulk
-// (one elected thread issues the copies, an mbarrier per stage counts the bytes), so all of a CTA's state traffic
-// is in flight from its first instructions on, whatever the occupancy.
+// (the lanes of the first warp issue the copies, an mbarrier per stage counts the bytes), so all of a CTA's state
+// traffic is in flight from its first instructions on, whatever the occupancy.  On a slot's m-th token the kernel
+// only appends (the head's counter is left at m); the fold launch that follows (fold_kernel.cuh) rewrites the state.
 //
 // Thread mapping (128 threads): a state row (d_k codes) is cut into 16-column chunks, one per lane: LPR = d_k / 16
 // lanes per row (8 bytes of int4 or 16 bytes of int8 per lane), 32 / LPR rows per warp pass, warp w owns rows

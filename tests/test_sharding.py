@@ -59,7 +59,7 @@ def _worker(rank, world, port, ret):
         dist.all_reduce(total)                           # test-side gather: rows of other ranks are zero
         outs.append(total)
     if rank == 0:
-        ret.put(torch.stack(outs))
+        ret.put(torch.stack(outs).numpy())               # plain bytes: no shared-memory handle that dies with the rank
     dist.destroy_process_group()
 
 
@@ -80,4 +80,4 @@ def test_two_ranks_reproduce_one(tmp_path):
     p.start()
     one = ret1.get(timeout=120)
     p.join(60)
-    assert torch.equal(two, one)
+    assert (two == one).all() and two.shape == one.shape

@@ -15,13 +15,12 @@ pytestmark = pytest.mark.gpu
 DEV = 'cuda'
 
 
-@pytest.fixture(params=['pipeline', 'staged', 'generic'])
+@pytest.fixture(params=['staged', 'generic'])
 def kernel_path(request):
-    """Every device code path: the persistent producer / consumer pipeline (default wherever its alignment and
-    shape conditions hold), the kernel with one CTA per tile that stages the state through shared memory, and the
-    generic one."""
+    """Both device code paths: the staged kernel with its fold launch (default wherever its alignment and shape
+    conditions hold) and the generic kernel, which folds inside its own launch."""
     from statequant_b200 import _cabi
-    _cabi.set_option('kernel_path', {'generic': 1, 'staged': 2, 'pipeline': 3}[request.param])
+    _cabi.set_option('kernel_path', {'generic': 1, 'staged': 2}[request.param])
     yield request.param
     _cabi.set_option('kernel_path', 0)
     assert _cabi.device_status() == 0, 'a bounded wait ran out on the device'
