@@ -122,6 +122,7 @@ class Stack:
         self.dt_bias = torch.randn(HV, generator=gen).to(device)
         self.outs = [torch.empty(batch, HV, DV, dtype=torch.bfloat16, device=device) for _ in range(LAYERS)]
         self.graph = None
+        self.launches_per_step = None
 
     def step(self):
         for l in range(LAYERS):
@@ -145,8 +146,11 @@ class Stack:
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
         self.graph = torch.cuda.CUDAGraph()
+        from statequant_b200 import _cabi
+        n0 = _cabi.launch_count()
         with torch.cuda.graph(self.graph):
             self.step()
+        self.launches_per_step = _cabi.launch_count() - n0     # kernel nodes of the captured step
 
     def timed(self, steps):
         """ms for `steps` graph replays, CUDA events on the launching stream."""
@@ -211,6 +215,18 @@ def cpu_baseline(batch, steps, warmup, preset='int8k'):
         oracle.gdn_step(lay, V, idx, q, k, v, out, DK ** -0.5, gate=(a, b, A_log, dtb))
     dt = time.perf_counter() - t0
     return steps / dt, oracle.num_threads(), dt
+
+
+# DRAM bytes (read + write) per layer-step from ncu captures at batch 256 (profiles/): the step kernel of a non-fold
+# step, and on every 8th step the fold kernel on top; traffic grows in proportion to the batch.
+NCU_TRAFFIC_B256 = {'int8k': (160.0e6 + 5.6e6, 155.8e6 + 84.2e6)}
+
+
+def ncu_traffic(preset, batch):
+    if preset not in NCU_TRAFFIC_B256:
+        return None
+    step, fold = NCU_TRAFFIC_B256[preset]
+    return (step + fold / M) * batch / 256
 
 
 def main():
@@ -308,7 +324,8 @@ def main():
                            'state_gbs_per_gpu': args.batch * state / per_launch_s / 1e9,
                            'bytes_per_slot_layer_step': total}
         if pi == 0:
-            launches = args.steps * LAYERS
+            launches = (stack.launches_per_step * args.steps if stack.launches_per_step is not None
+                        else _cabi.launch_count() - l0)
         if pi == 0 and not args.no_e2e and not args.eager:
             barrier()
             ems, h2d, d2h = run_e2e(stack, max(1, min(args.steps, 32)), 3)
@@ -334,8 +351,11 @@ def main():
         'state_gbs_per_gpu': head['state_gbs_per_gpu'], 'state_frac_of_8tbs': head['state_gbs_per_gpu'] / 8000.0,
         'total_frac_of_8tbs': head['total_gbs_per_gpu'] / 8000.0,
         'roofline': {'bound': 'hbm', 'achieved': head['total_gbs_per_gpu'], 'peak': peak, 'unit': 'GB/s',
-                     'frac': head['total_gbs_per_gpu'] / peak, 'traffic': None, 'peak_source': which,
-                     'kernel': 'delta_step_kernel<GDN>', 'algorithmic_bytes_per_launch': args.batch * head['bytes_per_slot_layer_step']},
+                     'frac': head['total_gbs_per_gpu'] / peak, 'traffic': ncu_traffic(args.preset, args.batch),
+                     'peak_source': which,
+                     'kernel': 'step_tma_kernel<GDN> + fold_kernel: the two launches of one layer-step (one C-ABI call), '
+                               'averaged over the fold period of 8 steps',
+                     'algorithmic_bytes_per_launch': args.batch * head['bytes_per_slot_layer_step']},
         'variants': results, 'clocks': clocks, 'e2e': e2e, 'gpu_launches': launches,
     }
     if world == 1 and not args.no_cpu:

@@ -40,10 +40,27 @@ __device__ __forceinline__ float bf2f(unsigned short b) { return __uint_as_float
 __device__ __forceinline__ unsigned short f2bf(float f) { return __bfloat16_as_ushort(__float2bfloat16_rn(f)); }
 
 // Quantizer scale of a group with absolute maximum amax (see the contract above).
+// x / qmax for the two code ranges in use, without the division: with r = RN(1 / qmax), q0 = RN(x r),
+// q = fma(fma(-qmax, q0, x), r, q0) equals div_rn(x, qmax) for EVERY finite float x in [1e-8, 3e38] when qmax is 127
+// or 7 (checked exhaustively on the host, tests/div_const_check.c); anything else takes the IEEE division.
+__device__ __forceinline__ float div_qmax(float x, float qmax) {
+  if ((qmax == 127.0f || qmax == 7.0f) && x <= 3.0e38f) {
+    const float r = qmax == 127.0f ? 0x1.020408p-7f : 0x1.24924ap-3f;
+    const float q0 = __fmul_rn(x, r);
+    return __fmaf_rn(__fmaf_rn(-qmax, q0, x), r, q0);
+  }
+  return __fdiv_rn(x, qmax);
+}
 __device__ __forceinline__ float fp16_scale(float amax, float qmax) {
-  float s = __fdiv_rn(fmaxf(amax, 1e-8f), qmax);
+  float s = div_qmax(fmaxf(amax, 1e-8f), qmax);
   s = h2f(f2h(s));
   return fmaxf(s, FP16_TINY);
+}
+// 1 / s to within a few ulp (one MUFU instruction); enough wherever the result is verified afterwards (round_fast)
+__device__ __forceinline__ float rcp_approx(float s) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(s));
+  return r;
 }
 // clamp(rint(x / s), +-qmax), exact
 __device__ __forceinline__ float rq_exact(float x, float s, float qmax) {

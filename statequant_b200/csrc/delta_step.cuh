@@ -149,20 +149,21 @@ template <> struct Fmt<32> {   // fp32 values
 // ---- rounding of one chunk ----------------------------------------------------------------------------------------
 // t[j] = fma(x, r, MAGIC + bias) has the rounded quotient in its low mantissa bits; c = t - (MAGIC + bias) is the
 // candidate code, rem = x - c s is exact, and the candidate equals rint(div_rn(x, s)) whenever |rem| stays clear
-// of s/2.  Returns true if every element of the chunk passed that test.
+// of s/2 -- whatever the error of r (a wrong candidate is off by at least one step, so its |rem| exceeds s/2), which
+// is why r may be an approximate reciprocal.  Returns true if every element of the chunk passed that test.
 template <int NP>
 __device__ __forceinline__ bool round_fast(const float2 (&x)[NP], float s, float r, float mb, float2 (&t)[NP]) {
   const float thr = s * 0.49998474f;   // s * (1/2 - 2^-16)
   const float2 r2 = make_float2(r, r), m2 = make_float2(mb, mb), nm2 = make_float2(-mb, -mb), ns2 = make_float2(-s, -s);
-  bool ok = true;
+  float worst = 0.f;
 #pragma unroll
   for (int p = 0; p < NP; p++) {
     t[p] = __ffma2_rn(x[p], r2, m2);
     const float2 c = __fadd2_rn(t[p], nm2);
     const float2 rem = __ffma2_rn(c, ns2, x[p]);
-    ok = ok && (fabsf(rem.x) < thr) && (fabsf(rem.y) < thr);
+    worst = fmaxf(worst, fmaxf(fabsf(rem.x), fabsf(rem.y)));
   }
-  return ok;
+  return worst < thr;
 }
 
 template <int KIND, int BITS, bool AXK>
@@ -698,7 +699,7 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
         bool ok;
         if constexpr (AXK) {
           const float s = sc[pp];
-          ok = s >= FP16_MIN_NORMAL && round_fast<NP>(acc[pp], s, __fdiv_rn(1.0f, s), MB, t);
+          ok = s >= FP16_MIN_NORMAL && round_fast<NP>(acc[pp], s, rcp_approx(s), MB, t);
           if (!ok) {
 #pragma unroll
             for (int p = 0; p < NP; p++) {

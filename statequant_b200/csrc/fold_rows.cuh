@@ -123,14 +123,14 @@ __device__ __forceinline__ bool fold_rows(const uint8_t* codes, const unsigned s
       if (v0) {
         if (lead) SCh[r0 * NG + gl] = f2h(sc0);
         uint4 pk;
-        if (sc0 >= FP16_MIN_NORMAL && round_fast<8>(a0, sc0, __fdiv_rn(1.0f, sc0), MB, tt)) pk = pack_codes16<BITS>(tt);
+        if (sc0 >= FP16_MIN_NORMAL && round_fast<8>(a0, sc0, rcp_approx(sc0), MB, tt)) pk = pack_codes16<BITS>(tt);
         else pk = round_exact_pack<BITS>(a0[0], a0[1], a0[2], a0[3], a0[4], a0[5], a0[6], a0[7], sc0);
         store_packed16<BITS>(Sh + (long long)r0 * ROWB + c * CB, pk);
       }
       if (v1) {
         if (lead) SCh[r1 * NG + gl] = f2h(sc1);
         uint4 pk;
-        if (sc1 >= FP16_MIN_NORMAL && round_fast<8>(a1, sc1, __fdiv_rn(1.0f, sc1), MB, tt)) pk = pack_codes16<BITS>(tt);
+        if (sc1 >= FP16_MIN_NORMAL && round_fast<8>(a1, sc1, rcp_approx(sc1), MB, tt)) pk = pack_codes16<BITS>(tt);
         else pk = round_exact_pack<BITS>(a1[0], a1[1], a1[2], a1[3], a1[4], a1[5], a1[6], a1[7], sc1);
         store_packed16<BITS>(Sh + (long long)r1 * ROWB + c * CB, pk);
       }

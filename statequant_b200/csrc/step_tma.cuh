@@ -635,7 +635,7 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
         if (A.qbuf) {
           const float usc = fp16_scale(fmaxf(fmaxf(red[hi * NW], red[hi * NW + 1]), fmaxf(red[hi * NW + 2], red[hi * NW + 3])), 127.0f);
           const bool fast_ok = usc >= FP16_MIN_NORMAL;
-          const float r = __fdiv_rn(1.0f, usc);
+          const float r = rcp_approx(usc);
           for (int e = lane; e < DV / 4; e += 32) {
             float dq4[4];
             *reinterpret_cast<uint32_t*>(UBh + (long long)n * DV + 4 * e) = round4_i8(usb + 4 * e, usc, r, fast_ok, dq4);

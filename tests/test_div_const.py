@@ -1,0 +1,14 @@
+"""The scale division x / qmax is done on the device by a multiply and two FMAs; this is the exhaustive proof that
+the result is the IEEE quotient for every input the kernels can see (all floats in [1e-8, 3e38], qmax 127 and 7)."""
+import os
+import subprocess
+
+
+def test_fma_division_by_qmax_is_exact(tmp_path):
+    here = os.path.dirname(os.path.abspath(__file__))
+    exe = str(tmp_path / 'div_const_check')
+    subprocess.run(['gcc', '-O2', '-fopenmp', '-ffp-contract=off', '-o', exe, os.path.join(here, 'div_const_check.c'), '-lm'],
+                   check=True)
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout
+    assert r.stdout.count('mismatches 0') == 2, r.stdout
