@@ -49,7 +49,7 @@ __host__ __device__ inline SmemF smemf_plan(bool vdec, int bits, int axk, int gr
   s.L = f; f += DV * s.lm;
   s.ae = f; f += vdec ? DK : 32;            // KDA: exp(gcur) per key channel; else: the slots' decay factors
   s.ksf = f; f += 64;                       // buffer scales of the slots: keys, then values
-  s.cmax = f; f += (axk ? 0 : 2 * NW * DK);
+  s.cmax = f; f += (axk ? 0 : 3 * NW * DK);         // axis v: column maxima, then scales and their reciprocals
   s.total = s.f0 + ((f + 3) & ~3) * 4;
   return s;
 }

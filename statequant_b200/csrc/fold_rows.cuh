@@ -71,6 +71,38 @@ __device__ __forceinline__ void fold_dequant(float2 (&a)[8], float sc, float alp
   }
 }
 
+// The verified candidates of round_fast, clamped to the code range.  A scale that is subnormal in fp16 can be far
+// enough below absmax / qmax for the largest quotients to round beyond qmax; the candidate is then still the right
+// unclamped integer, and clamping it is what clamp(rint(div_rn(x, s))) does.
+template <int BITS>
+__device__ __forceinline__ float2 (&clamp_codes(float2 (&t)[8]))[8] {
+  constexpr float QMAX = BITS == 4 ? 7.0f : 127.0f;
+  constexpr float MB = BITS == 4 ? MAGIC + 8.0f : MAGIC;
+#pragma unroll
+  for (int p = 0; p < 8; p++) {
+    t[p].x = fminf(fmaxf(t[p].x, MB - QMAX), MB + QMAX);
+    t[p].y = fminf(fmaxf(t[p].y, MB - QMAX), MB + QMAX);
+  }
+  return t;
+}
+
+// round_fast with one scale (sc[j]) and approximate reciprocal (rc[j]) per column: the same test, per element
+__device__ __forceinline__ bool round_fast_cols(const float2 (&x)[8], const float* sc, const float* rc, float mb,
+                                                float2 (&t)[8]) {
+  const float2 m2 = make_float2(mb, mb), nm2 = make_float2(-mb, -mb), h2 = make_float2(0.49998474f, 0.49998474f);
+  float worst = -1.0f;                                   // max over elements of |rem| - thr; the chunk passes if < 0
+#pragma unroll
+  for (int p = 0; p < 8; p++) {
+    const float2 s2 = *reinterpret_cast<const float2*>(sc + 2 * p), r2 = *reinterpret_cast<const float2*>(rc + 2 * p);
+    t[p] = __ffma2_rn(x[p], r2, m2);
+    const float2 c = __fadd2_rn(t[p], nm2);
+    const float2 rem = __ffma2_rn(make_float2(-c.x, -c.y), s2, x[p]);
+    const float2 thr = __fmul2_rn(s2, h2);
+    worst = fmaxf(worst, fmaxf(fabsf(rem.x) - thr.x, fabsf(rem.y) - thr.y));
+  }
+  return worst < 0.f;
+}
+
 // sync(): barrier among the 128 threads that fold (returns false if the CTA is aborting).  Returns false on abort.
 template <int BITS, bool AXK, int LPR, bool VDEC, class Sync>
 __device__ __forceinline__ bool fold_rows(const uint8_t* codes, const unsigned short* scs, const float* R,
@@ -123,14 +155,14 @@ __device__ __forceinline__ bool fold_rows(const uint8_t* codes, const unsigned s
       if (v0) {
         if (lead) SCh[r0 * NG + gl] = f2h(sc0);
         uint4 pk;
-        if (sc0 >= FP16_MIN_NORMAL && round_fast<8>(a0, sc0, rcp_approx(sc0), MB, tt)) pk = pack_codes16<BITS>(tt);
+        if (round_fast<8>(a0, sc0, rcp_approx(sc0), MB, tt)) pk = pack_codes16<BITS>(clamp_codes<BITS>(tt));
         else pk = round_exact_pack<BITS>(a0[0], a0[1], a0[2], a0[3], a0[4], a0[5], a0[6], a0[7], sc0);
         store_packed16<BITS>(Sh + (long long)r0 * ROWB + c * CB, pk);
       }
       if (v1) {
         if (lead) SCh[r1 * NG + gl] = f2h(sc1);
         uint4 pk;
-        if (sc1 >= FP16_MIN_NORMAL && round_fast<8>(a1, sc1, rcp_approx(sc1), MB, tt)) pk = pack_codes16<BITS>(tt);
+        if (round_fast<8>(a1, sc1, rcp_approx(sc1), MB, tt)) pk = pack_codes16<BITS>(clamp_codes<BITS>(tt));
         else pk = round_exact_pack<BITS>(a1[0], a1[1], a1[2], a1[3], a1[4], a1[5], a1[6], a1[7], sc1);
         store_packed16<BITS>(Sh + (long long)r1 * ROWB + c * CB, pk);
       }
@@ -186,21 +218,33 @@ __device__ __forceinline__ bool fold_rows(const uint8_t* codes, const unsigned s
       }
       if (!sync()) return false;
       float* ssc = cmax + NW * DK;                    // scale of every column of every group in flight
+      float* rsc = ssc + NW * DK;                     // and its approximate reciprocal
       for (int e = tid; e < gpi * DK; e += NT) {
         const int gi = e / DK, k = e - gi * DK;
         float am = 0.f;
         for (int w = 0; w < wpg; w++) am = fmaxf(am, cmax[(gi * wpg + w) * DK + k]);
         const float sc = fp16_scale(am, QMAX);
         ssc[gi * DK + k] = sc;
+        rsc[gi * DK + k] = rcp_approx(sc);
         const int gvr = it * gpi + gi;
         if (gvr * G < DV) SCh[gvr * DK + k] = f2h(sc);
       }
       if (!sync()) return false;
       const float* myssc = ssc + (warp / wpg) * DK + c * 16;
-      if (v0) store_packed16<BITS>(Sh + (long long)r0 * ROWB + c * CB,
-                                   round_exact_pack_cols<BITS>(a0[0], a0[1], a0[2], a0[3], a0[4], a0[5], a0[6], a0[7], myssc));
-      if (v1) store_packed16<BITS>(Sh + (long long)r1 * ROWB + c * CB,
-                                   round_exact_pack_cols<BITS>(a1[0], a1[1], a1[2], a1[3], a1[4], a1[5], a1[6], a1[7], myssc));
+      const float* myrsc = rsc + (warp / wpg) * DK + c * 16;
+      float2 tt[8];
+      if (v0) {
+        uint4 pk;
+        if (round_fast_cols(a0, myssc, myrsc, MB, tt)) pk = pack_codes16<BITS>(clamp_codes<BITS>(tt));
+        else pk = round_exact_pack_cols<BITS>(a0[0], a0[1], a0[2], a0[3], a0[4], a0[5], a0[6], a0[7], myssc);
+        store_packed16<BITS>(Sh + (long long)r0 * ROWB + c * CB, pk);
+      }
+      if (v1) {
+        uint4 pk;
+        if (round_fast_cols(a1, myssc, myrsc, MB, tt)) pk = pack_codes16<BITS>(clamp_codes<BITS>(tt));
+        else pk = round_exact_pack_cols<BITS>(a1[0], a1[1], a1[2], a1[3], a1[4], a1[5], a1[6], a1[7], myssc);
+        store_packed16<BITS>(Sh + (long long)r1 * ROWB + c * CB, pk);
+      }
     }
     return true;
   }
