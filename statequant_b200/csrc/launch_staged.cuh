@@ -24,7 +24,7 @@ int launch_staged_one(const StepArgs& a, cudaStream_t stream) {
   }
   const long long ctas = static_cast<long long>(a.rows) * a.HK;
   if (ctas > 2147483647LL) return 1;
-  kern<<<static_cast<unsigned>(ctas), NT, plan.total, stream>>>(a, nst);
+  kern<<<static_cast<unsigned>(ctas), NT, plan.total, stream>>>(a, plan, nst);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return -1000 - static_cast<int>(e);
   return 0;

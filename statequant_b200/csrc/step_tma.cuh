@@ -72,8 +72,8 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 
 // shared-memory plan of the staged kernel (byte offsets; float offsets from f0)
 struct Smem2 {
-  int bars, stage0, stage_bytes, codes_b, scales_b, ub_b, kb, gbt, rl, f0, total;
-  int xq, xk, ga, ae, krnd, us, Dq, Dk, hd, decf, ubs, red, misc, cmax, rdk, ldv;
+  int bars, stage0, stage_bytes, codes_b, scales_b, ub_b, kb, gbt, f0, total;
+  int xq, xk, ga, ae, wq, wk, wg, us, Dq, Dk, hd, decf, ubs, red, misc;
 };
 constexpr int HD_W = 8;     // per-head scalars: g, beta | dt, gcur, alpha, a, gnew, D, n
 __host__ __device__ inline int al16i(int x) { return (x + 15) & ~15; }
@@ -81,9 +81,6 @@ __host__ __device__ inline Smem2 smem2_plan(int kind, int bits, int axk, int gro
                                             int nst, int gqa) {
   Smem2 s;
   const int bsz = qbuf ? 1 : 2;
-  const int lpr = DK / 16;
-  s.rdk = lpr * 20;                 // 16 columns + 4 floats of padding per lane chunk
-  s.ldv = fold_lm(M);               // floats per row of the value-major L tile
   s.codes_b = DV * DK * bits / 8;
   s.scales_b = al16i((axk ? DV * (DK / group) : (DV / group) * DK) * 2);
   s.ub_b = al16i(M * DV * bsz);
@@ -91,7 +88,6 @@ __host__ __device__ inline Smem2 smem2_plan(int kind, int bits, int axk, int gro
   int o = 0;
   s.bars = o; o += 64;
   s.stage0 = o; o += nst * s.stage_bytes;
-  s.rl = 0;
   s.kb = o; o += al16i(M * DK * bsz);
   s.gbt = o; o += (kind == K_KDA ? M * DK * 4 : 0);
   s.f0 = o;
@@ -100,7 +96,9 @@ __host__ __device__ inline Smem2 smem2_plan(int kind, int bits, int axk, int gro
   s.xk = f; f += DK;
   s.ga = f; f += (kind == K_KDA ? DK : 0);
   s.ae = f; f += (kind == K_KDA ? DK : 0);
-  s.krnd = f;
+  s.wq = f; f += DK;                // the dot-product warp's own copy of the normalised q, k (KDA: log decay)
+  s.wk = f; f += DK;
+  s.wg = f; f += (kind == K_KDA ? DK : 0);
   s.us = f; f += gqa * DV;
   s.Dq = f; f += 32;
   s.Dk = f; f += 32;
@@ -109,7 +107,6 @@ __host__ __device__ inline Smem2 smem2_plan(int kind, int bits, int axk, int gro
   s.ubs = f; f += gqa * M;
   s.red = f; f += gqa * NW;
   s.misc = f; f += 8;
-  s.cmax = f;
   s.total = s.f0 + ((f + 3) & ~3) * 4;
   return s;
 }
@@ -255,7 +252,8 @@ namespace sqb {
 #define SQB_MINB 4
 #endif
 template <int KIND, int BITS, bool AXK, int LPR>
-__global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_constant__ StepArgs A, const int nst) {
+__global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_constant__ StepArgs A, const __grid_constant__ Smem2 P,
+                                                                const int nst) {
   constexpr int DK = LPR * 16;
   constexpr int RPP = 32 / LPR;                  // rows per warp pass
   constexpr int CB = 16 * BITS / 8;              // bytes of a lane chunk
@@ -276,7 +274,7 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
 
   // ---- activation loads that do not depend on the slot: issued before anything else ----------------------------
   float qr[CW], kr[CW], g4[4];
-  if (warp == 0) {
+  if (warp == 0 || warp == 3) {
 #pragma unroll
     for (int j = 0; j < CW; j++) {
       qr[j] = ldf(A.q + (long long)b * A.sq, A.dt_qk, (long long)hk * DK + lane * CW + j);
@@ -313,13 +311,12 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
       return;
     }
   }
-  const Smem2 P = smem2_plan(KIND, BITS, AXK, G, DK, DV, M, A.qbuf, nst, gqa);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smraw + P.bars);
   uint8_t* kbt = smraw + P.kb;
   float* fsm = reinterpret_cast<float*>(smraw + P.f0);
   float *xq = fsm + P.xq, *xk = fsm + P.xk, *ga = fsm + P.ga, *ae = fsm + P.ae, *us = fsm + P.us,
         *Dq = fsm + P.Dq, *Dk = fsm + P.Dk, *hd = fsm + P.hd, *decf = fsm + P.decf, *ubsf = fsm + P.ubs,
-        *red = fsm + P.red, *misc = fsm + P.misc;
+        *red = fsm + P.red, *misc = fsm + P.misc, *wq = fsm + P.wq, *wk = fsm + P.wk, *wg = fsm + P.wg;
   const float* gbt = reinterpret_cast<const float*>(smraw + P.gbt);
   const int bsz = A.qbuf ? 1 : 2;
   const int NG = AXK ? DK / G : 1;
@@ -348,19 +345,14 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
 
   // ---- prologue, by role ----------------------------------------------------------------------------------------
   if (warp == 0) {
-    // producer: barriers, then the key tile and stage 0, one copy per lane
+    // producer: the stage barriers, then stage 0, one copy per lane (the key tile belongs to warp 3)
     if (lane == 0) {
-      for (int s = 0; s <= nst; s++) mbar_init(&bars[s], 1);
+      for (int s = 0; s < nst; s++) mbar_init(&bars[s], 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
       misc[2] = 0.f;                                      // "a copy never arrived" flag
     }
     __syncwarp();
-    if (lane == 0) {
-      mbar_expect_tx(&bars[nst], M * DK * bsz + (VDEC ? M * DK * 4 : 0));
-      bulk_g2s(kbt, KBh, M * DK * bsz, &bars[nst]);
-    } else if (lane == 1) {
-      if (VDEC) bulk_g2s(smraw + P.gbt, GBseq + (long long)h0 * M * DK, M * DK * 4, &bars[nst]);
-    } else if (lane == 2) {
+    if (lane == 2) {
       mbar_expect_tx(&bars[0], stage_tx);
       bulk_g2s(smraw + P.stage0, Sseq + (long long)h0 * P.codes_b, P.codes_b, &bars[0]);
     } else if (lane == 3) {
@@ -368,10 +360,8 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
     } else if (lane == 4) {
       bulk_g2s(smraw + P.stage0 + P.codes_b + P.scales_b, UBseq + (long long)h0 * M * DV * bsz, M * DV * bsz, &bars[0]);
     }
-    // the key head: counters and buffered-key scales first (their latency overlaps the normalisation)
+    // the key head: its counter first (the latency overlaps the normalisation)
     const int n0 = NPseq[h0] & (M - 1);       // the heads of a slot advance together
-    float ksv = 0.f;                          // scale of buffered key `lane`
-    if (A.qbuf && lane < M) ksv = h2f(KBSh[lane]);
     float gnr[CW];
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
@@ -426,7 +416,45 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
         reinterpret_cast<unsigned short*>(KBh)[(long long)n0 * DK + lane * CW + j] = bb;
       }
     }
-    __syncwarp();                              // xq, xk (ga) written by this warp are read below
+  } else if (warp == 3) {
+    // the buffered keys: this warp owns the key tile (barrier, copy) and takes its dot products with q and k, from
+    // its own copy of the normalised vectors (same arithmetic as warp 0, so the same bits)
+    if (lane == 0) {
+      mbar_init(&bars[nst], 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      mbar_expect_tx(&bars[nst], M * DK * bsz + (VDEC ? M * DK * 4 : 0));
+      bulk_g2s(kbt, KBh, M * DK * bsz, &bars[nst]);
+      if (VDEC) bulk_g2s(smraw + P.gbt, GBseq + (long long)h0 * M * DK, M * DK * 4, &bars[nst]);
+    }
+    const int n0 = NPseq[h0] & (M - 1);
+    float ksv = 0.f;                          // scale of buffered key `lane`
+    if (A.qbuf && lane < M) ksv = h2f(KBSh[lane]);
+    float gnr[CW];
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < CW; j++) {
+      s0 += qr[j] * qr[j];
+      s1 += kr[j] * kr[j];
+      if (VDEC) gnr[j] = GCseq[(long long)h0 * DK + lane * CW + j] +
+                         ldf(A.g + (long long)b * A.sg, A.dt_g, (long long)h0 * DK + lane * CW + j);
+    }
+    if (KIND != K_M2) {
+      s0 = warp_sum(s0);
+      s1 = warp_sum(s1);
+      const float nq = __fsqrt_rn(s0 + 1e-6f), nk = __fsqrt_rn(s1 + 1e-6f);
+#pragma unroll
+      for (int j = 0; j < CW; j++) {
+        qr[j] = __fdiv_rn(qr[j], nq) * A.scale;
+        kr[j] = __fdiv_rn(kr[j], nk);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < CW; j++) {
+      wq[lane * CW + j] = qr[j];
+      wk[lane * CW + j] = kr[j];
+      if (VDEC) wg[lane * CW + j] = gnr[j];
+    }
+    __syncwarp();
     if (!mbar_wait(&bars[nst], 0) && lane == 0) misc[2] = 1.f;
     // dot products of the buffered keys with q and k: lane = (slot, quarter of d_k), 8 slots per round
     for (int i0 = 0; i0 < M; i0 += 8) {
@@ -447,10 +475,10 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
             kv[0] = __uint_as_float(w2.x << 16); kv[1] = __uint_as_float(w2.x & 0xFFFF0000u);
             kv[2] = __uint_as_float(w2.y << 16); kv[3] = __uint_as_float(w2.y & 0xFFFF0000u);
           }
-          const float4 q4 = *reinterpret_cast<const float4*>(xq + k);
-          const float4 k4 = *reinterpret_cast<const float4*>(xk + k);
+          const float4 q4 = *reinterpret_cast<const float4*>(wq + k);
+          const float4 k4 = *reinterpret_cast<const float4*>(wk + k);
           if (VDEC) {
-            const float4 g4v = *reinterpret_cast<const float4*>(ga + k);
+            const float4 g4v = *reinterpret_cast<const float4*>(wg + k);
             const float4 b4 = *reinterpret_cast<const float4*>(gbt + i * DK + k);
             kv[0] = kv[0] * expf(g4v.x - b4.x); kv[1] = kv[1] * expf(g4v.y - b4.y);
             kv[2] = kv[2] * expf(g4v.z - b4.z); kv[3] = kv[3] * expf(g4v.w - b4.w);
