@@ -567,20 +567,36 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
   const int RW = DV / NW;
   const int npass = RW / RPP;
   float2 vq[8], vk[8];
-  auto load_slice = [&](const unsigned short* scrow) {
+  auto load_slice = [&](const unsigned short* scrow) {      // this lane's 16 columns of q and k, as 128-bit reads
+    const float* sq = xq + c * 16;
+    const float* sk = xk + c * 16;
+    const float* sa = ae + c * 16;
 #pragma unroll
-    for (int p = 0; p < 8; p++) {
-      const int k0 = c * 16 + 2 * p;
-      float q0 = xq[k0], q1 = xq[k0 + 1], k0v = 0.f, k1v = 0.f;
-      if (TWO) { k0v = xk[k0]; k1v = xk[k0 + 1]; }
-      if (VDEC) { q0 = ae[k0] * q0; q1 = ae[k0 + 1] * q1; k0v = ae[k0] * k0v; k1v = ae[k0 + 1] * k1v; }
-      if (!AXK) {
-        const float s0 = h2f(scrow[k0]), s1 = h2f(scrow[k0 + 1]);
-        q0 = q0 * s0; q1 = q1 * s1; k0v = k0v * s0; k1v = k1v * s1;
+    for (int p4 = 0; p4 < 4; p4++) {
+      const float4 q4 = *reinterpret_cast<const float4*>(sq + 4 * p4);
+      float4 k4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (TWO) k4 = *reinterpret_cast<const float4*>(sk + 4 * p4);
+      float qv[4] = {q4.x, q4.y, q4.z, q4.w}, kv[4] = {k4.x, k4.y, k4.z, k4.w};
+      if (VDEC) {
+        const float4 a4 = *reinterpret_cast<const float4*>(sa + 4 * p4);
+        const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+        for (int e = 0; e < 4; e++) { qv[e] = av[e] * qv[e]; kv[e] = av[e] * kv[e]; }
       }
-      const float p0 = presc<BITS>(2 * p), p1 = presc<BITS>(2 * p + 1);
-      vq[p] = make_float2(q0 * p0, q1 * p1);
-      vk[p] = make_float2(k0v * p0, k1v * p1);
+      if (!AXK) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const float sc = h2f(scrow[c * 16 + 4 * p4 + e]);
+          qv[e] = qv[e] * sc; kv[e] = kv[e] * sc;
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 4; e += 2) {
+        const int p = 2 * p4 + e / 2;
+        const float p0 = presc<BITS>(2 * p), p1 = presc<BITS>(2 * p + 1);
+        vq[p] = make_float2(qv[e] * p0, qv[e + 1] * p1);
+        vk[p] = make_float2(kv[e] * p0, kv[e + 1] * p1);
+      }
     }
   };
   if (AXK) load_slice(nullptr);
