@@ -29,6 +29,8 @@ for p in (ROOT, os.path.join(ROOT, 'tests')):
     if p not in sys.path:
         sys.path.insert(0, p)
 
+import math  # noqa: E402
+
 import torch  # noqa: E402
 
 HV, HK, DK, DV, M = 32, 16, 128, 128, 8
@@ -124,6 +126,9 @@ class Stack:
         self.graph = None
         self.launches_per_step = None
 
+    def bytes_per_slot(self):
+        return algorithmic_bytes(self.lay)
+
     def step(self):
         for l in range(LAYERS):
             q, k, v, a, b = self.inputs[l]
@@ -164,6 +169,137 @@ class Stack:
         e1.record()
         torch.cuda.synchronize()
         return e0.elapsed_time(e1)
+
+
+class Mamba2Stack(Stack):
+    """Mamba2 / SSD layers at Nemotron-H shapes (128 heads in 8 groups, head_dim 64, d_state 128), int8 k g32."""
+    H, GR, DS, HD = 128, 8, 128, 64
+
+    def __init__(self, preset, batch, device, seed):
+        import statequant_b200 as sq
+        from statequant_b200.kernels import Mamba2SlotLayout
+        fmt = {'int8k': (8, 'k', 32), 'int8k128': (8, 'k', 128), 'pace4': (4, 'k', 64)}[preset]
+        self.lay = Mamba2SlotLayout(sq.Quantizer(*fmt), self.H, self.GR, self.DS, self.HD, m=M, buffer_bits=8)
+        self.batch, self.device = batch, device
+        gen = torch.Generator().manual_seed(seed)
+        self.blobs = [self.lay.alloc(batch + 1, device) for _ in range(LAYERS)]
+        self.views = [self.lay.views(b) for b in self.blobs]
+        self.idx = (torch.randperm(batch, generator=gen) + 1).to(torch.int32).to(device)
+        self.inputs = [self.make(batch, gen, device) for _ in range(LAYERS)]
+        self.A = (-torch.exp(torch.rand(self.H, generator=gen) * math.log(16.0))).to(device)
+        self.D = torch.randn(self.H, generator=gen).to(device)
+        self.dt_bias = (torch.rand(self.H, generator=gen) * 2.0 - 4.0).to(device)
+        self.outs = [torch.empty(batch, self.H, self.HD, dtype=torch.bfloat16, device=device) for _ in range(LAYERS)]
+        self.graph, self.launches_per_step = None, None
+
+    def make(self, batch, gen, device):
+        f = lambda *s: torch.randn(*s, generator=gen)                                    # noqa: E731
+        return [t.to(device) for t in (f(batch, self.H, self.HD).bfloat16(), f(batch, self.H).bfloat16(),
+                                       f(batch, self.GR, self.DS).bfloat16(), f(batch, self.GR, self.DS).bfloat16())]
+
+    def step(self):
+        for l in range(LAYERS):
+            x, dt, B, C = self.inputs[l]
+            self.lay.step(self.views[l], self.idx, x, dt, B, C, self.outs[l], self.A, D=self.D, dt_bias=self.dt_bias)
+
+    def prewarm(self, steps, gen):
+        for t in range(steps):
+            if t % 64 == 0:
+                self.inputs = [self.make(self.batch, gen, self.device) for _ in range(LAYERS)]
+            self.step()
+        torch.cuda.synchronize()
+
+    def bytes_per_slot(self):
+        b, m, L = self.lay.breakdown(), self.lay.m, self.lay
+        state = (b['S'] + b.get('SC', 0)) * (1 + 1 / m)
+        buf = b['KB'] + b['UB'] + b.get('KBS', 0) + b.get('UBS', 0) + b['GB']
+        io = 2 * (2 * self.GR * self.DS + self.H * self.HD + self.H) + 2 * self.H * self.HD
+        return state + buf * (m - 1) / (2 * m) + buf / m + 2 * (b['GCUR'] + b['NPTR']) + io, state
+
+
+class KDAStack(Stack):
+    """KDA layers at Kimi-Linear-like shapes (32 heads, d 128), per-channel decays, pace4 state."""
+    H = 32
+
+    def __init__(self, preset, batch, device, seed):
+        import statequant_b200 as sq
+        from statequant_b200.kernels import KDASlotLayout
+        self.lay = KDASlotLayout(sq.Quantizer(*PRESETS[preset]), self.H, DK, DV, m=M, buffer_bits=8)
+        self.batch, self.device = batch, device
+        gen = torch.Generator().manual_seed(seed)
+        self.blobs = [self.lay.alloc(batch + 1, device) for _ in range(LAYERS)]
+        self.views = [self.lay.views(b) for b in self.blobs]
+        self.idx = (torch.randperm(batch, generator=gen) + 1).to(torch.int32).to(device)
+        self.inputs = [self.make(batch, gen, device) for _ in range(LAYERS)]
+        self.outs = [torch.empty(batch, self.H, DV, dtype=torch.bfloat16, device=device) for _ in range(LAYERS)]
+        self.graph, self.launches_per_step = None, None
+
+    def make(self, batch, gen, device):
+        f = lambda *s: torch.randn(*s, generator=gen)                                    # noqa: E731
+        q, k = f(batch, self.H, DK), f(batch, self.H, DK)
+        q, k = q / q.norm(dim=-1, keepdim=True), k / k.norm(dim=-1, keepdim=True)
+        g = torch.nn.functional.logsigmoid(f(batch, self.H, DK) + 3.0)
+        return [t.to(device) for t in (q.bfloat16(), k.bfloat16(), f(batch, self.H, DV).bfloat16(), g.float(),
+                                       torch.sigmoid(f(batch, self.H)).float())]
+
+    def step(self):
+        for l in range(LAYERS):
+            q, k, v, g, beta = self.inputs[l]
+            self.lay.step(self.views[l], self.idx, q, k, v, g, beta, self.outs[l], DK ** -0.5)
+
+    prewarm = Mamba2Stack.prewarm
+
+    def bytes_per_slot(self):
+        b, m = self.lay.breakdown(), self.lay.m
+        state = (b['S'] + b.get('SC', 0)) * (1 + 1 / m)
+        buf = b['KB'] + b['UB'] + b.get('KBS', 0) + b.get('UBS', 0) + b['GB']
+        io = 2 * (2 * self.H * DK + self.H * DV) + 4 * (self.H * DK + self.H) + 2 * self.H * DV
+        return state + buf * (m - 1) / (2 * m) + buf / m + 2 * (b['GCUR'] + b['NPTR']) + io, state
+
+
+class GGAStack(Stack):
+    """GDN layers on the GGA mixed-width state (per-layer widths 4,6,4,4,6,4 repeating, no pivots) with the
+    pure-write window of 8 pairs: the whole head is read, re-fitted and rewritten every token."""
+
+    def __init__(self, preset, batch, device, seed):
+        from statequant_b200.kernels import GGAPacked
+        from statequant_b200.kernels.gga import StepPlan
+        gen = torch.Generator().manual_seed(seed)
+        widths = [4, 6, 4, 4, 6, 4]
+        plan = StepPlan({l: (torch.full((HV,), widths[l % 6]), torch.rand(HV, DK, generator=gen) + 0.5)
+                         for l in range(LAYERS)}, 32, name='bench')
+        self.lay = GGAPacked(plan, HV, HK, DK, DV, pw=True, m=M)
+        self.batch, self.device = batch, device
+        self.blobs = [self.lay.alloc(batch + 1, device) for _ in range(LAYERS)]
+        self.views = [self.lay.views(b) for b in self.blobs]
+        self.idx = (torch.randperm(batch, generator=gen) + 1).to(torch.int32).to(device)
+        self.inputs = [make_inputs(batch, gen, device) for _ in range(LAYERS)]
+        self.A_log = (torch.randn(HV, generator=gen) * 0.3).to(device)
+        self.dt_bias = torch.randn(HV, generator=gen).to(device)
+        self.outs = [torch.empty(batch, HV, DV, dtype=torch.bfloat16, device=device) for _ in range(LAYERS)]
+        self.graph, self.launches_per_step = None, None
+        self.widths = widths
+
+    def step(self):
+        for l in range(LAYERS):
+            q, k, v, a, b = self.inputs[l]
+            self.lay.step(self.views[l], self.idx, q, k, v, self.outs[l], DK ** -0.5,
+                          gate=(a, b, self.A_log, self.dt_bias), layer=l)
+
+    def bytes_per_slot(self):
+        # state read + written every token, window read, one pair and the P scales rewritten, bf16 I/O
+        per = {4: 691616.0, 6: 953760.0}
+        tot = sum(per[self.widths[l % 6]] for l in range(LAYERS)) / LAYERS
+        st = sum({4: 557056.0, 6: 819200.0}[self.widths[l % 6]] for l in range(LAYERS)) / LAYERS
+        return tot, st
+
+
+WORKLOADS = {'gdn': Stack, 'mamba2': Mamba2Stack, 'kda': KDAStack, 'gga': GGAStack}
+WORKLOAD_TEXT = {
+    'mamba2': 'Mamba2 / SSD decode stack, Nemotron-H shapes (128 heads in 8 groups, head_dim 64, d_state 128, m 8, int8 buffer)',
+    'kda': 'KDA decode stack, Kimi-Linear-like shapes (32 heads, d 128, per-channel decays, m 8, int8 buffer)',
+    'gga': 'GDN decode stack on the GGA mixed-width state (widths 4,6,4,4,6,4 repeating) with the pure-write window (8 pairs)',
+}
 
 
 def run_e2e(stack, steps, warmup):
@@ -237,12 +373,14 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--batch', type=int, default=256)
     ap.add_argument('--prewarm', type=int, default=512)
-    ap.add_argument('--preset', default='int8k', choices=list(PRESETS))
+    ap.add_argument('--preset', default='int8k', choices=list(PRESETS) + ['int8k128'])
     ap.add_argument('--no-variants', action='store_true', help='time the headline preset only')
     ap.add_argument('--layers', type=int, default=24, help='layers of the stack (24 = the benchmark; fewer for ncu captures)')
     ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer leg')
     ap.add_argument('--no-cpu', action='store_true', help='skip the CPU-baseline leg')
     ap.add_argument('--eager', action='store_true', help='launch eagerly instead of replaying a CUDA graph')
+    ap.add_argument('--workload', default='gdn', choices=list(WORKLOADS),
+                    help='gdn = the benchmark; mamba2 / kda / gga time the other kernel families on their shapes')
     ap.add_argument('--kernel-path', type=int, default=0, choices=[0, 1, 2],
                     help='0 best kernel for the shape; 1 generic; 2 staged + fold launch (profiling / comparison)')
     args = ap.parse_args()
@@ -295,12 +433,16 @@ def main():
         return float(t.item())
 
     results = {}
+    if args.workload != 'gdn':
+        args.no_variants, args.no_e2e, args.no_cpu = True, True, True
+        config['workload'] = (f'{WORKLOAD_TEXT[args.workload]}, state preset {args.preset}, batch {args.batch} slots per '
+                              f'GPU, bf16 activations')
     presets = [args.preset] + ([] if args.no_variants else [p for p in PRESETS if p != args.preset])
     clocks = None
     launches = 0
     e2e = None
     for pi, preset in enumerate(presets):
-        stack = Stack(preset, args.batch, device, seed=1234 + rank)
+        stack = WORKLOADS[args.workload](preset, args.batch, device, seed=1234 + rank)
         stack.prewarm(args.prewarm, torch.Generator().manual_seed(4321 + rank))
         if not args.eager:
             stack.capture()
@@ -315,7 +457,7 @@ def main():
         ms = max_over_ranks(ms)
         if sampler is not None:
             clocks = sampler.stop(t0, t1)
-        total, state = algorithmic_bytes(stack.lay)
+        total, state = stack.bytes_per_slot()
         lsteps = args.steps * LAYERS
         per_launch_s = ms * 1e-3 / lsteps
         results[preset] = {'layer_steps_per_s': world * lsteps / (ms * 1e-3), 'us_per_layer_step': per_launch_s * 1e6,
@@ -344,14 +486,14 @@ def main():
     head = results[args.preset]
     peak, which = measured_peak_gbs()
     line = {
-        'metric': METRIC, 'value': head['layer_steps_per_s'], 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
+        'metric': METRIC if args.workload == 'gdn' else f'decode layer-steps/s ({args.workload} stack)', 'value': head['layer_steps_per_s'], 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
         'warmup': max(3, args.warmup), 'ms_per_step': head['ms_per_step'], 'higher_is_better': True, 'scaling': 'weak',
         'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic', 'config': config,
         'us_per_layer_step': head['us_per_layer_step'],
         'state_gbs_per_gpu': head['state_gbs_per_gpu'], 'state_frac_of_8tbs': head['state_gbs_per_gpu'] / 8000.0,
         'total_frac_of_8tbs': head['total_gbs_per_gpu'] / 8000.0,
         'roofline': {'bound': 'hbm', 'achieved': head['total_gbs_per_gpu'], 'peak': peak, 'unit': 'GB/s',
-                     'frac': head['total_gbs_per_gpu'] / peak, 'traffic': ncu_traffic(args.preset, args.batch),
+                     'frac': head['total_gbs_per_gpu'] / peak, 'traffic': ncu_traffic(args.preset, args.batch) if args.workload == 'gdn' else None,
                      'peak_source': which,
                      'kernel': 'step_tma_kernel<GDN> + fold_kernel: the two launches of one layer-step (one C-ABI call), '
                                'averaged over the fold period of 8 steps',
