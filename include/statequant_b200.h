@@ -185,6 +185,20 @@ int sqb_stepquant_fit(const float *x, float *y, const int32_t *bits, const float
                       int32_t dk, int32_t dv, int32_t group, void *cuda_stream);
 
 /* message of the last error returned on this thread ("" if none) */
+/*
+ * The prefill boundary of a slot table, on the device (4 / 8-bit states, d_k 64 or 128; SQB_EINVAL otherwise, and the
+ * caller keeps its own path).  kind: 0 GDN, 1 Mamba2, 2 KDA.  idx int32 [rows] (NULL: row r is sequence r).
+ *   sqb_slot_read   out fp32 [rows, hv, dv, dk] = the state of each slot advanced across its pending buffer,
+ *                   S_n = a_n S_0 + sum_{i<n} (a_n / a_i) u_i k_i^T (KDA: decays per key channel); slots are not
+ *                   modified.  Replaces the torch gather + einsum of src/statequant/kernels/slots.py:210-233 and
+ *                   kernels/kda.py:351-372.
+ *   sqb_slot_write  S fp32 [rows, hv, dv, dk] packed into the slots (scales and codes byte for byte those of
+ *                   pack_vk, src/statequant/kernels/fold.py:111-147) and their buffers emptied.  Replaces
+ *                   kernels/slots.py:236-252, kernels/kda.py:375-386.
+ */
+int sqb_slot_read(const sqb_state_t *st, int kind, const int32_t *idx, int32_t rows, float *out, void *stream);
+int sqb_slot_write(const sqb_state_t *st, int kind, const int32_t *idx, int32_t rows, const float *S, void *stream);
+
 const char *sqb_last_error(void);
 /* ABI version of this header; bumped whenever a struct changes */
 int sqb_abi_version(void);

@@ -95,6 +95,9 @@ def lib():
         L.sqb_gga_store.argtypes = [vp, vp, i64, vp, vp]
         L.sqb_gga_load.argtypes = [vp, vp, i64, vp, vp]
         L.sqb_stepquant_fit.argtypes = [vp, vp, vp, vp, i64, i32, i32, i32, i32, vp]
+        L.sqb_slot_read.restype = L.sqb_slot_write.restype = C.c_int
+        L.sqb_slot_read.argtypes = [vp, i32, vp, i32, vp, vp]
+        L.sqb_slot_write.argtypes = [vp, i32, vp, i32, vp, vp]
         L.sqb_set_option.restype = C.c_int
         L.sqb_set_option.argtypes = [C.c_char_p, C.c_int]
         L.sqb_device_status.restype = C.c_int

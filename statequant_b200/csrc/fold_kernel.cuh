@@ -60,6 +60,7 @@ struct FoldArgs {
   const int* idx;
   int group, qbuf, M, HV, HK, DV, rows;
   int* status;
+  float* out;                // read mode: fp32 [rows, HV, d_v, d_k], the state advanced across its pending buffer
 };
 
 template <bool VDEC, int BITS, bool AXK, int LPR>
@@ -125,7 +126,7 @@ __global__ void __launch_bounds__(NT, 4) fold_kernel(const __grid_constant__ Fol
       long long seq = b;
       bool live = true;
       if (A.idx != nullptr) { seq = A.idx[b]; live = seq > 0; }
-      if (live) due = reinterpret_cast<const int*>(A.NPTR + seq * A.sN)[h] == M;
+      if (live) due = A.out != nullptr || reinterpret_cast<const int*>(A.NPTR + seq * A.sN)[h] == M;
     }
     const unsigned bal = __ballot_sync(0xffffffffu, due);
     int wbase = 0;
@@ -159,6 +160,8 @@ __global__ void __launch_bounds__(NT, 4) fold_kernel(const __grid_constant__ Fol
       // small per-head scalars straight from global memory while the copies land
       float gnew = 0.f;
       if (!VDEC) gnew = *GCh;
+      const bool reading = A.out != nullptr;
+      const int nlive = reading ? (reinterpret_cast<const int*>(A.NPTR + seq * A.sN)[h] & (M - 1)) : M;   // buffer entries in use
       const bool landed = mbar_wait(&bars[s], (phases >> s) & 1);
       phases ^= 1u << s;
       if (!__syncthreads_and(landed)) {          // uniform: every thread leaves, or none
@@ -167,7 +170,7 @@ __global__ void __launch_bounds__(NT, 4) fold_kernel(const __grid_constant__ Fol
         break;
       }
       if (tid < M) {
-        if (!VDEC) dec[tid] = tid == M - 1 ? 1.0f : expf(gnew - GBh[tid]);
+        if (!VDEC) dec[tid] = tid >= nlive ? 0.f : (!reading && tid == M - 1 ? 1.0f : expf(gnew - GBh[tid]));
         ksf[tid] = A.qbuf ? h2f(KBSh[tid]) : 1.0f;
         usf[tid] = A.qbuf ? h2f(UBSh[tid]) : 1.0f;
       }
@@ -178,7 +181,8 @@ __global__ void __launch_bounds__(NT, 4) fold_kernel(const __grid_constant__ Fol
         float kv;
         if (A.qbuf) kv = static_cast<float>(reinterpret_cast<const int8_t*>(kbt)[x]) * ksf[i];
         else kv = bf2f(reinterpret_cast<const unsigned short*>(kbt)[x]);
-        if (VDEC && i != M - 1) kv = kv * expf(gct[k] - gbt[x]);
+        if (VDEC && (reading || i != M - 1)) kv = i < nlive ? kv * expf(gct[k] - gbt[x]) : 0.f;
+        if (i >= nlive) kv = 0.f;
         R[i * RDK + (k / 16) * 20 + (k % 16)] = kv;
       }
       if (VDEC) {
@@ -189,7 +193,8 @@ __global__ void __launch_bounds__(NT, 4) fold_kernel(const __grid_constant__ Fol
         float ub;
         if (A.qbuf) ub = static_cast<float>(reinterpret_cast<const int8_t*>(ubt)[x]) * usf[i];
         else ub = bf2f(reinterpret_cast<const unsigned short*>(ubt)[x]);
-        if (!VDEC && i != M - 1) ub = dec[i] * ub;
+        if (!VDEC && (reading || i != M - 1)) ub = dec[i] * ub;
+        if (i >= nlive) ub = 0.f;
         L[v * LM + i] = ub;
       }
       __syncthreads();
@@ -197,14 +202,17 @@ __global__ void __launch_bounds__(NT, 4) fold_kernel(const __grid_constant__ Fol
       fold_rows<BITS, AXK, LPR, VDEC>(codes, scs, R, L, ae, alphan, DV, G, M, cmax,
                                       A.S + seq * A.sS + (long long)h * P.codes_b,
                                       reinterpret_cast<unsigned short*>(A.SC + seq * A.sSC) + (long long)h * scn, warp,
-                                      lane, tid, [] { __syncthreads(); return true; });
-      // counters back to 0: the buffer is empty again
-      if (VDEC) {
-        for (int k = tid; k < DK; k += NT) GCh[k] = 0.f;
-      } else if (tid == 0) {
-        *GCh = 0.f;
+                                      lane, tid, [] { __syncthreads(); return true; },
+                                      reading ? A.out + (long long)pair * DV * DK : nullptr);
+      if (!reading) {
+        // counters back to 0: the buffer is empty again
+        if (VDEC) {
+          for (int k = tid; k < DK; k += NT) GCh[k] = 0.f;
+        } else if (tid == 0) {
+          *GCh = 0.f;
+        }
+        if (tid == 0) reinterpret_cast<int*>(A.NPTR + seq * A.sN)[h] = 0;
       }
-      if (tid == 0) reinterpret_cast<int*>(A.NPTR + seq * A.sN)[h] = 0;
       __syncthreads();                         // the stage, R and L are free
       if (tid == 0 && e + 2 < cnt) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

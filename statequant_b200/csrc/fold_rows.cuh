@@ -86,6 +86,12 @@ __device__ __forceinline__ float2 (&clamp_codes(float2 (&t)[8]))[8] {
   return t;
 }
 
+__device__ __forceinline__ void fold_store_f32(float* p, const float2 (&a)[8]) {
+#pragma unroll
+  for (int j = 0; j < 4; j++)
+    reinterpret_cast<float4*>(p)[j] = make_float4(a[2 * j].x, a[2 * j].y, a[2 * j + 1].x, a[2 * j + 1].y);
+}
+
 // round_fast with one scale (sc[j]) and approximate reciprocal (rc[j]) per column: the same test, per element
 __device__ __forceinline__ bool round_fast_cols(const float2 (&x)[8], const float* sc, const float* rc, float mb,
                                                 float2 (&t)[8]) {
@@ -108,7 +114,7 @@ template <int BITS, bool AXK, int LPR, bool VDEC, class Sync>
 __device__ __forceinline__ bool fold_rows(const uint8_t* codes, const unsigned short* scs, const float* R,
                                           const float* L, const float* ae, float alphan, int DV, int G, int M,
                                           float* cmax, uint8_t* Sh, unsigned short* SCh, int warp, int lane, int tid,
-                                          Sync sync) {
+                                          Sync sync, float* Yout = nullptr) {
   constexpr int DK = LPR * 16;
   constexpr int RPP = 32 / LPR;
   constexpr int CB = 16 * BITS / 8;
@@ -138,6 +144,11 @@ __device__ __forceinline__ bool fold_rows(const uint8_t* codes, const unsigned s
       fold_dequant<BITS, VDEC>(a1, h2f(scs[r1 * NG + gl]), alphan, aec);
       if (SQB_FOLD_UNROLL8 && M == 8) fold_mac<LPR, 8>(a0, a1, Rc, L + r0 * LM, L + r1 * LM, M);
       else fold_mac<LPR, 0>(a0, a1, Rc, L + r0 * LM, L + r1 * LM, M);
+      if (Yout != nullptr) {                          // read-out mode: the advanced state as fp32, nothing re-rounded
+        if (v0) fold_store_f32(Yout + (long long)r0 * DK + c * 16, a0);
+        if (v1) fold_store_f32(Yout + (long long)r1 * DK + c * 16, a1);
+        continue;
+      }
       // fresh scales: absmax over the group's lanes
       float am0 = 0.f, am1 = 0.f;
 #pragma unroll
@@ -197,6 +208,11 @@ __device__ __forceinline__ bool fold_rows(const uint8_t* codes, const unsigned s
       }
       if (SQB_FOLD_UNROLL8 && M == 8) fold_mac<LPR, 8>(a0, a1, Rc, L + r0 * LM, L + r1 * LM, M);
       else fold_mac<LPR, 0>(a0, a1, Rc, L + r0 * LM, L + r1 * LM, M);
+      if (Yout != nullptr) {
+        if (v0) fold_store_f32(Yout + (long long)r0 * DK + c * 16, a0);
+        if (v1) fold_store_f32(Yout + (long long)r1 * DK + c * 16, a1);
+        continue;
+      }
       // column maxima over the group's rows: this lane's rows, the lanes of other rows, the other warps
       float cm[16];
 #pragma unroll

@@ -89,20 +89,23 @@ __device__ void gga_decode_head(const uint8_t* S, int b, int dk, int dv, int gro
   const unsigned short* R = reinterpret_cast<const unsigned short*>(S + static_cast<size_t>(dk) * dv * b / 8);
   const unsigned short* C = R + nr;
   const int rowb = dv * b / 8;
-  for (int e = tid; e < dk * dv; e += GNT) {
-    const int k = e / dv, v = e - k * dv;
+  const int lane = tid & 31, warp = tid >> 5;
+  for (int k = warp; k < dk; k += GNW) {                      // a row per warp, the columns over the lanes
     const uint8_t* row = S + static_cast<size_t>(k) * rowb;
-    float z;
-    if (b == 8) z = static_cast<float>(static_cast<int>(row[v]) - qmax);
-    else if (b == 4) z = static_cast<float>(static_cast<int>((row[v >> 1] >> (4 * (v & 1))) & 15) - qmax);
-    else if (b == 2) z = static_cast<float>((row[v >> 2] >> (2 * (v & 3))) & 3) * 2.0f - 3.0f;
-    else {
-      const uint8_t* t = row + 3 * (v >> 2);
-      const uint32_t wd = t[0] | (static_cast<uint32_t>(t[1]) << 8) | (static_cast<uint32_t>(t[2]) << 16);
-      z = static_cast<float>(static_cast<int>((wd >> (6 * (v & 3))) & 63) - qmax);
+    const float rrow = b == 2 ? 0.f : h2f(R[k]);
+    for (int v = lane; v < dv; v += 32) {
+      float z;
+      if (b == 8) z = static_cast<float>(static_cast<int>(row[v]) - qmax);
+      else if (b == 4) z = static_cast<float>(static_cast<int>((row[v >> 1] >> (4 * (v & 1))) & 15) - qmax);
+      else if (b == 2) z = static_cast<float>((row[v >> 2] >> (2 * (v & 3))) & 3) * 2.0f - 3.0f;
+      else {
+        const uint8_t* t = row + 3 * (v >> 2);
+        const uint32_t wd = t[0] | (static_cast<uint32_t>(t[1]) << 8) | (static_cast<uint32_t>(t[2]) << 16);
+        z = static_cast<float>(static_cast<int>((wd >> (6 * (v & 3))) & 63) - qmax);
+      }
+      const float rf = b == 2 ? h2f(R[k * ng + v / group]) : rrow;
+      T[k * LD + v] = (rf * h2f(C[v])) * z;
     }
-    const float rf = h2f(b == 2 ? R[k * ng + v / group] : R[k]);
-    T[k * LD + v] = (rf * h2f(C[v])) * z;
   }
 }
 
@@ -212,6 +215,123 @@ __device__ void gga_fit_store(float* T, int LD, const float* w, int b, int dk, i
   for (int v = tid; v < dv; v += GNT) C[v] = f2h(cs[v]);
 }
 
+// ---- the same fit + pack for the widths 4 / 6 / 8 with the tile's columns owned by threads ---------------------------
+// Thread (half, col) owns rows [half dk/2, (half + 1) dk/2) of column col (2 dv <= 256 threads, KR = dk / 2 rows).  Its
+// quotients y = x / r stay in registers across the three sweeps (column maximum, refit, final codes), so each element
+// is divided by its row factor once; the division by the column factor is a reciprocal multiply whose candidate code
+// is checked by an exact residual (the IEEE division only near ties, see round_fast), and the division of the column
+// maximum by qmax is taken out of the loop (a positive constant divisor keeps the maximum the maximum).  Codes of a
+// packing unit (2 or 4 adjacent columns) meet in one lane by shuffles.
+__device__ __forceinline__ float gga_code(float y, float c, float rc, float qmax) {
+  const float p = y * rc;
+  float z;
+  if (fabsf(p) < 2097152.0f) {
+    const float t = __fmaf_rn(y, rc, MAGIC);
+    z = t - MAGIC;
+    const float rem = __fmaf_rn(-z, c, y);
+    if (!(fabsf(rem) < c * 0.49998474f)) z = rintf(__fdiv_rn(y, c));
+  } else {
+    z = rintf(__fdiv_rn(y, c));
+  }
+  return fminf(fmaxf(z, -qmax), qmax);
+}
+
+template <int KR>
+__device__ void gga_fit_pack_cols(const float* T, int LD, const float* w, int b, int dv, uint8_t* S, float* rs,
+                                  float* cs, float* ps, float* wsm) {
+  constexpr int dk = 2 * KR;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float qmax = static_cast<float>((1 << (b - 1)) - 1);
+  for (int k = tid; k < dk; k += GNT) wsm[k] = w[k];
+  __syncthreads();
+  // row factors: r = half(sqrt(max(mean |x|, 1e-20) / w)), one warp per row
+  const float inv_dv = 1.0f / dv;
+  for (int k = warp; k < dk; k += GNW) {
+    float sum = 0.f;
+    for (int v = lane; v < dv; v += 32) sum += fabsf(T[k * LD + v]);
+    sum = warp_sum(sum);
+    if (lane == 0) rs[k] = halfc(__fsqrt_rn(__fdiv_rn(fmaxf(sum * inv_dv, 1e-20f), wsm[k])));
+  }
+  __syncthreads();
+  const int half_id = tid / dv, col = tid - half_id * dv;
+  const bool act = tid < 2 * dv;
+  const int k0 = half_id * KR;
+  const float* Tc = T + k0 * LD + col;
+  float y[KR];
+  float m = 0.f;
+  if (act) {
+#pragma unroll
+    for (int i = 0; i < KR; i++) {
+      y[i] = __fdiv_rn(Tc[i * LD], rs[k0 + i]);
+      m = fmaxf(m, fabsf(y[i]));
+    }
+    ps[half_id * dv + col] = m;
+  }
+  __syncthreads();
+  if (tid < dv) cs[tid] = halfc(__fdiv_rn(fmaxf(ps[tid], ps[dv + tid]), qmax));
+  __syncthreads();
+  // weighted least-squares refit of c with the codes fixed
+  if (act) {
+    const float c0 = cs[col], rc0 = rcp_approx(c0);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int i = 0; i < KR; i++) {
+      const float z = gga_code(y[i], c0, rc0, qmax);
+      const float vv = rs[k0 + i] * z, ww = wsm[k0 + i] * wsm[k0 + i];
+      num += (ww * vv) * Tc[i * LD];
+      den += ww * (vv * vv);
+    }
+    ps[half_id * dv + col] = num;
+    ps[2 * dv + half_id * dv + col] = den;
+  }
+  __syncthreads();
+  if (tid < dv) {
+    const float num = ps[tid] + ps[dv + tid], den = ps[2 * dv + tid] + ps[3 * dv + tid];
+    cs[tid] = halfc(den > 0.f ? __fdiv_rn(num, fmaxf(den, 1e-30f)) : cs[tid]);
+  }
+  __syncthreads();
+  // codes with the refitted c, packed along d_v: 8 bit one byte per lane, 4 bit two lanes per byte, 6 bit four lanes
+  // per three bytes
+  const int iq = static_cast<int>(qmax);
+  const int rowb = dv * b / 8;
+  const float c1 = act ? cs[col] : 1.0f, rc1 = rcp_approx(c1);
+  if (tid < 2 * dv || (GNT > 2 * dv && (tid & ~31) < 2 * dv)) {      // whole warps, for the shuffles
+#pragma unroll
+    for (int i = 0; i < KR; i++) {
+      const int u = act ? static_cast<int>(gga_code(y[i], c1, rc1, qmax)) + iq : 0;
+      uint8_t* row = S + static_cast<size_t>(k0 + i) * rowb;
+      if (b == 8) {
+        if (act) row[col] = static_cast<uint8_t>(u);
+      } else if (b == 4) {
+        const int hi = __shfl_down_sync(0xffffffffu, u, 1);
+        if (act && !(col & 1)) row[col >> 1] = static_cast<uint8_t>(u | (hi << 4));
+      } else {
+        const int u1 = __shfl_down_sync(0xffffffffu, u, 1), u2 = __shfl_down_sync(0xffffffffu, u, 2),
+                  u3 = __shfl_down_sync(0xffffffffu, u, 3);
+        if (act && !(col & 3)) {
+          const uint32_t wd = static_cast<uint32_t>(u) | (static_cast<uint32_t>(u1) << 6) |
+                              (static_cast<uint32_t>(u2) << 12) | (static_cast<uint32_t>(u3) << 18);
+          uint8_t* p = row + 3 * (col >> 2);
+          p[0] = static_cast<uint8_t>(wd & 255u); p[1] = static_cast<uint8_t>((wd >> 8) & 255u); p[2] = static_cast<uint8_t>(wd >> 16);
+        }
+      }
+    }
+  }
+  unsigned short* R = reinterpret_cast<unsigned short*>(S + static_cast<size_t>(dk) * dv * b / 8);
+  for (int i = tid; i < dk; i += GNT) R[i] = f2h(rs[i]);
+  unsigned short* C = R + dk;
+  for (int v = tid; v < dv; v += GNT) C[v] = f2h(cs[v]);
+}
+
+// fit + pack, picking the column-owner version where it applies
+__device__ __forceinline__ void gga_fit_pack(float* T, int LD, const float* w, int b, int dk, int dv, int group,
+                                             uint8_t* S, float* rs, float* cs, float* ps, float* wsm) {
+  const bool cols = (b == 4 || b == 6 || b == 8) && 2 * dv <= GNT && dv % 32 == 0;
+  if (cols && dk == 128) gga_fit_pack_cols<64>(T, LD, w, b, dv, S, rs, cs, ps, wsm);
+  else if (cols && dk == 64) gga_fit_pack_cols<32>(T, LD, w, b, dv, S, rs, cs, ps, wsm);
+  else gga_fit_store(T, LD, w, b, dk, dv, group, S, nullptr, rs, cs, ps, wsm);
+}
+
 // shared-memory plan (floats) of the GGA kernels
 struct GgaSmem { int T, q, k, bk, v, o, kO, rs, cs, ps, wsm, Pw, Vw, r0, coef, red, total, LD; };
 __host__ __device__ inline GgaSmem gga_smem(int dk, int dv, int M, int group) {
@@ -286,9 +406,9 @@ __global__ void __launch_bounds__(GNT) gga_step_kernel(const __grid_constant__ G
   if (tid < dv) kO[tid] = kO[tid] + kO[dv + tid];
   __syncthreads();
   // A O in place
-  for (int e = tid; e < dk * dv; e += GNT) {
-    const int i = e / dv, j = e - i * dv;
-    T[i * LD + j] = a * (T[i * LD + j] - bk[i] * kO[j]);
+  for (int i = warp; i < dk; i += GNW) {
+    const float bki = bk[i];
+    for (int j = lane; j < dv; j += 32) T[i * LD + j] = a * (T[i * LD + j] - bki * kO[j]);
   }
   __syncthreads();
   if (act) {
@@ -349,9 +469,9 @@ __global__ void __launch_bounds__(GNT) gga_step_kernel(const __grid_constant__ G
       o[tid] = acc;
     }
     if (n == M) {                                               // merge the evicted (oldest) pair into the state
-      for (int e = tid; e < dk * dv; e += GNT) {
-        const int i = e / dv, j = e - i * dv;
-        T[i * LD + j] = T[i * LD + j] + Pw[i] * Vw[j];
+      for (int i = warp; i < dk; i += GNW) {
+        const float pi = Pw[i];
+        for (int j = lane; j < dv; j += 32) T[i * LD + j] = T[i * LD + j] + pi * Vw[j];
       }
     }
     // enqueue (R(beta k), R(v)) at the slot after the youngest pair (the evicted one's when the window is full)
@@ -369,15 +489,14 @@ __global__ void __launch_bounds__(GNT) gga_step_kernel(const __grid_constant__ G
       if (lane == 0) (warp == 0 ? PS : VS)[jn] = sc;
     }
   } else {
-    for (int e = tid; e < dk * dv; e += GNT) {
-      const int i = e / dv, j = e - i * dv;
-      T[i * LD + j] = T[i * LD + j] + bk[i] * v[j];
+    for (int i = warp; i < dk; i += GNW) {
+      const float bki = bk[i];
+      for (int j = lane; j < dv; j += 32) T[i * LD + j] = T[i * LD + j] + bki * v[j];
     }
   }
   __syncthreads();
   for (int j = tid; j < dv; j += GNT) stf(orow, A.dt_out, j, o[j]);
-  gga_fit_store(T, LD, A.w + (long long)h * dk, bits, dk, dv, A.group, S, nullptr, gsm + P.rs, gsm + P.cs, gsm + P.ps,
-                gsm + P.wsm);
+  gga_fit_pack(T, LD, A.w + (long long)h * dk, bits, dk, dv, A.group, S, gsm + P.rs, gsm + P.cs, gsm + P.ps, gsm + P.wsm);
 }
 
 // window counters, after every head of the slot has read them
@@ -405,8 +524,8 @@ __global__ void __launch_bounds__(GNT) gga_store_kernel(const __grid_constant__ 
   for (int e = tid; e < dk * dv; e += GNT) T[(e / dv) * P.LD + (e % dv)] = x[e];
   __syncthreads();
   uint8_t* base = A.blob + seq * A.stride;
-  gga_fit_store(T, P.LD, A.w + (long long)h * dk, A.bits[h], dk, dv, A.group, base + A.offs[h], nullptr, gsm + P.rs,
-                gsm + P.cs, gsm + P.ps, gsm + P.wsm);
+  gga_fit_pack(T, P.LD, A.w + (long long)h * dk, A.bits[h], dk, dv, A.group, base + A.offs[h], gsm + P.rs, gsm + P.cs,
+               gsm + P.ps, gsm + P.wsm);
   if (h == 0 && tid < 2) reinterpret_cast<int*>(base)[tid] = 0;
 }
 

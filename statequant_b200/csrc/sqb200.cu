@@ -201,6 +201,37 @@ int sqb_device_status(int* wait_timeouts) {
   return 0;
 }
 
+namespace {
+int slot_io_args(const sqb_state_t* st, int kind, const int32_t* idx, int32_t rows, sqb::StepArgs& a) {
+  int lpr_log2 = 0;
+  if (kind < 0 || kind > 2) return fail(SQB_EINVAL, "kind %d is not 0 (GDN), 1 (Mamba2) or 2 (KDA)", kind);
+  if (int rc = check_state(st, kind, &lpr_log2)) return rc;
+  if (rows < 0) return fail(SQB_EINVAL, "rows %d < 0", rows);
+  memset(&a, 0, sizeof a);
+  fill_state(a, st, lpr_log2);
+  a.rows = rows; a.idx = idx; a.per_key_head = 1;
+  if (!tma_ok(a, st->bits, st->bits > 8 || st->axis_k, kind == sqb::K_KDA))
+    return fail(SQB_EINVAL, "the device read / write kernels take 4 / 8-bit states with d_k 64 or 128 and 16-byte aligned fields");
+  return 0;
+}
+}  // namespace
+
+int sqb_slot_read(const sqb_state_t* st, int kind, const int32_t* idx, int32_t rows, float* out, void* stream) {
+  sqb::StepArgs a;
+  if (int rc = slot_io_args(st, kind, idx, rows, a)) return rc;
+  if (!out) return fail(SQB_EINVAL, "out is NULL");
+  if (rows == 0) return 0;
+  return sub_rc(sqb::launch_read(kind, a, st->bits, st->axis_k, out, static_cast<cudaStream_t>(stream)));
+}
+
+int sqb_slot_write(const sqb_state_t* st, int kind, const int32_t* idx, int32_t rows, const float* S, void* stream) {
+  sqb::StepArgs a;
+  if (int rc = slot_io_args(st, kind, idx, rows, a)) return rc;
+  if (!S) return fail(SQB_EINVAL, "S is NULL");
+  if (rows == 0) return 0;
+  return sub_rc(sqb::launch_write(kind, a, st->bits, st->axis_k, S, static_cast<cudaStream_t>(stream)));
+}
+
 int sqb_gdn_step(const sqb_state_t* st, const sqb_gdn_inputs_t* in, void* stream) {
   int lpr_log2 = 0;
   if (int rc = check_state(st, sqb::K_GDN, &lpr_log2)) return rc;

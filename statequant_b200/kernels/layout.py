@@ -17,6 +17,7 @@ so a blob written by the reference can be stepped by these kernels and the other
 """
 from __future__ import annotations
 
+import ctypes
 import math
 
 import torch
@@ -121,12 +122,29 @@ class BlobLayout:
             self._structs[key] = st
         return st
 
-    # -- prefill side (torch) -------------------------------------------------------------------------------
+    # -- prefill side: device kernels for CUDA blobs of the 4 / 8-bit formats, torch otherwise -------------------
+    def _device_io(self, views):
+        """True if the slot read / write kernels take this layout and blob (4 / 8-bit state, d_k 64 or 128, groups
+        the kernels support, blob on a GPU)."""
+        if self.fmt is None or not views['S'].is_cuda or self.DK not in (64, 128):
+            return False
+        g = self.group
+        if self.axk:
+            return g % 16 == 0 and self.DK % g == 0
+        rpp = 32 // (self.DK // 16)
+        return g % rpp == 0 and self.DV % g == 0 and self.DV % (4 * rpp) == 0 and g // (rpp * min(4, g // rpp)) <= 2
+
     @torch.no_grad()
     def read(self, views, idx):
         """Current state of slots ``idx`` as fp32 ``[P, HV, d_v, d_k]``: the stored state advanced across its
         pending buffer, S_n = a_n S_0 + sum_{i<n} (a_n / a_i) u_i k_i^T (KDA: the decays per key channel).
         Slots holding garbage give garbage.  Reference: ``slots.py:210-233``, ``kda.py:351-372``."""
+        if self._device_io(views):
+            i32 = idx.to(torch.int32).contiguous()
+            out = torch.empty(i32.shape[0], self.HV, self.DV, self.DK, dtype=torch.float32, device=i32.device)
+            _cabi.check(_cabi.lib().sqb_slot_read(ctypes.byref(self._struct(views)), self.kind, i32.data_ptr(),
+                                                  i32.shape[0], out.data_ptr(), _cabi.current_stream(i32.device)), 'sqb_slot_read')
+            return out
         idx = idx.long()
         P, m = idx.shape[0], self.m
         V = views
@@ -156,6 +174,12 @@ class BlobLayout:
     def write(self, views, idx, S):
         """Store states ``S [P, HV, d_v, d_k]`` packed into slots ``idx`` and empty their buffers (counter and
         running decay zeroed).  Reference: ``slots.py:236-252``."""
+        if self._device_io(views):
+            i32 = idx.to(torch.int32).contiguous()
+            X = S.reshape(i32.shape[0], self.HV, self.DV, self.DK).to(device=i32.device, dtype=torch.float32).contiguous()
+            _cabi.check(_cabi.lib().sqb_slot_write(ctypes.byref(self._struct(views)), self.kind, i32.data_ptr(),
+                                                   i32.shape[0], X.data_ptr(), _cabi.current_stream(i32.device)), 'sqb_slot_write')
+            return
         idx = idx.long()
         P = idx.shape[0]
         V = views

@@ -376,3 +376,43 @@ def test_bad_tensors_raise():
         l2.step(l2.views(b2), torch.tensor([1], dtype=torch.int32, device=DEV), torch.zeros(1, 2, 96, device=DEV),
                 torch.zeros(1, 2, 96, device=DEV), torch.zeros(1, 4, 128, device=DEV), torch.zeros(1, 4, 128, device=DEV),
                 1.0, g=torch.zeros(1, 4, device=DEV), beta=torch.zeros(1, 4, device=DEV))
+
+
+@pytest.mark.parametrize('kind,fmt', [('gdn', (4, 'k', 64)), ('gdn', (8, 'k', 32)), ('gdn', (4, 'v', 32)),
+                                      ('gdn', (8, 'v', 32)), ('m2', (8, 'k', 32)), ('kda', (4, 'k', 64))])
+def test_device_read_write_match_torch(kind, fmt):
+    """The device-side prefill boundary: write packs byte for byte like the torch packer, read gives the state
+    advanced across the pending buffer (reference: slots.py:210-252, kda.py:351-386)."""
+    g0 = torch.Generator().manual_seed(5)
+    q = sq.Quantizer(*fmt)
+    if kind == 'gdn':
+        lay = SlotLayout(q, 8, 4, 128, 128, m=8)
+    elif kind == 'm2':
+        lay = Mamba2SlotLayout(q, 8, 2, 128, 64, m=8)
+    else:
+        lay = KDASlotLayout(q, 4, 128, 128, m=8)
+    hv, dk, dv = lay.HV, lay.DK, lay.DV
+    P = 5
+    blob = lay.alloc(P + 2, DEV)
+    blob.random_(0, 255)                                   # garbage everywhere: write must leave a clean slot
+    V = lay.views(blob)
+    idx = torch.tensor([3, 1, 6, 2, 5], dtype=torch.int32, device=DEV)
+    S = torch.randn(P, hv, dv, dk, generator=g0) * torch.rand(P, hv, dv, 1, generator=g0) * 0.5
+    assert lay._device_io(V)
+    lay.write(V, idx, S.to(DEV))
+    hb = torch.zeros(P + 2, lay.nbytes, dtype=torch.uint8)
+    Vh = lay.views(hb)
+    lay.write(Vh, idx.cpu(), S)                            # the torch path on a host blob
+    for f in ('S', 'SC', 'NPTR', 'GCUR'):
+        assert torch.equal(V[f][idx.long()].cpu(), Vh[f][idx.long().cpu()]), f
+    # a few decode steps on the device, reading after each: the device read-out against torch on the same bytes
+    c = dict(kind=kind, fmt=fmt, B=P, hv=hv, hk=lay.HK, dk=dk, dv=dv, m=8, bb=8, T=5, seed=9)
+    inp = make_inputs(c)
+    for t in range(5):
+        args = {k: v.to(DEV) for k, v in step_args(c, inp, t, torch.float32).items()}
+        out_d = torch.empty(P, hv, dv, device=DEV)
+        run_step(c, lay, V, idx, args, out_d, inp)
+        got = lay.read(V, idx).cpu()
+        want = lay.read(lay.views(blob.cpu()), idx.cpu())   # the torch path on the same bytes
+        assert ((got - want).abs().max() / want.abs().max()).item() < 1e-5, t
+    assert int(V['NPTR'][idx.long(), 0].max()) == 5         # reading leaves the slots alone
