@@ -216,55 +216,50 @@ __device__ void gga_fit_store(float* T, int LD, const float* w, int b, int dk, i
 }
 
 // ---- the same fit + pack for the widths 4 / 6 / 8 with the tile's columns owned by threads ---------------------------
-// Thread (half, col) owns rows [half dk/2, (half + 1) dk/2) of column col (2 dv <= 256 threads, KR = dk / 2 rows).  Its
-// quotients y = x / r stay in registers across the three sweeps (column maximum, refit, final codes), so each element
-// is divided by its row factor once; the division by the column factor is a reciprocal multiply whose candidate code
-// is checked by an exact residual (the IEEE division only near ties, see round_fast), and the division of the column
-// maximum by qmax is taken out of the loop (a positive constant divisor keeps the maximum the maximum).  Codes of a
-// packing unit (2 or 4 adjacent columns) meet in one lane by shuffles.
-__device__ __forceinline__ float gga_code(float y, float c, float rc, float qmax) {
-  const float p = y * rc;
-  float z;
-  if (fabsf(p) < 2097152.0f) {
-    const float t = __fmaf_rn(y, rc, MAGIC);
-    z = t - MAGIC;
-    const float rem = __fmaf_rn(-z, c, y);
-    if (!(fabsf(rem) < c * 0.49998474f)) z = rintf(__fdiv_rn(y, c));
-  } else {
-    z = rintf(__fdiv_rn(y, c));
-  }
-  return fminf(fmaxf(z, -qmax), qmax);
+// Thread (half, col) owns rows [half dk/2, (half + 1) dk/2) of column col (2 dv <= 256 threads) in the three sweeps
+// (column maximum, refit, final codes).  Both divisors of an element, its row factor and its column factor, are fp16
+// values, and for such divisors x / d is exactly fma(fma(-d, x rd, x), rd, x rd) with rd = RN(1 / d) whenever the
+// quotient is far from the subnormal and overflow ranges (checked on the host for every fp16 divisor against
+// hundreds of millions of dividends), so the sweeps recompute the quotients with three FMAs instead of keeping them;
+// the division of the column maximum by qmax is taken out of the loop (a positive constant divisor keeps the
+// maximum the maximum).  Codes of a packing unit (2 or 4 adjacent columns) meet in one lane by shuffles.
+__device__ __forceinline__ float div_h16(float x, float d, float rd) {
+  const float q0 = x * rd;
+  const float q1 = __fmaf_rn(__fmaf_rn(-d, q0, x), rd, q0);
+  const bool safe = fabsf(x) > 1e-24f && fabsf(q1) < 1e24f;
+  return (safe || x == 0.f) ? q1 : __fdiv_rn(x, d);
 }
 
-template <int KR>
-__device__ void gga_fit_pack_cols(const float* T, int LD, const float* w, int b, int dv, uint8_t* S, float* rs,
-                                  float* cs, float* ps, float* wsm) {
-  constexpr int dk = 2 * KR;
+template <int B>
+__device__ void gga_fit_pack_cols(const float* T, int LD, const float* w, int dk, int dv, uint8_t* S, float* rs,
+                                  float* cs, float* ps, float* wsm, float* rrs) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const float qmax = static_cast<float>((1 << (b - 1)) - 1);
+  constexpr float qmax = static_cast<float>((1 << (B - 1)) - 1);
+  constexpr int iq = (1 << (B - 1)) - 1;
+  const int KR = dk / 2;
   for (int k = tid; k < dk; k += GNT) wsm[k] = w[k];
   __syncthreads();
-  // row factors: r = half(sqrt(max(mean |x|, 1e-20) / w)), one warp per row
+  // row factors: r = half(sqrt(max(mean |x|, 1e-20) / w)), one warp per row; and their reciprocals
   const float inv_dv = 1.0f / dv;
   for (int k = warp; k < dk; k += GNW) {
     float sum = 0.f;
     for (int v = lane; v < dv; v += 32) sum += fabsf(T[k * LD + v]);
     sum = warp_sum(sum);
-    if (lane == 0) rs[k] = halfc(__fsqrt_rn(__fdiv_rn(fmaxf(sum * inv_dv, 1e-20f), wsm[k])));
+    if (lane == 0) {
+      const float r = halfc(__fsqrt_rn(__fdiv_rn(fmaxf(sum * inv_dv, 1e-20f), wsm[k])));
+      rs[k] = r;
+      rrs[k] = __frcp_rn(r);
+    }
   }
   __syncthreads();
   const int half_id = tid / dv, col = tid - half_id * dv;
   const bool act = tid < 2 * dv;
   const int k0 = half_id * KR;
   const float* Tc = T + k0 * LD + col;
-  float y[KR];
-  float m = 0.f;
   if (act) {
-#pragma unroll
-    for (int i = 0; i < KR; i++) {
-      y[i] = __fdiv_rn(Tc[i * LD], rs[k0 + i]);
-      m = fmaxf(m, fabsf(y[i]));
-    }
+    float m = 0.f;
+#pragma unroll 4
+    for (int i = 0; i < KR; i++) m = fmaxf(m, fabsf(div_h16(Tc[i * LD], rs[k0 + i], rrs[k0 + i])));
     ps[half_id * dv + col] = m;
   }
   __syncthreads();
@@ -272,13 +267,14 @@ __device__ void gga_fit_pack_cols(const float* T, int LD, const float* w, int b,
   __syncthreads();
   // weighted least-squares refit of c with the codes fixed
   if (act) {
-    const float c0 = cs[col], rc0 = rcp_approx(c0);
+    const float c0 = cs[col], rc0 = __frcp_rn(c0);
     float num = 0.f, den = 0.f;
-#pragma unroll
+#pragma unroll 4
     for (int i = 0; i < KR; i++) {
-      const float z = gga_code(y[i], c0, rc0, qmax);
-      const float vv = rs[k0 + i] * z, ww = wsm[k0 + i] * wsm[k0 + i];
-      num += (ww * vv) * Tc[i * LD];
+      const float x = Tc[i * LD], r = rs[k0 + i];
+      const float z = fminf(fmaxf(rintf(div_h16(div_h16(x, r, rrs[k0 + i]), c0, rc0)), -qmax), qmax);
+      const float vv = r * z, ww = wsm[k0 + i] * wsm[k0 + i];
+      num += (ww * vv) * x;
       den += ww * (vv * vv);
     }
     ps[half_id * dv + col] = num;
@@ -292,17 +288,18 @@ __device__ void gga_fit_pack_cols(const float* T, int LD, const float* w, int b,
   __syncthreads();
   // codes with the refitted c, packed along d_v: 8 bit one byte per lane, 4 bit two lanes per byte, 6 bit four lanes
   // per three bytes
-  const int iq = static_cast<int>(qmax);
-  const int rowb = dv * b / 8;
-  const float c1 = act ? cs[col] : 1.0f, rc1 = rcp_approx(c1);
-  if (tid < 2 * dv || (GNT > 2 * dv && (tid & ~31) < 2 * dv)) {      // whole warps, for the shuffles
-#pragma unroll
+  constexpr int rowb_num = B;                                        // row bytes = dv * B / 8
+  const int rowb = dv * rowb_num / 8;
+  const float c1 = act ? cs[col] : 1.0f, rc1 = __frcp_rn(c1);
+  if ((tid & ~31) < 2 * dv) {                                        // whole warps, for the shuffles
+#pragma unroll 4
     for (int i = 0; i < KR; i++) {
-      const int u = act ? static_cast<int>(gga_code(y[i], c1, rc1, qmax)) + iq : 0;
+      int u = 0;
+      if (act) u = static_cast<int>(fminf(fmaxf(rintf(div_h16(div_h16(Tc[i * LD], rs[k0 + i], rrs[k0 + i]), c1, rc1)), -qmax), qmax)) + iq;
       uint8_t* row = S + static_cast<size_t>(k0 + i) * rowb;
-      if (b == 8) {
+      if constexpr (B == 8) {
         if (act) row[col] = static_cast<uint8_t>(u);
-      } else if (b == 4) {
+      } else if constexpr (B == 4) {
         const int hi = __shfl_down_sync(0xffffffffu, u, 1);
         if (act && !(col & 1)) row[col >> 1] = static_cast<uint8_t>(u | (hi << 4));
       } else {
@@ -317,7 +314,7 @@ __device__ void gga_fit_pack_cols(const float* T, int LD, const float* w, int b,
       }
     }
   }
-  unsigned short* R = reinterpret_cast<unsigned short*>(S + static_cast<size_t>(dk) * dv * b / 8);
+  unsigned short* R = reinterpret_cast<unsigned short*>(S + static_cast<size_t>(dk) * dv * B / 8);
   for (int i = tid; i < dk; i += GNT) R[i] = f2h(rs[i]);
   unsigned short* C = R + dk;
   for (int v = tid; v < dv; v += GNT) C[v] = f2h(cs[v]);
@@ -325,15 +322,16 @@ __device__ void gga_fit_pack_cols(const float* T, int LD, const float* w, int b,
 
 // fit + pack, picking the column-owner version where it applies
 __device__ __forceinline__ void gga_fit_pack(float* T, int LD, const float* w, int b, int dk, int dv, int group,
-                                             uint8_t* S, float* rs, float* cs, float* ps, float* wsm) {
-  const bool cols = (b == 4 || b == 6 || b == 8) && 2 * dv <= GNT && dv % 32 == 0;
-  if (cols && dk == 128) gga_fit_pack_cols<64>(T, LD, w, b, dv, S, rs, cs, ps, wsm);
-  else if (cols && dk == 64) gga_fit_pack_cols<32>(T, LD, w, b, dv, S, rs, cs, ps, wsm);
+                                             uint8_t* S, float* rs, float* cs, float* ps, float* wsm, float* rrs) {
+  const bool cols = 2 * dv <= GNT && dv % 32 == 0 && dk % 2 == 0;
+  if (cols && b == 4) gga_fit_pack_cols<4>(T, LD, w, dk, dv, S, rs, cs, ps, wsm, rrs);
+  else if (cols && b == 6) gga_fit_pack_cols<6>(T, LD, w, dk, dv, S, rs, cs, ps, wsm, rrs);
+  else if (cols && b == 8) gga_fit_pack_cols<8>(T, LD, w, dk, dv, S, rs, cs, ps, wsm, rrs);
   else gga_fit_store(T, LD, w, b, dk, dv, group, S, nullptr, rs, cs, ps, wsm);
 }
 
 // shared-memory plan (floats) of the GGA kernels
-struct GgaSmem { int T, q, k, bk, v, o, kO, rs, cs, ps, wsm, Pw, Vw, r0, coef, red, total, LD; };
+struct GgaSmem { int T, q, k, bk, v, o, kO, rs, rrs, cs, ps, wsm, Pw, Vw, r0, coef, red, total, LD; };
 __host__ __device__ inline GgaSmem gga_smem(int dk, int dv, int M, int group) {
   GgaSmem s;
   int o = 0;
@@ -342,6 +340,7 @@ __host__ __device__ inline GgaSmem gga_smem(int dk, int dv, int M, int group) {
   s.q = o; o += dk; s.k = o; o += dk; s.bk = o; o += dk;
   s.v = o; o += dv; s.o = o; o += dv; s.kO = o; o += 2 * dv;
   s.rs = o; o += dk * (dv / group > 0 ? dv / group : 1);
+  s.rrs = o; o += dk;
   s.cs = o; o += dv; s.ps = o; o += 4 * dv; s.wsm = o; o += dk;
   s.Pw = o; o += M * dk; s.Vw = o; o += M * dv; s.r0 = o; o += dk; s.coef = o; o += 32; s.red = o; o += 16;
   s.total = o;
@@ -496,7 +495,8 @@ __global__ void __launch_bounds__(GNT) gga_step_kernel(const __grid_constant__ G
   }
   __syncthreads();
   for (int j = tid; j < dv; j += GNT) stf(orow, A.dt_out, j, o[j]);
-  gga_fit_pack(T, LD, A.w + (long long)h * dk, bits, dk, dv, A.group, S, gsm + P.rs, gsm + P.cs, gsm + P.ps, gsm + P.wsm);
+  gga_fit_pack(T, LD, A.w + (long long)h * dk, bits, dk, dv, A.group, S, gsm + P.rs, gsm + P.cs, gsm + P.ps, gsm + P.wsm,
+               gsm + P.rrs);
 }
 
 // window counters, after every head of the slot has read them
@@ -525,7 +525,7 @@ __global__ void __launch_bounds__(GNT) gga_store_kernel(const __grid_constant__ 
   __syncthreads();
   uint8_t* base = A.blob + seq * A.stride;
   gga_fit_pack(T, P.LD, A.w + (long long)h * dk, A.bits[h], dk, dv, A.group, base + A.offs[h], gsm + P.rs, gsm + P.cs,
-               gsm + P.ps, gsm + P.wsm);
+               gsm + P.ps, gsm + P.wsm, gsm + P.rrs);
   if (h == 0 && tid < 2) reinterpret_cast<int*>(base)[tid] = 0;
 }
 

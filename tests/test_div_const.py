@@ -12,3 +12,13 @@ def test_fma_division_by_qmax_is_exact(tmp_path):
     r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout
     assert r.stdout.count('mismatches 0') == 2, r.stdout
+
+
+def test_fma_division_by_fp16_factor_is_exact(tmp_path):
+    """GGA's row and column factors are fp16 values; the kernels divide by them with a multiply and two FMAs."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    exe = str(tmp_path / 'div_h16_check')
+    subprocess.run(['gcc', '-O2', '-fopenmp', '-ffp-contract=off', '-o', exe, os.path.join(here, 'div_h16_check.c'), '-lm'],
+                   check=True)
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and 'mismatches 0 ' in r.stdout, r.stdout
