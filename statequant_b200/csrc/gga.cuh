@@ -90,6 +90,31 @@ __device__ void gga_decode_head(const uint8_t* S, int b, int dk, int dv, int gro
   const unsigned short* C = R + nr;
   const int rowb = dv * b / 8;
   const int lane = tid & 31, warp = tid >> 5;
+  if (b != 2 && dv <= 128) {
+    // widths 4 / 6 / 8: a row per warp, lane l takes columns l, l + 32, l + 64, l + 96 (column factors in registers)
+    float cf[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) cf[j] = lane + 32 * j < dv ? h2f(C[lane + 32 * j]) : 0.f;
+    auto rows = [&](auto code_of) {
+      for (int k = warp; k < dk; k += GNW) {
+        const uint8_t* row = S + static_cast<size_t>(k) * rowb;
+        const float rrow = h2f(R[k]);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          const int v = lane + 32 * j;
+          if (v < dv) T[k * LD + v] = (rrow * cf[j]) * static_cast<float>(code_of(row, v) - qmax);
+        }
+      }
+    };
+    if (b == 8) rows([](const uint8_t* row, int v) { return static_cast<int>(row[v]); });
+    else if (b == 4) rows([](const uint8_t* row, int v) { return static_cast<int>((row[v >> 1] >> (4 * (v & 1))) & 15); });
+    else rows([](const uint8_t* row, int v) {
+      const uint8_t* t = row + 3 * (v >> 2);
+      const uint32_t wd = t[0] | (static_cast<uint32_t>(t[1]) << 8) | (static_cast<uint32_t>(t[2]) << 16);
+      return static_cast<int>((wd >> (6 * (v & 3))) & 63);
+    });
+    return;
+  }
   for (int k = warp; k < dk; k += GNW) {                      // a row per warp, the columns over the lanes
     const uint8_t* row = S + static_cast<size_t>(k) * rowb;
     const float rrow = b == 2 ? 0.f : h2f(R[k]);
@@ -223,16 +248,16 @@ __device__ void gga_fit_store(float* T, int LD, const float* w, int b, int dk, i
 // hundreds of millions of dividends), so the sweeps recompute the quotients with three FMAs instead of keeping them;
 // the division of the column maximum by qmax is taken out of the loop (a positive constant divisor keeps the
 // maximum the maximum).  Codes of a packing unit (2 or 4 adjacent columns) meet in one lane by shuffles.
+// The range condition is checked once per head on the tile (all non-zero |x| within [1e-14, 1e14]: with factors in
+// [2^-24, 65504] every quotient then stays within [1e-24, 1e30]); a head outside it takes gga_fit_store.
 __device__ __forceinline__ float div_h16(float x, float d, float rd) {
   const float q0 = x * rd;
-  const float q1 = __fmaf_rn(__fmaf_rn(-d, q0, x), rd, q0);
-  const bool safe = fabsf(x) > 1e-24f && fabsf(q1) < 1e24f;
-  return (safe || x == 0.f) ? q1 : __fdiv_rn(x, d);
+  return __fmaf_rn(__fmaf_rn(-d, q0, x), rd, q0);
 }
 
 template <int B>
-__device__ void gga_fit_pack_cols(const float* T, int LD, const float* w, int dk, int dv, uint8_t* S, float* rs,
-                                  float* cs, float* ps, float* wsm, float* rrs) {
+__device__ bool gga_fit_pack_cols(const float* T, int LD, const float* w, int dk, int dv, uint8_t* S, float* rs,
+                                  float* cs, float* ps, float* wsm, float* rrs, float* red) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr float qmax = static_cast<float>((1 << (B - 1)) - 1);
   constexpr int iq = (1 << (B - 1)) - 1;
@@ -241,9 +266,15 @@ __device__ void gga_fit_pack_cols(const float* T, int LD, const float* w, int dk
   __syncthreads();
   // row factors: r = half(sqrt(max(mean |x|, 1e-20) / w)), one warp per row; and their reciprocals
   const float inv_dv = 1.0f / dv;
+  float hi = 0.f, lo = 1.0f;                                         // largest |x|, smallest non-zero |x| (capped at 1)
   for (int k = warp; k < dk; k += GNW) {
     float sum = 0.f;
-    for (int v = lane; v < dv; v += 32) sum += fabsf(T[k * LD + v]);
+    for (int v = lane; v < dv; v += 32) {
+      const float ax = fabsf(T[k * LD + v]);
+      sum += ax;
+      hi = fmaxf(hi, ax);
+      lo = fminf(lo, ax > 0.f ? ax : 1.0f);
+    }
     sum = warp_sum(sum);
     if (lane == 0) {
       const float r = halfc(__fsqrt_rn(__fdiv_rn(fmaxf(sum * inv_dv, 1e-20f), wsm[k])));
@@ -251,6 +282,9 @@ __device__ void gga_fit_pack_cols(const float* T, int LD, const float* w, int dk
       rrs[k] = __frcp_rn(r);
     }
   }
+  hi = block_reduce256<true>(hi, red);
+  lo = -block_reduce256<true>(-lo, red);
+  if (!(hi < 1e14f && lo > 1e-14f)) return false;                    // uniform: the caller takes the IEEE path
   __syncthreads();
   const int half_id = tid / dv, col = tid - half_id * dv;
   const bool act = tid < 2 * dv;
@@ -318,16 +352,22 @@ __device__ void gga_fit_pack_cols(const float* T, int LD, const float* w, int dk
   for (int i = tid; i < dk; i += GNT) R[i] = f2h(rs[i]);
   unsigned short* C = R + dk;
   for (int v = tid; v < dv; v += GNT) C[v] = f2h(cs[v]);
+  return true;
 }
 
 // fit + pack, picking the column-owner version where it applies
 __device__ __forceinline__ void gga_fit_pack(float* T, int LD, const float* w, int b, int dk, int dv, int group,
-                                             uint8_t* S, float* rs, float* cs, float* ps, float* wsm, float* rrs) {
+                                             uint8_t* S, float* rs, float* cs, float* ps, float* wsm, float* rrs,
+                                             float* red) {
   const bool cols = 2 * dv <= GNT && dv % 32 == 0 && dk % 2 == 0;
-  if (cols && b == 4) gga_fit_pack_cols<4>(T, LD, w, dk, dv, S, rs, cs, ps, wsm, rrs);
-  else if (cols && b == 6) gga_fit_pack_cols<6>(T, LD, w, dk, dv, S, rs, cs, ps, wsm, rrs);
-  else if (cols && b == 8) gga_fit_pack_cols<8>(T, LD, w, dk, dv, S, rs, cs, ps, wsm, rrs);
-  else gga_fit_store(T, LD, w, b, dk, dv, group, S, nullptr, rs, cs, ps, wsm);
+  bool done = false;
+  if (cols && b == 4) done = gga_fit_pack_cols<4>(T, LD, w, dk, dv, S, rs, cs, ps, wsm, rrs, red);
+  else if (cols && b == 6) done = gga_fit_pack_cols<6>(T, LD, w, dk, dv, S, rs, cs, ps, wsm, rrs, red);
+  else if (cols && b == 8) done = gga_fit_pack_cols<8>(T, LD, w, dk, dv, S, rs, cs, ps, wsm, rrs, red);
+  if (!done) {
+    __syncthreads();
+    gga_fit_store(T, LD, w, b, dk, dv, group, S, nullptr, rs, cs, ps, wsm);
+  }
 }
 
 // shared-memory plan (floats) of the GGA kernels
@@ -496,7 +536,7 @@ __global__ void __launch_bounds__(GNT) gga_step_kernel(const __grid_constant__ G
   __syncthreads();
   for (int j = tid; j < dv; j += GNT) stf(orow, A.dt_out, j, o[j]);
   gga_fit_pack(T, LD, A.w + (long long)h * dk, bits, dk, dv, A.group, S, gsm + P.rs, gsm + P.cs, gsm + P.ps, gsm + P.wsm,
-               gsm + P.rrs);
+               gsm + P.rrs, gsm + P.red);
 }
 
 // window counters, after every head of the slot has read them
@@ -525,7 +565,7 @@ __global__ void __launch_bounds__(GNT) gga_store_kernel(const __grid_constant__ 
   __syncthreads();
   uint8_t* base = A.blob + seq * A.stride;
   gga_fit_pack(T, P.LD, A.w + (long long)h * dk, A.bits[h], dk, dv, A.group, base + A.offs[h], gsm + P.rs, gsm + P.cs,
-               gsm + P.ps, gsm + P.wsm, gsm + P.rrs);
+               gsm + P.ps, gsm + P.wsm, gsm + P.rrs, gsm + P.red);
   if (h == 0 && tid < 2) reinterpret_cast<int*>(base)[tid] = 0;
 }
 
