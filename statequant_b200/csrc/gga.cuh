@@ -1,7 +1,7 @@
 // GGA / STEP mixed-bit state with the pure-write window (PW-S m): the fused decode step, the prefill-side
 // store / load, and STEP's dual-axis fit as a stand-alone pass.
 //
-// One CTA (256 threads) per (batch row, value head) holds the head's whole [d_k, d_v] tile in shared memory
+// One CTA (512 threads) per (batch row, value head) holds the head's whole [d_k, d_v] tile in shared memory
 // (fp32, rows padded by one float so that row-wise and column-wise sweeps are both free of bank conflicts):
 //   decode codes -> O;  A O = a (O - beta k (k^T O));  the queued left factors are propagated and re-encoded in FP8,
 //   one warp per window row;  o = (A O)^T q + sum_i (R(A p_i) . q) v_i + (beta k . q) v;  the evicted pair is merged;
@@ -17,8 +17,8 @@
 
 namespace sqb {
 
-constexpr int GNT = 256;   // threads per CTA of the GGA kernels
-constexpr int GNW = 8;
+constexpr int GNT = 512;   // threads per CTA of the GGA kernels
+constexpr int GNW = 16;
 
 struct GgaArgs {
   uint8_t* blob; long long stride;
@@ -42,7 +42,8 @@ __device__ __forceinline__ float e4m3_round(float y) {
   int e = static_cast<int>((__float_as_uint(y) >> 23) & 255u) - 127;
   e = max(e, -6);
   const float ulp = __uint_as_float(static_cast<uint32_t>(e - 3 + 127) << 23);
-  return rintf(__fdiv_rn(y, ulp)) * ulp;
+  const float inv = __uint_as_float(static_cast<uint32_t>(3 - e + 127) << 23);     // 1 / ulp, a power of two: exact
+  return rintf(y * inv) * ulp;
 }
 __device__ __forceinline__ uint8_t e4m3_byte(float y) {          // y on the grid, |y| <= 448
   const uint32_t u = __float_as_uint(y);
@@ -261,7 +262,6 @@ __device__ bool gga_fit_pack_cols(const float* T, int LD, const float* w, int dk
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr float qmax = static_cast<float>((1 << (B - 1)) - 1);
   constexpr int iq = (1 << (B - 1)) - 1;
-  const int KR = dk / 2;
   for (int k = tid; k < dk; k += GNT) wsm[k] = w[k];
   __syncthreads();
   // row factors: r = half(sqrt(max(mean |x|, 1e-20) / w)), one warp per row; and their reciprocals
@@ -286,18 +286,24 @@ __device__ bool gga_fit_pack_cols(const float* T, int LD, const float* w, int dk
   lo = -block_reduce256<true>(-lo, red);
   if (!(hi < 1e14f && lo > 1e-14f)) return false;                    // uniform: the caller takes the IEEE path
   __syncthreads();
-  const int half_id = tid / dv, col = tid - half_id * dv;
-  const bool act = tid < 2 * dv;
-  const int k0 = half_id * KR;
+  const int np = GNT / dv < 8 ? GNT / dv : 8;                        // threads per column; each takes dk / np rows
+  const int KR = dk / np;
+  const int part = tid / dv, col = tid - part * dv;
+  const bool act = tid < np * dv;
+  const int k0 = part * KR;
   const float* Tc = T + k0 * LD + col;
   if (act) {
     float m = 0.f;
 #pragma unroll 4
     for (int i = 0; i < KR; i++) m = fmaxf(m, fabsf(div_h16(Tc[i * LD], rs[k0 + i], rrs[k0 + i])));
-    ps[half_id * dv + col] = m;
+    ps[part * dv + col] = m;
   }
   __syncthreads();
-  if (tid < dv) cs[tid] = halfc(__fdiv_rn(fmaxf(ps[tid], ps[dv + tid]), qmax));
+  if (tid < dv) {
+    float mm = ps[tid];
+    for (int pp = 1; pp < np; pp++) mm = fmaxf(mm, ps[pp * dv + tid]);
+    cs[tid] = halfc(__fdiv_rn(mm, qmax));
+  }
   __syncthreads();
   // weighted least-squares refit of c with the codes fixed
   if (act) {
@@ -311,12 +317,13 @@ __device__ bool gga_fit_pack_cols(const float* T, int LD, const float* w, int dk
       num += (ww * vv) * x;
       den += ww * (vv * vv);
     }
-    ps[half_id * dv + col] = num;
-    ps[2 * dv + half_id * dv + col] = den;
+    ps[part * dv + col] = num;
+    ps[(np + part) * dv + col] = den;
   }
   __syncthreads();
   if (tid < dv) {
-    const float num = ps[tid] + ps[dv + tid], den = ps[2 * dv + tid] + ps[3 * dv + tid];
+    float num = 0.f, den = 0.f;
+    for (int pp = 0; pp < np; pp++) { num += ps[pp * dv + tid]; den += ps[(np + pp) * dv + tid]; }
     cs[tid] = halfc(den > 0.f ? __fdiv_rn(num, fmaxf(den, 1e-30f)) : cs[tid]);
   }
   __syncthreads();
@@ -325,7 +332,7 @@ __device__ bool gga_fit_pack_cols(const float* T, int LD, const float* w, int dk
   constexpr int rowb_num = B;                                        // row bytes = dv * B / 8
   const int rowb = dv * rowb_num / 8;
   const float c1 = act ? cs[col] : 1.0f, rc1 = __frcp_rn(c1);
-  if ((tid & ~31) < 2 * dv) {                                        // whole warps, for the shuffles
+  if ((tid & ~31) < np * dv) {                                       // whole warps, for the shuffles
 #pragma unroll 4
     for (int i = 0; i < KR; i++) {
       int u = 0;
@@ -359,7 +366,7 @@ __device__ bool gga_fit_pack_cols(const float* T, int LD, const float* w, int dk
 __device__ __forceinline__ void gga_fit_pack(float* T, int LD, const float* w, int b, int dk, int dv, int group,
                                              uint8_t* S, float* rs, float* cs, float* ps, float* wsm, float* rrs,
                                              float* red) {
-  const bool cols = 2 * dv <= GNT && dv % 32 == 0 && dk % 2 == 0;
+  const bool cols = 2 * dv <= GNT && dv % 32 == 0 && dk % 8 == 0;
   bool done = false;
   if (cols && b == 4) done = gga_fit_pack_cols<4>(T, LD, w, dk, dv, S, rs, cs, ps, wsm, rrs, red);
   else if (cols && b == 6) done = gga_fit_pack_cols<6>(T, LD, w, dk, dv, S, rs, cs, ps, wsm, rrs, red);
@@ -378,11 +385,11 @@ __host__ __device__ inline GgaSmem gga_smem(int dk, int dv, int M, int group) {
   s.LD = dv + 1;
   s.T = o; o += dk * s.LD;
   s.q = o; o += dk; s.k = o; o += dk; s.bk = o; o += dk;
-  s.v = o; o += dv; s.o = o; o += dv; s.kO = o; o += 2 * dv;
+  s.v = o; o += dv; s.o = o; o += dv; s.kO = o; o += GNT;
   s.rs = o; o += dk * (dv / group > 0 ? dv / group : 1);
   s.rrs = o; o += dk;
-  s.cs = o; o += dv; s.ps = o; o += 4 * dv; s.wsm = o; o += dk;
-  s.Pw = o; o += M * dk; s.Vw = o; o += M * dv; s.r0 = o; o += dk; s.coef = o; o += 32; s.red = o; o += 16;
+  s.cs = o; o += dv; s.ps = o; o += 2 * GNT; s.wsm = o; o += dk;
+  s.Pw = o; o += M * dk; s.Vw = o; o += M * dv; s.r0 = o; o += dk; s.coef = o; o += 32; s.red = o; o += 32;
   s.total = o;
   return s;
 }
@@ -432,17 +439,24 @@ __global__ void __launch_bounds__(GNT) gga_step_kernel(const __grid_constant__ G
   }
   gga_decode_head(S, bits, dk, dv, A.group, T, LD);
   const float bq = block_reduce256<false>(bqp, red);            // (beta k) . q; also orders the tile writes
-  // kO = k^T O, two threads per column
-  const int half_id = tid / dv, col = tid - half_id * dv;
-  const bool act = tid < 2 * dv;
-  const int k0 = half_id * (dk / 2), k1 = k0 + dk / 2;
-  if (act) {
-    float s = 0.f;
-    for (int i = k0; i < k1; i++) s = fmaf(k[i], T[i * LD + col], s);
-    kO[half_id * dv + col] = s;
+  // kO = k^T O, np threads per column
+  const int np = GNT / dv < 8 ? GNT / dv : 8;
+  const int part = tid / dv, col = tid - part * dv;
+  const bool act = tid < np * dv && dk % np == 0;
+  const int KRp = dk / np, k0 = part * KRp, k1 = k0 + KRp;
+  const bool single = dk % np != 0;                         // odd shapes: one thread per column
+  if (act || (single && tid < dv)) {
+    float sum = 0.f;
+    const int lo_ = single ? 0 : k0, hi_ = single ? dk : k1;
+    for (int i = lo_; i < hi_; i++) sum = fmaf(k[i], T[i * LD + col], sum);
+    kO[part * dv + col] = sum;
   }
   __syncthreads();
-  if (tid < dv) kO[tid] = kO[tid] + kO[dv + tid];
+  if (tid < dv && !single) {
+    float sum = kO[tid];
+    for (int pp = 1; pp < np; pp++) sum += kO[pp * dv + tid];
+    kO[tid] = sum;
+  }
   __syncthreads();
   // A O in place
   for (int i = warp; i < dk; i += GNW) {
@@ -450,13 +464,18 @@ __global__ void __launch_bounds__(GNT) gga_step_kernel(const __grid_constant__ G
     for (int j = lane; j < dv; j += 32) T[i * LD + j] = a * (T[i * LD + j] - bki * kO[j]);
   }
   __syncthreads();
-  if (act) {
-    float s = 0.f;
-    for (int i = k0; i < k1; i++) s = fmaf(T[i * LD + col], q[i], s);
-    kO[half_id * dv + col] = s;
+  if (act || (single && tid < dv)) {
+    float sum = 0.f;
+    const int lo_ = single ? 0 : k0, hi_ = single ? dk : k1;
+    for (int i = lo_; i < hi_; i++) sum = fmaf(T[i * LD + col], q[i], sum);
+    kO[part * dv + col] = sum;
   }
   __syncthreads();
-  if (tid < dv) o[tid] = (kO[tid] + kO[dv + tid]) + bq * v[tid];
+  if (tid < dv) {
+    float sum = kO[tid];
+    if (!single) for (int pp = 1; pp < np; pp++) sum += kO[pp * dv + tid];
+    o[tid] = sum + bq * v[tid];
+  }
   __syncthreads();
 
   const bool window = A.pw && bits != 16;
