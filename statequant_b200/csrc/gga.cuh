@@ -249,8 +249,10 @@ __device__ void gga_fit_store(float* T, int LD, const float* w, int b, int dk, i
 // hundreds of millions of dividends), so the sweeps recompute the quotients with three FMAs instead of keeping them;
 // the division of the column maximum by qmax is taken out of the loop (a positive constant divisor keeps the
 // maximum the maximum).  Codes of a packing unit (2 or 4 adjacent columns) meet in one lane by shuffles.
-// The range condition is checked once per head on the tile (all non-zero |x| within [1e-14, 1e14]: with factors in
-// [2^-24, 65504] every quotient then stays within [1e-24, 1e30]); a head outside it takes gga_fit_store.
+// The range condition is checked once per head on the tile: all non-zero |x| within [1e-30, 1e14].  With factors in
+// [2^-24, 65504] the first quotient y = x / r is then exact (no subnormal residual); the second one, y / c, can be an
+// ulp off only where y is below 1e-31, i.e. where its code is 0 whatever the last bit.  A head outside the range takes
+// gga_fit_store.
 __device__ __forceinline__ float div_h16(float x, float d, float rd) {
   const float q0 = x * rd;
   return __fmaf_rn(__fmaf_rn(-d, q0, x), rd, q0);
@@ -284,7 +286,7 @@ __device__ bool gga_fit_pack_cols(const float* T, int LD, const float* w, int dk
   }
   hi = block_reduce256<true>(hi, red);
   lo = -block_reduce256<true>(-lo, red);
-  if (!(hi < 1e14f && lo > 1e-14f)) return false;                    // uniform: the caller takes the IEEE path
+  if (!(hi < 1e14f && lo > 1e-30f)) return false;                    // uniform: the caller takes the IEEE path
   __syncthreads();
   const int np = GNT / dv < 8 ? GNT / dv : 8;                        // threads per column; each takes dk / np rows
   const int KR = dk / np;

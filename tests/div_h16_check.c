@@ -4,7 +4,7 @@
 #include <math.h>
 #include <stdlib.h>
 /* Check behind div_h16() in statequant_b200/csrc/gga.cuh: for EVERY positive fp16 divisor r (subnormals included,
-   2^-24 .. 65504) and 20 000 pseudo-random dividends x of either sign with exponents in [2^-83, 2^82] each,
+   2^-24 .. 65504) and 20 000 pseudo-random dividends x of either sign with exponents in [2^-100, 2^82] each,
    fma(fma(-r, x rr, x), rr, x rr) with rr = RN(1 / r) equals the IEEE quotient x / r.  Returns the mismatch count. */
 static float h2f(uint16_t h) { // positive only
   int e = (h >> 10) & 31, m = h & 1023;
@@ -22,7 +22,7 @@ int main(void) {
       s ^= s << 13; s ^= s >> 7; s ^= s << 17;
       uint32_t u = (uint32_t)(s >> 32);
       // exponent range limited so that the quotient stays normal: x in [2^-60, 2^40]
-      uint32_t ex = 44 + (u >> 23) % 166;   // x in [2^-83, 2^82]
+      uint32_t ex = 27 + (u >> 23) % 183;   // x in [2^-100, 2^82]
       uint32_t bits = (u & 0x807FFFFFu) | (ex << 23);
       float x; memcpy(&x, &bits, 4);
       const float q = x / r;
