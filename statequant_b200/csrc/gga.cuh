@@ -79,7 +79,7 @@ __device__ __forceinline__ float enc_level(float y, float qmax, bool two) {
 }
 
 // ---- head codes -> fp32 tile T[k * LD + v] ------------------------------------------------------------------------
-__device__ void gga_decode_head(const uint8_t* S, int b, int dk, int dv, int group, float* T, int LD) {
+__device__ __forceinline__ void gga_decode_head(const uint8_t* S, int b, int dk, int dv, int group, float* T, int LD) {
   const int tid = threadIdx.x;
   if (b == 16) {
     const unsigned short* p = reinterpret_cast<const unsigned short*>(S);
@@ -259,7 +259,7 @@ __device__ __forceinline__ float div_h16(float x, float d, float rd) {
 }
 
 template <int B>
-__device__ bool gga_fit_pack_cols(const float* T, int LD, const float* w, int dk, int dv, uint8_t* S, float* rs,
+__device__ __forceinline__ bool gga_fit_pack_cols(const float* T, int LD, const float* w, int dk, int dv, uint8_t* S, float* rs,
                                   float* cs, float* ps, float* wsm, float* rrs, float* red) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr float qmax = static_cast<float>((1 << (B - 1)) - 1);
@@ -398,10 +398,13 @@ __host__ __device__ inline GgaSmem gga_smem(int dk, int dv, int M, int group) {
 
 
 // ---- the decode step ----------------------------------------------------------------------------------------------
+// DKT, DVT: the head dims as compile-time constants (0: taken from the arguments), so that the tile's index
+// arithmetic folds into immediates for the usual 128 x 128 head
+template <int DKT, int DVT>
 __global__ void __launch_bounds__(GNT) gga_step_kernel(const __grid_constant__ GgaArgs A) {
   extern __shared__ __align__(16) float gsm[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int dk = A.DK, dv = A.DV, M = A.M, HV = A.HV;
+  const int dk = DKT ? DKT : A.DK, dv = DVT ? DVT : A.DV, M = A.M, HV = A.HV;
   const int bh = blockIdx.x, b = bh / HV, h = bh - b * HV, hk = h / (HV / A.HK);
   uint8_t* orow = A.out + (long long)b * A.so + (long long)h * dv * dt_size(A.dt_out);
   const long long seq = A.idx[b];
@@ -410,7 +413,7 @@ __global__ void __launch_bounds__(GNT) gga_step_kernel(const __grid_constant__ G
     return;
   }
   const GgaSmem P = gga_smem(dk, dv, M, A.group);
-  const int LD = P.LD;
+  const int LD = dv + 1;
   float *T = gsm + P.T, *q = gsm + P.q, *k = gsm + P.k, *bk = gsm + P.bk, *v = gsm + P.v, *o = gsm + P.o,
         *kO = gsm + P.kO, *Pw = gsm + P.Pw, *Vw = gsm + P.Vw, *r0 = gsm + P.r0, *coef = gsm + P.coef, *red = gsm + P.red;
   uint8_t* base = A.blob + seq * A.stride;

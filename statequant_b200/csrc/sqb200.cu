@@ -369,7 +369,11 @@ int sqb_gga_step(const sqb_gga_layout_t* L, const sqb_gdn_inputs_t* in, void* st
   a.dt_qk = in->qk_dtype; a.dt_v = in->v_dtype; a.dt_ab = in->ab_dtype; a.dt_alog = in->alog_dtype;
   a.dt_dtb = in->dtb_dtype; a.dt_out = in->out_dtype; a.scale = in->scale;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (int rc = launch_gga(sqb::gga_step_kernel, a, static_cast<long long>(in->rows) * L->hv, st)) return rc;
+  if (L->dk == 128 && L->dv == 128) {
+    if (int rc = launch_gga(sqb::gga_step_kernel<128, 128>, a, static_cast<long long>(in->rows) * L->hv, st)) return rc;
+  } else {
+    if (int rc = launch_gga(sqb::gga_step_kernel<0, 0>, a, static_cast<long long>(in->rows) * L->hv, st)) return rc;
+  }
   if (L->pw) {
     sqb::gga_advance_kernel<<<(in->rows + 127) / 128, 128, 0, st>>>(a.blob, a.stride, a.idx, in->rows, L->m);
     cudaError_t e = cudaGetLastError();
