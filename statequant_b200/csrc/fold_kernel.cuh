@@ -49,7 +49,7 @@ __host__ __device__ inline SmemF smemf_plan(bool vdec, int bits, int axk, int gr
   s.L = f; f += DV * s.lm;
   s.ae = f; f += vdec ? DK : 32;            // KDA: exp(gcur) per key channel; else: the slots' decay factors
   s.ksf = f; f += 64;                       // buffer scales of the slots: keys, then values
-  s.cmax = f; f += (axk ? 0 : 3 * NW * DK);         // axis v: column maxima, then scales and their reciprocals
+  s.cmax = f; f += (axk ? 0 : 3 * NW * s.rdk);      // axis v: column maxima, then scales and their reciprocals (padded)
   s.total = s.f0 + ((f + 3) & ~3) * 4;
   return s;
 }
@@ -188,14 +188,33 @@ __global__ void __launch_bounds__(NT, 4) fold_kernel(const __grid_constant__ Fol
       if (VDEC) {
         for (int k = tid; k < DK; k += NT) ae[k] = expf(gct[k]);
       }
-      for (int x = tid; x < M * DV; x += NT) {
-        const int i = x / DV, v = x - i * DV;
-        float ub;
-        if (A.qbuf) ub = static_cast<float>(reinterpret_cast<const int8_t*>(ubt)[x]) * usf[i];
-        else ub = bf2f(reinterpret_cast<const unsigned short*>(ubt)[x]);
-        if (!VDEC && (reading || i != M - 1)) ub = dec[i] * ub;
-        if (i >= nlive) ub = 0.f;
-        L[v * LM + i] = ub;
+      if ((M & 3) == 0) {
+        // four slots of a row at a time: one 128-bit store each, rows over consecutive threads (conflict-free)
+        for (int x = tid; x < (M / 4) * DV; x += NT) {
+          const int i0 = (x / DV) * 4, v = x - (x / DV) * DV;
+          float ub4[4];
+#pragma unroll
+          for (int t = 0; t < 4; t++) {
+            const int i = i0 + t;
+            float ub;
+            if (A.qbuf) ub = static_cast<float>(reinterpret_cast<const int8_t*>(ubt)[i * DV + v]) * usf[i];
+            else ub = bf2f(reinterpret_cast<const unsigned short*>(ubt)[i * DV + v]);
+            if (!VDEC && (reading || i != M - 1)) ub = dec[i] * ub;
+            if (i >= nlive) ub = 0.f;
+            ub4[t] = ub;
+          }
+          *reinterpret_cast<float4*>(L + v * LM + i0) = make_float4(ub4[0], ub4[1], ub4[2], ub4[3]);
+        }
+      } else {
+        for (int x = tid; x < M * DV; x += NT) {
+          const int i = x / DV, v = x - i * DV;
+          float ub;
+          if (A.qbuf) ub = static_cast<float>(reinterpret_cast<const int8_t*>(ubt)[x]) * usf[i];
+          else ub = bf2f(reinterpret_cast<const unsigned short*>(ubt)[x]);
+          if (!VDEC && (reading || i != M - 1)) ub = dec[i] * ub;
+          if (i >= nlive) ub = 0.f;
+          L[v * LM + i] = ub;
+        }
       }
       __syncthreads();
       const float alphan = VDEC ? 1.0f : expf(gnew);

@@ -186,6 +186,7 @@ __device__ __forceinline__ bool fold_rows(const uint8_t* codes, const unsigned s
     const int gpi = NW / wpg;                       // groups in flight
     const int BR = gpi * G;
     const int niter = (DV + BR - 1) / BR;
+    constexpr int CDK = LPR * 20;                   // floats per row of the padded column tables
     for (int it = 0; it < niter; it++) {
       const int gvrow = it * gpi + warp / wpg;
       const bool gvalid = gvrow * G < DV;
@@ -195,10 +196,15 @@ __device__ __forceinline__ bool fold_rows(const uint8_t* codes, const unsigned s
       float2 a0[8], a1[8];
       decode16<BITS>(codes + r0 * ROWB + c * CB, a0);
       decode16<BITS>(codes + r1 * ROWB + c * CB, a1);
+      uint32_t sw[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};     // the lane's 16 column scales (fp16 pairs), two 128-bit reads
+      if (gvalid) {
+        const uint4* sp = reinterpret_cast<const uint4*>(scs + gvrow * DK + c * 16);
+        const uint4 u0 = sp[0], u1 = sp[1];
+        sw[0] = u0.x; sw[1] = u0.y; sw[2] = u0.z; sw[3] = u0.w; sw[4] = u1.x; sw[5] = u1.y; sw[6] = u1.z; sw[7] = u1.w;
+      }
 #pragma unroll
       for (int p = 0; p < 8; p++) {
-        const int k0 = c * 16 + 2 * p;
-        const float s0 = gvalid ? h2f(scs[gvrow * DK + k0]) : 0.f, s1 = gvalid ? h2f(scs[gvrow * DK + k0 + 1]) : 0.f;
+        const float s0 = h2f(static_cast<unsigned short>(sw[p] & 0xFFFFu)), s1 = h2f(static_cast<unsigned short>(sw[p] >> 16));
         float2 s2 = make_float2(s0, s1);
         if constexpr (BITS == 4) s2 = make_float2(s0 * nib_prescale((2 * p) & 7), s1 * nib_prescale((2 * p + 1) & 7));
         float2 d2 = make_float2(alphan, alphan);
@@ -230,24 +236,25 @@ __device__ __forceinline__ bool fold_rows(const uint8_t* codes, const unsigned s
       if (!sync()) return false;                      // cmax free (the previous iteration's readers are done)
       if (rl == 0) {
 #pragma unroll
-        for (int j = 0; j < 16; j++) cmax[warp * DK + c * 16 + j] = cm[j];
+        for (int j = 0; j < 16; j++) cmax[warp * CDK + c * 20 + j] = cm[j];
       }
       if (!sync()) return false;
-      float* ssc = cmax + NW * DK;                    // scale of every column of every group in flight
-      float* rsc = ssc + NW * DK;                     // and its approximate reciprocal
+      float* ssc = cmax + NW * CDK;                   // scale of every column of every group in flight
+      float* rsc = ssc + NW * CDK;                    // and its approximate reciprocal
       for (int e = tid; e < gpi * DK; e += NT) {
         const int gi = e / DK, k = e - gi * DK;
+        const int pk_ = (k >> 4) * 20 + (k & 15);       // lane-chunk layout: 16 columns + 4 floats of padding
         float am = 0.f;
-        for (int w = 0; w < wpg; w++) am = fmaxf(am, cmax[(gi * wpg + w) * DK + k]);
+        for (int w = 0; w < wpg; w++) am = fmaxf(am, cmax[(gi * wpg + w) * CDK + pk_]);
         const float sc = fp16_scale(am, QMAX);
-        ssc[gi * DK + k] = sc;
-        rsc[gi * DK + k] = rcp_approx(sc);
+        ssc[gi * CDK + pk_] = sc;
+        rsc[gi * CDK + pk_] = rcp_approx(sc);
         const int gvr = it * gpi + gi;
         if (gvr * G < DV) SCh[gvr * DK + k] = f2h(sc);
       }
       if (!sync()) return false;
-      const float* myssc = ssc + (warp / wpg) * DK + c * 16;
-      const float* myrsc = rsc + (warp / wpg) * DK + c * 16;
+      const float* myssc = ssc + (warp / wpg) * CDK + c * 20;
+      const float* myrsc = rsc + (warp / wpg) * CDK + c * 20;
       float2 tt[8];
       if (v0) {
         uint4 pk;

@@ -584,11 +584,11 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
         for (int e = 0; e < 4; e++) { qv[e] = av[e] * qv[e]; kv[e] = av[e] * kv[e]; }
       }
       if (!AXK) {
+        const uint2 sw = reinterpret_cast<const uint2*>(scrow + c * 16)[p4];          // four fp16 scales
+        const float sc4[4] = {h2f(static_cast<unsigned short>(sw.x & 0xFFFFu)), h2f(static_cast<unsigned short>(sw.x >> 16)),
+                              h2f(static_cast<unsigned short>(sw.y & 0xFFFFu)), h2f(static_cast<unsigned short>(sw.y >> 16))};
 #pragma unroll
-        for (int e = 0; e < 4; e++) {
-          const float sc = h2f(scrow[c * 16 + 4 * p4 + e]);
-          qv[e] = qv[e] * sc; kv[e] = kv[e] * sc;
-        }
+        for (int e = 0; e < 4; e++) { qv[e] = qv[e] * sc4[e]; kv[e] = kv[e] * sc4[e]; }
       }
 #pragma unroll
       for (int e = 0; e < 4; e += 2) {
