@@ -31,7 +31,8 @@ __device__ __forceinline__ float transpose_reduce_n(float (&v)[PU], int c) {
 }
 
 // scs: the head's scales; for axis-v states load_slice(gv) reloads vq / vk with group gv's scales folded in.
-template <int BITS, bool AXK, bool TWO, int LPR, class Slice>
+// CHECK: (axis-v states) look at every pass whether its rows belong to a new scale group
+template <int BITS, bool AXK, bool TWO, int LPR, bool CHECK = true, class Slice>
 __device__ __forceinline__ void pass_rows(const uint8_t* codes, const unsigned short* scs, const float2 (&vq)[8],
                                           const float2 (&vk)[8], int p0, int npass, int row_base, int G, int NG, int gl,
                                           int c, int rl, int& cur_gv, Slice load_slice, float& tq, float& tk) {
@@ -52,7 +53,7 @@ __device__ __forceinline__ void pass_rows(const uint8_t* codes, const unsigned s
       const int pass = p0 + g * PU + p;
       if (pass < npass) {                                  // uniform
         const int row = row_base + pass * RPP + rl;
-        if constexpr (!AXK) {
+        if constexpr (!AXK && CHECK) {
           const int gv = (row_base + pass * RPP) / G;      // uniform over the warp: G is a multiple of RPP
           if (gv != cur_gv) { cur_gv = gv; load_slice(gv); }
         }

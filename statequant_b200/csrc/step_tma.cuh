@@ -566,6 +566,7 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
   // ---- the value heads of this key head ---------------------------------------------------------------------------
   const int RW = DV / NW;
   const int npass = RW / RPP;
+  const bool one_group = !AXK && RW <= G && (warp * RW) % G + RW <= G;
   float2 vq[8], vk[8];
   auto load_slice = [&](const unsigned short* scrow) {      // this lane's 16 columns of q and k, as 128-bit reads
     const float* sq = xq + c * 16;
@@ -621,13 +622,18 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
     // ---- state pass ----
     int cur_gv = -1;
     float umax = 0.f;
+    if (!AXK && one_group) load_slice(scs + ((warp * RW) / G) * DK);     // this warp's rows lie in one scale group
     for (int p0 = 0; p0 < npass; p0 += LPR) {
       const bool own = p0 + c < npass;                         // this lane finishes the row of pass p0 + c
       const int orow_i = warp * RW + (own ? p0 + c : 0) * RPP + rl;
       const float vt = ldf(A.v + (long long)b * A.sv, A.dt_v, (long long)h * DV + orow_i);
       float tq, tk;
-      pass_rows<BITS, AXK, TWO, LPR>(codes, scs, vq, vk, p0, npass, warp * RW, G, NG, gl, c, rl, cur_gv,
-                                     [&](int gv) { load_slice(scs + gv * DK); }, tq, tk);
+      if (AXK || one_group)
+        pass_rows<BITS, AXK, TWO, LPR, false>(codes, scs, vq, vk, p0, npass, warp * RW, G, NG, gl, c, rl, cur_gv,
+                                              [&](int) {}, tq, tk);
+      else
+        pass_rows<BITS, AXK, TWO, LPR, true>(codes, scs, vq, vk, p0, npass, warp * RW, G, NG, gl, c, rl, cur_gv,
+                                             [&](int gv) { load_slice(scs + gv * DK); }, tq, tk);
       if (own) {
         const int row = orow_i;
         if (!VDEC) { tq = alpha * tq; tk = alpha * tk; }
