@@ -199,3 +199,53 @@ def test_cuda_graph_capture_gga():
         pk.step(ev, idxd, *stat[:3], oe, D ** -0.5, gate=(stat[3], stat[4], A_log, dtb), layer=0)
         assert torch.equal(out, oe)
     assert torch.equal(blob, eb)
+
+
+@pytest.mark.gpu
+def test_full_batch_properties_gga_qwen_shapes():
+    """Qwen3.5-4B head shapes (32 value heads, 16 key heads, 128 x 128), the 4 / 6-bit plan with the window, batch 64:
+    determinism, padding rows, and a sample of slots against the oracle from their pre-step bytes across a window
+    wrap (the queue fills at 8, merges start at 9)."""
+    from statequant_b200.kernels.gga import StepPlan
+    hv, hk, D, m, B = 32, 16, 128, 8, 64
+    g0 = torch.Generator().manual_seed(11)
+    plan = StepPlan({0: (torch.tensor([4, 6] * (hv // 2)), torch.rand(hv, D, generator=g0) + 0.5)}, 32, name='t')
+    pk = GGAPacked(plan, hv, hk, D, D, pw=True, m=m)
+    blob = pk.alloc(B + 1, DEV)
+    V = pk.views(blob)
+    idx = (torch.randperm(B, generator=g0) + 1).to(torch.int32)
+    idx[::13] = 0
+    idxd = idx.to(DEV)
+    live = idxd[idxd > 0]
+    pk.write(V, live, (torch.randn(int(live.numel()), hv, D, D, generator=g0) * 0.3).to(DEV), layer=0)
+    blob2 = blob.clone()
+    V2 = pk.views(blob2)
+    sample = [int(s) for s in idx[1:4] if s > 0]
+    rows = [int((idx == s).nonzero()[0]) for s in sample]
+    A_log, dtb = torch.randn(hv, generator=g0) * 0.3, torch.randn(hv, generator=g0)
+    for t in range(m + 2):
+        f = lambda *s: torch.randn(*s, generator=g0)                                     # noqa: E731
+        q, k, v = f(B, hk, D).bfloat16(), f(B, hk, D).bfloat16(), f(B, hv, D).bfloat16()
+        a, b = (f(B, hv) + 2.0).bfloat16(), f(B, hv).bfloat16()
+        out = torch.empty(B, hv, D, dtype=torch.bfloat16, device=DEV)
+        out2 = torch.empty_like(out)
+        pre = blob[torch.tensor(sample, device=DEV)].cpu()
+        gate = tuple(x.to(DEV) for x in (a, b, A_log, dtb))
+        args = [x.to(DEV) for x in (q, k, v)]
+        pk.step(V, idxd, *args, out, D ** -0.5, gate=gate, layer=0)
+        pk.step(V2, idxd, *args, out2, D ** -0.5, gate=gate, layer=0)
+        assert torch.equal(out, out2) and torch.equal(blob, blob2), t
+        assert torch.equal(out[idxd <= 0], torch.zeros_like(out[idxd <= 0]))
+        hb = torch.zeros(B + 1, blob.shape[1], dtype=torch.uint8)
+        hb[torch.tensor(sample)] = pre
+        Vh = pk.views(hb)
+        oh = torch.empty(len(rows), hv, D, dtype=torch.bfloat16)
+        oracle.gga_step(pk, Vh, idx[rows].contiguous(), q[rows].contiguous(), k[rows].contiguous(), v[rows].contiguous(),
+                        oh, D ** -0.5, (a[rows].contiguous(), b[rows].contiguous(), A_log, dtb), 0)
+        assert torch.allclose(out[rows].cpu().float(), oh.float(), rtol=1e-2, atol=2e-3), t
+        sl = torch.tensor(sample, dtype=torch.int32)
+        Sd = pk.stored(V, sl.to(DEV), 0).cpu()
+        Sh = oracle.gga_load(pk, Vh, sl, 0)
+        flips = ((Sd - Sh).abs() > 1e-3 * Sh.abs().amax()).float().mean().item()
+        assert flips < 2e-3, (t, flips)
+        assert torch.equal(blob.cpu()[sl.long(), :8], hb[sl.long(), :8])               # window counters

@@ -416,3 +416,76 @@ def test_device_read_write_match_torch(kind, fmt):
         want = lay.read(lay.views(blob.cpu()), idx.cpu())   # the torch path on the same bytes
         assert ((got - want).abs().max() / want.abs().max()).item() < 1e-5, t
     assert int(V['NPTR'][idx.long(), 0].max()) == 5         # reading leaves the slots alone
+
+
+def _full_batch(lay, steps, make, run_dev, run_oracle, sample_n=4, hv=None, dv=None):
+    """BASELINE-size batch through the device twice (determinism), padding rows, and a sample of rows against the
+    oracle from their pre-step bytes, across one fold period."""
+    B = 256
+    g0 = torch.Generator().manual_seed(3)
+    blob = lay.alloc(B + 1, DEV)
+    V = lay.views(blob)
+    lay.write(V, torch.arange(1, B + 1, device=DEV), (torch.randn(B, hv, dv, lay.DK, generator=g0) * 0.3).to(DEV))
+    idx = (torch.randperm(B, generator=g0) + 1).to(torch.int32)
+    idx[::19] = 0
+    idxd = idx.to(DEV)
+    blob2 = blob.clone()
+    V2 = lay.views(blob2)
+    sample = [int(s) for s in idx[1:1 + sample_n] if s > 0]
+    rows = [int((idx == s).nonzero()[0]) for s in sample]
+    for t in range(steps):
+        inp = make(B, g0)
+        out = torch.empty(B, hv, dv, dtype=torch.bfloat16, device=DEV)
+        out2 = torch.empty_like(out)
+        pre = blob[torch.tensor(sample, device=DEV)].cpu()
+        dev_inp = [x.to(DEV) for x in inp]
+        run_dev(V, idxd, dev_inp, out)
+        run_dev(V2, idxd, dev_inp, out2)
+        assert torch.equal(out, out2) and torch.equal(blob, blob2), t                   # deterministic
+        assert torch.equal(out[idxd <= 0], torch.zeros_like(out[idxd <= 0]))
+        hb = torch.zeros(B + 1, lay.nbytes, dtype=torch.uint8)
+        hb[torch.tensor(sample)] = pre
+        oh = torch.empty(len(rows), hv, dv, dtype=torch.bfloat16)
+        run_oracle(lay.views(hb), idx[rows].contiguous(), [x[rows].contiguous() for x in inp], oh)
+        assert torch.allclose(out[rows].cpu().float(), oh.float(), rtol=1e-2, atol=1e-3), t
+        d = field_diff(lay, blob.cpu(), hb, sample)
+        assert d['S'] <= 1e-4 * len(sample) * hv * dv * lay.DK + 1 and d['UB'] + d['KB'] <= 4, (t, d)
+    n = V['NPTR'][idxd[idxd > 0].long(), 0]
+    assert int(n.min()) == int(n.max()) == steps % lay.m
+
+
+def test_full_batch_properties_mamba2_shapes():
+    """Nemotron-H shapes (128 heads in 8 groups, head_dim 64, d_state 128), batch 256, int8 k g32."""
+    H, GR, DS, HD = 128, 8, 128, 64
+    lay = Mamba2SlotLayout(sq.Quantizer(8, 'k', 32), H, GR, DS, HD, m=8)
+    g1 = torch.Generator().manual_seed(8)
+    A = -torch.exp(torch.rand(H, generator=g1) * 2.77)
+    D = torch.randn(H, generator=g1)
+    dtb = torch.rand(H, generator=g1) * 2.0 - 4.0
+    Ad, Dd, dtbd = A.to(DEV), D.to(DEV), dtb.to(DEV)
+
+    def make(B, g):
+        f = lambda *s: torch.randn(*s, generator=g)                                      # noqa: E731
+        return [f(B, H, HD).bfloat16(), f(B, H).bfloat16(), f(B, GR, DS).bfloat16(), f(B, GR, DS).bfloat16()]
+
+    _full_batch(lay, 9, make,
+                lambda V, i, x, o: lay.step(V, i, x[0], x[1], x[2], x[3], o, Ad, D=Dd, dt_bias=dtbd),
+                lambda V, i, x, o: oracle.mamba2_step(lay, V, i, x[0], x[1], x[2], x[3], o, A, D, dtb),
+                sample_n=2, hv=H, dv=HD)
+
+
+def test_full_batch_properties_kda_shapes():
+    """Kimi-Linear-like shapes (32 heads, d 128, per-channel decays), batch 256, pace4 state."""
+    H, Dm = 32, 128
+    lay = KDASlotLayout(sq.Quantizer(4, 'k', 64), H, Dm, Dm, m=8)
+
+    def make(B, g):
+        f = lambda *s: torch.randn(*s, generator=g)                                      # noqa: E731
+        q, k = f(B, H, Dm), f(B, H, Dm)
+        return [(q / q.norm(dim=-1, keepdim=True)).bfloat16(), (k / k.norm(dim=-1, keepdim=True)).bfloat16(),
+                f(B, H, Dm).bfloat16(), torch.nn.functional.logsigmoid(f(B, H, Dm) + 3.0), torch.sigmoid(f(B, H))]
+
+    _full_batch(lay, 9, make,
+                lambda V, i, x, o: lay.step(V, i, x[0], x[1], x[2], x[3], x[4], o, Dm ** -0.5),
+                lambda V, i, x, o: oracle.kda_step(lay, V, i, x[0], x[1], x[2], x[3], x[4], o, Dm ** -0.5),
+                sample_n=3, hv=H, dv=Dm)
