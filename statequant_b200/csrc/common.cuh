@@ -90,23 +90,33 @@ __device__ __forceinline__ float byte_to_f(uint32_t wx) {
 // (u - 8) * 16^e exactly after the bias is subtracted, with e = i for i <= 4 and e = i - 5 for i = 5, 6, 7 (those
 // three come from the word shifted down by 20).  The factor 16^-e is a power of two, so it is folded exactly into
 // whatever the code is multiplied with (the read-out vector, or the scale).  Pair p holds columns 2p, 2p+1.
+// (w & mask) | k as ONE lop3 (the mask is the immediate, k comes in a register; written as two C operators the
+// compiler spends an AND and an OR with two immediates)
+template <uint32_t MASK>
+__device__ __forceinline__ float nib_f(uint32_t w, uint32_t k) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(w), "n"(MASK), "r"(k));
+  return __uint_as_float(r);
+}
 __device__ __forceinline__ void unpack_nib8(uint32_t w, float2 f[4]) {
   const uint32_t w2 = w >> 20;
-  const uint32_t K = 0x4B000000u;
+  uint32_t K = 0x4B000000u;
+  asm volatile("" : "+r"(K));                 // keep the constant in a register
   float2 t;
-  t.x = __uint_as_float((w & 0x0000000Fu) | K);
-  t.y = __uint_as_float((w & 0x000000F0u) | K);
+  t.x = nib_f<0x0000000Fu>(w, K);
+  t.y = nib_f<0x000000F0u>(w, K);
   f[0] = __fadd2_rn(t, make_float2(-8388616.0f, -8388736.0f));     // 2^23 + 8, 2^23 + 8*16
-  t.x = __uint_as_float((w & 0x00000F00u) | K);
-  t.y = __uint_as_float((w & 0x0000F000u) | K);
+  t.x = nib_f<0x00000F00u>(w, K);
+  t.y = nib_f<0x0000F000u>(w, K);
   f[1] = __fadd2_rn(t, make_float2(-8390656.0f, -8421376.0f));     // + 8*16^2, + 8*16^3
-  t.x = __uint_as_float((w & 0x000F0000u) | K);
-  t.y = __uint_as_float((w2 & 0x0000000Fu) | K);
+  t.x = nib_f<0x000F0000u>(w, K);
+  t.y = nib_f<0x0000000Fu>(w2, K);
   f[2] = __fadd2_rn(t, make_float2(-8912896.0f, -8388616.0f));     // + 8*16^4, + 8
-  t.x = __uint_as_float((w2 & 0x000000F0u) | K);
-  t.y = __uint_as_float((w2 & 0x00000F00u) | K);
+  t.x = nib_f<0x000000F0u>(w2, K);
+  t.y = nib_f<0x00000F00u>(w2, K);
   f[3] = __fadd2_rn(t, make_float2(-8388736.0f, -8390656.0f));
 }
+
 // 16^-e of column j (0..7) of a word, matching unpack_nib8
 __device__ __forceinline__ float nib_prescale(int j) {
   const int e = j <= 4 ? j : j - 5;
