@@ -73,7 +73,7 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 // shared-memory plan of the staged kernel (byte offsets; float offsets from f0)
 struct Smem2 {
   int bars, stage0, stage_bytes, codes_b, scales_b, ub_b, kb, gbt, f0, total;
-  int xq, xk, ga, ae, wq, wk, wg, us, Dq, Dk, hd, decf, ubs, red, misc;
+  int xq, xk, ga, ae, wq, wk, wg, fx, us, Dq, Dk, hd, decf, ubs, red, misc;
 };
 constexpr int HD_W = 8;     // per-head scalars: g, beta | dt, gcur, alpha, a, gnew, D, n
 __host__ __device__ inline int al16i(int x) { return (x + 15) & ~15; }
@@ -99,6 +99,7 @@ __host__ __device__ inline Smem2 smem2_plan(int kind, int bits, int axk, int gro
   s.wq = f; f += DK;                // the dot-product warp's own copy of the normalised q, k (KDA: log decay)
   s.wk = f; f += DK;
   s.wg = f; f += (kind == K_KDA ? DK : 0);
+  s.fx = f; f += (axk && DK == 128 ? 6 * DK / 4 : 0);   // byte slices of the fixed-point q and k (pass_rows_fx)
   s.us = f; f += gqa * DV;
   s.Dq = f; f += 32;
   s.Dk = f; f += 32;
@@ -262,6 +263,7 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
   constexpr int QD = DK / 4;                     // columns per lane in the buffered-key dot products
   constexpr bool TWO = KIND != K_M2;
   constexpr bool VDEC = KIND == K_KDA;
+  constexpr bool FX = AXK && LPR == 8;            // integer dot products against fixed-point q, k
   constexpr float QMAX = BITS == 4 ? 7.0f : 127.0f;
 
   extern __shared__ __align__(128) uint8_t smraw[];
@@ -382,13 +384,24 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
       }
     }
     float d = 0.f, mx = 0.f;
+    float eq[CW], ek[CW], mq = 0.f, mk = 0.f;              // the vectors the state is read against
 #pragma unroll
     for (int j = 0; j < CW; j++) {
       d += kr[j] * qr[j];
       mx = fmaxf(mx, fabsf(kr[j]));
       xq[lane * CW + j] = qr[j];
       xk[lane * CW + j] = kr[j];
-      if (VDEC) { ga[lane * CW + j] = gnr[j]; ae[lane * CW + j] = expf(gnr[j]); }
+      eq[j] = qr[j];
+      ek[j] = kr[j];
+      if (VDEC) {
+        const float av = expf(gnr[j]);
+        ga[lane * CW + j] = gnr[j];
+        ae[lane * CW + j] = av;
+        eq[j] = av * qr[j];
+        ek[j] = av * kr[j];
+      }
+      mq = fmaxf(mq, fabsf(eq[j]));
+      mk = fmaxf(mk, fabsf(ek[j]));
     }
     // the remaining stages
     if (lane == 0) {
@@ -397,6 +410,23 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
     d = warp_sum(d);
     mx = warp_max(mx);
     if (lane == 0) { misc[0] = d; misc[1] = __int_as_float(n0); }
+    if constexpr (FX) {
+      // q and k as 24-bit fixed point, byte slices of four columns per word (this lane's four columns)
+      uint32_t* fxw = reinterpret_cast<uint32_t*>(fsm + P.fx);
+      mq = warp_max(mq);
+      if (TWO) mk = VDEC ? warp_max(mk) : mx;
+      float mult, inv;
+      fx_scale(mq, mult, inv);
+      if (lane == 0) misc[4] = inv;
+      put_fx_slices<BITS>(fxw, lane, fx_fixed(eq[0], mult), fx_fixed(eq[CW > 1 ? 1 : 0], mult),
+                          fx_fixed(eq[CW > 2 ? 2 : 0], mult), fx_fixed(eq[CW > 3 ? 3 : 0], mult));
+      if (TWO) {
+        fx_scale(mk, mult, inv);
+        if (lane == 0) misc[5] = inv;
+        put_fx_slices<BITS>(fxw + 3 * (DK / 4), lane, fx_fixed(ek[0], mult), fx_fixed(ek[CW > 1 ? 1 : 0], mult),
+                            fx_fixed(ek[CW > 2 ? 2 : 0], mult), fx_fixed(ek[CW > 3 ? 3 : 0], mult));
+      }
+    }
     // append the key at slot n0; its rounded value is what the fold uses for slot M-1
     if (A.qbuf) {
       const float ksc = fp16_scale(mx, 127.0f);
@@ -600,7 +630,37 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
       }
     }
   };
-  if (AXK) load_slice(nullptr);
+  uint32_t fq[3][4], fk[3][4];
+  int iq[3] = {0, 0, 0}, ik[3] = {0, 0, 0};
+  float invq = 1.f, invk = 1.f;
+  if constexpr (FX) {
+    const uint4* fxv = reinterpret_cast<const uint4*>(fsm + P.fx);
+#pragma unroll
+    for (int i = 0; i < 3; i++) {
+      const uint4 a4 = fxv[i * 8 + c];
+      fq[i][0] = a4.x; fq[i][1] = a4.y; fq[i][2] = a4.z; fq[i][3] = a4.w;
+      if (TWO) {
+        const uint4 b4 = fxv[(3 + i) * 8 + c];
+        fk[i][0] = b4.x; fk[i][1] = b4.y; fk[i][2] = b4.z; fk[i][3] = b4.w;
+      } else {
+        fk[i][0] = fk[i][1] = fk[i][2] = fk[i][3] = 0u;
+      }
+      if (BITS == 4) {                                     // nibbles carry an offset of 8
+        int sq_ = 0, sk_ = 0;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+          sq_ = i == 0 ? dp4a_ss(fq[i][w], 0x01010101u, sq_) : static_cast<int>(__dp4a(fq[i][w], 0x01010101u, static_cast<unsigned>(sq_)));
+          sk_ = i == 0 ? dp4a_ss(fk[i][w], 0x01010101u, sk_) : static_cast<int>(__dp4a(fk[i][w], 0x01010101u, static_cast<unsigned>(sk_)));
+        }
+        iq[i] = -8 * sq_;
+        ik[i] = -8 * sk_;
+      }
+    }
+    invq = misc[4];
+    if (TWO) invk = misc[5];
+  } else if (AXK) {
+    load_slice(nullptr);
+  }
   for (int hi = 0; hi < gqa; hi++) {
     const int h = h0 + hi;
     const int s = hi % nst;
@@ -628,7 +688,9 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
       const int orow_i = warp * RW + (own ? p0 + c : 0) * RPP + rl;
       const float vt = ldf(A.v + (long long)b * A.sv, A.dt_v, (long long)h * DV + orow_i);
       float tq, tk;
-      if (AXK || one_group)
+      if constexpr (FX)
+        pass_rows_fx<BITS, TWO, LPR>(codes, scs, fq, fk, iq, ik, p0, npass, warp * RW, NG, gl, c, rl, tq, tk);
+      else if (AXK || one_group)
         pass_rows<BITS, AXK, TWO, LPR, false>(codes, scs, vq, vk, p0, npass, warp * RW, G, NG, gl, c, rl, cur_gv,
                                               [&](int) {}, tq, tk);
       else
@@ -636,6 +698,7 @@ __global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_con
                                              [&](int gv) { load_slice(scs + gv * DK); }, tq, tk);
       if (own) {
         const int row = orow_i;
+        if (FX) { tq = invq * tq; tk = invk * tk; }             // powers of two: exact
         if (!VDEC) { tq = alpha * tq; tk = alpha * tk; }
         for (int i = 0; i < n; i++) {                          // live slots only; dead ones may hold garbage
           float ub;
