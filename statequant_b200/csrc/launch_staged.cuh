@@ -4,6 +4,15 @@
 #include "launchers.h"
 #include "step_tma.cuh"
 
+// Stages are dropped until the CTA's shared memory fits under a cap: 32 000 bytes lets seven CTAs share an SM (the
+// kernels for states scaled along k are built for that many), the larger one is for the others.
+#ifndef SQB_STAGE_CAP_K
+#define SQB_STAGE_CAP_K 32000
+#endif
+#ifndef SQB_STAGE_CAP
+#define SQB_STAGE_CAP (100 * 1024)
+#endif
+
 namespace sqb {
 template <int KIND, int BITS, bool AXK, int LPR>
 int launch_staged_one(const StepArgs& a, cudaStream_t stream) {
@@ -11,7 +20,7 @@ int launch_staged_one(const StepArgs& a, cudaStream_t stream) {
   const int gqa = a.HV / a.HK;
   int nst = gqa < 2 ? gqa : (KIND == K_M2 && gqa >= 3 ? 3 : 2);
   Smem2 plan = smem2_plan(KIND, BITS, AXK, a.group, a.DK, a.DV, a.M, a.qbuf, nst, gqa);
-  while (nst > 1 && plan.total > 100 * 1024) {
+  while (nst > 1 && plan.total > (AXK ? SQB_STAGE_CAP_K : SQB_STAGE_CAP)) {
     nst--;
     plan = smem2_plan(KIND, BITS, AXK, a.group, a.DK, a.DV, a.M, a.qbuf, nst, gqa);
   }

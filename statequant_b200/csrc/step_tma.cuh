@@ -249,11 +249,16 @@ __device__ __forceinline__ uint32_t round4_i8(const float* x, float s, float r, 
 #include "pass_rows.cuh"
 namespace sqb {
 
+// resident CTAs per SM the register allocation aims at: states scaled along k run the integer pass and fit 72
+// registers without spilling; states scaled along v keep their scale slices in registers and do not
 #ifndef SQB_MINB
 #define SQB_MINB 4
 #endif
+#ifndef SQB_MINB_K
+#define SQB_MINB_K 7
+#endif
 template <int KIND, int BITS, bool AXK, int LPR>
-__global__ void __launch_bounds__(NT, SQB_MINB) step_tma_kernel(const __grid_constant__ StepArgs A, const __grid_constant__ Smem2 P,
+__global__ void __launch_bounds__(NT, AXK ? SQB_MINB_K : SQB_MINB) step_tma_kernel(const __grid_constant__ StepArgs A, const __grid_constant__ Smem2 P,
                                                                 const int nst) {
   constexpr int DK = LPR * 16;
   constexpr int RPP = 32 / LPR;                  // rows per warp pass
