@@ -22,3 +22,14 @@ def test_fma_division_by_fp16_factor_is_exact(tmp_path):
                    check=True)
     r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and 'mismatches 0 ' in r.stdout, r.stdout
+
+
+def test_fixed_point_pass_arithmetic(tmp_path):
+    """The staged kernel's integer state pass: byte slices of the 24-bit fixed-point q / k recombine exactly, the
+    int4 offset is carried by the slice sums' start values, and a chunk sum stays within the fixed-point rounding of
+    the double-precision dot product."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    exe = str(tmp_path / 'fx_pass_check')
+    subprocess.run(['gcc', '-O2', '-ffp-contract=off', '-o', exe, os.path.join(here, 'fx_pass_check.c'), '-lm'], check=True)
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and 'failures 0' in r.stdout, r.stdout
