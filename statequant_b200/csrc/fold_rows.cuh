@@ -73,7 +73,8 @@ __device__ __forceinline__ void fold_dequant(float2 (&a)[8], float sc, float alp
 
 // The verified candidates of round_fast, clamped to the code range.  A scale that is subnormal in fp16 can be far
 // enough below absmax / qmax for the largest quotients to round beyond qmax; the candidate is then still the right
-// unclamped integer, and clamping it is what clamp(rint(div_rn(x, s))) does.
+// unclamped integer, and clamping it is what clamp(rint(div_rn(x, s))) does.  A normal fp16 scale is within 2^-11 of
+// absmax / qmax, so no quotient exceeds qmax (1 + 2^-10) and none rounds beyond qmax: callers skip the clamp then.
 template <int BITS>
 __device__ __forceinline__ float2 (&clamp_codes(float2 (&t)[8]))[8] {
   constexpr float QMAX = BITS == 4 ? 7.0f : 127.0f;
@@ -166,14 +167,20 @@ __device__ __forceinline__ bool fold_rows(const uint8_t* codes, const unsigned s
       if (v0) {
         if (lead) SCh[r0 * NG + gl] = f2h(sc0);
         uint4 pk;
-        if (round_fast<8>(a0, sc0, rcp_approx(sc0), MB, tt)) pk = pack_codes16<BITS>(clamp_codes<BITS>(tt));
+        if (round_fast<8>(a0, sc0, rcp_approx(sc0), MB, tt)) {
+          if (sc0 < FP16_MIN_NORMAL) clamp_codes<BITS>(tt);     // only a subnormal scale lets a quotient pass qmax
+          pk = pack_codes16<BITS>(tt);
+        }
         else pk = round_exact_pack<BITS>(a0[0], a0[1], a0[2], a0[3], a0[4], a0[5], a0[6], a0[7], sc0);
         store_packed16<BITS>(Sh + (long long)r0 * ROWB + c * CB, pk);
       }
       if (v1) {
         if (lead) SCh[r1 * NG + gl] = f2h(sc1);
         uint4 pk;
-        if (round_fast<8>(a1, sc1, rcp_approx(sc1), MB, tt)) pk = pack_codes16<BITS>(clamp_codes<BITS>(tt));
+        if (round_fast<8>(a1, sc1, rcp_approx(sc1), MB, tt)) {
+          if (sc1 < FP16_MIN_NORMAL) clamp_codes<BITS>(tt);     // only a subnormal scale lets a quotient pass qmax
+          pk = pack_codes16<BITS>(tt);
+        }
         else pk = round_exact_pack<BITS>(a1[0], a1[1], a1[2], a1[3], a1[4], a1[5], a1[6], a1[7], sc1);
         store_packed16<BITS>(Sh + (long long)r1 * ROWB + c * CB, pk);
       }

@@ -5,7 +5,8 @@
 #include "step_tma.cuh"
 
 // Stages are dropped until the CTA's shared memory fits under a cap: 32 000 bytes lets seven CTAs share an SM (the
-// kernels for states scaled along k are built for that many), the larger one is for the others.
+// kernels for states scaled along k are built for seven or eight; at the usual shapes they then take 24 to 25 KB,
+// which fits eight), the larger one is for the others.
 #ifndef SQB_STAGE_CAP_K
 #define SQB_STAGE_CAP_K 32000
 #endif

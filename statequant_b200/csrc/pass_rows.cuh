@@ -176,7 +176,7 @@ __device__ __forceinline__ float fx_dot16(const uint32_t (&b)[4], const uint32_t
   return fmaf(static_cast<float>(a0), 65536.0f, static_cast<float>(a1 * 256 + a2));
 }
 
-template <int BITS, bool TWO, int LPR>
+template <int BITS, bool TWO, int LPR, int PUX = SQB_PASS_UNROLL>
 __device__ __forceinline__ void pass_rows_fx(const uint8_t* codes, const unsigned short* scs,
                                              const uint32_t (&fq)[3][4], const uint32_t (&fk)[3][4],
                                              const int (&iq)[3], const int (&ik)[3], int p0, int npass, int row_base,
@@ -185,7 +185,7 @@ __device__ __forceinline__ void pass_rows_fx(const uint8_t* codes, const unsigne
   constexpr int RPP = 32 / LPR;
   constexpr int CB = 16 * BITS / 8;
   constexpr int ROWB = DK * BITS / 8;
-  constexpr int PU = SQB_PASS_UNROLL < LPR ? SQB_PASS_UNROLL : LPR;
+  constexpr int PU = PUX < LPR ? PUX : LPR;
   tq = 0.f;
   tk = 0.f;
   for (int g = 0; g < LPR / PU; g++) {

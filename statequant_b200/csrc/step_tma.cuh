@@ -249,16 +249,20 @@ __device__ __forceinline__ uint32_t round4_i8(const float* x, float s, float r, 
 #include "pass_rows.cuh"
 namespace sqb {
 
-// resident CTAs per SM the register allocation aims at: states scaled along k run the integer pass and fit 72
-// registers without spilling; states scaled along v keep their scale slices in registers and do not
+// resident CTAs per SM the register allocation aims at: states scaled along k run the integer pass in 64 registers
+// with a few spilled words (measured faster than 72 registers and 7 CTAs for GDN and KDA; Mamba2, whose CTAs walk 16
+// heads, is faster at 7); states scaled along v keep their scale slices in registers and stay at 4
 #ifndef SQB_MINB
 #define SQB_MINB 4
 #endif
 #ifndef SQB_MINB_K
-#define SQB_MINB_K 7
+#define SQB_MINB_K 8
+#endif
+#ifndef SQB_MINB_K_M2
+#define SQB_MINB_K_M2 7
 #endif
 template <int KIND, int BITS, bool AXK, int LPR>
-__global__ void __launch_bounds__(NT, AXK ? SQB_MINB_K : SQB_MINB) step_tma_kernel(const __grid_constant__ StepArgs A, const __grid_constant__ Smem2 P,
+__global__ void __launch_bounds__(NT, AXK ? (KIND == K_M2 ? SQB_MINB_K_M2 : SQB_MINB_K) : SQB_MINB) step_tma_kernel(const __grid_constant__ StepArgs A, const __grid_constant__ Smem2 P,
                                                                 const int nst) {
   constexpr int DK = LPR * 16;
   constexpr int RPP = 32 / LPR;                  // rows per warp pass
@@ -694,7 +698,7 @@ __global__ void __launch_bounds__(NT, AXK ? SQB_MINB_K : SQB_MINB) step_tma_kern
       const float vt = ldf(A.v + (long long)b * A.sv, A.dt_v, (long long)h * DV + orow_i);
       float tq, tk;
       if constexpr (FX)
-        pass_rows_fx<BITS, TWO, LPR>(codes, scs, fq, fk, iq, ik, p0, npass, warp * RW, NG, gl, c, rl, tq, tk);
+        pass_rows_fx<BITS, TWO, LPR, (KIND == K_M2 ? 4 : 8)>(codes, scs, fq, fk, iq, ik, p0, npass, warp * RW, NG, gl, c, rl, tq, tk);
       else if (AXK || one_group)
         pass_rows<BITS, AXK, TWO, LPR, false>(codes, scs, vq, vk, p0, npass, warp * RW, G, NG, gl, c, rl, cur_gv,
                                               [&](int) {}, tq, tk);
