@@ -394,7 +394,7 @@ def cpu_baseline(batch, steps, warmup, preset='int8k'):
 
 # DRAM bytes (read + write) per layer-step from ncu captures at batch 256 (profiles/): the step kernel of a non-fold
 # step, and on every 8th step the fold kernel on top; traffic grows in proportion to the batch.
-NCU_TRAFFIC_B256 = {'int8k': (160.0e6 + 5.8e6, 155.9e6 + 84.5e6)}
+NCU_TRAFFIC_B256 = {'int8k': (160.0e6 + 5.2e6, 155.8e6 + 84.3e6)}
 
 
 def ncu_traffic(preset, batch):
