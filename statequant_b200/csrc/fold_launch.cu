@@ -12,11 +12,10 @@ int launch_fold_one(const StepArgs& a, cudaStream_t stream, float* out) {
   auto kern = fold_kernel<VDEC, BITS, AXK, LPR>;
   const SmemF plan = smemf_plan(VDEC, BITS, AXK, a.group, a.DK, a.DV, a.M, a.qbuf);
   if (plan.total > 220 * 1024) return 1;
-  static std::atomic<int> configured{0};
-  if (plan.total > configured.load()) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.total);
+  static SmemLimit limit;                   // per instantiation
+  {
+    cudaError_t e = limit.ensure(kern, plan.total);
     if (e != cudaSuccess) return -1000 - static_cast<int>(e);
-    configured.store(plan.total);
   }
   static thread_local int sms[64];
   int dev = 0;

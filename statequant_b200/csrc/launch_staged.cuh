@@ -26,11 +26,10 @@ int launch_staged_one(const StepArgs& a, cudaStream_t stream) {
     plan = smem2_plan(KIND, BITS, AXK, a.group, a.DK, a.DV, a.M, a.qbuf, nst, gqa);
   }
   if (plan.total > 220 * 1024) return 1;    // does not fit: the caller falls back to the generic kernel
-  static std::atomic<int> configured{0};
-  if (plan.total > configured.load()) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.total);
+  static SmemLimit limit;                   // per instantiation
+  {
+    cudaError_t e = limit.ensure(kern, plan.total);
     if (e != cudaSuccess) return -1000 - static_cast<int>(e);
-    configured.store(plan.total);
   }
   const long long ctas = static_cast<long long>(a.rows) * a.HK;
   if (ctas > 2147483647LL) return 1;

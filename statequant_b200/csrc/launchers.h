@@ -2,10 +2,27 @@
 // parallel) and of the fold kernel.  Return 0: launched; 1: the kernel does not take this shape (the caller falls back);
 // < 0: -(1000 + cudaError_t).
 #pragma once
+#include <atomic>
 #include <cuda_runtime.h>
 #include "delta_step.cuh"
 
 namespace sqb {
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device setting of a kernel: remember, per device, the largest
+// size already set, so that the attribute call is made only when a launch needs more on the device it runs on.
+struct SmemLimit {
+  std::atomic<int> set[64];
+  template <class K>
+  cudaError_t ensure(K kern, int bytes) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const bool cached = dev >= 0 && dev < 64;
+    if (cached && bytes <= set[dev].load(std::memory_order_relaxed)) return cudaSuccess;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess && cached) set[dev].store(bytes, std::memory_order_relaxed);
+    return e;
+  }
+};
 int launch_staged_gdn(const StepArgs& a, int bits, bool axk, cudaStream_t stream);
 int launch_staged_m2(const StepArgs& a, int bits, bool axk, cudaStream_t stream);
 int launch_staged_kda(const StepArgs& a, int bits, bool axk, cudaStream_t stream);

@@ -97,12 +97,11 @@ int launch_one(const sqb::StepArgs& a, cudaStream_t stream) {
   auto kern = sqb::delta_step_kernel<KIND, BITS, AXK>;
   const sqb::Smem plan = sqb::smem_plan(KIND, a.DK, a.DV, a.M, 128 / BITS, 1 << a.lpr_log2);
   const size_t smem = static_cast<size_t>(plan.total) * sizeof(float);
-  static std::atomic<size_t> configured{0};       // per instantiation
-  if (smem > 48 * 1024 && smem > configured.load()) {
+  static sqb::SmemLimit limit;                    // per instantiation
+  if (smem > 48 * 1024) {
     if (smem > 200 * 1024) return fail(SQB_EINVAL, "shape needs %zu bytes of shared memory per CTA", smem);
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaError_t e = limit.ensure(kern, static_cast<int>(smem));
     if (e != cudaSuccess) return fail(SQB_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    configured.store(smem);
   }
   const long long ctas = static_cast<long long>(a.rows) * a.HV;
   if (ctas > 2147483647LL) return fail(SQB_EINVAL, "rows * hv = %lld exceeds the grid limit", ctas);

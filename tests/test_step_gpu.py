@@ -489,3 +489,37 @@ def test_full_batch_properties_kda_shapes():
                 lambda V, i, x, o: lay.step(V, i, x[0], x[1], x[2], x[3], x[4], o, Dm ** -0.5),
                 lambda V, i, x, o: oracle.kda_step(lay, V, i, x[0], x[1], x[2], x[3], x[4], o, Dm ** -0.5),
                 sample_n=3, hv=H, dv=Dm)
+
+
+@pytest.mark.gpu
+def test_two_devices_in_one_process():
+    """The same decode run on two GPUs from one process (each under its own device guard) gives identical bytes:
+    the kernels' shared-memory limits are per-device settings and are made on the device each launch runs on.
+    Nine tokens, so that one fold launch (more than 48 KB of shared memory per CTA) runs on both."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs two GPUs')
+    import statequant_b200 as sq
+    from statequant_b200.kernels import SlotLayout
+    lay = SlotLayout(sq.Quantizer(8, 'k', 32), 32, 16, 128, 128, m=8)
+    g = torch.Generator().manual_seed(3)
+    B = 8
+    steps = [(torch.randn(B, 16, 128, generator=g).bfloat16(), torch.randn(B, 16, 128, generator=g).bfloat16(),
+              torch.randn(B, 32, 128, generator=g).bfloat16(), torch.nn.functional.logsigmoid(torch.randn(B, 32, generator=g) + 2),
+              torch.sigmoid(torch.randn(B, 32, generator=g))) for _ in range(9)]
+    idx = torch.arange(1, B + 1, dtype=torch.int32)
+    res = []
+    for d in (0, 1):
+        dev = torch.device('cuda', d)
+        with torch.cuda.device(dev):
+            blob = lay.alloc(B + 1, dev)
+            views = lay.views(blob)
+            out = torch.empty(B, 32, 128, dtype=torch.bfloat16, device=dev)
+            outs = []
+            for q, k, v, gg, bt in steps:
+                lay.step(views, idx.to(dev), q.to(dev), k.to(dev), v.to(dev), out, 128 ** -0.5, g=gg.to(dev), beta=bt.to(dev))
+                outs.append(out.cpu().clone())
+            torch.cuda.synchronize(dev)
+            res.append((blob.cpu(), outs))
+    assert torch.equal(res[0][0], res[1][0])
+    assert all(torch.equal(a, b) for a, b in zip(res[0][1], res[1][1]))
+    assert res[0][0].any()
