@@ -194,8 +194,12 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
       return;
     }
   }
+  // LPR: lanes per row rounded up to a power of two; a d_k that is not a power of two (96, 192) leaves the last lanes
+  // of every row without columns: such a lane (lv false) loads nothing, reads the state against zeros and stores
+  // nothing, but takes part in every shuffle
   const int LPR = 1 << A.lpr_log2, RPP = 32 >> A.lpr_log2;
   const int c = lane & (LPR - 1), rl = lane >> A.lpr_log2;
+  const bool lv = c * CPL < DK;
   const Smem P = smem_plan(KIND, DK, DV, M, CPL, LPR);
   float *xq = sm + P.xq, *xk = sm + P.xk, *kxs = sm + P.kx, *ga = sm + P.ga, *ae = sm + P.ae, *vin = sm + P.vin,
         *us = sm + P.us, *R = sm + P.R, *L = sm + P.L, *cq = sm + P.cq, *ck = sm + P.ck, *dec = sm + P.dec,
@@ -205,7 +209,7 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
   const int rowbytes = DK * EB / 8;
   uint8_t* Sh = A.S + seq * A.sS + (long long)h * DV * rowbytes;
   const int G = A.group;
-  const int NG = QUANT && AXK ? DK / G : 1;                      // key-axis groups per row
+  const int NG = QUANT && AXK ? (DK + G - 1) / G : 1;            // key-axis groups per row (the last one may be short)
   unsigned short* SCh = nullptr;
   if (QUANT) SCh = reinterpret_cast<unsigned short*>(A.SC + seq * A.sSC) + (long long)h * (AXK ? DV * NG : (DV / G) * DK);
   const int gl = QUANT && AXK ? (c * CPL) / G : 0;               // this lane's key group
@@ -229,7 +233,7 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
     const int rr = p * RPP + rl;
     cw[p] = make_uint4(0, 0, 0, 0);
     scw[p] = 0;
-    if (p < npass && rr < RW) {
+    if (p < npass && rr < RW && lv) {
       const int row = warp * RW + rr;
       cw[p] = *reinterpret_cast<const uint4*>(Sh + (long long)row * rowbytes + c * 16);
       if (QUANT && AXK) scw[p] = SCh[row * NG + gl];
@@ -383,6 +387,11 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
   auto load_slice = [&](const unsigned short* scrow) {
 #pragma unroll
     for (int p = 0; p < NP; p++) {
+      if (!lv) {
+        vq[p] = make_float2(0.f, 0.f);
+        vk[p] = make_float2(0.f, 0.f);
+        continue;
+      }
       const int k0 = c * CPL + 2 * p;
       float q0 = xq[k0], q1 = xq[k0 + 1], k0v = 0.f, k1v = 0.f;
       if (TWO) { k0v = xk[k0]; k1v = xk[k0 + 1]; }
@@ -405,7 +414,7 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
         const int rr = (p0 + p) * RPP + rl;
         cw[p] = make_uint4(0, 0, 0, 0);
         scw[p] = 0;
-        if (p0 + p < npass && rr < RW) {
+        if (p0 + p < npass && rr < RW && lv) {
           const int row = warp * RW + rr;
           cw[p] = *reinterpret_cast<const uint4*>(Sh + (long long)row * rowbytes + c * 16);
           if (QUANT && AXK) scw[p] = SCh[row * NG + gl];
@@ -578,10 +587,10 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
       rv[pp] = pp < ppw && row < DV;
       rows[pp] = rv[pp] ? row : 0;
       uint4 cwv = make_uint4(0, 0, 0, 0);
-      if (rv[pp]) cwv = *reinterpret_cast<const uint4*>(Sh + (long long)rows[pp] * rowbytes + c * 16);
+      if (rv[pp] && lv) cwv = *reinterpret_cast<const uint4*>(Sh + (long long)rows[pp] * rowbytes + c * 16);
       F::decode(cwv, acc[pp]);
       if (QUANT && AXK) {
-        const float s = rv[pp] ? h2f(SCh[rows[pp] * NG + gl]) : 0.f;
+        const float s = rv[pp] && lv ? h2f(SCh[rows[pp] * NG + gl]) : 0.f;
 #pragma unroll
         for (int p = 0; p < NP; p++) {
           const float2 s2 = make_float2(s * F::prescale(2 * p), s * F::prescale(2 * p + 1));
@@ -590,7 +599,7 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
       }
     }
     if (QUANT && !AXK) {
-      const bool gvalid = gvrow * G < DV;
+      const bool gvalid = gvrow * G < DV && lv;
 #pragma unroll
       for (int p = 0; p < NP; p++) {
         const int k0 = c * CPL + 2 * p;
@@ -603,7 +612,7 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
 #pragma unroll
     for (int p = 0; p < NP; p++) {
       float2 d2 = make_float2(alphan, alphan);
-      if (VDEC) d2 = make_float2(ae[c * CPL + 2 * p], ae[c * CPL + 2 * p + 1]);
+      if (VDEC && lv) d2 = make_float2(ae[c * CPL + 2 * p], ae[c * CPL + 2 * p + 1]);
 #pragma unroll
       for (int pp = 0; pp < PPW; pp++) acc[pp][p] = __fmul2_rn(acc[pp][p], d2);
     }
@@ -631,7 +640,7 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
     if constexpr (!QUANT) {
 #pragma unroll
       for (int pp = 0; pp < PPW; pp++) {
-        if (!rv[pp]) continue;
+        if (!rv[pp] || !lv) continue;
         uint4 o;
         if constexpr (BITS == 16) {
           o.x = f2bf(acc[pp][0].x) | (static_cast<uint32_t>(f2bf(acc[pp][0].y)) << 16);
@@ -654,9 +663,10 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
           float am = 0.f;
 #pragma unroll
           for (int p = 0; p < NP; p++) am = fmaxf(am, fmaxf(fabsf(acc[pp][p].x), fabsf(acc[pp][p].y)));
+          if (!lv) am = 0.f;                     // a short last group: its missing lanes hold nothing
           for (int o = 1; o < lpg; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
           sc[pp] = fp16_scale(am, QMAX);
-          if (rv[pp] && (c & (lpg - 1)) == 0) SCh[rows[pp] * NG + gl] = f2h(sc[pp]);
+          if (rv[pp] && lv && (c & (lpg - 1)) == 0) SCh[rows[pp] * NG + gl] = f2h(sc[pp]);
         }
       } else {
         // column maxima over the group's rows: this lane's passes, then the lanes of other rows, then other warps
@@ -675,17 +685,18 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
           sc[2 * p + 1] = m1;
         }
         __syncthreads();      // cmax free (previous iteration's readers are done)
-        if (rl == 0) {
+        if (rl == 0 && lv) {
 #pragma unroll
           for (int j = 0; j < CPL; j++) cmax[warp * DK + c * CPL + j] = sc[j];
         }
         __syncthreads();
         const int w0 = (warp / wpg) * wpg;
-        const bool gvalid = gvrow * G < DV;
+        const bool gvalid = gvrow * G < DV && lv;
 #pragma unroll
         for (int j = 0; j < CPL; j++) {
           float am = 0.f;
-          for (int w = 0; w < wpg; w++) am = fmaxf(am, cmax[(w0 + w) * DK + c * CPL + j]);
+          if (lv)
+            for (int w = 0; w < wpg; w++) am = fmaxf(am, cmax[(w0 + w) * DK + c * CPL + j]);
           sc[j] = fp16_scale(am, QMAX);
           if (gvalid && rl == 0 && warp == w0) SCh[gvrow * DK + c * CPL + j] = f2h(sc[j]);
         }
@@ -693,7 +704,7 @@ __global__ void __launch_bounds__(NT) delta_step_kernel(const __grid_constant__ 
       // codes
 #pragma unroll
       for (int pp = 0; pp < PPW; pp++) {
-        if (!rv[pp]) continue;
+        if (!rv[pp] || !lv) continue;
         float2 t[NP];
         constexpr float MB = BITS == 4 ? MAGIC + 8.0f : MAGIC;
         bool ok;

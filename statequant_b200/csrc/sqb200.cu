@@ -40,14 +40,16 @@ int check_state(const sqb_state_t* st, int kind, int* lpr_log2) {
   if (st->hv <= 0 || st->hk <= 0 || st->hv % st->hk) return fail(SQB_EINVAL, "heads hv %d, hk %d: hv must be a multiple of hk", st->hv, st->hk);
   if (kind == sqb::K_KDA && st->hv != st->hk) return fail(SQB_EINVAL, "KDA: key heads must equal value heads");
   const int cpl = 128 / bits;
-  if (dk % cpl || !pow2(dk / cpl) || dk / cpl > 32)
-    return fail(SQB_EINVAL, "d_k %d with %d-bit codes: d_k * bits / 128 must be a power of two <= 32", dk, bits);
-  const int lpr = dk / cpl, rpp = 32 / lpr;
+  if (dk <= 0 || dk % cpl || dk / cpl > 32)
+    return fail(SQB_EINVAL, "d_k %d with %d-bit codes: a row must be 1 to 32 whole 16-byte chunks", dk, bits);
+  int lpr = 1;                                // lanes per row, rounded up to a power of two (d_k 96, 192: the last lanes idle)
+  while (lpr < dk / cpl) lpr <<= 1;
+  const int rpp = 32 / lpr;
   if (dv % 4 || dv <= 0) return fail(SQB_EINVAL, "d_v %d: expected a positive multiple of 4", dv);
   if (bits <= 8) {
     if (!pow2(g)) return fail(SQB_EINVAL, "group %d: expected a power of two", g);
     if (st->axis_k) {
-      if (g % cpl || dk % g) return fail(SQB_EINVAL, "key-axis group %d on d_k %d with %d-bit codes: the group must be a multiple of %d and divide d_k", g, dk, bits, cpl);
+      if (g % cpl) return fail(SQB_EINVAL, "key-axis group %d with %d-bit codes: the group must be a multiple of %d", g, bits, cpl);
     } else {
       if (dv % g) return fail(SQB_EINVAL, "value-axis group %d must divide d_v %d", g, dv);
       if (g % rpp || dv % (sqb::NW * rpp)) return fail(SQB_EINVAL, "value-axis group %d, d_v %d: both must be multiples of %d rows", g, dv, rpp);

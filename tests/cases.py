@@ -17,6 +17,10 @@ CASES = {
     'gdn_bf16_m4_b8':      dict(kind='gdn', fmt='bf16', B=2, hv=2, hk=1, dk=64, dv=64, m=4, bb=8, T=9, seed=15),
     'gdn_pace4_qwen':      dict(kind='gdn', fmt=(4, 'k', 64), B=1, hv=4, hk=2, dk=128, dv=128, m=8, bb=8, T=17, seed=16),
     'gdn_int4k64_m1_b8':   dict(kind='gdn', fmt=(4, 'k', 64), B=1, hv=2, hk=2, dk=128, dv=128, m=1, bb=8, T=4, seed=17),
+    # head dims that are not powers of two (reference: tests/test_kernels_nonpow2.py): idle lanes, a short last key group
+    'gdn_int8k32_96x192':  dict(kind='gdn', fmt=(8, 'k', 32), B=1, hv=4, hk=2, dk=96, dv=192, m=4, bb=8, T=9, seed=18),
+    'gdn_int4k64_96x64':   dict(kind='gdn', fmt=(4, 'k', 64), B=2, hv=2, hk=1, dk=96, dv=64, m=8, bb=8, T=17, seed=19),
+    'gdn_int4v32_192x96':  dict(kind='gdn', fmt=(4, 'v', 32), B=1, hv=2, hk=2, dk=192, dv=96, m=2, bb=16, T=5, seed=20),
     'm2_int8k32_m8_b8':    dict(kind='m2', fmt=(8, 'k', 32), B=2, hv=4, hk=2, dk=128, dv=64, m=8, bb=8, T=18, seed=21),
     'm2_int4k64_m4_b16':   dict(kind='m2', fmt=(4, 'k', 64), B=2, hv=4, hk=1, dk=128, dv=64, m=4, bb=16, T=9, seed=22,
                                 softplus=False),

@@ -54,8 +54,8 @@ def test_bad_arguments_are_refused_with_a_message():
     assert L.sqb_gdn_step(C.byref(st), C.byref(a), None) == -1 and b'power of two' in L.sqb_last_error()
     st.m, st.hk = 8, 3
     assert L.sqb_gdn_step(C.byref(st), C.byref(a), None) == -1 and b'multiple of hk' in L.sqb_last_error()
-    st.hk, st.dk = 2, 96                      # not yet supported: d_k * bits / 128 not a power of two
-    assert L.sqb_gdn_step(C.byref(st), C.byref(a), None) == -1 and b'd_k 96' in L.sqb_last_error()
+    st.hk, st.dk = 2, 80                      # rows that are not whole 16-byte chunks
+    assert L.sqb_gdn_step(C.byref(st), C.byref(a), None) == -1 and b'd_k 80' in L.sqb_last_error()
     st.dk = 128
     assert L.sqb_gdn_step(C.byref(st), C.byref(a), None) == -1 and b'NULL' in L.sqb_last_error()
     assert L.sqb_gdn_step(None, C.byref(a), None) == -1

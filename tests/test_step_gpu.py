@@ -370,11 +370,11 @@ def test_bad_tensors_raise():
         lay.step(V, torch.tensor([1, 2], dtype=torch.int32, device=DEV), q.double(), q.double(), v, out, 1.0, g=gb, beta=gb)
     with pytest.raises(AssertionError):
         lay.step(V, torch.tensor([1, 2], dtype=torch.int32, device=DEV), q, q, v, out.transpose(1, 2), 1.0, g=gb, beta=gb)
-    with pytest.raises(RuntimeError, match='d_k 96'):
-        l2 = SlotLayout(sq.Quantizer(4, 'k', 64), 4, 2, 96, 128)
+    with pytest.raises(RuntimeError, match='d_k 80'):               # rows of 40 bytes: not whole 16-byte chunks
+        l2 = SlotLayout(sq.Quantizer(4, 'k', 64), 4, 2, 80, 128)
         b2 = l2.alloc(2, DEV)
-        l2.step(l2.views(b2), torch.tensor([1], dtype=torch.int32, device=DEV), torch.zeros(1, 2, 96, device=DEV),
-                torch.zeros(1, 2, 96, device=DEV), torch.zeros(1, 4, 128, device=DEV), torch.zeros(1, 4, 128, device=DEV),
+        l2.step(l2.views(b2), torch.tensor([1], dtype=torch.int32, device=DEV), torch.zeros(1, 2, 80, device=DEV),
+                torch.zeros(1, 2, 80, device=DEV), torch.zeros(1, 4, 128, device=DEV), torch.zeros(1, 4, 128, device=DEV),
                 1.0, g=torch.zeros(1, 4, device=DEV), beta=torch.zeros(1, 4, device=DEV))
 
 
@@ -523,3 +523,29 @@ def test_two_devices_in_one_process():
     assert torch.equal(res[0][0], res[1][0])
     assert all(torch.equal(a, b) for a, b in zip(res[0][1], res[1][1]))
     assert res[0][0].any()
+
+
+LONG_TAIL = [
+    dict(kind='gdn', fmt=(8, 'k', 32), B=2, hv=4, hk=2, dk=128, dv=192, m=8, bb=8, seed=41),
+    dict(kind='gdn', fmt=(4, 'k', 64), B=2, hv=4, hk=2, dk=128, dv=192, m=8, bb=8, seed=42),
+    dict(kind='gdn', fmt=(4, 'v', 32), B=2, hv=4, hk=2, dk=128, dv=192, m=8, bb=8, seed=43),
+    dict(kind='gdn', fmt=(4, 'k', 32), B=2, hv=4, hk=2, dk=64, dv=160, m=8, bb=16, seed=45),
+    dict(kind='gdn', fmt=(8, 'k', 64), B=2, hv=4, hk=2, dk=192, dv=96, m=8, bb=8, seed=51),
+    dict(kind='gdn', fmt='bf16', B=1, hv=2, hk=1, dk=96, dv=64, m=4, bb=8, seed=54),
+    dict(kind='m2', fmt=(8, 'k', 32), B=2, hv=4, hk=2, dk=128, dv=96, m=8, bb=8, seed=46),
+    dict(kind='m2', fmt=(8, 'k', 32), B=2, hv=4, hk=2, dk=96, dv=64, m=8, bb=8, seed=52),
+    dict(kind='m2', fmt=(8, 'k', 32), B=2, hv=4, hk=2, dk=128, dv=80, m=8, bb=8, seed=56),   # head_dim 80
+    dict(kind='m2', fmt=(4, 'k', 32), B=1, hv=4, hk=1, dk=96, dv=96, m=4, bb=16, seed=55),   # Mamba2: no short groups
+]
+
+
+@pytest.mark.parametrize('c', LONG_TAIL, ids=lambda c: f"{c['kind']}-{c['fmt']}-{c['dk']}x{c['dv']}")
+def test_long_tail_shapes_match_oracle(c, kernel_path):
+    """Head dims that are not powers of two (the reference covers them in tests/test_kernels_nonpow2.py and
+    docs/kernels.md:90-93): d_v 96 / 160 / 192 with the staged kernels, d_k 96 / 192 (idle lanes, a short last key
+    group) with the generic one.  Same bar as the power-of-two cases."""
+    st = _oracle_lockstep(c, T=2 * c['m'] + 3, act_dtype=torch.float32)
+    assert st['worst'] < 2e-5, st
+    assert st['buf'] <= max(1, 1e-4 * st['nbuf']), st
+    assert st['codes'] <= max(1, 1e-4 * st['ncodes']), st
+    assert st['scal'] <= max(1, 1e-4 * st['ncodes']), st
