@@ -65,7 +65,9 @@ typedef struct sqb_state {
   int32_t buffer_bits;   /* 8: int8 + fp16 absmax scale per vector; 16: bf16 */
   int32_t m;             /* buffer length, a power of two <= 32 */
   int32_t hv, hk;        /* value heads, key heads (Mamba2: heads, groups); hv % hk == 0 */
-  int32_t dk, dv;        /* head dims */
+  int32_t dk, dv;        /* head dims: dk * bits a multiple of 128 (whole 16-byte chunks per row, at most 32: 64, 96,
+                            128, 192 ...), dv a multiple of 4; scale groups: a power of two (key-axis: a multiple of
+                            128 / bits, the last one may be short; value-axis: dividing dv) */
   int32_t reserved;
 } sqb_state_t;
 
