@@ -536,14 +536,20 @@ LONG_TAIL = [
     dict(kind='m2', fmt=(8, 'k', 32), B=2, hv=4, hk=2, dk=96, dv=64, m=8, bb=8, seed=52),
     dict(kind='m2', fmt=(8, 'k', 32), B=2, hv=4, hk=2, dk=128, dv=80, m=8, bb=8, seed=56),   # head_dim 80
     dict(kind='m2', fmt=(4, 'k', 32), B=1, hv=4, hk=1, dk=96, dv=96, m=4, bb=16, seed=55),   # Mamba2: no short groups
+    # long buffers (the reference allows m up to 32)
+    dict(kind='gdn', fmt=(8, 'k', 32), B=2, hv=4, hk=2, dk=128, dv=128, m=16, bb=8, seed=61),
+    dict(kind='gdn', fmt=(4, 'k', 64), B=1, hv=4, hk=2, dk=128, dv=128, m=32, bb=8, seed=62),
+    dict(kind='m2', fmt=(8, 'k', 32), B=1, hv=4, hk=2, dk=128, dv=64, m=32, bb=8, seed=64),
+    dict(kind='kda', fmt=(4, 'k', 64), B=1, hv=2, hk=2, dk=128, dv=128, m=16, bb=8, seed=66),
+    dict(kind='gdn', fmt=(8, 'k', 32), B=1, hv=4, hk=2, dk=96, dv=192, m=16, bb=8, seed=68),
 ]
 
 
-@pytest.mark.parametrize('c', LONG_TAIL, ids=lambda c: f"{c['kind']}-{c['fmt']}-{c['dk']}x{c['dv']}")
+@pytest.mark.parametrize('c', LONG_TAIL, ids=lambda c: f"{c['kind']}-{c['fmt']}-{c['dk']}x{c['dv']}-m{c['m']}")
 def test_long_tail_shapes_match_oracle(c, kernel_path):
     """Head dims that are not powers of two (the reference covers them in tests/test_kernels_nonpow2.py and
     docs/kernels.md:90-93): d_v 96 / 160 / 192 with the staged kernels, d_k 96 / 192 (idle lanes, a short last key
-    group) with the generic one.  Same bar as the power-of-two cases."""
+    group) with the generic one; and buffers of 16 and 32 entries.  Same bar as the other cases."""
     st = _oracle_lockstep(c, T=2 * c['m'] + 3, act_dtype=torch.float32)
     assert st['worst'] < 2e-5, st
     assert st['buf'] <= max(1, 1e-4 * st['nbuf']), st
