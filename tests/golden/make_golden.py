@@ -87,7 +87,7 @@ def run_case(name, c, sq, K):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--reference', default='/root/reference/src')
+    ap.add_argument('--reference', required=True, help='the src directory of a StateQuant checkout')
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     import statequant as sq

@@ -30,7 +30,7 @@ from cases import GGA_CASES, fit_input, gga_inputs, gga_plan  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--reference', default='/root/reference/src')
+    ap.add_argument('--reference', required=True, help='the src directory of a StateQuant checkout')
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     import statequant as sq
