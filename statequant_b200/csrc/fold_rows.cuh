@@ -93,14 +93,17 @@ __device__ __forceinline__ void fold_store_f32(float* p, const float2 (&a)[8]) {
     reinterpret_cast<float4*>(p)[j] = make_float4(a[2 * j].x, a[2 * j].y, a[2 * j + 1].x, a[2 * j + 1].y);
 }
 
-// round_fast with one scale (sc[j]) and approximate reciprocal (rc[j]) per column: the same test, per element
+// round_fast with one scale (sc[j]) and approximate reciprocal (rc[j]) per column: the same test, per element;
+// smin: the smallest of the 16 scales (the caller clamps the candidates only if one of them is subnormal in fp16)
 __device__ __forceinline__ bool round_fast_cols(const float2 (&x)[8], const float* sc, const float* rc, float mb,
-                                                float2 (&t)[8]) {
+                                                float2 (&t)[8], float& smin) {
   const float2 m2 = make_float2(mb, mb), nm2 = make_float2(-mb, -mb), h2 = make_float2(0.49998474f, 0.49998474f);
   float worst = -1.0f;                                   // max over elements of |rem| - thr; the chunk passes if < 0
+  smin = 1.0f;
 #pragma unroll
   for (int p = 0; p < 8; p++) {
     const float2 s2 = *reinterpret_cast<const float2*>(sc + 2 * p), r2 = *reinterpret_cast<const float2*>(rc + 2 * p);
+    smin = fminf(smin, fminf(s2.x, s2.y));
     t[p] = __ffma2_rn(x[p], r2, m2);
     const float2 c = __fadd2_rn(t[p], nm2);
     const float2 rem = __ffma2_rn(make_float2(-c.x, -c.y), s2, x[p]);
@@ -265,13 +268,21 @@ __device__ __forceinline__ bool fold_rows(const uint8_t* codes, const unsigned s
       float2 tt[8];
       if (v0) {
         uint4 pk;
-        if (round_fast_cols(a0, myssc, myrsc, MB, tt)) pk = pack_codes16<BITS>(clamp_codes<BITS>(tt));
+        float smin;
+        if (round_fast_cols(a0, myssc, myrsc, MB, tt, smin)) {
+          if (smin < FP16_MIN_NORMAL) clamp_codes<BITS>(tt);
+          pk = pack_codes16<BITS>(tt);
+        }
         else pk = round_exact_pack_cols<BITS>(a0[0], a0[1], a0[2], a0[3], a0[4], a0[5], a0[6], a0[7], myssc);
         store_packed16<BITS>(Sh + (long long)r0 * ROWB + c * CB, pk);
       }
       if (v1) {
         uint4 pk;
-        if (round_fast_cols(a1, myssc, myrsc, MB, tt)) pk = pack_codes16<BITS>(clamp_codes<BITS>(tt));
+        float smin;
+        if (round_fast_cols(a1, myssc, myrsc, MB, tt, smin)) {
+          if (smin < FP16_MIN_NORMAL) clamp_codes<BITS>(tt);
+          pk = pack_codes16<BITS>(tt);
+        }
         else pk = round_exact_pack_cols<BITS>(a1[0], a1[1], a1[2], a1[3], a1[4], a1[5], a1[6], a1[7], myssc);
         store_packed16<BITS>(Sh + (long long)r1 * ROWB + c * CB, pk);
       }
