@@ -36,6 +36,10 @@ def _oracle_lockstep(c, T, act_dtype, seed_slots=7, gate=False):
     """Step the same blob through CUDA and through the oracle from identical pre-step bytes, every step; compare
     outputs and every blob field; continue from the CUDA blob.  Slots are a random subset with padding rows."""
     inp = make_inputs(dict(c, T=T))
+    if c.get('extreme'):                                      # read-out vectors: all zero, tiny, huge, by step
+        for key in (('Cm',) if c['kind'] == 'm2' else ('q', 'k')):
+            for t in range(T):
+                inp[key][t] *= (1.0, 0.0, 1e-30, 1e20)[t % 4]
     lay = layout_of(c)
     B, hv, hk, dk, dv, m = c['B'], c['hv'], c['hk'], c['dk'], c['dv'], c['m']
     n_slots = 9
@@ -555,3 +559,14 @@ def test_long_tail_shapes_match_oracle(c, kernel_path):
     assert st['buf'] <= max(1, 1e-4 * st['nbuf']), st
     assert st['codes'] <= max(1, 1e-4 * st['ncodes']), st
     assert st['scal'] <= max(1, 1e-4 * st['ncodes']), st
+
+
+@pytest.mark.parametrize('name', ['gdn_pace4_qwen', 'm2_int8k32_m8_b8', 'kda_pace4'])
+def test_extreme_read_out_vectors(name, kernel_path):
+    """Read-out vectors that are all zero, tiny (1e-30) or huge (1e20) on alternating steps: the staged kernels hold
+    them as fixed point with a per-vector power-of-two scale, which must cover the whole float range."""
+    c = dict(CASES[name], extreme=True)
+    st = _oracle_lockstep(c, T=2 * c['m'] + 3, act_dtype=torch.float32)
+    assert st['worst'] < 2e-5, st
+    assert st['buf'] <= max(1, 1e-4 * st['nbuf']), st
+    assert st['codes'] <= max(1, 1e-4 * st['ncodes']), st
