@@ -49,6 +49,8 @@ struct StepArgs {
   int per_key_head, gate, dt_softplus, dt_clamp;
   float scale, dt_min, dt_max;
   int* status;               // device health word: [0] counts CTAs whose bounded wait ran out
+  unsigned long long wait_ns;   // how long a wait for a bulk copy may take before the CTA gives up
+  int test_extra_tx;         // test hook: bytes a stage barrier expects beyond what is copied (so its wait runs out)
 };
 
 // shared-memory plan (floats)

@@ -114,7 +114,8 @@ __device__ __forceinline__ bool round_fast_cols(const float2 (&x)[8], const floa
 }
 
 // sync(): barrier among the 128 threads that fold (returns false if the CTA is aborting).  Returns false on abort.
-template <int BITS, bool AXK, int LPR, bool VDEC, class Sync>
+// PAD: the codes lie in the padded pieces of the tensor-core kernel (16 bytes after every 16 rows, mma_pass.cuh)
+template <int BITS, bool AXK, int LPR, bool VDEC, bool PAD = false, class Sync>
 __device__ __forceinline__ bool fold_rows(const uint8_t* codes, const unsigned short* scs, const float* R,
                                           const float* L, const float* ae, float alphan, int DV, int G, int M,
                                           float* cmax, uint8_t* Sh, unsigned short* SCh, int warp, int lane, int tid,
@@ -142,8 +143,8 @@ __device__ __forceinline__ bool fold_rows(const uint8_t* codes, const unsigned s
       const bool v0 = row0 < DV, v1 = row1 < DV;
       const int r0 = v0 ? row0 : 0, r1 = v1 ? row1 : 0;
       float2 a0[8], a1[8];
-      decode16<BITS>(codes + r0 * ROWB + c * CB, a0);
-      decode16<BITS>(codes + r1 * ROWB + c * CB, a1);
+      decode16<BITS>(codes + r0 * ROWB + (PAD ? (r0 >> 4) * 16 : 0) + c * CB, a0);
+      decode16<BITS>(codes + r1 * ROWB + (PAD ? (r1 >> 4) * 16 : 0) + c * CB, a1);
       fold_dequant<BITS, VDEC>(a0, h2f(scs[r0 * NG + gl]), alphan, aec);
       fold_dequant<BITS, VDEC>(a1, h2f(scs[r1 * NG + gl]), alphan, aec);
       if (SQB_FOLD_UNROLL8 && M == 8) fold_mac<LPR, 8>(a0, a1, Rc, L + r0 * LM, L + r1 * LM, M);

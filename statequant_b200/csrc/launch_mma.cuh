@@ -1,0 +1,89 @@
+// Host side of the tensor-core decode-step kernels (step_mma.cuh): which shapes they take, shared-memory sizing,
+// launch (see launchers.h for the return convention).
+#pragma once
+#include "launchers.h"
+#include "step_mma.cuh"
+
+namespace sqb {
+
+// Shapes the tensor-core kernels take: 4 / 8-bit codes scaled along k in groups of 32, 64 or 128, d_k 128, d_v 64 or
+// 128 (whole stages of 128 rows per key head), int8 buffer, q / k per key head, every per-head chunk and table
+// stride a multiple of 16 bytes.
+inline bool mma_shape_ok(const StepArgs& a, int bits, bool axk, bool kda) {
+  if ((bits != 4 && bits != 8) || !axk || a.DK != 128 || !a.qbuf) return false;
+  if (a.DV != 64 && a.DV != 128) return false;
+  if (a.group != 32 && a.group != 64 && a.group != 128) return false;
+  if (!a.per_key_head && a.HV != a.HK) return false;
+  const int gqa = a.HV / a.HK, hps = 128 / a.DV;
+  if (gqa % hps) return false;
+  if (a.M < 1 || a.M > 32 || (a.M & (a.M - 1))) return false;
+  auto a16 = [](const void* p, long long s) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && s % 16 == 0; };
+  if (!a16(a.S, a.sS) || !a16(a.SC, a.sSC) || !a16(a.UB, a.sUB) || !a16(a.KB, a.sKB)) return false;
+  if (((long long)a.M * a.DV) % 16) return false;
+  if (kda && (!a16(a.GB, a.sGB) || !a16(a.GCUR, a.sGC))) return false;
+  return true;
+}
+
+// stages resident per CTA and the plan; false if the CTA does not fit
+template <int KIND>
+inline bool mma_plan(const StepArgs& a, int bits, int mode, SmemM& plan, int& nst) {
+  const int gqa = a.HV / a.HK, nsh = gqa / (128 / a.DV), upg = a.group / 32;
+  nst = nsh < 4 ? nsh : 4;
+  plan = smemm_plan(KIND, bits, upg, a.DV, a.M, nst, gqa, mode == 2);
+  while (nst > 1 && plan.total > 96 * 1024) {
+    nst--;
+    plan = smemm_plan(KIND, bits, upg, a.DV, a.M, nst, gqa, mode == 2);
+  }
+  return plan.total <= 220 * 1024;
+}
+
+template <int KIND, int BITS, int UPG, int DV, int MODE>
+int launch_mma_one(const StepArgs& a, cudaStream_t stream) {
+  auto kern = step_mma_kernel<KIND, BITS, UPG, DV, MODE>;
+  SmemM plan;
+  int nst;
+  if (!mma_plan<KIND>(a, BITS, MODE, plan, nst)) return 1;
+  static SmemLimit limit;                   // per instantiation
+  {
+    cudaError_t e = limit.ensure(kern, plan.total);
+    if (e != cudaSuccess) return -1000 - static_cast<int>(e);
+  }
+  const long long ctas = static_cast<long long>(a.rows) * a.HK;
+  if (ctas > 2147483647LL) return 1;
+  kern<<<static_cast<unsigned>(ctas), NT, plan.total, stream>>>(a, plan, nst);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return -1000 - static_cast<int>(e);
+  return 0;
+}
+
+template <int KIND, int DV, int MODE>
+int launch_mma_fmt(const StepArgs& a, int bits, cudaStream_t stream) {
+  const int upg = a.group / 32;
+  if (bits == 4) {
+    if (upg == 1) return launch_mma_one<KIND, 4, 1, DV, MODE>(a, stream);
+    if (upg == 2) return launch_mma_one<KIND, 4, 2, DV, MODE>(a, stream);
+    return launch_mma_one<KIND, 4, 4, DV, MODE>(a, stream);
+  }
+  if (upg == 1) return launch_mma_one<KIND, 8, 1, DV, MODE>(a, stream);
+  if (upg == 2) return launch_mma_one<KIND, 8, 2, DV, MODE>(a, stream);
+  return launch_mma_one<KIND, 8, 4, DV, MODE>(a, stream);
+}
+
+// mode: 0 every token (the fold launch follows), 1 all but a slot's m-th token, 2 the m-th token with the fold
+template <int KIND, bool DV64>
+int launch_mma(const StepArgs& a, int bits, int mode, cudaStream_t stream) {
+  if (a.DV == 64) {
+    if constexpr (DV64) {
+      if (mode == 0) return launch_mma_fmt<KIND, 64, 0>(a, bits, stream);
+      if (mode == 1) return launch_mma_fmt<KIND, 64, 1>(a, bits, stream);
+      return launch_mma_fmt<KIND, 64, 2>(a, bits, stream);
+    } else {
+      return 1;
+    }
+  }
+  if (mode == 0) return launch_mma_fmt<KIND, 128, 0>(a, bits, stream);
+  if (mode == 1) return launch_mma_fmt<KIND, 128, 1>(a, bits, stream);
+  return launch_mma_fmt<KIND, 128, 2>(a, bits, stream);
+}
+
+}  // namespace sqb

@@ -26,6 +26,11 @@ struct SmemLimit {
 int launch_staged_gdn(const StepArgs& a, int bits, bool axk, cudaStream_t stream);
 int launch_staged_m2(const StepArgs& a, int bits, bool axk, cudaStream_t stream);
 int launch_staged_kda(const StepArgs& a, int bits, bool axk, cudaStream_t stream);
+// the tensor-core kernels (step_mma.cuh); mode 0: every token (the fold launch follows), 1: all but a slot's m-th
+// token, 2: the m-th token together with the fold
+int launch_mma_gdn(const StepArgs& a, int bits, int mode, cudaStream_t stream);
+int launch_mma_m2(const StepArgs& a, int bits, int mode, cudaStream_t stream);
+int launch_mma_kda(const StepArgs& a, int bits, int mode, cudaStream_t stream);
 // the fold launch that follows a staged step (that kernel only appends on a slot's m-th token)
 int launch_fold(int kind, const StepArgs& a, int bits, bool axk, cudaStream_t stream);
 // the fold kernel in its read-out mode: out fp32 [rows, HV, d_v, d_k] = the state advanced across its pending buffer

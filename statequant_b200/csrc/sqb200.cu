@@ -7,6 +7,8 @@
 #include "../../include/statequant_b200.h"
 #include "delta_step.cuh"
 #include "launchers.h"
+#include "fold_kernel.cuh"
+#include "launch_mma.cuh"
 #include "gga.cuh"
 
 namespace sqb {
@@ -81,8 +83,16 @@ int* status_ptr() {
   return p;
 }
 
-void fill_state(sqb::StepArgs& a, const sqb_state_t* st, int lpr_log2) {
+std::atomic<int> g_force_generic{0};     // set through sqb_set_option (tests time and check every kernel)
+std::atomic<int> g_kernel_path{0};       // see sqb_set_option in the header
+std::atomic<long long> g_wait_ns{1000000000ll};   // bound of a device-side wait for a bulk copy
+std::atomic<int> g_test_extra_tx{0};     // test hook: makes the stage barriers of the tensor-core kernels wait in vain
+
+int fill_state(sqb::StepArgs& a, const sqb_state_t* st, int lpr_log2) {
   a.status = status_ptr();
+  if (!a.status) return fail(SQB_ECUDA, "the device status word is not reachable (cudaGetSymbolAddress failed)");
+  a.wait_ns = static_cast<unsigned long long>(g_wait_ns.load(std::memory_order_relaxed));
+  a.test_extra_tx = g_test_extra_tx.load(std::memory_order_relaxed);
   a.S = static_cast<uint8_t*>(st->S); a.SC = static_cast<uint8_t*>(st->SC);
   a.KB = static_cast<uint8_t*>(st->KB); a.KBS = static_cast<uint8_t*>(st->KBS);
   a.UB = static_cast<uint8_t*>(st->UB); a.UBS = static_cast<uint8_t*>(st->UBS);
@@ -92,6 +102,7 @@ void fill_state(sqb::StepArgs& a, const sqb_state_t* st, int lpr_log2) {
   a.sGB = st->sGB; a.sGC = st->sGC; a.sN = st->sN;
   a.group = st->group; a.qbuf = st->buffer_bits == 8; a.M = st->m; a.HV = st->hv; a.HK = st->hk;
   a.DK = st->dk; a.DV = st->dv; a.lpr_log2 = lpr_log2; a.state_f32 = 0;
+  return 0;
 }
 
 template <int KIND, int BITS, bool AXK>
@@ -138,9 +149,6 @@ bool tma_ok(const sqb::StepArgs& a, int bits, bool axk, bool kda) {
   return true;
 }
 
-int g_force_generic = 0;     // set through sqb_set_option (tests time and check every kernel)
-int g_kernel_path = 0;       // 0: best available; 1: generic; 2: staged + fold launch
-
 // launchers of the staged kernels and of the fold kernel live in their own translation units (launchers.h)
 int sub_rc(int rc) {
   if (rc >= 0) {
@@ -157,14 +165,52 @@ int launch_tma(const sqb::StepArgs& a, int bits, bool axk, cudaStream_t stream) 
 }
 
 template <int KIND>
+int launch_mma_kind(const sqb::StepArgs& a, int bits, int mode, cudaStream_t stream) {
+  if (KIND == sqb::K_GDN) return sub_rc(sqb::launch_mma_gdn(a, bits, mode, stream));
+  if (KIND == sqb::K_M2) return sub_rc(sqb::launch_mma_m2(a, bits, mode, stream));
+  return sub_rc(sqb::launch_mma_kda(a, bits, mode, stream));
+}
+
+// the fold launch of this shape fits an SM's shared memory (checked before the step kernel that relies on it starts)
+bool fold_fits(const sqb::StepArgs& a, int bits, bool axk, bool kda) {
+  return sqb::smemf_plan(kda, bits, axk, a.group, a.DK, a.DV, a.M, a.qbuf).total <= 220 * 1024;
+}
+
+template <int KIND>
 int launch(const sqb::StepArgs& a, int bits, bool axk, cudaStream_t stream) {
-  const int path = g_force_generic ? 1 : g_kernel_path;
-  if (path != 1 && tma_ok(a, bits, axk, KIND == sqb::K_KDA)) {
+  const int path = g_force_generic.load(std::memory_order_relaxed) ? 1 : g_kernel_path.load(std::memory_order_relaxed);
+  constexpr bool kda = KIND == sqb::K_KDA;
+  // Every check that could refuse a launch is made before the first one: a positive "shape not taken" code after a
+  // step kernel has appended would leave the slot between two states.
+  if ((path == 0 || path >= 3) && sqb::mma_shape_ok(a, bits, axk, kda)) {
+    sqb::SmemM plan;
+    int nst;
+    if (path == 4 || path == 0) {
+      // tensor-core kernels, the stored state read once: slots on their m-th token go to the launch that also folds
+      if (sqb::mma_plan<KIND>(a, bits, 1, plan, nst) && sqb::mma_plan<KIND>(a, bits, 2, plan, nst)) {
+        // (first the launch that folds: it marks the slots it took, see step_mma.cuh)
+        const int rc = launch_mma_kind<KIND>(a, bits, 2, stream);
+        if (rc != 0) return rc < 0 ? rc : fail(SQB_ECUDA, "tensor-core fold-step kernel refused a checked shape");
+        if (a.M == 1) return 0;
+        const int r1 = launch_mma_kind<KIND>(a, bits, 1, stream);
+        return r1 <= 0 ? r1 : fail(SQB_ECUDA, "tensor-core step kernel refused a checked shape");
+      }
+    } else if (sqb::mma_plan<KIND>(a, bits, 0, plan, nst) && fold_fits(a, bits, axk, kda)) {
+      const int rc = launch_mma_kind<KIND>(a, bits, 0, stream);
+      if (rc != 0) return rc < 0 ? rc : fail(SQB_ECUDA, "tensor-core step kernel refused a checked shape");
+      const int rf = sub_rc(sqb::launch_fold(KIND, a, bits, axk, stream));
+      return rf <= 0 ? rf : fail(SQB_ECUDA, "fold kernel refused a checked shape");
+    }
+  }
+  if (path != 1 && tma_ok(a, bits, axk, kda) && fold_fits(a, bits, axk, kda)) {
     // the staged kernel only appends on a slot's m-th token; the fold launch that follows it rewrites the state of
     // the heads whose buffer is full (the generic kernel folds inside its own launch)
     const int rc = launch_tma<KIND>(a, bits, axk, stream);
     if (rc < 0) return rc;
-    if (rc == 0) return sub_rc(sqb::launch_fold(KIND, a, bits, axk, stream));
+    if (rc == 0) {
+      const int rf = sub_rc(sqb::launch_fold(KIND, a, bits, axk, stream));
+      return rf <= 0 ? rf : fail(SQB_ECUDA, "fold kernel refused a checked shape");
+    }
   }
   switch (bits) {
     case 4: return axk ? launch_one<KIND, 4, true>(a, stream) : launch_one<KIND, 4, false>(a, stream);
@@ -190,7 +236,9 @@ int64_t sqb_launch_count(void) { return g_launches.load(); }
 
 int sqb_set_option(const char* name, int value) {
   if (name && !strcmp(name, "force_generic_kernel")) { g_force_generic = value; return 0; }
-  if (name && !strcmp(name, "kernel_path") && value >= 0 && value <= 2) { g_kernel_path = value; return 0; }
+  if (name && !strcmp(name, "kernel_path") && value >= 0 && value <= 4) { g_kernel_path = value; return 0; }
+  if (name && !strcmp(name, "wait_limit_us") && value > 0) { g_wait_ns = 1000ll * value; return 0; }
+  if (name && !strcmp(name, "test_extra_tx") && value >= 0 && value % 16 == 0) { g_test_extra_tx = value; return 0; }
   return fail(SQB_EINVAL, "unknown option");
 }
 
@@ -209,7 +257,7 @@ int slot_io_args(const sqb_state_t* st, int kind, const int32_t* idx, int32_t ro
   if (int rc = check_state(st, kind, &lpr_log2)) return rc;
   if (rows < 0) return fail(SQB_EINVAL, "rows %d < 0", rows);
   memset(&a, 0, sizeof a);
-  fill_state(a, st, lpr_log2);
+  if (int rc = fill_state(a, st, lpr_log2)) return rc;
   a.rows = rows; a.idx = idx; a.per_key_head = 1;
   if (!tma_ok(a, st->bits, st->bits > 8 || st->axis_k, kind == sqb::K_KDA))
     return fail(SQB_EINVAL, "the device read / write kernels take 4 / 8-bit states with d_k 64 or 128 and 16-byte aligned fields");
@@ -244,7 +292,7 @@ int sqb_gdn_step(const sqb_state_t* st, const sqb_gdn_inputs_t* in, void* stream
   if (check_dtype(in->qk_dtype, "q/k") || check_dtype(in->v_dtype, "v") || check_dtype(in->out_dtype, "out")) return SQB_EINVAL;
   sqb::StepArgs a;
   memset(&a, 0, sizeof a);
-  fill_state(a, st, lpr_log2);
+  if (int rc = fill_state(a, st, lpr_log2)) return rc;
   a.rows = in->rows; a.idx = in->idx;
   a.q = static_cast<const uint8_t*>(in->q); a.sq = in->sq;
   a.k = static_cast<const uint8_t*>(in->k); a.sk = in->sk;
@@ -270,7 +318,7 @@ int sqb_mamba2_step(const sqb_state_t* st, const sqb_mamba2_inputs_t* in, void* 
   if (check_dtype(in->x_dtype, "x") || check_dtype(in->bc_dtype, "B/C") || check_dtype(in->out_dtype, "out")) return SQB_EINVAL;
   sqb::StepArgs a;
   memset(&a, 0, sizeof a);
-  fill_state(a, st, lpr_log2);
+  if (int rc = fill_state(a, st, lpr_log2)) return rc;
   a.rows = in->rows; a.idx = in->idx;
   a.q = static_cast<const uint8_t*>(in->C); a.sq = in->sC;
   a.k = static_cast<const uint8_t*>(in->B); a.sk = in->sB;
@@ -297,7 +345,7 @@ int sqb_kda_step(const sqb_state_t* st, const sqb_kda_inputs_t* in, void* stream
       check_dtype(in->out_dtype, "out")) return SQB_EINVAL;
   sqb::StepArgs a;
   memset(&a, 0, sizeof a);
-  fill_state(a, st, lpr_log2);
+  if (int rc = fill_state(a, st, lpr_log2)) return rc;
   a.rows = in->rows; a.idx = in->idx;
   a.q = static_cast<const uint8_t*>(in->q); a.sq = in->sq;
   a.k = static_cast<const uint8_t*>(in->k); a.sk = in->sk;

@@ -1,0 +1,588 @@
+// The fused packed-state decode step with the state pass on the tensor pipe (mma_pass.cuh): integer states scaled
+// along k in groups of 32, 64 or 128, head dim d_k = 128, d_v 64 or 128, int8 decode buffer.
+//
+// One CTA (128 threads) per (batch row, KEY head) walks the value heads that share the key head in STAGES of 128
+// state rows (one head of d_v 128, two heads of d_v 64).  A stage -- codes as 8 padded pieces, scales, buffered
+// values -- arrives by bulk async copies on one mbarrier; the copies of the first stages and of the key tile are
+// issued by the lanes of one warp in the CTA's first instructions.  Per stage each warp takes a tile of 32 rows
+// through the tensor-core pass and finishes one row per lane (buffer term, u, o); the appends follow after the last
+// stage (MODE 0) or per stage, together with the fold of the stage's heads (MODE 2).
+//
+// MODE 0: every token is stepped and appended; on a slot's m-th token the head's counter is left at m for the fold
+//         launch that follows (fold_kernel.cuh).
+// MODE 2: only slots on their m-th token: step, append, then the fold from the staged tile, so the stored state is
+//         read once; the running decay is written as 0 and the counters are left at m, the mark by which
+// MODE 1, launched right after MODE 2, tells the slots that were just folded (it resets their counters to 0) from
+//         the others, which it steps and appends like MODE 0.  (m = 1: every token folds, MODE 2 alone is launched
+//         and writes the counters as 0 itself.)
+//
+// Prologue by role: warp 0 normalises q and k, builds the fixed-point B fragments and (GDN, Mamba2) takes the
+// buffered keys' dot products on the tensor pipe; warp 1 the gates; warp 2 issues the copies and computes decay
+// factors and value scales of every (head, slot); warp 3 rounds and appends the key (KDA: takes the buffered keys'
+// dot products, whose per-channel decays keep them in fp32, while warp 0 appends the key).
+//
+// Arithmetic is that of delta_step.cuh (same rounding of scales, payloads and buffer entries); only the order of the
+// reductions differs, and the read-out vectors pass through 30-bit fixed point (mma_pass.cuh).
+#pragma once
+#include "step_tma.cuh"
+#include "mma_pass.cuh"
+
+namespace sqb {
+
+struct SmemM {
+  int bars, stage0, stage_bytes, sc_off, ub_off, kb, gbt, bf, f0, total;
+  int hd, dcu, dqk, us, red, misc, ga, ae, wq, wk, wg, R, L, fdec, ksf;     // float offsets from f0
+};
+__host__ __device__ inline SmemM smemm_plan(int kind, int bits, int upg, int DV, int M, int nst, int gqa, bool fold) {
+  SmemM s;
+  const int rowb = 128 * bits / 8, pitch = 16 * rowb + 16, ng = 4 / upg;
+  s.sc_off = 8 * pitch;
+  s.ub_off = s.sc_off + 128 * ng * 2;
+  s.stage_bytes = s.ub_off + al16i(M * 128);
+  int o = 0;
+  s.bars = o; o += 128;
+  s.stage0 = o; o += nst * s.stage_bytes;
+  s.kb = o; o += al16i(M * 128);
+  s.gbt = o; o += (kind == K_KDA ? M * 128 * 4 : 0);
+  s.bf = o; o += 2048;            // B fragments: the state's layout, then the byte layout (key tile)
+  s.f0 = o;
+  int f = 0;
+  s.hd = f; f += gqa * HD_W;
+  s.dcu = f; f += (2 * gqa * M + 3) & ~3;
+  s.dqk = f; f += 2 * (M < 16 ? 16 : M);
+  s.us = f; f += gqa * DV;
+  s.red = f; f += gqa * NW;
+  s.misc = f; f += 16;
+  s.ga = f; f += (kind == K_KDA ? 128 : 0);
+  s.ae = f; f += (kind == K_KDA ? 128 : 0);
+  s.wq = f; f += (kind == K_KDA ? 128 : 0);
+  s.wk = f; f += (kind == K_KDA ? 128 : 0);
+  s.wg = f; f += (kind == K_KDA ? 128 : 0);
+  f = (f + 3) & ~3;
+  s.R = f; f += fold ? M * 160 : 0;
+  s.L = f; f += fold ? DV * fold_lm(M) : 0;
+  s.fdec = f; f += fold ? 32 : 0;
+  s.ksf = f; f += fold ? 64 : 0;
+  s.total = s.f0 + ((f + 3) & ~3) * 4;
+  return s;
+}
+
+#ifndef SQB_MMA_MINB8
+#define SQB_MMA_MINB8 5
+#endif
+#ifndef SQB_MMA_MINB4
+#define SQB_MMA_MINB4 6
+#endif
+
+template <int KIND, int BITS, int UPG, int DV, int MODE>
+__global__ void __launch_bounds__(NT, MODE == 2 ? 2 : (BITS == 4 ? SQB_MMA_MINB4 : SQB_MMA_MINB8))
+    step_mma_kernel(const __grid_constant__ StepArgs A, const __grid_constant__ SmemM P, const int nst) {
+  constexpr int DK = 128, NG = 4 / UPG, G = 32 * UPG;
+  constexpr int ROWB = DK * BITS / 8, PITCH = 16 * ROWB + 16;
+  constexpr int HPS = 128 / DV;                  // heads per stage
+  constexpr int CW = 4;                          // columns per lane in the prologue
+  constexpr bool TWO = KIND != K_M2, VDEC = KIND == K_KDA, FOLD = MODE == 2;
+  static_assert(DV == 64 || DV == 128, "a stage is 128 rows: one or two heads");
+
+  extern __shared__ __align__(128) uint8_t smraw[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int M = A.M, HV = A.HV;
+  const int gqa = HV / A.HK;
+  const int NSH = gqa / HPS;
+  const int b = blockIdx.x / A.HK, hk = blockIdx.x - b * A.HK;
+  const int h0 = hk * gqa;
+  const int osz = dt_size(A.dt_out);
+
+  // ---- activation loads that do not depend on the slot: issued before anything else ----------------------------
+  float qr[CW], kr[CW], g4[4];
+  if (warp == 0 || warp == 3) {
+#pragma unroll
+    for (int j = 0; j < CW; j++) {
+      qr[j] = ldf(A.q + (long long)b * A.sq, A.dt_qk, (long long)hk * DK + lane * CW + j);
+      kr[j] = ldf(A.k + (long long)b * A.sk, A.dt_qk, (long long)hk * DK + lane * CW + j);
+    }
+  } else if (warp == 1) {
+    g4[0] = g4[1] = g4[2] = g4[3] = 0.f;
+  }
+
+  long long seq = b;
+  if (A.idx != nullptr) {
+    seq = A.idx[b];
+    if (seq <= 0) {
+      if (MODE != 2 || M == 1) {                           // the launch that runs for every token zeroes padding rows
+        uint8_t* orow = A.out + (long long)b * A.so + (long long)h0 * DV * osz;
+        for (int v = tid; v < gqa * DV; v += NT) stf(orow, A.dt_out, v, 0.0f);
+      }
+      return;
+    }
+  }
+  int* NPseq = reinterpret_cast<int*>(A.NPTR + seq * A.sN);
+  const int nraw = NPseq[h0];                              // the heads of a slot advance together
+  if (MODE == 1 && nraw == M) {
+    // the launch before this one (MODE 2) stepped and folded this slot and left the marker: the buffer is empty
+    for (int hi = tid; hi < gqa; hi += NT) NPseq[h0 + hi] = 0;
+    return;
+  }
+  const int n0 = nraw & (M - 1);
+  if (MODE == 2 && n0 != M - 1) return;
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smraw + P.bars);
+  uint8_t* kbt = smraw + P.kb;
+  uint32_t* Bfw = reinterpret_cast<uint32_t*>(smraw + P.bf);
+  float* fsm = reinterpret_cast<float*>(smraw + P.f0);
+  float *hd = fsm + P.hd, *us = fsm + P.us, *red = fsm + P.red, *misc = fsm + P.misc, *ga = fsm + P.ga, *ae = fsm + P.ae,
+        *wq = fsm + P.wq, *wk = fsm + P.wk, *wg = fsm + P.wg;
+  float2* dcu = reinterpret_cast<float2*>(fsm + P.dcu);    // (decay factor, value scale) of every (head, slot)
+  float2* dqk = reinterpret_cast<float2*>(fsm + P.dqk);    // dot products of the buffered keys with q and k
+  const float* gbt = reinterpret_cast<const float*>(smraw + P.gbt);
+  [[maybe_unused]] float* Rf = fsm + P.R;
+
+  uint8_t* Sseq = A.S + seq * A.sS;
+  uint8_t* SCseq = A.SC + seq * A.sSC;
+  uint8_t* KBh = A.KB + seq * A.sKB + (long long)hk * M * DK;
+  uint8_t* UBseq = A.UB + seq * A.sUB;
+  unsigned short* KBSh = reinterpret_cast<unsigned short*>(A.KBS + seq * A.sKBS) + hk * M;
+  unsigned short* UBSseq = reinterpret_cast<unsigned short*>(A.UBS + seq * A.sUBS);
+  float* GBseq = reinterpret_cast<float*>(A.GB + seq * A.sGB);
+  float* GCseq = reinterpret_cast<float*>(A.GCUR + seq * A.sGC);
+  const uint32_t stage_tx = 128 * ROWB + 128 * NG * 2 + M * 128 + A.test_extra_tx;
+
+  // the copies of stage `sh` into ring position s, one per lane (lanes 0..9 of the calling warp)
+  auto issue_stage = [&](int s, int sh, int l) {
+    uint8_t* st = smraw + P.stage0 + s * P.stage_bytes;
+    const long long row0 = (long long)h0 * DV + sh * 128;
+    if (l < 8) bulk_g2s(st + l * PITCH, Sseq + (row0 + l * 16) * ROWB, 16 * ROWB, &bars[s]);
+    else if (l == 8) bulk_g2s(st + P.sc_off, SCseq + row0 * NG * 2, 128 * NG * 2, &bars[s]);
+    else if (l == 9) bulk_g2s(st + P.ub_off, UBseq + (long long)(h0 + sh * HPS) * M * DV, M * 128, &bars[s]);
+  };
+
+  // ---- prologue, by role ----------------------------------------------------------------------------------------
+  if (warp == 2) {
+    if (lane == 0) {
+      for (int s = 0; s <= nst; s++) mbar_init(&bars[s], 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      misc[2] = 0.f;                                      // "a copy never arrived" flag
+      for (int s = 0; s < nst && s < NSH; s++) mbar_expect_tx(&bars[s], stage_tx);
+      mbar_expect_tx(&bars[nst], M * DK + (VDEC ? M * DK * 4 : 0));
+    }
+    __syncwarp();
+    for (int s = 0; s < nst && s < NSH; s++) issue_stage(s, s, lane);
+    if (lane == 10) bulk_g2s(kbt, KBh, M * DK, &bars[nst]);
+    if (VDEC && lane == 11) bulk_g2s(smraw + P.gbt, GBseq + (long long)h0 * M * DK, M * DK * 4, &bars[nst]);
+    // per (value head, buffer slot): decay factors of the live slots and their value scales
+    for (int e = lane; e < gqa * M; e += 32) {
+      const int hi = e / M, i = e - hi * M, h = h0 + hi;
+      float dcy = 0.f, us_i = 0.f;
+      if (i < n0) {
+        dcy = VDEC ? 1.0f : expf(GCseq[h] - GBseq[(long long)h * M + i]);
+        us_i = h2f(UBSseq[h * M + i]);
+      }
+      dcu[e] = make_float2(dcy, us_i);
+    }
+  } else if (warp == 0) {
+    float ksv = 0.f;                          // scale of buffered key `lane`
+    if (!VDEC && lane < M) ksv = h2f(KBSh[lane]);
+    float gnr[CW];
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < CW; j++) {
+      s0 += qr[j] * qr[j];
+      s1 += kr[j] * kr[j];
+      if (VDEC) gnr[j] = GCseq[(long long)h0 * DK + lane * CW + j] +
+                         ldf(A.g + (long long)b * A.sg, A.dt_g, (long long)h0 * DK + lane * CW + j);
+    }
+    if (KIND != K_M2) {
+      s0 = warp_sum(s0);
+      s1 = warp_sum(s1);
+      const float nq = __fsqrt_rn(s0 + 1e-6f), nk = __fsqrt_rn(s1 + 1e-6f);
+#pragma unroll
+      for (int j = 0; j < CW; j++) {
+        qr[j] = __fdiv_rn(qr[j], nq) * A.scale;
+        kr[j] = __fdiv_rn(kr[j], nk);
+      }
+    }
+    float d = 0.f, mx = 0.f;
+    float eq[CW], ek[CW], mq = 0.f, mk = 0.f;              // the vectors the state is read against
+#pragma unroll
+    for (int j = 0; j < CW; j++) {
+      d += kr[j] * qr[j];
+      mx = fmaxf(mx, fabsf(kr[j]));
+      eq[j] = qr[j];
+      ek[j] = kr[j];
+      if (VDEC) {
+        const float av = expf(gnr[j]);
+        ga[lane * CW + j] = gnr[j];
+        ae[lane * CW + j] = av;
+        eq[j] = av * qr[j];
+        ek[j] = av * kr[j];
+      }
+      mq = fmaxf(mq, fabsf(eq[j]));
+      mk = fmaxf(mk, fabsf(ek[j]));
+    }
+    d = warp_sum(d);
+    mx = warp_max(mx);
+    mq = warp_max(mq);
+    if (TWO) mk = VDEC ? warp_max(mk) : mx;
+    const FxScale fq = fx30_scale(mq), fk = fx30_scale(mk);
+    if (lane == 0) {
+      misc[0] = d;
+      misc[4] = fq.i1; misc[5] = fq.i2; misc[6] = fk.i1; misc[7] = fk.i2;
+    }
+    uint32_t yq[CW], yk[CW];
+#pragma unroll
+    for (int j = 0; j < CW; j++) { yq[j] = fx30_digits(eq[j], fq); yk[j] = TWO ? fx30_digits(ek[j], fk) : 0u; }
+    put_b_words<BITS>(Bfw, lane, 0, yq[0], yq[1], yq[2], yq[3]);
+    put_b_words<BITS>(Bfw, lane, 1, yk[0], yk[1], yk[2], yk[3]);
+    if (BITS == 4 && !VDEC) {               // the key tile holds bytes: its product takes the byte layout
+      put_b_words<8>(Bfw + 256, lane, 0, yq[0], yq[1], yq[2], yq[3]);
+      put_b_words<8>(Bfw + 256, lane, 1, yk[0], yk[1], yk[2], yk[3]);
+    }
+    if constexpr (VDEC) {
+      // KDA: this warp appends the key (warp 3 is busy with the buffered keys' dot products)
+      const float ksc = fp16_scale(mx, 127.0f);
+      uint32_t w = 0;
+#pragma unroll
+      for (int j = 0; j < CW; j++) {
+        const float cc = rq_exact(kr[j], ksc, 127.0f);
+        w |= (static_cast<uint32_t>(static_cast<int>(cc)) & 0xFFu) << (8 * j);
+        if (FOLD) Rf[(M - 1) * 160 + ((lane * CW + j) >> 4) * 20 + ((lane * CW + j) & 15)] = cc * ksc;
+      }
+      *reinterpret_cast<uint32_t*>(KBh + (long long)n0 * DK + lane * 4) = w;
+      if (lane == 0) KBSh[n0] = f2h(ksc);
+    } else {
+      // the buffered keys' dot products with q and k: the key tile [M, 128] int8 is the A operand (rows = slots),
+      // the B fragments are those of the state pass (the 8-bit layout: the key tile holds bytes)
+      __syncwarp();
+      uint32_t bf8[8];
+#pragma unroll
+      for (int r = 0; r < 8; r++) bf8[r] = Bfw[(BITS == 8 ? 0 : 256) + r * 32 + lane];
+      if (!mbar_wait(&bars[nst], 0, A.wait_ns) && lane == 0) misc[2] = 1.f;
+      const float iq1 = fq.i1, iq2 = fq.i2, ik1 = fk.i1, ik2 = fk.i2;
+      for (int sb = 0; sb < M; sb += 16) {
+        int acc[4] = {MAGIC_I, MAGIC_I, MAGIC_I, MAGIC_I};
+        int srow = sb + ((lane >> 3) & 1) * 8 + (lane & 7);       // slot whose row this lane addresses
+        srow &= (M - 1);                                          // rows past the buffer: any valid row (ignored)
+        const uint32_t arow = smem_u32(kbt) + srow * DK + (lane >> 4) * 16;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          uint32_t m[4];
+          ldsm_x4(m, arow + 32 * j);
+          mma_i8<false>(acc, m[0], m[1], m[2], m[3], bf8[2 * j], bf8[2 * j + 1]);
+        }
+        const int i8 = lane >> 2, t = lane & 3;
+        const float k0s = __shfl_sync(0xffffffffu, ksv, (sb + i8) & 31), k1s = __shfl_sync(0xffffffffu, ksv, (sb + i8 + 8) & 31);
+        float p[4] = {(__int_as_float(acc[0]) - 12582912.0f) * k0s, (__int_as_float(acc[1]) - 12582912.0f) * k0s,
+                      (__int_as_float(acc[2]) - 12582912.0f) * k1s, (__int_as_float(acc[3]) - 12582912.0f) * k1s};
+        float T = join_digits(p, t);          // t = 0: q, slot sb + i8; t = 1: q, slot sb + i8 + 8; t = 2, 3: k
+        T = t < 2 ? (T * iq1) * iq2 : (T * ik1) * ik2;
+        const int slot = sb + i8 + (t & 1) * 8;
+        if (slot < M) {
+          if (t < 2) dqk[slot].x = T;
+          else dqk[slot].y = T;
+        }
+      }
+    }
+  } else if (warp == 3) {
+    if constexpr (!VDEC) {
+      // round and append the key at slot n0; its rounded value is what the fold uses for slot M - 1.  The
+      // normalisation is redone here (same arithmetic as warp 0, so the same bits)
+      float s1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < CW; j++) s1 += kr[j] * kr[j];
+      if (KIND != K_M2) {
+        s1 = warp_sum(s1);
+        const float nk = __fsqrt_rn(s1 + 1e-6f);
+#pragma unroll
+        for (int j = 0; j < CW; j++) kr[j] = __fdiv_rn(kr[j], nk);
+      }
+      float mx = 0.f;
+#pragma unroll
+      for (int j = 0; j < CW; j++) mx = fmaxf(mx, fabsf(kr[j]));
+      mx = warp_max(mx);
+      const float ksc = fp16_scale(mx, 127.0f);
+      uint32_t w = 0;
+#pragma unroll
+      for (int j = 0; j < CW; j++) {
+        const float cc = rq_exact(kr[j], ksc, 127.0f);
+        w |= (static_cast<uint32_t>(static_cast<int>(cc)) & 0xFFu) << (8 * j);
+        if (FOLD) Rf[(M - 1) * 160 + ((lane * CW + j) >> 4) * 20 + ((lane * CW + j) & 15)] = cc * ksc;
+      }
+      *reinterpret_cast<uint32_t*>(KBh + (long long)n0 * DK + lane * 4) = w;
+      if (lane == 0) KBSh[n0] = f2h(ksc);
+    } else {
+      // KDA: dot products of the buffered keys (times their per-channel decay ratios) with q and k, in fp32, from
+      // this warp's own copy of the normalised vectors (same arithmetic as warp 0, so the same bits)
+      constexpr int QD = DK / 4;
+      float ksv = 0.f;
+      if (lane < M) ksv = h2f(KBSh[lane]);
+      float gnr[CW];
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < CW; j++) {
+        s0 += qr[j] * qr[j];
+        s1 += kr[j] * kr[j];
+        gnr[j] = GCseq[(long long)h0 * DK + lane * CW + j] + ldf(A.g + (long long)b * A.sg, A.dt_g, (long long)h0 * DK + lane * CW + j);
+      }
+      s0 = warp_sum(s0);
+      s1 = warp_sum(s1);
+      const float nq = __fsqrt_rn(s0 + 1e-6f), nk = __fsqrt_rn(s1 + 1e-6f);
+#pragma unroll
+      for (int j = 0; j < CW; j++) {
+        wq[lane * CW + j] = __fdiv_rn(qr[j], nq) * A.scale;
+        wk[lane * CW + j] = __fdiv_rn(kr[j], nk);
+        wg[lane * CW + j] = gnr[j];
+      }
+      __syncwarp();
+      if (!mbar_wait(&bars[nst], 0, A.wait_ns) && lane == 0) misc[2] = 1.f;
+      for (int i0 = 0; i0 < M; i0 += 8) {
+        const int i = i0 + (lane >> 2), part = lane & 3;
+        const float ks_i = __shfl_sync(0xffffffffu, ksv, i & 31);
+        float dq = 0.f, dk = 0.f;
+        if (i < n0) {
+#pragma unroll
+          for (int j0 = 0; j0 < QD; j0 += 4) {
+            const int k = part * QD + j0;
+            float kv[4];
+            const uint32_t wx = *reinterpret_cast<const uint32_t*>(kbt + i * DK + k) ^ 0x80808080u;
+            kv[0] = byte_to_f<0>(wx) * ks_i; kv[1] = byte_to_f<1>(wx) * ks_i;
+            kv[2] = byte_to_f<2>(wx) * ks_i; kv[3] = byte_to_f<3>(wx) * ks_i;
+            const float4 q4 = *reinterpret_cast<const float4*>(wq + k);
+            const float4 k4 = *reinterpret_cast<const float4*>(wk + k);
+            const float4 g4v = *reinterpret_cast<const float4*>(wg + k);
+            const float4 b4 = *reinterpret_cast<const float4*>(gbt + i * DK + k);
+            kv[0] = kv[0] * expf(g4v.x - b4.x); kv[1] = kv[1] * expf(g4v.y - b4.y);
+            kv[2] = kv[2] * expf(g4v.z - b4.z); kv[3] = kv[3] * expf(g4v.w - b4.w);
+            dq = fmaf(kv[0], q4.x, dq); dq = fmaf(kv[1], q4.y, dq); dq = fmaf(kv[2], q4.z, dq); dq = fmaf(kv[3], q4.w, dq);
+            dk = fmaf(kv[0], k4.x, dk); dk = fmaf(kv[1], k4.y, dk); dk = fmaf(kv[2], k4.z, dk); dk = fmaf(kv[3], k4.w, dk);
+          }
+        }
+        dq += __shfl_xor_sync(0xffffffffu, dq, 1); dq += __shfl_xor_sync(0xffffffffu, dq, 2);
+        dk += __shfl_xor_sync(0xffffffffu, dk, 1); dk += __shfl_xor_sync(0xffffffffu, dk, 2);
+        if (part == 0 && i < M) dqk[i] = make_float2(dq, dk);
+      }
+    }
+  } else {
+    // warp 1, per value head: gates and the scalars derived from them
+    for (int hi = lane; hi < gqa; hi += 32) {
+      const int h = h0 + hi;
+      g4[0] = g4[1] = g4[2] = g4[3] = 0.f;
+      if (KIND == K_GDN) {
+        if (A.gate) {
+          g4[0] = ldf(A.a + (long long)b * A.sa, A.dt_ab, h); g4[1] = ldf(A.dt_bias, A.dt_dtb, h);
+          g4[2] = ldf(A.A_log, A.dt_alog, h);                 g4[3] = ldf(A.b + (long long)b * A.sb, A.dt_ab, h);
+        } else {
+          g4[0] = ldf(A.g + (long long)b * A.sg, A.dt_g, h);  g4[1] = ldf(A.beta + (long long)b * A.sbeta, A.dt_g, h);
+        }
+      } else if (KIND == K_M2) {
+        g4[0] = ldf(A.g + (long long)b * A.sg, A.dt_g, h);
+        if (A.dt_bias) g4[1] = ldf(A.dt_bias, A.dt_dtb, h);
+        g4[2] = ldf(A.A_log, A.dt_alog, h);
+        if (A.beta) g4[3] = ldf(A.beta, A.dt_beta, h);
+      } else {
+        g4[0] = ldf(A.beta + (long long)b * A.sbeta, A.dt_beta, h);
+      }
+      const float gcur = VDEC ? 0.f : GCseq[h];
+      float g = 0.f, bt = 0.f, Dv = 0.f;
+      if (KIND == K_GDN) {
+        if (A.gate) {
+          const float x = g4[0] + g4[1];
+          const float sp = x <= 20.0f ? logf(1.0f + expf(x)) : x;
+          g = -expf(g4[2]) * sp;
+          bt = __fdiv_rn(1.0f, 1.0f + expf(-g4[3]));
+        } else {
+          g = g4[0];
+          bt = g4[1];
+        }
+      } else if (KIND == K_M2) {
+        float dtv = g4[0];
+        if (A.dt_bias) dtv = dtv + g4[1];
+        if (A.dt_softplus) dtv = dtv <= 20.0f ? logf(1.0f + expf(dtv)) : dtv;
+        if (A.dt_clamp) dtv = fminf(fmaxf(dtv, A.dt_min), A.dt_max);
+        g = __fmul_rn(g4[2], dtv);
+        bt = dtv;
+        Dv = g4[3];
+      } else {
+        bt = g4[0];
+      }
+      float* o = hd + hi * HD_W;
+      o[0] = g; o[1] = bt; o[2] = gcur; o[3] = VDEC ? 1.0f : expf(gcur); o[4] = VDEC ? 1.0f : expf(g);
+      o[5] = gcur + g; o[6] = Dv;
+    }
+  }
+  __syncthreads();
+  // a copy that never completed: wait (bounded) for what may still be in flight, count it, leave
+  auto bail = [&]() {
+    uint8_t* orow = A.out + (long long)b * A.so + (long long)h0 * DV * osz;
+    for (int v = tid; v < gqa * DV; v += NT) stf(orow, A.dt_out, v, 0.0f);
+    if (tid == 0) {
+      for (int s = 0; s <= nst; s++) mbar_wait(&bars[s], 0, A.wait_ns);
+      atomicAdd(&A.status[0], 1);
+    }
+  };
+  if (misc[2] != 0.f) { bail(); return; }
+
+  // ---- the stages of this key head ----------------------------------------------------------------------------------
+  uint32_t bf[8];
+#pragma unroll
+  for (int r = 0; r < 8; r++) bf[r] = Bfw[r * 32 + lane];
+  int ci[NG][2];
+  acc_start<BITS, UPG>(bf, ci);
+  const float kq = misc[0];
+  const float iq1 = misc[4], iq2 = misc[5], ik1 = misc[6], ik2 = misc[7];
+  const int rho = (lane >> 2) * 16 + 4 * warp + (lane & 3);     // this lane's row within a stage
+  const int hh = rho / DV, rv = rho % DV;                        // head within the stage, row within the head
+  const float2 dq01 = dqk[0];
+  bool lost = false;
+
+  // rounds the u of this lane's row of stage sh and appends it; returns the dequantised rounded value
+  auto append_row = [&](int sh) -> float {
+    const int hi = sh * HPS + hh, h = h0 + hi;
+    const float u = us[hi * DV + rv];
+    const float4 r4 = *reinterpret_cast<const float4*>(red + hi * NW);
+    const float usc = fp16_scale(fmaxf(fmaxf(r4.x, r4.y), fmaxf(r4.z, r4.w)), 127.0f);
+    const float tt = fmaf(u, rcp_approx(usc), MAGIC);
+    float cc = tt - MAGIC;
+    const float rem = fmaf(-cc, usc, u);
+    if (!(fabsf(rem) < usc * 0.49998474f) || usc < FP16_MIN_NORMAL) cc = rq_exact(u, usc, 127.0f);
+    UBseq[((long long)h * M + n0) * DV + rv] = static_cast<uint8_t>(static_cast<int>(cc));
+    if (rv == 0) {
+      UBSseq[h * M + n0] = f2h(usc);
+      if (!VDEC) {
+        const float gnew = hd[hi * HD_W + 5];
+        GBseq[(long long)h * M + n0] = gnew;
+        GCseq[h] = FOLD ? 0.f : gnew;
+      }
+      NPseq[h] = FOLD ? (M == 1 ? 0 : M) : n0 + 1;
+    }
+    return cc * usc;
+  };
+
+  for (int sh = 0; sh < NSH; sh++) {
+    const int s = sh % nst;
+    const uint32_t parity = (sh / nst) & 1;
+    const int hi = sh * HPS + hh, h = h0 + hi;
+    uint8_t* st = smraw + P.stage0 + s * P.stage_bytes;
+    const unsigned short* scs = reinterpret_cast<const unsigned short*>(st + P.sc_off);
+    const int8_t* ubt = reinterpret_cast<const int8_t*>(st + P.ub_off) + hh * M * DV;
+    const float vt = ldf(A.v + (long long)b * A.sv, A.dt_v, (long long)h * DV + rv);
+    const float4 hda = *reinterpret_cast<const float4*>(hd + hi * HD_W);          // g, beta | dt, gcur, alpha
+    const float4 hdb = *reinterpret_cast<const float4*>(hd + hi * HD_W + 4);      // a, gnew, D, -
+    const float beta = hda.y, alpha = hda.w, a = hdb.x, Dv = hdb.z;
+    const float2* dcf = dcu + hi * M;
+
+    if (!mbar_wait(&bars[s], parity, A.wait_ns)) lost = true;
+
+    float tq, tk;
+    tile_pass<BITS, UPG, 16>(smem_u32(st), scs, bf, ci, warp, lane, tq, tk);
+    tq = (tq * iq1) * iq2;                                    // powers of two: exact
+    if (TWO) tk = (tk * ik1) * ik2;
+    if (!VDEC) { tq = alpha * tq; tk = alpha * tk; }
+    for (int i = 0; i < n0; i++) {                             // live slots only; dead ones may hold garbage
+      const float2 du = dcf[i];
+      const float2 dd = i == 0 ? dq01 : dqk[i];
+      const float ub = static_cast<float>(ubt[i * DV + rv]) * du.y;
+      tq = fmaf(ub, du.x * dd.x, tq);
+      if (TWO) tk = fmaf(ub, du.x * dd.y, tk);
+    }
+    float u, o;
+    if (KIND == K_GDN) {
+      u = beta * fmaf(-a, tk, vt);
+      o = fmaf(kq, u, a * tq);
+    } else if (KIND == K_KDA) {
+      u = beta * (vt - tk);
+      o = fmaf(kq, u, tq);
+    } else {
+      u = beta * vt;                                           // beta holds dt
+      o = fmaf(kq, u, a * tq);
+      if (A.beta) o = fmaf(Dv, vt, o);
+    }
+    us[hi * DV + rv] = u;
+    stf(A.out + (long long)b * A.so + (long long)h * DV * osz, A.dt_out, rv, o);
+    float umax = fabsf(u);
+#pragma unroll
+    for (int x = 1; x < (HPS == 1 ? 32 : 16); x <<= 1) umax = fmaxf(umax, __shfl_xor_sync(0xffffffffu, umax, x));
+    if ((lane & (HPS == 1 ? 31 : 15)) == 0) red[hi * NW + warp] = umax;
+
+    if constexpr (FOLD) {
+      // append and fold the heads of this stage from the staged tile, then hand the stage back
+      float* Lf = fsm + P.L;
+      float* fdec = fsm + P.fdec;
+      float* ksf = fsm + P.ksf;
+      const int LM = fold_lm(M);
+      if (__syncthreads_or(lost)) { bail(); return; }         // (a barrier: u and its maxima are complete)
+      const float udq = append_row(sh);
+      if (VDEC) {
+        GBseq[((long long)h * M + n0) * DK + tid] = ga[tid];
+        GCseq[(long long)h * DK + tid] = 0.f;
+      }
+      if (sh == 0) {
+        // R: the keys of slots 0 .. M - 2 (KDA: times their decay ratio); row M - 1 was written by the key append
+        if (tid < M) ksf[tid] = h2f(KBSh[tid]);
+        mbar_wait(&bars[nst], 0, A.wait_ns);                  // the key tile has landed (warp 0 or 3 saw it before)
+        __syncthreads();
+        for (int x = tid; x < (M - 1) * DK; x += NT) {
+          const int i = x / DK, k = x - i * DK;
+          float kv = static_cast<float>(reinterpret_cast<const int8_t*>(kbt)[x]) * ksf[i];
+          if (VDEC) kv = kv * expf(ga[k] - gbt[x]);
+          Rf[i * 160 + (k >> 4) * 20 + (k & 15)] = kv;
+        }
+      }
+      for (int hq = 0; hq < HPS; hq++) {
+        const int hf = sh * HPS + hq, hg = h0 + hf;
+        const float gnew = hd[hf * HD_W + 5];
+        __syncthreads();                                       // L, fdec free (previous head folded); R complete
+        if (tid < M) {
+          fdec[tid] = (VDEC || tid == M - 1) ? 1.0f : expf(gnew - GBseq[(long long)hg * M + tid]);
+          ksf[32 + tid] = h2f(UBSseq[hg * M + tid]);
+        }
+        if (hh == hq) Lf[rv * LM + M - 1] = udq;               // the value appended just now, as stored
+        __syncthreads();
+        const int8_t* ubh = reinterpret_cast<const int8_t*>(st + P.ub_off) + hq * M * DV;
+        for (int x = tid; x < (M - 1) * DV; x += NT) {
+          const int i = x / DV, v = x - i * DV;
+          float ub = static_cast<float>(ubh[x]) * ksf[32 + i];
+          if (!VDEC) ub = fdec[i] * ub;
+          Lf[v * LM + i] = ub;
+        }
+        __syncthreads();
+        const float alphan = VDEC ? 1.0f : expf(gnew);
+        fold_rows<BITS, true, 8, VDEC, true>(st + hq * (DV / 16) * PITCH,
+                                             reinterpret_cast<const unsigned short*>(st + P.sc_off) + hq * DV * NG, Rf, Lf, ae,
+                                             alphan, DV, G, M, nullptr, Sseq + (long long)hg * DV * ROWB,
+                                             reinterpret_cast<unsigned short*>(SCseq) + (long long)hg * DV * NG, warp, lane, tid,
+                                             [] { __syncthreads(); return true; });
+      }
+      if (sh + nst < NSH) {
+        __syncthreads();
+        if (warp == 0) {
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          if (lane == 0) mbar_expect_tx(&bars[s], stage_tx);
+          __syncwarp();
+          issue_stage(s, sh + nst, lane);
+        }
+      }
+    } else {
+      // a stage that is needed again is refilled once every warp has read it
+      if (sh + nst < NSH) {
+        __syncthreads();
+        if (warp == 0) {
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          if (lane == 0) mbar_expect_tx(&bars[s], stage_tx);
+          __syncwarp();
+          issue_stage(s, sh + nst, lane);
+        }
+      }
+    }
+  }
+  if constexpr (!FOLD) {
+    // ---- append the values of all heads at slot n0, every lane its own rows ----
+    if (__syncthreads_or(lost)) { bail(); return; }
+    for (int sh = 0; sh < NSH; sh++) append_row(sh);
+    if (VDEC) {
+      GBseq[((long long)h0 * M + n0) * DK + tid] = ga[tid];
+      GCseq[(long long)h0 * DK + tid] = ga[tid];
+    }
+  }
+}
+
+}  // namespace sqb

@@ -15,12 +15,14 @@ pytestmark = pytest.mark.gpu
 DEV = 'cuda'
 
 
-@pytest.fixture(params=['staged', 'generic'])
+@pytest.fixture(params=['fused', 'mma', 'staged', 'generic'])
 def kernel_path(request):
-    """Both device code paths: the staged kernel with its fold launch (default wherever its alignment and shape
-    conditions hold) and the generic kernel, which folds inside its own launch."""
+    """Every device code path: the tensor-core kernels with the fold fused into the m-th token's launch (default
+    wherever their shape conditions hold), the tensor-core step followed by the separate fold launch, the staged
+    SIMT kernel with the fold launch, and the generic kernel, which folds inside its own launch.  A path that does
+    not take a shape falls through to the next one."""
     from statequant_b200 import _cabi
-    _cabi.set_option('kernel_path', {'generic': 1, 'staged': 2}[request.param])
+    _cabi.set_option('kernel_path', {'generic': 1, 'staged': 2, 'mma': 3, 'fused': 4}[request.param])
     yield request.param
     _cabi.set_option('kernel_path', 0)
     assert _cabi.device_status() == 0, 'a bounded wait ran out on the device'
