@@ -50,6 +50,7 @@ struct StepArgs {
   float scale, dt_min, dt_max;
   int* status;               // device health word: [0] counts CTAs whose bounded wait ran out
   unsigned long long wait_ns;   // how long a wait for a bulk copy may take before the CTA gives up
+  int hpc;                   // tensor-core kernels: value heads a CTA takes (divides hv / hk)
   int test_extra_tx;         // test hook: bytes a stage barrier expects beyond what is copied (so its wait runs out)
 };
 

@@ -25,14 +25,22 @@ inline bool mma_shape_ok(const StepArgs& a, int bits, bool axk, bool kda) {
 }
 
 // stages resident per CTA and the plan; false if the CTA does not fit
+// value heads a CTA takes: a whole key head's, unless told otherwise (a.hpc set by the caller: a divisor of the key
+// head's value heads that fills whole stages)
+inline int mma_hpc(const StepArgs& a) {
+  const int gqa = a.HV / a.HK, hps = 128 / a.DV;
+  if (a.hpc > 0 && gqa % a.hpc == 0 && a.hpc % hps == 0) return a.hpc;
+  return gqa;
+}
+
 template <int KIND>
 inline bool mma_plan(const StepArgs& a, int bits, int mode, SmemM& plan, int& nst) {
-  const int gqa = a.HV / a.HK, nsh = gqa / (128 / a.DV), upg = a.group / 32;
+  const int gqa = mma_hpc(a), nsh = gqa / (128 / a.DV), upg = a.group / 32;
   nst = nsh < 4 ? nsh : 4;
-  plan = smemm_plan(KIND, bits, upg, a.DV, a.M, nst, gqa, mode == 2);
+  plan = smemm_plan(KIND, bits, upg, a.DV, a.M, nst, gqa, mode == 3);
   while (nst > 1 && plan.total > 96 * 1024) {
     nst--;
-    plan = smemm_plan(KIND, bits, upg, a.DV, a.M, nst, gqa, mode == 2);
+    plan = smemm_plan(KIND, bits, upg, a.DV, a.M, nst, gqa, mode == 3);
   }
   return plan.total <= 220 * 1024;
 }
@@ -48,9 +56,11 @@ int launch_mma_one(const StepArgs& a, cudaStream_t stream) {
     cudaError_t e = limit.ensure(kern, plan.total);
     if (e != cudaSuccess) return -1000 - static_cast<int>(e);
   }
-  const long long ctas = static_cast<long long>(a.rows) * a.HK;
+  StepArgs b = a;
+  b.hpc = mma_hpc(a);
+  const long long ctas = static_cast<long long>(a.rows) * (a.HV / b.hpc);
   if (ctas > 2147483647LL) return 1;
-  kern<<<static_cast<unsigned>(ctas), NT, plan.total, stream>>>(a, plan, nst);
+  kern<<<static_cast<unsigned>(ctas), NT, plan.total, stream>>>(b, plan, nst);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return -1000 - static_cast<int>(e);
   return 0;
@@ -69,21 +79,19 @@ int launch_mma_fmt(const StepArgs& a, int bits, cudaStream_t stream) {
   return launch_mma_one<KIND, 8, 4, DV, MODE>(a, stream);
 }
 
-// mode: 0 every token (the fold launch follows), 1 all but a slot's m-th token, 2 the m-th token with the fold
+// mode: 0 the step alone (the fold launch follows), 3 the step with the fold of the m-th token inside
 template <int KIND, bool DV64>
 int launch_mma(const StepArgs& a, int bits, int mode, cudaStream_t stream) {
   if (a.DV == 64) {
     if constexpr (DV64) {
       if (mode == 0) return launch_mma_fmt<KIND, 64, 0>(a, bits, stream);
-      if (mode == 1) return launch_mma_fmt<KIND, 64, 1>(a, bits, stream);
-      return launch_mma_fmt<KIND, 64, 2>(a, bits, stream);
+      return launch_mma_fmt<KIND, 64, 3>(a, bits, stream);
     } else {
       return 1;
     }
   }
   if (mode == 0) return launch_mma_fmt<KIND, 128, 0>(a, bits, stream);
-  if (mode == 1) return launch_mma_fmt<KIND, 128, 1>(a, bits, stream);
-  return launch_mma_fmt<KIND, 128, 2>(a, bits, stream);
+  return launch_mma_fmt<KIND, 128, 3>(a, bits, stream);
 }
 
 }  // namespace sqb

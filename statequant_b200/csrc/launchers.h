@@ -26,8 +26,8 @@ struct SmemLimit {
 int launch_staged_gdn(const StepArgs& a, int bits, bool axk, cudaStream_t stream);
 int launch_staged_m2(const StepArgs& a, int bits, bool axk, cudaStream_t stream);
 int launch_staged_kda(const StepArgs& a, int bits, bool axk, cudaStream_t stream);
-// the tensor-core kernels (step_mma.cuh); mode 0: every token (the fold launch follows), 1: all but a slot's m-th
-// token, 2: the m-th token together with the fold
+// the tensor-core kernels (step_mma.cuh); mode 0: the step alone (the fold launch follows), 3: the step with the fold
+// of a slot's m-th token inside
 int launch_mma_gdn(const StepArgs& a, int bits, int mode, cudaStream_t stream);
 int launch_mma_m2(const StepArgs& a, int bits, int mode, cudaStream_t stream);
 int launch_mma_kda(const StepArgs& a, int bits, int mode, cudaStream_t stream);

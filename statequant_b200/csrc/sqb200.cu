@@ -87,12 +87,14 @@ std::atomic<int> g_force_generic{0};     // set through sqb_set_option (tests ti
 std::atomic<int> g_kernel_path{0};       // see sqb_set_option in the header
 std::atomic<long long> g_wait_ns{1000000000ll};   // bound of a device-side wait for a bulk copy
 std::atomic<int> g_test_extra_tx{0};     // test hook: makes the stage barriers of the tensor-core kernels wait in vain
+std::atomic<int> g_mma_hpc{0};           // tensor-core kernels: value heads per CTA (0: all of a key head)
 
 int fill_state(sqb::StepArgs& a, const sqb_state_t* st, int lpr_log2) {
   a.status = status_ptr();
   if (!a.status) return fail(SQB_ECUDA, "the device status word is not reachable (cudaGetSymbolAddress failed)");
   a.wait_ns = static_cast<unsigned long long>(g_wait_ns.load(std::memory_order_relaxed));
   a.test_extra_tx = g_test_extra_tx.load(std::memory_order_relaxed);
+  a.hpc = g_mma_hpc.load(std::memory_order_relaxed);
   a.S = static_cast<uint8_t*>(st->S); a.SC = static_cast<uint8_t*>(st->SC);
   a.KB = static_cast<uint8_t*>(st->KB); a.KBS = static_cast<uint8_t*>(st->KBS);
   a.UB = static_cast<uint8_t*>(st->UB); a.UBS = static_cast<uint8_t*>(st->UBS);
@@ -186,14 +188,10 @@ int launch(const sqb::StepArgs& a, int bits, bool axk, cudaStream_t stream) {
     sqb::SmemM plan;
     int nst;
     if (path == 4 || path == 0) {
-      // tensor-core kernels, the stored state read once: slots on their m-th token go to the launch that also folds
-      if (sqb::mma_plan<KIND>(a, bits, 1, plan, nst) && sqb::mma_plan<KIND>(a, bits, 2, plan, nst)) {
-        // (first the launch that folds: it marks the slots it took, see step_mma.cuh)
-        const int rc = launch_mma_kind<KIND>(a, bits, 2, stream);
-        if (rc != 0) return rc < 0 ? rc : fail(SQB_ECUDA, "tensor-core fold-step kernel refused a checked shape");
-        if (a.M == 1) return 0;
-        const int r1 = launch_mma_kind<KIND>(a, bits, 1, stream);
-        return r1 <= 0 ? r1 : fail(SQB_ECUDA, "tensor-core step kernel refused a checked shape");
+      // tensor-core kernel with the fold inside: one launch, the stored state read once per token
+      if (sqb::mma_plan<KIND>(a, bits, 3, plan, nst)) {
+        const int rc = launch_mma_kind<KIND>(a, bits, 3, stream);
+        return rc <= 0 ? rc : fail(SQB_ECUDA, "tensor-core step kernel refused a checked shape");
       }
     } else if (sqb::mma_plan<KIND>(a, bits, 0, plan, nst) && fold_fits(a, bits, axk, kda)) {
       const int rc = launch_mma_kind<KIND>(a, bits, 0, stream);
@@ -237,6 +235,7 @@ int64_t sqb_launch_count(void) { return g_launches.load(); }
 int sqb_set_option(const char* name, int value) {
   if (name && !strcmp(name, "force_generic_kernel")) { g_force_generic = value; return 0; }
   if (name && !strcmp(name, "kernel_path") && value >= 0 && value <= 4) { g_kernel_path = value; return 0; }
+  if (name && !strcmp(name, "mma_heads_per_cta") && value >= 0) { g_mma_hpc = value; return 0; }
   if (name && !strcmp(name, "wait_limit_us") && value > 0) { g_wait_ns = 1000ll * value; return 0; }
   if (name && !strcmp(name, "test_extra_tx") && value >= 0 && value % 16 == 0) { g_test_extra_tx = value; return 0; }
   return fail(SQB_EINVAL, "unknown option");

@@ -10,11 +10,10 @@
 //
 // MODE 0: every token is stepped and appended; on a slot's m-th token the head's counter is left at m for the fold
 //         launch that follows (fold_kernel.cuh).
-// MODE 2: only slots on their m-th token: step, append, then the fold from the staged tile, so the stored state is
-//         read once; the running decay is written as 0 and the counters are left at m, the mark by which
-// MODE 1, launched right after MODE 2, tells the slots that were just folded (it resets their counters to 0) from
-//         the others, which it steps and appends like MODE 0.  (m = 1: every token folds, MODE 2 alone is launched
-//         and writes the counters as 0 itself.)
+// MODE 3: the same, and a slot on its m-th token is folded right here from the staged tile (the stored state is read
+//         once per token, fold or not): per stage the append and the fold of the stage's heads follow the read-out.
+//         Nothing a CTA fetches depends on the slot's counter, so every copy and every scalar load leaves in the
+//         CTA's first instructions.
 //
 // Prologue by role: warp 0 normalises q and k, builds the fixed-point B fragments and (GDN, Mamba2) takes the
 // buffered keys' dot products on the tensor pipe; warp 1 the gates; warp 2 issues the copies and computes decay
@@ -28,6 +27,14 @@
 #include "mma_pass.cuh"
 
 namespace sqb {
+
+#ifdef SQB_TRACE
+// debug builds only: per-warp cycle stamps of sampled CTAs (never compiled into the shipped library)
+__device__ long long g_mma_trace[64 * 4 * 16];
+#define SQB_STAMP(k) do { if ((blockIdx.x & 63) == 5 && lane == 0) g_mma_trace[((blockIdx.x >> 6) * 4 + warp) * 16 + (k)] = clock64() - t_start; } while (0)
+#else
+#define SQB_STAMP(k) do { } while (0)
+#endif
 
 struct SmemM {
   int bars, stage0, stage_bytes, sc_off, ub_off, kb, gbt, bf, f0, total;
@@ -74,57 +81,102 @@ __host__ __device__ inline SmemM smemm_plan(int kind, int bits, int upg, int DV,
 #define SQB_MMA_MINB4 6
 #endif
 
+// Activation loads in two steps, so that a group of loads is in flight together: the raw bits first (nothing waits
+// for them), the conversion to fp32 where the values are needed.  (ldf converts at once, which makes every load of a
+// sequence wait for the one before.)
+__device__ __forceinline__ uint32_t ld1_raw(const void* p, int dt, long long i) {
+  if (dt == DT_F32) return reinterpret_cast<const uint32_t*>(p)[i];
+  return reinterpret_cast<const unsigned short*>(p)[i];
+}
+__device__ __forceinline__ float cvt_raw(uint32_t w, int dt) {
+  if (dt == DT_F32) return __uint_as_float(w);
+  if (dt == DT_BF16) return __uint_as_float(w << 16);
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(w)));
+}
+// Elements i .. i + 3 (i a multiple of 4) as loaded, untouched: unpacking a loaded word is already a use that waits
+// for the load, so it is left to cvt4_raw.  vec: the row is read by one 8- or 16-byte load (the address allows it).
+struct Raw4 { uint4 v; bool vec; };
+__device__ __forceinline__ Raw4 ld4_raw(const uint8_t* p, int dt, long long i) {
+  Raw4 r;
+  r.v = make_uint4(0u, 0u, 0u, 0u);
+  if (dt == DT_F32) {
+    const uint8_t* q = p + 4 * i;
+    r.vec = (reinterpret_cast<uintptr_t>(q) & 15) == 0;
+    if (r.vec) {
+      r.v = *reinterpret_cast<const uint4*>(q);
+    } else {
+      r.v.x = reinterpret_cast<const uint32_t*>(q)[0]; r.v.y = reinterpret_cast<const uint32_t*>(q)[1];
+      r.v.z = reinterpret_cast<const uint32_t*>(q)[2]; r.v.w = reinterpret_cast<const uint32_t*>(q)[3];
+    }
+  } else {
+    const uint8_t* q = p + 2 * i;
+    r.vec = (reinterpret_cast<uintptr_t>(q) & 7) == 0;
+    if (r.vec) {
+      const uint2 t = *reinterpret_cast<const uint2*>(q);
+      r.v.x = t.x; r.v.y = t.y;
+    } else {
+      r.v.x = reinterpret_cast<const unsigned short*>(q)[0]; r.v.y = reinterpret_cast<const unsigned short*>(q)[1];
+      r.v.z = reinterpret_cast<const unsigned short*>(q)[2]; r.v.w = reinterpret_cast<const unsigned short*>(q)[3];
+    }
+  }
+  return r;
+}
+__device__ __forceinline__ void cvt4_raw(const Raw4& r, int dt, float (&f)[4]) {
+  if (dt == DT_F32 || !r.vec) {
+    f[0] = cvt_raw(r.v.x, dt); f[1] = cvt_raw(r.v.y, dt); f[2] = cvt_raw(r.v.z, dt); f[3] = cvt_raw(r.v.w, dt);
+  } else {
+    f[0] = cvt_raw(r.v.x & 0xFFFFu, dt); f[1] = cvt_raw(r.v.x >> 16, dt);
+    f[2] = cvt_raw(r.v.y & 0xFFFFu, dt); f[3] = cvt_raw(r.v.y >> 16, dt);
+  }
+}
+
+#ifndef SQB_MMA_MINB_FOLD
+#define SQB_MMA_MINB_FOLD 4
+#endif
+
 template <int KIND, int BITS, int UPG, int DV, int MODE>
-__global__ void __launch_bounds__(NT, MODE == 2 ? 2 : (BITS == 4 ? SQB_MMA_MINB4 : SQB_MMA_MINB8))
+__global__ void __launch_bounds__(NT, MODE == 3 ? SQB_MMA_MINB_FOLD : (BITS == 4 ? SQB_MMA_MINB4 : SQB_MMA_MINB8))
     step_mma_kernel(const __grid_constant__ StepArgs A, const __grid_constant__ SmemM P, const int nst) {
   constexpr int DK = 128, NG = 4 / UPG, G = 32 * UPG;
   constexpr int ROWB = DK * BITS / 8, PITCH = 16 * ROWB + 16;
   constexpr int HPS = 128 / DV;                  // heads per stage
   constexpr int CW = 4;                          // columns per lane in the prologue
-  constexpr bool TWO = KIND != K_M2, VDEC = KIND == K_KDA, FOLD = MODE == 2;
+  constexpr bool TWO = KIND != K_M2, VDEC = KIND == K_KDA, CANFOLD = MODE == 3;
   static_assert(DV == 64 || DV == 128, "a stage is 128 rows: one or two heads");
 
   extern __shared__ __align__(128) uint8_t smraw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int M = A.M, HV = A.HV;
-  const int gqa = HV / A.HK;
+  const int gqa = A.hpc;                          // value heads of this CTA: all heads of a key head, or a part of them
+  const int cpk = HV / A.HK / gqa;                // CTAs per key head
   const int NSH = gqa / HPS;
-  const int b = blockIdx.x / A.HK, hk = blockIdx.x - b * A.HK;
-  const int h0 = hk * gqa;
+  const int b = blockIdx.x / (A.HK * cpk), rem = blockIdx.x - b * (A.HK * cpk);
+  const int hk = rem / cpk, part = rem - hk * cpk;
+  const int h0 = hk * (HV / A.HK) + part * gqa;
+  const bool first = part == 0;                   // the CTA that appends the key head's key
   const int osz = dt_size(A.dt_out);
 
-  // ---- activation loads that do not depend on the slot: issued before anything else ----------------------------
-  float qr[CW], kr[CW], g4[4];
-  if (warp == 0 || warp == 3) {
-#pragma unroll
-    for (int j = 0; j < CW; j++) {
-      qr[j] = ldf(A.q + (long long)b * A.sq, A.dt_qk, (long long)hk * DK + lane * CW + j);
-      kr[j] = ldf(A.k + (long long)b * A.sk, A.dt_qk, (long long)hk * DK + lane * CW + j);
-    }
-  } else if (warp == 1) {
-    g4[0] = g4[1] = g4[2] = g4[3] = 0.f;
-  }
-
+#ifdef SQB_TRACE
+  const long long t_start = clock64();
+#endif
+  // The slot index first, and nothing else in flight beside it: every other fetch of the CTA (bulk copies, scalars,
+  // activations) leaves in one burst as soon as it is known, and a load that shares a scoreboard with slower ones
+  // would hold that burst back.
   long long seq = b;
   if (A.idx != nullptr) {
     seq = A.idx[b];
     if (seq <= 0) {
-      if (MODE != 2 || M == 1) {                           // the launch that runs for every token zeroes padding rows
-        uint8_t* orow = A.out + (long long)b * A.so + (long long)h0 * DV * osz;
-        for (int v = tid; v < gqa * DV; v += NT) stf(orow, A.dt_out, v, 0.0f);
-      }
+      uint8_t* orow = A.out + (long long)b * A.so + (long long)h0 * DV * osz;
+      for (int v = tid; v < gqa * DV; v += NT) stf(orow, A.dt_out, v, 0.0f);
       return;
     }
   }
+  const int rho = (lane >> 2) * 16 + 4 * warp + (lane & 3);     // this lane's row within a stage
+  const int hh = rho / DV, rv = rho % DV;                        // head within the stage, row within the head
   int* NPseq = reinterpret_cast<int*>(A.NPTR + seq * A.sN);
-  const int nraw = NPseq[h0];                              // the heads of a slot advance together
-  if (MODE == 1 && nraw == M) {
-    // the launch before this one (MODE 2) stepped and folded this slot and left the marker: the buffer is empty
-    for (int hi = tid; hi < gqa; hi += NT) NPseq[h0 + hi] = 0;
-    return;
-  }
-  const int n0 = nraw & (M - 1);
-  if (MODE == 2 && n0 != M - 1) return;
+  SQB_STAMP(0);
+  // The slot's counter (the heads of a slot advance together) is loaded by the roles that need it, where they need
+  // it: nothing that is fetched depends on it, and no warp waits for it before its own loads and copies are out.
 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smraw + P.bars);
   uint8_t* kbt = smraw + P.kb;
@@ -156,32 +208,98 @@ __global__ void __launch_bounds__(NT, MODE == 2 ? 2 : (BITS == 4 ? SQB_MMA_MINB4
     else if (l == 9) bulk_g2s(st + P.ub_off, UBseq + (long long)(h0 + sh * HPS) * M * DV, M * 128, &bars[s]);
   };
 
-  // ---- prologue, by role ----------------------------------------------------------------------------------------
-  if (warp == 2) {
+  // The key tile (and KDA's decay tile) has its own barrier, initialised, armed and waited on by ONE warp (warp 0;
+  // KDA: warp 3), so that no wait can meet a barrier another warp has not initialised yet.
+  auto fetch_key_tile = [&]() {
     if (lane == 0) {
-      for (int s = 0; s <= nst; s++) mbar_init(&bars[s], 1);
+      mbar_init(&bars[nst], 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-      misc[2] = 0.f;                                      // "a copy never arrived" flag
-      for (int s = 0; s < nst && s < NSH; s++) mbar_expect_tx(&bars[s], stage_tx);
       mbar_expect_tx(&bars[nst], M * DK + (VDEC ? M * DK * 4 : 0));
+      bulk_g2s(kbt, KBh, M * DK, &bars[nst]);
+      if (VDEC) bulk_g2s(smraw + P.gbt, GBseq + (long long)h0 * M * DK, M * DK * 4, &bars[nst]);
     }
     __syncwarp();
-    for (int s = 0; s < nst && s < NSH; s++) issue_stage(s, s, lane);
-    if (lane == 10) bulk_g2s(kbt, KBh, M * DK, &bars[nst]);
-    if (VDEC && lane == 11) bulk_g2s(smraw + P.gbt, GBseq + (long long)h0 * M * DK, M * DK * 4, &bars[nst]);
+  };
+
+  SQB_STAMP(13);
+  // ---- activation loads, as raw bits (converted where they are used) ------------------------------------------------
+  Raw4 rq, rk;
+  uint32_t rg[4] = {0u, 0u, 0u, 0u};
+  if (warp == 0 || warp == 3) {
+    rq = ld4_raw(A.q + (long long)b * A.sq, A.dt_qk, (long long)hk * DK + lane * CW);
+    rk = ld4_raw(A.k + (long long)b * A.sk, A.dt_qk, (long long)hk * DK + lane * CW);
+  } else if (warp == 1 && lane < gqa) {
+    const int h = h0 + lane;                               // one lane per value head (at most 32 per key head)
+    if (KIND == K_GDN) {
+      if (A.gate) {
+        rg[0] = ld1_raw(A.a + (long long)b * A.sa, A.dt_ab, h); rg[1] = ld1_raw(A.dt_bias, A.dt_dtb, h);
+        rg[2] = ld1_raw(A.A_log, A.dt_alog, h);                 rg[3] = ld1_raw(A.b + (long long)b * A.sb, A.dt_ab, h);
+      } else {
+        rg[0] = ld1_raw(A.g + (long long)b * A.sg, A.dt_g, h);  rg[1] = ld1_raw(A.beta + (long long)b * A.sbeta, A.dt_g, h);
+      }
+    } else if (KIND == K_M2) {
+      rg[0] = ld1_raw(A.g + (long long)b * A.sg, A.dt_g, h);
+      if (A.dt_bias) rg[1] = ld1_raw(A.dt_bias, A.dt_dtb, h);
+      rg[2] = ld1_raw(A.A_log, A.dt_alog, h);
+      if (A.beta) rg[3] = ld1_raw(A.beta, A.dt_beta, h);
+    } else {
+      rg[0] = ld1_raw(A.beta + (long long)b * A.sbeta, A.dt_beta, h);
+    }
+  }
+
+
+  SQB_STAMP(14);
+  // this lane's value-vector entries of the first two stages (needed after the first pass): each role issues these
+  // loads once its urgent fetches are out
+  uint32_t rvt[2];
+  auto load_v = [&]() {
+    rvt[0] = ld1_raw(A.v + (long long)b * A.sv, A.dt_v, (long long)(h0 + hh) * DV + rv);
+    rvt[1] = ld1_raw(A.v + (long long)b * A.sv, A.dt_v, (long long)(h0 + (NSH > 1 ? HPS : 0) + hh) * DV + rv);
+  };
+  // A stage barrier of the first fill is initialised, armed and its copies issued by ONE warp (a warp's copies leave one
+  // after the other, so the stages are spread over warps 2, 3 and 1); everybody else meets it after the block barrier.
+  auto start_stage = [&](int s) {
+    if (s < nst && s < NSH) {
+      if (lane == 0) {
+        mbar_init(&bars[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_expect_tx(&bars[s], stage_tx);
+      }
+      __syncwarp();
+      issue_stage(s, s, lane);
+    }
+  };
+
+  // ---- prologue, by role ----------------------------------------------------------------------------------------
+  if (warp == 2) {
+    SQB_STAMP(1);
+    start_stage(0);
+    start_stage(3);
+    SQB_STAMP(2);
+    load_v();
+    const int n0 = NPseq[h0] & (M - 1);
+    if (lane == 0) misc[1] = __int_as_float(n0);
     // per (value head, buffer slot): decay factors of the live slots and their value scales
     for (int e = lane; e < gqa * M; e += 32) {
       const int hi = e / M, i = e - hi * M, h = h0 + hi;
-      float dcy = 0.f, us_i = 0.f;
-      if (i < n0) {
-        dcy = VDEC ? 1.0f : expf(GCseq[h] - GBseq[(long long)h * M + i]);
-        us_i = h2f(UBSseq[h * M + i]);
-      }
-      dcu[e] = make_float2(dcy, us_i);
+      // loaded whether the slot is live or not (dead entries may hold anything; they are selected away), so that
+      // the loads do not wait for the slot's counter
+      const float gb = VDEC ? 0.f : GBseq[(long long)h * M + i], gc = VDEC ? 0.f : GCseq[h];
+      const float us_i = h2f(UBSseq[h * M + i]);
+      const float dcy = VDEC ? 1.0f : expf(gc - gb);
+      dcu[e] = i < n0 ? make_float2(dcy, us_i) : make_float2(0.f, 0.f);
     }
   } else if (warp == 0) {
+    if (!VDEC) fetch_key_tile();
+    load_v();
     float ksv = 0.f;                          // scale of buffered key `lane`
     if (!VDEC && lane < M) ksv = h2f(KBSh[lane]);
+    [[maybe_unused]] int n0 = 0;
+    if (VDEC) n0 = NPseq[h0] & (M - 1);       // KDA: this warp appends the key
+    [[maybe_unused]] const bool FOLD = CANFOLD && n0 == M - 1;
+    float qr[CW], kr[CW];
+    cvt4_raw(rq, A.dt_qk, qr);
+    cvt4_raw(rk, A.dt_qk, kr);
     float gnr[CW];
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
@@ -191,6 +309,7 @@ __global__ void __launch_bounds__(NT, MODE == 2 ? 2 : (BITS == 4 ? SQB_MMA_MINB4
       if (VDEC) gnr[j] = GCseq[(long long)h0 * DK + lane * CW + j] +
                          ldf(A.g + (long long)b * A.sg, A.dt_g, (long long)h0 * DK + lane * CW + j);
     }
+    SQB_STAMP(1);
     if (KIND != K_M2) {
       s0 = warp_sum(s0);
       s1 = warp_sum(s1);
@@ -247,8 +366,10 @@ __global__ void __launch_bounds__(NT, MODE == 2 ? 2 : (BITS == 4 ? SQB_MMA_MINB4
         w |= (static_cast<uint32_t>(static_cast<int>(cc)) & 0xFFu) << (8 * j);
         if (FOLD) Rf[(M - 1) * 160 + ((lane * CW + j) >> 4) * 20 + ((lane * CW + j) & 15)] = cc * ksc;
       }
-      *reinterpret_cast<uint32_t*>(KBh + (long long)n0 * DK + lane * 4) = w;
-      if (lane == 0) KBSh[n0] = f2h(ksc);
+      if (first) {
+        *reinterpret_cast<uint32_t*>(KBh + (long long)n0 * DK + lane * 4) = w;
+        if (lane == 0) KBSh[n0] = f2h(ksc);
+      }
     } else {
       // the buffered keys' dot products with q and k: the key tile [M, 128] int8 is the A operand (rows = slots),
       // the B fragments are those of the state pass (the 8-bit layout: the key tile holds bytes)
@@ -256,7 +377,10 @@ __global__ void __launch_bounds__(NT, MODE == 2 ? 2 : (BITS == 4 ? SQB_MMA_MINB4
       uint32_t bf8[8];
 #pragma unroll
       for (int r = 0; r < 8; r++) bf8[r] = Bfw[(BITS == 8 ? 0 : 256) + r * 32 + lane];
-      if (!mbar_wait(&bars[nst], 0, A.wait_ns) && lane == 0) misc[2] = 1.f;
+      SQB_STAMP(2);
+      const bool landed = mbar_wait(&bars[nst], 0, A.wait_ns);
+      SQB_STAMP(15);
+      if (lane == 0) misc[2] = landed ? 0.f : 1.f;          // "a copy never arrived" flag
       const float iq1 = fq.i1, iq2 = fq.i2, ik1 = fk.i1, ik2 = fk.i2;
       for (int sb = 0; sb < M; sb += 16) {
         int acc[4] = {MAGIC_I, MAGIC_I, MAGIC_I, MAGIC_I};
@@ -283,9 +407,16 @@ __global__ void __launch_bounds__(NT, MODE == 2 ? 2 : (BITS == 4 ? SQB_MMA_MINB4
       }
     }
   } else if (warp == 3) {
+    start_stage(1);
+    load_v();
+    float qr[CW], kr[CW];
+    cvt4_raw(rq, A.dt_qk, qr);
+    cvt4_raw(rk, A.dt_qk, kr);
     if constexpr (!VDEC) {
       // round and append the key at slot n0; its rounded value is what the fold uses for slot M - 1.  The
       // normalisation is redone here (same arithmetic as warp 0, so the same bits)
+      const int n0 = NPseq[h0] & (M - 1);
+      const bool FOLD = CANFOLD && n0 == M - 1;
       float s1 = 0.f;
 #pragma unroll
       for (int j = 0; j < CW; j++) s1 += kr[j] * kr[j];
@@ -307,12 +438,16 @@ __global__ void __launch_bounds__(NT, MODE == 2 ? 2 : (BITS == 4 ? SQB_MMA_MINB4
         w |= (static_cast<uint32_t>(static_cast<int>(cc)) & 0xFFu) << (8 * j);
         if (FOLD) Rf[(M - 1) * 160 + ((lane * CW + j) >> 4) * 20 + ((lane * CW + j) & 15)] = cc * ksc;
       }
-      *reinterpret_cast<uint32_t*>(KBh + (long long)n0 * DK + lane * 4) = w;
-      if (lane == 0) KBSh[n0] = f2h(ksc);
+      if (first) {
+        *reinterpret_cast<uint32_t*>(KBh + (long long)n0 * DK + lane * 4) = w;
+        if (lane == 0) KBSh[n0] = f2h(ksc);
+      }
     } else {
       // KDA: dot products of the buffered keys (times their per-channel decay ratios) with q and k, in fp32, from
       // this warp's own copy of the normalised vectors (same arithmetic as warp 0, so the same bits)
       constexpr int QD = DK / 4;
+      fetch_key_tile();
+      const int n0 = NPseq[h0] & (M - 1);
       float ksv = 0.f;
       if (lane < M) ksv = h2f(KBSh[lane]);
       float gnr[CW];
@@ -333,7 +468,8 @@ __global__ void __launch_bounds__(NT, MODE == 2 ? 2 : (BITS == 4 ? SQB_MMA_MINB4
         wg[lane * CW + j] = gnr[j];
       }
       __syncwarp();
-      if (!mbar_wait(&bars[nst], 0, A.wait_ns) && lane == 0) misc[2] = 1.f;
+      const bool landed = mbar_wait(&bars[nst], 0, A.wait_ns);
+      if (lane == 0) misc[2] = landed ? 0.f : 1.f;          // "a copy never arrived" flag
       for (int i0 = 0; i0 < M; i0 += 8) {
         const int i = i0 + (lane >> 2), part = lane & 3;
         const float ks_i = __shfl_sync(0xffffffffu, ksv, i & 31);
@@ -362,26 +498,25 @@ __global__ void __launch_bounds__(NT, MODE == 2 ? 2 : (BITS == 4 ? SQB_MMA_MINB4
       }
     }
   } else {
-    // warp 1, per value head: gates and the scalars derived from them
-    for (int hi = lane; hi < gqa; hi += 32) {
-      const int h = h0 + hi;
-      g4[0] = g4[1] = g4[2] = g4[3] = 0.f;
+    // warp 1, per value head: gates and the scalars derived from them (one lane per head)
+    start_stage(2);
+    load_v();
+    if (lane < gqa) {
+      const int hi = lane, h = h0 + hi;
+      const float gcur = VDEC ? 0.f : GCseq[h];
+      float g4[4];
       if (KIND == K_GDN) {
         if (A.gate) {
-          g4[0] = ldf(A.a + (long long)b * A.sa, A.dt_ab, h); g4[1] = ldf(A.dt_bias, A.dt_dtb, h);
-          g4[2] = ldf(A.A_log, A.dt_alog, h);                 g4[3] = ldf(A.b + (long long)b * A.sb, A.dt_ab, h);
+          g4[0] = cvt_raw(rg[0], A.dt_ab); g4[1] = cvt_raw(rg[1], A.dt_dtb); g4[2] = cvt_raw(rg[2], A.dt_alog); g4[3] = cvt_raw(rg[3], A.dt_ab);
         } else {
-          g4[0] = ldf(A.g + (long long)b * A.sg, A.dt_g, h);  g4[1] = ldf(A.beta + (long long)b * A.sbeta, A.dt_g, h);
+          g4[0] = cvt_raw(rg[0], A.dt_g); g4[1] = cvt_raw(rg[1], A.dt_g); g4[2] = g4[3] = 0.f;
         }
       } else if (KIND == K_M2) {
-        g4[0] = ldf(A.g + (long long)b * A.sg, A.dt_g, h);
-        if (A.dt_bias) g4[1] = ldf(A.dt_bias, A.dt_dtb, h);
-        g4[2] = ldf(A.A_log, A.dt_alog, h);
-        if (A.beta) g4[3] = ldf(A.beta, A.dt_beta, h);
+        g4[0] = cvt_raw(rg[0], A.dt_g); g4[1] = A.dt_bias ? cvt_raw(rg[1], A.dt_dtb) : 0.f;
+        g4[2] = cvt_raw(rg[2], A.dt_alog); g4[3] = A.beta ? cvt_raw(rg[3], A.dt_beta) : 0.f;
       } else {
-        g4[0] = ldf(A.beta + (long long)b * A.sbeta, A.dt_beta, h);
+        g4[0] = cvt_raw(rg[0], A.dt_beta); g4[1] = g4[2] = g4[3] = 0.f;
       }
-      const float gcur = VDEC ? 0.f : GCseq[h];
       float g = 0.f, bt = 0.f, Dv = 0.f;
       if (KIND == K_GDN) {
         if (A.gate) {
@@ -409,13 +544,16 @@ __global__ void __launch_bounds__(NT, MODE == 2 ? 2 : (BITS == 4 ? SQB_MMA_MINB4
       o[5] = gcur + g; o[6] = Dv;
     }
   }
+  SQB_STAMP(3);
   __syncthreads();
+  SQB_STAMP(4);
   // a copy that never completed: wait (bounded) for what may still be in flight, count it, leave
   auto bail = [&]() {
     uint8_t* orow = A.out + (long long)b * A.so + (long long)h0 * DV * osz;
     for (int v = tid; v < gqa * DV; v += NT) stf(orow, A.dt_out, v, 0.0f);
     if (tid == 0) {
-      for (int s = 0; s <= nst; s++) mbar_wait(&bars[s], 0, A.wait_ns);
+      for (int s = 0; s < nst && s < NSH; s++) mbar_wait(&bars[s], 0, A.wait_ns);     // the barriers that were armed
+      mbar_wait(&bars[nst], 0, A.wait_ns);
       atomicAdd(&A.status[0], 1);
     }
   };
@@ -428,9 +566,9 @@ __global__ void __launch_bounds__(NT, MODE == 2 ? 2 : (BITS == 4 ? SQB_MMA_MINB4
   int ci[NG][2];
   acc_start<BITS, UPG>(bf, ci);
   const float kq = misc[0];
+  const int n0 = __float_as_int(misc[1]);                       // live buffer entries of this slot
+  const bool FOLD = CANFOLD && n0 == M - 1;                     // this token fills the buffer: fold after the read-out
   const float iq1 = misc[4], iq2 = misc[5], ik1 = misc[6], ik2 = misc[7];
-  const int rho = (lane >> 2) * 16 + 4 * warp + (lane & 3);     // this lane's row within a stage
-  const int hh = rho / DV, rv = rho % DV;                        // head within the stage, row within the head
   const float2 dq01 = dqk[0];
   bool lost = false;
 
@@ -452,7 +590,7 @@ __global__ void __launch_bounds__(NT, MODE == 2 ? 2 : (BITS == 4 ? SQB_MMA_MINB4
         GBseq[(long long)h * M + n0] = gnew;
         GCseq[h] = FOLD ? 0.f : gnew;
       }
-      NPseq[h] = FOLD ? (M == 1 ? 0 : M) : n0 + 1;
+      NPseq[h] = FOLD ? 0 : n0 + 1;
     }
     return cc * usc;
   };
@@ -464,16 +602,18 @@ __global__ void __launch_bounds__(NT, MODE == 2 ? 2 : (BITS == 4 ? SQB_MMA_MINB4
     uint8_t* st = smraw + P.stage0 + s * P.stage_bytes;
     const unsigned short* scs = reinterpret_cast<const unsigned short*>(st + P.sc_off);
     const int8_t* ubt = reinterpret_cast<const int8_t*>(st + P.ub_off) + hh * M * DV;
-    const float vt = ldf(A.v + (long long)b * A.sv, A.dt_v, (long long)h * DV + rv);
+    const float vt = sh < 2 ? cvt_raw(rvt[sh], A.dt_v) : ldf(A.v + (long long)b * A.sv, A.dt_v, (long long)h * DV + rv);
     const float4 hda = *reinterpret_cast<const float4*>(hd + hi * HD_W);          // g, beta | dt, gcur, alpha
     const float4 hdb = *reinterpret_cast<const float4*>(hd + hi * HD_W + 4);      // a, gnew, D, -
     const float beta = hda.y, alpha = hda.w, a = hdb.x, Dv = hdb.z;
     const float2* dcf = dcu + hi * M;
 
     if (!mbar_wait(&bars[s], parity, A.wait_ns)) lost = true;
+    SQB_STAMP(5 + 3 * (sh & 1));
 
     float tq, tk;
     tile_pass<BITS, UPG, 16>(smem_u32(st), scs, bf, ci, warp, lane, tq, tk);
+    SQB_STAMP(6 + 3 * (sh & 1));
     tq = (tq * iq1) * iq2;                                    // powers of two: exact
     if (TWO) tk = (tk * ik1) * ik2;
     if (!VDEC) { tq = alpha * tq; tk = alpha * tk; }
@@ -498,12 +638,14 @@ __global__ void __launch_bounds__(NT, MODE == 2 ? 2 : (BITS == 4 ? SQB_MMA_MINB4
     }
     us[hi * DV + rv] = u;
     stf(A.out + (long long)b * A.so + (long long)h * DV * osz, A.dt_out, rv, o);
-    float umax = fabsf(u);
-#pragma unroll
-    for (int x = 1; x < (HPS == 1 ? 32 : 16); x <<= 1) umax = fmaxf(umax, __shfl_xor_sync(0xffffffffu, umax, x));
+    // largest |u| of the head's rows in this warp: non-negative floats order like their bit patterns (a NaN ends up
+    // as the maximum, as it should)
+    const uint32_t umask = HPS == 1 ? 0xffffffffu : (lane < 16 ? 0x0000ffffu : 0xffff0000u);
+    const float umax = __uint_as_float(__reduce_max_sync(umask, __float_as_uint(fabsf(u))));
     if ((lane & (HPS == 1 ? 31 : 15)) == 0) red[hi * NW + warp] = umax;
+    SQB_STAMP(7 + 3 * (sh & 1));
 
-    if constexpr (FOLD) {
+    if (CANFOLD && FOLD) {
       // append and fold the heads of this stage from the staged tile, then hand the stage back
       float* Lf = fsm + P.L;
       float* fdec = fsm + P.fdec;
@@ -574,10 +716,12 @@ __global__ void __launch_bounds__(NT, MODE == 2 ? 2 : (BITS == 4 ? SQB_MMA_MINB4
       }
     }
   }
-  if constexpr (!FOLD) {
+  if (!FOLD) {
     // ---- append the values of all heads at slot n0, every lane its own rows ----
     if (__syncthreads_or(lost)) { bail(); return; }
+    SQB_STAMP(11);
     for (int sh = 0; sh < NSH; sh++) append_row(sh);
+    SQB_STAMP(12);
     if (VDEC) {
       GBseq[((long long)h0 * M + n0) * DK + tid] = ga[tid];
       GCseq[(long long)h0 * DK + tid] = ga[tid];
