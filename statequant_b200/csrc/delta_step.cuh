@@ -51,6 +51,8 @@ struct StepArgs {
   int* status;               // device health word: [0] counts CTAs whose bounded wait ran out
   unsigned long long wait_ns;   // how long a wait for a bulk copy may take before the CTA gives up
   int hpc;                   // tensor-core kernels: value heads a CTA takes (divides hv / hk)
+  int m_log2, gqa_full;      // tensor-core kernels: log2(m), value heads per key head
+  int prefetch_dist;         // tensor-core kernels: a CTA prefetches into L2 for the CTA this many blocks later (0: off)
   int test_extra_tx;         // test hook: bytes a stage barrier expects beyond what is copied (so its wait runs out)
 };
 

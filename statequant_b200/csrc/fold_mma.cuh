@@ -1,0 +1,220 @@
+// The fold of a stage (128 state rows) on the tensor pipe, for the tensor-core decode kernel (step_mma.cuh), buffer
+// length 8, decays per head (Gated DeltaNet, Mamba2):
+//     S[v][k] = alpha (code[v][k] scale) + sum_i L_i[v] key_i[k],     L_i[v] = (dec_i u_i[v]) ks_i,  key_i = int8 codes
+// The sum over the 8 buffer slots is a K = 8 contraction.  L is fp32: it is cut into three bf16 pieces (8 + 8 + 8
+// mantissa bits: exact), the int8 key codes are exact in bf16, so every product of an mma.m16n8k16 (bf16 x bf16 -> fp32)
+// is exact and only the accumulation (fp32, in the tensor core's order) rounds.  K index = piece * 8 + slot: k-block 0
+// holds pieces 0 and 1, k-block 1 piece 2 and eight zero rows.  The stored state enters as the start value of the
+// accumulators, rounded twice as the reference does (code * scale, then * alpha).
+//
+// The codes never leave the ldmatrix fragment layout of the state pass (mma_pass.cuh): a span = 16 rows x 32 bytes is
+// one ldmatrix.x4; its values are the C fragments of 4 (8-bit) or 8 (4-bit) N-blocks whose column order is chosen to
+// match (a thread's bytes are its accumulator columns), re-rounded in registers and put back with stmatrix.x4.  The
+// stage is then written to the slot by bulk copies (shared -> global).
+#pragma once
+#include "mma_pass.cuh"
+
+namespace sqb {
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void stsm_x4(uint32_t saddr, const uint32_t (&r)[4]) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};"
+               ::"r"(saddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* dst, const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the bulk stores of this thread have read their shared-memory source (which may then be reused or released)
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t bf2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+// x = p1 + p2 + p3 exactly, each a bf16 (x finite; pieces that underflow are dropped, far below the rounding of the sum)
+__device__ __forceinline__ void split3(float x, float& p1, float& p2, float& p3) {
+  p1 = __bfloat162float(__float2bfloat16_rn(x));
+  const float r1 = x - p1;
+  p2 = __bfloat162float(__float2bfloat16_rn(r1));
+  p3 = __bfloat162float(__float2bfloat16_rn(r1 - p2));
+}
+
+// Column of the head that accumulator column n (0..7) of N-block q of span j stands for.
+template <int BITS>
+__host__ __device__ __forceinline__ int fold_col(int j, int q, int n) {
+  const int tq = n >> 1, e = n & 1;
+  if (BITS == 8) return 32 * j + (q >> 1) * 16 + 4 * tq + (q & 1) * 2 + e;        // 4 N-blocks per span of 32 columns
+  return 64 * j + (q >> 2) * 32 + 8 * tq + 2 * (q & 3) + e;                        // 8 N-blocks per span of 64 columns
+}
+
+// The B operand of the fold: for every (span, N-block) the thread's register: the key codes of slots (2t, 2t + 1) at the
+// column of fold_col, as a bf16 pair.  KBf[(j * NQ + q) * 32 + lane]; built by all 128 threads.
+// kbt: buffered keys [8][128] int8 (slots 0..6 valid), kcur: the key appended by this token (its rounded codes).
+template <int BITS>
+__device__ __forceinline__ void build_key_frags(uint32_t* KBf, const int8_t* kbt, const int8_t* kcur, int tid) {
+  constexpr int NQ = BITS == 8 ? 4 : 8, NSPAN = BITS == 8 ? 4 : 2;
+  for (int x = tid; x < NSPAN * NQ * 32; x += NT) {
+    const int l = x & 31, q = (x >> 5) % NQ, j = x / (32 * NQ);
+    const int col = fold_col<BITS>(j, q, l >> 2), s0 = 2 * (l & 3);
+    const float k0 = static_cast<float>(kbt[s0 * 128 + col]);
+    const float k1 = s0 + 1 == 7 ? static_cast<float>(kcur[col]) : static_cast<float>(kbt[(s0 + 1) * 128 + col]);
+    KBf[x] = bf2(k0, k1);
+  }
+}
+
+// Folds the 32 rows of warp w (row blocks 2w and 2w + 1) of a stage.  HPS heads of d_v = 128 / HPS rows per stage.
+//   st_addr / scs: the stage's codes (padded pieces) and scales [row][NG] in shared memory, both rewritten in place
+//   ubt: the stage's buffered values [HPS][8][DV] int8 (slots 0..6); udq: this token's rounded values [HPS][DV]
+//   tab: per head of the stage 8 floats dec_i (dec_7 unused), 8 floats value scales, then alpha; ksf: key scales [8]
+template <int BITS, int UPG, int DV>
+__device__ __forceinline__ void fold_stage_mma(uint32_t st_addr, unsigned short* scs, const int8_t* ubt, const float* udq,
+                                               const float* tab, const float* ksf, const uint32_t* KBf, int w, int lane) {
+  constexpr int NG = 4 / UPG, ROWB = 128 * BITS / 8, PITCH = 16 * ROWB + 16;
+  constexpr int NQ = BITS == 8 ? 4 : 8, NSPAN = BITS == 8 ? 4 : 2, TABW = 20;
+  constexpr float QMAX = BITS == 4 ? 7.0f : 127.0f, MB = BITS == 4 ? MAGIC + 8.0f : MAGIC;
+  static_assert((BITS == 8 && UPG == 1) || (BITS == 4 && UPG == 2), "one scale group per span");
+  const int g = lane >> 2, t = lane & 3;
+  const uint32_t lrow = st_addr + (lane & 7) * PITCH + ((lane >> 3) & 1) * ROWB + (lane >> 4) * 16;
+  const int hh = (g * 16) / DV;                       // head of this thread's rows within the stage
+  const float* tb = tab + hh * TABW;
+  const float alphan = tb[16];
+#pragma unroll 1
+  for (int bb = 0; bb < 2; bb++) {
+    const int b = 2 * w + bb;
+    const int row0 = g * 16 + 2 * b;                   // stage rows row0, row0 + 1
+    const int rv0 = row0 % DV;
+    // ---- A fragments: L of rows row0, row0 + 1 at slots 2t, 2t + 1, in three bf16 pieces ----
+    uint32_t A1[2], A2[2], A3[2];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      float p1[2], p2[2], p3[2];
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        const int s = 2 * t + e;
+        float L;
+        if (s < 7) L = tb[s] * (static_cast<float>(ubt[(hh * 8 + s) * DV + rv0 + r]) * tb[8 + s]);
+        else L = udq[hh * DV + rv0 + r];
+        split3(L * ksf[s], p1[e], p2[e], p3[e]);
+      }
+      A1[r] = bf2(p1[0], p1[1]); A2[r] = bf2(p2[0], p2[1]); A3[r] = bf2(p3[0], p3[1]);
+    }
+#pragma unroll 1
+    for (int j = 0; j < NSPAN; j++) {
+      uint32_t m[4];
+      const uint32_t addr = lrow + 2 * b * ROWB + 32 * j;
+      ldsm_x4(m, addr);
+      const int gi = BITS == 8 ? j : j;                // scale group of the span (one group per span)
+      const float sc0 = h2f(scs[row0 * NG + gi]), sc1 = h2f(scs[(row0 + 1) * NG + gi]);
+      float acc[NQ][4];
+      // ---- start values: (code * scale) * alpha, two roundings ----
+      if constexpr (BITS == 8) {
+        const uint32_t x0 = m[0] ^ 0x80808080u, x1 = m[1] ^ 0x80808080u, x2 = m[2] ^ 0x80808080u, x3 = m[3] ^ 0x80808080u;
+        acc[0][0] = byte_to_f<0>(x0); acc[0][1] = byte_to_f<1>(x0); acc[0][2] = byte_to_f<0>(x1); acc[0][3] = byte_to_f<1>(x1);
+        acc[1][0] = byte_to_f<2>(x0); acc[1][1] = byte_to_f<3>(x0); acc[1][2] = byte_to_f<2>(x1); acc[1][3] = byte_to_f<3>(x1);
+        acc[2][0] = byte_to_f<0>(x2); acc[2][1] = byte_to_f<1>(x2); acc[2][2] = byte_to_f<0>(x3); acc[2][3] = byte_to_f<1>(x3);
+        acc[3][0] = byte_to_f<2>(x2); acc[3][1] = byte_to_f<3>(x2); acc[3][2] = byte_to_f<2>(x3); acc[3][3] = byte_to_f<3>(x3);
+      } else {
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+          const uint32_t w0 = m[2 * (q >> 2)] >> (8 * (q & 3)), w1 = m[2 * (q >> 2) + 1] >> (8 * (q & 3));
+          acc[q][0] = __uint_as_float((w0 & 15u) | 0x4B000000u) - 8388616.0f;            // 2^23 + 8
+          acc[q][1] = __uint_as_float(((w0 >> 4) & 15u) | 0x4B000000u) - 8388616.0f;
+          acc[q][2] = __uint_as_float((w1 & 15u) | 0x4B000000u) - 8388616.0f;
+          acc[q][3] = __uint_as_float(((w1 >> 4) & 15u) | 0x4B000000u) - 8388616.0f;
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < NQ; q++) {
+        acc[q][0] = (acc[q][0] * sc0) * alphan; acc[q][1] = (acc[q][1] * sc0) * alphan;
+        acc[q][2] = (acc[q][2] * sc1) * alphan; acc[q][3] = (acc[q][3] * sc1) * alphan;
+      }
+      // ---- the eight buffer slots ----
+#pragma unroll
+      for (int q = 0; q < NQ; q++) {
+        const uint32_t kw = KBf[(j * NQ + q) * 32 + lane];
+        mma_bf16(acc[q], A1[0], A1[1], A2[0], A2[1], kw, kw);
+        mma_bf16(acc[q], A3[0], A3[1], 0u, 0u, kw, kw);
+      }
+      // ---- fresh scales: absmax over the group = this span, over the quad ----
+      float am0 = 0.f, am1 = 0.f;
+#pragma unroll
+      for (int q = 0; q < NQ; q++) {
+        am0 = fmaxf(am0, fmaxf(fabsf(acc[q][0]), fabsf(acc[q][1])));
+        am1 = fmaxf(am1, fmaxf(fabsf(acc[q][2]), fabsf(acc[q][3])));
+      }
+      am0 = fmaxf(am0, __shfl_xor_sync(0xffffffffu, am0, 1)); am1 = fmaxf(am1, __shfl_xor_sync(0xffffffffu, am1, 1));
+      am0 = fmaxf(am0, __shfl_xor_sync(0xffffffffu, am0, 2)); am1 = fmaxf(am1, __shfl_xor_sync(0xffffffffu, am1, 2));
+      const float s0 = fp16_scale(am0, QMAX), s1 = fp16_scale(am1, QMAX);
+      const float r0 = rcp_approx(s0), r1 = rcp_approx(s1);
+      // ---- round: candidate by reciprocal multiply, verified by the exact residual (see round_fast) ----
+      float tv[NQ][4];
+      float worst0 = 0.f, worst1 = 0.f;
+#pragma unroll
+      for (int q = 0; q < NQ; q++) {
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          tv[q][e] = fmaf(acc[q][e], r0, MB);
+          worst0 = fmaxf(worst0, fabsf(fmaf(-(tv[q][e] - MB), s0, acc[q][e])));
+          tv[q][2 + e] = fmaf(acc[q][2 + e], r1, MB);
+          worst1 = fmaxf(worst1, fabsf(fmaf(-(tv[q][2 + e] - MB), s1, acc[q][2 + e])));
+        }
+      }
+      // A verified candidate is the right UNCLAMPED integer whatever the scale; only a scale in fp16's subnormal range
+      // (rounded far from absmax / qmax) lets a quotient pass qmax, and then clamping the candidate is what
+      // clamp(rint(div_rn(x, s))) does.
+      const bool ok0 = worst0 < s0 * 0.49998474f, ok1 = worst1 < s1 * 0.49998474f;
+      if (!ok0 || !ok1) {                             // rare: an element close to a tie
+#pragma unroll
+        for (int q = 0; q < NQ; q++) {
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            if (!ok0) tv[q][e] = rintf(__fdiv_rn(acc[q][e], s0)) + MB;
+            if (!ok1) tv[q][2 + e] = rintf(__fdiv_rn(acc[q][2 + e], s1)) + MB;
+          }
+        }
+      }
+      if (s0 < FP16_MIN_NORMAL || s1 < FP16_MIN_NORMAL) {
+#pragma unroll
+        for (int q = 0; q < NQ; q++) {
+#pragma unroll
+          for (int e = 0; e < 4; e++) tv[q][e] = fminf(fmaxf(tv[q][e], MB - QMAX), MB + QMAX);
+        }
+      }
+      // ---- repack into the fragment registers ----
+      uint32_t o[4];
+      if constexpr (BITS == 8) {
+        auto two = [](float a, float c) { return __byte_perm(__float_as_uint(a), __float_as_uint(c), 0x0040); };   // bytes (a, c)
+        o[0] = __byte_perm(two(tv[0][0], tv[0][1]), two(tv[1][0], tv[1][1]), 0x5410);
+        o[1] = __byte_perm(two(tv[0][2], tv[0][3]), two(tv[1][2], tv[1][3]), 0x5410);
+        o[2] = __byte_perm(two(tv[2][0], tv[2][1]), two(tv[3][0], tv[3][1]), 0x5410);
+        o[3] = __byte_perm(two(tv[2][2], tv[2][3]), two(tv[3][2], tv[3][3]), 0x5410);
+      } else {
+#pragma unroll
+        for (int hx = 0; hx < 2; hx++) {
+          uint32_t a = 0, c = 0;
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const int q = hx * 4 + i;
+            a |= ((__float_as_uint(tv[q][0]) & 15u) | ((__float_as_uint(tv[q][1]) & 15u) << 4)) << (8 * i);
+            c |= ((__float_as_uint(tv[q][2]) & 15u) | ((__float_as_uint(tv[q][3]) & 15u) << 4)) << (8 * i);
+          }
+          o[2 * hx] = a;
+          o[2 * hx + 1] = c;
+        }
+      }
+      __syncwarp();                                     // every lane has read the span's codes and old scales
+      stsm_x4(addr, o);
+      if (t == 0) {
+        scs[row0 * NG + gi] = f2h(s0);
+        scs[(row0 + 1) * NG + gi] = f2h(s1);
+      }
+    }
+  }
+}
+
+}  // namespace sqb

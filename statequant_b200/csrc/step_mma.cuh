@@ -25,6 +25,7 @@
 #pragma once
 #include "step_tma.cuh"
 #include "mma_pass.cuh"
+#include "fold_mma.cuh"
 
 namespace sqb {
 
@@ -37,10 +38,16 @@ __device__ long long g_mma_trace[64 * 4 * 16];
 #endif
 
 struct SmemM {
-  int bars, stage0, stage_bytes, sc_off, ub_off, kb, gbt, bf, f0, total;
-  int hd, dcu, dqk, us, red, misc, ga, ae, wq, wk, wg, R, L, fdec, ksf;     // float offsets from f0
+  int bars, stage0, stage_bytes, sc_off, ub_off, kb, gbt, bf, kbf, kcur, f0, total;
+  int hd, dcu, gbs, dqk, ksv, us, red, misc, ga, ae, wq, wk, wg, tab, R, L, fdec, ksf;     // float offsets from f0
 };
+// The fold of the m-th token runs on the tensor pipe (fold_mma.cuh) for decays per head, a buffer of 8 and one scale
+// group per 32-byte span of a row; otherwise in fp32 (fold_rows.cuh), which needs the R / L tiles.
+__host__ __device__ inline bool fold_on_tensor_pipe(int kind, int bits, int upg, int M) {
+  return kind != K_KDA && M == 8 && ((bits == 8 && upg == 1) || (bits == 4 && upg == 2));
+}
 __host__ __device__ inline SmemM smemm_plan(int kind, int bits, int upg, int DV, int M, int nst, int gqa, bool fold) {
+  const bool simt = fold && !fold_on_tensor_pipe(kind, bits, upg, M), tens = fold && !simt;
   SmemM s;
   const int rowb = 128 * bits / 8, pitch = 16 * rowb + 16, ng = 4 / upg;
   s.sc_off = 8 * pitch;
@@ -51,12 +58,16 @@ __host__ __device__ inline SmemM smemm_plan(int kind, int bits, int upg, int DV,
   s.stage0 = o; o += nst * s.stage_bytes;
   s.kb = o; o += al16i(M * 128);
   s.gbt = o; o += (kind == K_KDA ? M * 128 * 4 : 0);
-  s.bf = o; o += 2048;            // B fragments: the state's layout, then the byte layout (key tile)
+  s.bf = o; o += (bits == 4 && kind != K_KDA) ? 2048 : 1024;   // B fragments: the state's layout (+ the byte layout for the key tile)
+  s.kbf = o; o += tens ? 2048 : 0;   // the fold's key fragments
+  s.kcur = o; o += tens ? 128 : 0;   // the codes of the key appended by this token
   s.f0 = o;
   int f = 0;
   s.hd = f; f += gqa * HD_W;
   s.dcu = f; f += (2 * gqa * M + 3) & ~3;
+  s.gbs = f; f += fold ? (gqa * M + 3) & ~3 : 0;       // cumulative log decays of the buffered tokens, as stored
   s.dqk = f; f += 2 * (M < 16 ? 16 : M);
+  s.ksv = f; f += 32;                                  // scales of the buffered keys
   s.us = f; f += gqa * DV;
   s.red = f; f += gqa * NW;
   s.misc = f; f += 16;
@@ -66,9 +77,10 @@ __host__ __device__ inline SmemM smemm_plan(int kind, int bits, int upg, int DV,
   s.wk = f; f += (kind == K_KDA ? 128 : 0);
   s.wg = f; f += (kind == K_KDA ? 128 : 0);
   f = (f + 3) & ~3;
-  s.R = f; f += fold ? M * 160 : 0;
-  s.L = f; f += fold ? DV * fold_lm(M) : 0;
-  s.fdec = f; f += fold ? 32 : 0;
+  s.tab = f; f += tens ? 2 * 20 : 0;
+  s.R = f; f += simt ? M * 160 : 0;
+  s.L = f; f += simt ? DV * fold_lm(M) : 0;
+  s.fdec = f; f += simt ? 32 : 0;
   s.ksf = f; f += fold ? 64 : 0;
   s.total = s.f0 + ((f + 3) & ~3) * 4;
   return s;
@@ -130,38 +142,98 @@ __device__ __forceinline__ void cvt4_raw(const Raw4& r, int dt, float (&f)[4]) {
   }
 }
 
+__device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) {     // 16-byte aligned, a multiple of 16
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void prefetch_l2_line(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 #ifndef SQB_MMA_MINB_FOLD
 #define SQB_MMA_MINB_FOLD 4
 #endif
+#ifndef SQB_MMA_MINB_TFOLD
+#define SQB_MMA_MINB_TFOLD 5
+#endif
 
 template <int KIND, int BITS, int UPG, int DV, int MODE>
-__global__ void __launch_bounds__(NT, MODE == 3 ? SQB_MMA_MINB_FOLD : (BITS == 4 ? SQB_MMA_MINB4 : SQB_MMA_MINB8))
+__global__ void __launch_bounds__(NT, MODE == 3 ? (KIND != K_KDA && ((BITS == 8 && UPG == 1) || (BITS == 4 && UPG == 2)) ? SQB_MMA_MINB_TFOLD : SQB_MMA_MINB_FOLD)
+                                               : (BITS == 4 ? SQB_MMA_MINB4 : SQB_MMA_MINB8))
     step_mma_kernel(const __grid_constant__ StepArgs A, const __grid_constant__ SmemM P, const int nst) {
   constexpr int DK = 128, NG = 4 / UPG, G = 32 * UPG;
   constexpr int ROWB = DK * BITS / 8, PITCH = 16 * ROWB + 16;
   constexpr int HPS = 128 / DV;                  // heads per stage
   constexpr int CW = 4;                          // columns per lane in the prologue
   constexpr bool TWO = KIND != K_M2, VDEC = KIND == K_KDA, CANFOLD = MODE == 3;
+  constexpr bool TFMT = !VDEC && ((BITS == 8 && UPG == 1) || (BITS == 4 && UPG == 2));
   static_assert(DV == 64 || DV == 128, "a stage is 128 rows: one or two heads");
 
   extern __shared__ __align__(128) uint8_t smraw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int M = A.M, HV = A.HV;
+  // grid: x = batch row, y = (key head, part of its value heads); no division on the way to the first fetch
   const int gqa = A.hpc;                          // value heads of this CTA: all heads of a key head, or a part of them
-  const int cpk = HV / A.HK / gqa;                // CTAs per key head
+  const int gqf = A.gqa_full;                     // value heads per key head
   const int NSH = gqa / HPS;
-  const int b = blockIdx.x / (A.HK * cpk), rem = blockIdx.x - b * (A.HK * cpk);
-  const int hk = rem / cpk, part = rem - hk * cpk;
-  const int h0 = hk * (HV / A.HK) + part * gqa;
+  const int b = blockIdx.x;
+  int hk = blockIdx.y, part = 0;
+  if (gqa != gqf) { const int cpk = gqf / gqa; hk = blockIdx.y / cpk; part = blockIdx.y - hk * cpk; }
+  const int h0 = hk * gqf + part * gqa;
   const bool first = part == 0;                   // the CTA that appends the key head's key
+  // Software prefetch, one wave ahead: the CTA that will run prefetch_dist blocks later (on some SM, a CTA lifetime or
+  // two from now) gets its slot's state, buffer and scalars and its activations pulled into L2 by fire-and-forget
+  // prefetches, so that its own copies and loads find them there.  The bytes in flight from HBM then live in L2, not
+  // in shared memory, of which there is too little to cover the loaded HBM latency.
+  if (warp == 3 && A.prefetch_dist > 0 &&
+      (long long)blockIdx.y * gridDim.x + blockIdx.x + A.prefetch_dist < (long long)gridDim.x * gridDim.y) {
+    const long long fl = (long long)blockIdx.y * gridDim.x + blockIdx.x + A.prefetch_dist;
+    const int fy = static_cast<int>(fl / gridDim.x), fb = static_cast<int>(fl - (long long)fy * gridDim.x);
+    const int cpk = gqf / gqa;
+    const int fhk = fy / cpk, fh0 = fhk * gqf + (fy - fhk * cpk) * gqa;
+    const long long fseq = A.idx != nullptr ? static_cast<long long>(A.idx[fb]) : static_cast<long long>(fb);
+    const int esz = A.dt_qk == DT_F32 ? 4 : 2, vsz = A.dt_v == DT_F32 ? 4 : 2;
+    // activations of the future CTA
+    if (lane < 4) prefetch_l2_line(A.q + (long long)fb * A.sq + ((long long)fhk * 128 + lane * 32) * esz);
+    else if (lane < 8) prefetch_l2_line(A.k + (long long)fb * A.sk + ((long long)fhk * 128 + (lane - 4) * 32) * esz);
+    else if (lane < 16) {
+      const long long o = (long long)fh0 * DV * vsz + (lane - 8) * 128;
+      if (o < (long long)(fh0 + gqa) * DV * vsz) prefetch_l2_line(A.v + (long long)fb * A.sv + o);
+    }
+    if (fseq > 0 || A.idx == nullptr) {
+      const int rowb = 128 * BITS / 8;
+      const uint8_t* cs = A.S + fseq * A.sS + (long long)fh0 * DV * rowb;
+      const int cbytes = gqa * DV * rowb;
+      for (int o = lane * 4096; o < cbytes; o += 32 * 4096) prefetch_l2_bulk(cs + o, min(4096, cbytes - o));
+      if (lane == 16) prefetch_l2_bulk(A.SC + fseq * A.sSC + (long long)fh0 * DV * (4 / UPG) * 2, gqa * DV * (4 / UPG) * 2);
+      else if (lane == 17) prefetch_l2_bulk(A.UB + fseq * A.sUB + (long long)fh0 * M * DV, gqa * M * DV);
+      else if (lane == 18) prefetch_l2_bulk(A.KB + fseq * A.sKB + (long long)fhk * M * 128, M * 128);
+      else if (lane == 19) prefetch_l2_line(A.GB + fseq * A.sGB + (long long)fh0 * M * 4 * (KIND == K_KDA ? 128 : 1));
+      else if (lane == 20) prefetch_l2_line(A.GCUR + fseq * A.sGC + (long long)fh0 * 4 * (KIND == K_KDA ? 128 : 1));
+      else if (lane == 21) prefetch_l2_line(A.NPTR + fseq * A.sN + (long long)fh0 * 4);
+      else if (lane == 22) prefetch_l2_line(A.KBS + fseq * A.sKBS + (long long)fhk * M * 2);
+      else if (lane == 23) prefetch_l2_line(A.UBS + fseq * A.sUBS + (long long)fh0 * M * 2);
+    }
+  }
   const int osz = dt_size(A.dt_out);
+  const bool TFOLD = TFMT && M == 8;               // the fold, when it comes, runs on the tensor pipe
 
 #ifdef SQB_TRACE
   const long long t_start = clock64();
 #endif
-  // The slot index first, and nothing else in flight beside it: every other fetch of the CTA (bulk copies, scalars,
-  // activations) leaves in one burst as soon as it is known, and a load that shares a scoreboard with slower ones
-  // would hold that burst back.
+  // ---- fetches --------------------------------------------------------------------------------------------------------
+  // Under load a global load takes well over a microsecond here, so every fetch of the CTA leaves as early as its
+  // address is known, as raw bits (a loaded register is first touched where its value is needed: the conversion of
+  // a loaded word already waits for it), and a wait never sits in front of fetches that do not depend on it:
+  //   warps 0 and 3 need q and k first and the slot only later: their q / k loads leave before the slot index;
+  //   warps 1 and 2 issue the bulk copies, which need nothing but the slot index: they load it alone.
+  const int rho = (lane >> 2) * 16 + 4 * warp + (lane & 3);     // this lane's row within a stage
+  const int hh = rho / DV, rv = rho % DV;                        // head within the stage, row within the head
+  Raw4 rq, rk;
+  rq.v = make_uint4(0u, 0u, 0u, 0u); rk.v = rq.v; rq.vec = false; rk.vec = false;
+  if (warp == 0 || warp == 3) {
+    rq = ld4_raw(A.q + (long long)b * A.sq, A.dt_qk, (long long)hk * DK + lane * CW);
+    rk = ld4_raw(A.k + (long long)b * A.sk, A.dt_qk, (long long)hk * DK + lane * CW);
+  }
   long long seq = b;
   if (A.idx != nullptr) {
     seq = A.idx[b];
@@ -171,19 +243,15 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? SQB_MMA_MINB_FOLD : (BITS == 4
       return;
     }
   }
-  const int rho = (lane >> 2) * 16 + 4 * warp + (lane & 3);     // this lane's row within a stage
-  const int hh = rho / DV, rv = rho % DV;                        // head within the stage, row within the head
   int* NPseq = reinterpret_cast<int*>(A.NPTR + seq * A.sN);
   SQB_STAMP(0);
-  // The slot's counter (the heads of a slot advance together) is loaded by the roles that need it, where they need
-  // it: nothing that is fetched depends on it, and no warp waits for it before its own loads and copies are out.
 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smraw + P.bars);
   uint8_t* kbt = smraw + P.kb;
   uint32_t* Bfw = reinterpret_cast<uint32_t*>(smraw + P.bf);
   float* fsm = reinterpret_cast<float*>(smraw + P.f0);
   float *hd = fsm + P.hd, *us = fsm + P.us, *red = fsm + P.red, *misc = fsm + P.misc, *ga = fsm + P.ga, *ae = fsm + P.ae,
-        *wq = fsm + P.wq, *wk = fsm + P.wk, *wg = fsm + P.wg;
+        *wq = fsm + P.wq, *wk = fsm + P.wk, *wg = fsm + P.wg, *ksv = fsm + P.ksv;
   float2* dcu = reinterpret_cast<float2*>(fsm + P.dcu);    // (decay factor, value scale) of every (head, slot)
   float2* dqk = reinterpret_cast<float2*>(fsm + P.dqk);    // dot products of the buffered keys with q and k
   const float* gbt = reinterpret_cast<const float*>(smraw + P.gbt);
@@ -207,57 +275,8 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? SQB_MMA_MINB_FOLD : (BITS == 4
     else if (l == 8) bulk_g2s(st + P.sc_off, SCseq + row0 * NG * 2, 128 * NG * 2, &bars[s]);
     else if (l == 9) bulk_g2s(st + P.ub_off, UBseq + (long long)(h0 + sh * HPS) * M * DV, M * 128, &bars[s]);
   };
-
-  // The key tile (and KDA's decay tile) has its own barrier, initialised, armed and waited on by ONE warp (warp 0;
-  // KDA: warp 3), so that no wait can meet a barrier another warp has not initialised yet.
-  auto fetch_key_tile = [&]() {
-    if (lane == 0) {
-      mbar_init(&bars[nst], 1);
-      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-      mbar_expect_tx(&bars[nst], M * DK + (VDEC ? M * DK * 4 : 0));
-      bulk_g2s(kbt, KBh, M * DK, &bars[nst]);
-      if (VDEC) bulk_g2s(smraw + P.gbt, GBseq + (long long)h0 * M * DK, M * DK * 4, &bars[nst]);
-    }
-    __syncwarp();
-  };
-
-  SQB_STAMP(13);
-  // ---- activation loads, as raw bits (converted where they are used) ------------------------------------------------
-  Raw4 rq, rk;
-  uint32_t rg[4] = {0u, 0u, 0u, 0u};
-  if (warp == 0 || warp == 3) {
-    rq = ld4_raw(A.q + (long long)b * A.sq, A.dt_qk, (long long)hk * DK + lane * CW);
-    rk = ld4_raw(A.k + (long long)b * A.sk, A.dt_qk, (long long)hk * DK + lane * CW);
-  } else if (warp == 1 && lane < gqa) {
-    const int h = h0 + lane;                               // one lane per value head (at most 32 per key head)
-    if (KIND == K_GDN) {
-      if (A.gate) {
-        rg[0] = ld1_raw(A.a + (long long)b * A.sa, A.dt_ab, h); rg[1] = ld1_raw(A.dt_bias, A.dt_dtb, h);
-        rg[2] = ld1_raw(A.A_log, A.dt_alog, h);                 rg[3] = ld1_raw(A.b + (long long)b * A.sb, A.dt_ab, h);
-      } else {
-        rg[0] = ld1_raw(A.g + (long long)b * A.sg, A.dt_g, h);  rg[1] = ld1_raw(A.beta + (long long)b * A.sbeta, A.dt_g, h);
-      }
-    } else if (KIND == K_M2) {
-      rg[0] = ld1_raw(A.g + (long long)b * A.sg, A.dt_g, h);
-      if (A.dt_bias) rg[1] = ld1_raw(A.dt_bias, A.dt_dtb, h);
-      rg[2] = ld1_raw(A.A_log, A.dt_alog, h);
-      if (A.beta) rg[3] = ld1_raw(A.beta, A.dt_beta, h);
-    } else {
-      rg[0] = ld1_raw(A.beta + (long long)b * A.sbeta, A.dt_beta, h);
-    }
-  }
-
-
-  SQB_STAMP(14);
-  // this lane's value-vector entries of the first two stages (needed after the first pass): each role issues these
-  // loads once its urgent fetches are out
-  uint32_t rvt[2];
-  auto load_v = [&]() {
-    rvt[0] = ld1_raw(A.v + (long long)b * A.sv, A.dt_v, (long long)(h0 + hh) * DV + rv);
-    rvt[1] = ld1_raw(A.v + (long long)b * A.sv, A.dt_v, (long long)(h0 + (NSH > 1 ? HPS : 0) + hh) * DV + rv);
-  };
-  // A stage barrier of the first fill is initialised, armed and its copies issued by ONE warp (a warp's copies leave one
-  // after the other, so the stages are spread over warps 2, 3 and 1); everybody else meets it after the block barrier.
+  // A stage barrier of the first fill is initialised, armed and its copies issued by ONE warp (a warp's copies leave
+  // one after the other, so the stages are spread over warps 2 and 1); everybody else meets it after the block barrier.
   auto start_stage = [&](int s) {
     if (s < nst && s < NSH) {
       if (lane == 0) {
@@ -269,34 +288,146 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? SQB_MMA_MINB_FOLD : (BITS == 4
       issue_stage(s, s, lane);
     }
   };
+  // this lane's value-vector entries of the first two stages (needed after the first pass): each role issues these
+  // loads once its urgent fetches are out
+  uint32_t rvt[2];
+  auto load_v = [&]() {
+    rvt[0] = ld1_raw(A.v + (long long)b * A.sv, A.dt_v, (long long)(h0 + hh) * DV + rv);
+    rvt[1] = ld1_raw(A.v + (long long)b * A.sv, A.dt_v, (long long)(h0 + (NSH > 1 ? HPS : 0) + hh) * DV + rv);
+  };
+  // The key tile (and KDA's decay tile) is fetched by warp 2; the warp that takes the buffered keys' dot products
+  // (warp 0; KDA: warp 3) meets warp 2 at named barrier 1 (64 threads) before it waits for the tile, so that its wait
+  // can never meet a barrier that is not initialised yet; by then the key scales and the slot's counter are published.
+  constexpr int DOTS_WARP = VDEC ? 3 : 0, KEY_WARP = VDEC ? 0 : 3;
+  // the key as it goes into the buffer, rounded by KEY_WARP before the block barrier and stored after it
+  uint32_t kword = 0;
+  float kscale = 0.f;
+  float kdeq[CW] = {0.f, 0.f, 0.f, 0.f};
+  auto round_key = [&](const float (&kr)[CW], float mx) {
+    kscale = fp16_scale(mx, 127.0f);
+#pragma unroll
+    for (int j = 0; j < CW; j++) {
+      const float cc = rq_exact(kr[j], kscale, 127.0f);
+      kword |= (static_cast<uint32_t>(static_cast<int>(cc)) & 0xFFu) << (8 * j);
+      kdeq[j] = cc * kscale;
+    }
+  };
 
   // ---- prologue, by role ----------------------------------------------------------------------------------------
   if (warp == 2) {
+    // the slot's small fields first (raw), then the copies
+    const int nraw = NPseq[h0];                              // the heads of a slot advance together
+    unsigned short ks_raw = 0;
+    if (lane < M) ks_raw = KBSh[lane];
+    const int e0 = lane;                                     // first (head, slot) pair of this lane
+    float gb0 = 0.f, gc0 = 0.f;
+    unsigned short us0 = 0;
+    if (e0 < gqa * M) {
+      const int h = h0 + (e0 >> A.m_log2);
+      if (!VDEC) { gb0 = GBseq[(long long)h0 * M + e0]; gc0 = GCseq[h]; }
+      us0 = UBSseq[h0 * M + e0];
+    }
     SQB_STAMP(1);
     start_stage(0);
+    if (lane == 0) {
+      mbar_init(&bars[nst], 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      mbar_expect_tx(&bars[nst], M * DK + (VDEC ? M * DK * 4 : 0));
+      bulk_g2s(kbt, KBh, M * DK, &bars[nst]);
+      if (VDEC) bulk_g2s(smraw + P.gbt, GBseq + (long long)h0 * M * DK, M * DK * 4, &bars[nst]);
+    }
     start_stage(3);
     SQB_STAMP(2);
     load_v();
-    const int n0 = NPseq[h0] & (M - 1);
+    const int n0 = nraw & (M - 1);
+    if (lane < 32) ksv[lane] = lane < M ? h2f(ks_raw) : 0.f;
     if (lane == 0) misc[1] = __int_as_float(n0);
-    // per (value head, buffer slot): decay factors of the live slots and their value scales
+    __syncwarp();
+    asm volatile("bar.arrive 1, 64;" ::: "memory");
+    // per (value head, buffer slot): decay factors of the live slots and their value scales.  Loaded whether the slot is
+    // live or not (dead entries may hold anything; they are selected away), so that the loads do not wait for the counter.
     for (int e = lane; e < gqa * M; e += 32) {
-      const int hi = e / M, i = e - hi * M, h = h0 + hi;
-      // loaded whether the slot is live or not (dead entries may hold anything; they are selected away), so that
-      // the loads do not wait for the slot's counter
-      const float gb = VDEC ? 0.f : GBseq[(long long)h * M + i], gc = VDEC ? 0.f : GCseq[h];
-      const float us_i = h2f(UBSseq[h * M + i]);
+      const int hi = e >> A.m_log2, i = e - hi * M, h = h0 + hi;
+      float gb = gb0, gc = gc0;
+      unsigned short usr = us0;
+      if (e != e0) {
+        if (!VDEC) { gb = GBseq[(long long)h * M + i]; gc = GCseq[h]; }
+        usr = UBSseq[h * M + i];
+      }
       const float dcy = VDEC ? 1.0f : expf(gc - gb);
-      dcu[e] = i < n0 ? make_float2(dcy, us_i) : make_float2(0.f, 0.f);
+      dcu[e] = i < n0 ? make_float2(dcy, h2f(usr)) : make_float2(0.f, 0.f);
+      if (CANFOLD) fsm[P.gbs + e] = gb;
+    }
+  } else if (warp == 1) {
+    // the gate inputs of this warp's heads (one lane per value head, at most 32 per key head), then stages 1 and 2
+    uint32_t rg[4] = {0u, 0u, 0u, 0u};
+    float gcur = 0.f;
+    const int hi = lane, h = h0 + hi;
+    if (lane < gqa) {
+      if (KIND == K_GDN) {
+        if (A.gate) {
+          rg[0] = ld1_raw(A.a + (long long)b * A.sa, A.dt_ab, h); rg[1] = ld1_raw(A.dt_bias, A.dt_dtb, h);
+          rg[2] = ld1_raw(A.A_log, A.dt_alog, h);                 rg[3] = ld1_raw(A.b + (long long)b * A.sb, A.dt_ab, h);
+        } else {
+          rg[0] = ld1_raw(A.g + (long long)b * A.sg, A.dt_g, h);  rg[1] = ld1_raw(A.beta + (long long)b * A.sbeta, A.dt_g, h);
+        }
+      } else if (KIND == K_M2) {
+        rg[0] = ld1_raw(A.g + (long long)b * A.sg, A.dt_g, h);
+        if (A.dt_bias) rg[1] = ld1_raw(A.dt_bias, A.dt_dtb, h);
+        rg[2] = ld1_raw(A.A_log, A.dt_alog, h);
+        if (A.beta) rg[3] = ld1_raw(A.beta, A.dt_beta, h);
+      } else {
+        rg[0] = ld1_raw(A.beta + (long long)b * A.sbeta, A.dt_beta, h);
+      }
+      if (!VDEC) gcur = GCseq[h];
+    }
+    start_stage(1);
+    start_stage(2);
+    load_v();
+    if (lane < gqa) {
+      float g4[4];
+      if (KIND == K_GDN) {
+        if (A.gate) {
+          g4[0] = cvt_raw(rg[0], A.dt_ab); g4[1] = cvt_raw(rg[1], A.dt_dtb); g4[2] = cvt_raw(rg[2], A.dt_alog); g4[3] = cvt_raw(rg[3], A.dt_ab);
+        } else {
+          g4[0] = cvt_raw(rg[0], A.dt_g); g4[1] = cvt_raw(rg[1], A.dt_g); g4[2] = g4[3] = 0.f;
+        }
+      } else if (KIND == K_M2) {
+        g4[0] = cvt_raw(rg[0], A.dt_g); g4[1] = A.dt_bias ? cvt_raw(rg[1], A.dt_dtb) : 0.f;
+        g4[2] = cvt_raw(rg[2], A.dt_alog); g4[3] = A.beta ? cvt_raw(rg[3], A.dt_beta) : 0.f;
+      } else {
+        g4[0] = cvt_raw(rg[0], A.dt_beta); g4[1] = g4[2] = g4[3] = 0.f;
+      }
+      float g = 0.f, bt = 0.f, Dv = 0.f;
+      if (KIND == K_GDN) {
+        if (A.gate) {
+          const float x = g4[0] + g4[1];
+          const float sp = x <= 20.0f ? logf(1.0f + expf(x)) : x;
+          g = -expf(g4[2]) * sp;
+          bt = __fdiv_rn(1.0f, 1.0f + expf(-g4[3]));
+        } else {
+          g = g4[0];
+          bt = g4[1];
+        }
+      } else if (KIND == K_M2) {
+        float dtv = g4[0];
+        if (A.dt_bias) dtv = dtv + g4[1];
+        if (A.dt_softplus) dtv = dtv <= 20.0f ? logf(1.0f + expf(dtv)) : dtv;
+        if (A.dt_clamp) dtv = fminf(fmaxf(dtv, A.dt_min), A.dt_max);
+        g = __fmul_rn(g4[2], dtv);
+        bt = dtv;
+        Dv = g4[3];
+      } else {
+        bt = g4[0];
+      }
+      float* o = hd + hi * HD_W;
+      o[0] = g; o[1] = bt; o[2] = gcur; o[3] = VDEC ? 1.0f : expf(gcur); o[4] = VDEC ? 1.0f : expf(g);
+      o[5] = gcur + g; o[6] = Dv;
     }
   } else if (warp == 0) {
-    if (!VDEC) fetch_key_tile();
+    // q and k: normalised, in fixed point, as B fragments; GDN / Mamba2: the buffered keys' dot products on the tensor
+    // pipe; KDA: the key that goes into the buffer
     load_v();
-    float ksv = 0.f;                          // scale of buffered key `lane`
-    if (!VDEC && lane < M) ksv = h2f(KBSh[lane]);
-    [[maybe_unused]] int n0 = 0;
-    if (VDEC) n0 = NPseq[h0] & (M - 1);       // KDA: this warp appends the key
-    [[maybe_unused]] const bool FOLD = CANFOLD && n0 == M - 1;
     float qr[CW], kr[CW];
     cvt4_raw(rq, A.dt_qk, qr);
     cvt4_raw(rk, A.dt_qk, kr);
@@ -338,15 +469,11 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? SQB_MMA_MINB_FOLD : (BITS == 4
       mq = fmaxf(mq, fabsf(eq[j]));
       mk = fmaxf(mk, fabsf(ek[j]));
     }
-    d = warp_sum(d);
-    mx = warp_max(mx);
-    mq = warp_max(mq);
-    if (TWO) mk = VDEC ? warp_max(mk) : mx;
+    // maxima of non-negative floats: their bit patterns order like integers (one reduction instruction each)
+    mq = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(mq)));
+    if (TWO && VDEC) mk = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(mk)));
+    if (TWO && !VDEC) { mx = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(mx))); mk = mx; }
     const FxScale fq = fx30_scale(mq), fk = fx30_scale(mk);
-    if (lane == 0) {
-      misc[0] = d;
-      misc[4] = fq.i1; misc[5] = fq.i2; misc[6] = fk.i1; misc[7] = fk.i2;
-    }
     uint32_t yq[CW], yk[CW];
 #pragma unroll
     for (int j = 0; j < CW; j++) { yq[j] = fx30_digits(eq[j], fq); yk[j] = TWO ? fx30_digits(ek[j], fk) : 0u; }
@@ -356,20 +483,14 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? SQB_MMA_MINB_FOLD : (BITS == 4
       put_b_words<8>(Bfw + 256, lane, 0, yq[0], yq[1], yq[2], yq[3]);
       put_b_words<8>(Bfw + 256, lane, 1, yk[0], yk[1], yk[2], yk[3]);
     }
+    d = warp_sum(d);
+    if (lane == 0) {
+      misc[0] = d;
+      misc[4] = fq.i1; misc[5] = fq.i2; misc[6] = fk.i1; misc[7] = fk.i2;
+    }
     if constexpr (VDEC) {
-      // KDA: this warp appends the key (warp 3 is busy with the buffered keys' dot products)
-      const float ksc = fp16_scale(mx, 127.0f);
-      uint32_t w = 0;
-#pragma unroll
-      for (int j = 0; j < CW; j++) {
-        const float cc = rq_exact(kr[j], ksc, 127.0f);
-        w |= (static_cast<uint32_t>(static_cast<int>(cc)) & 0xFFu) << (8 * j);
-        if (FOLD) Rf[(M - 1) * 160 + ((lane * CW + j) >> 4) * 20 + ((lane * CW + j) & 15)] = cc * ksc;
-      }
-      if (first) {
-        *reinterpret_cast<uint32_t*>(KBh + (long long)n0 * DK + lane * 4) = w;
-        if (lane == 0) KBSh[n0] = f2h(ksc);
-      }
+      mx = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(mx)));
+      round_key(kr, mx);
     } else {
       // the buffered keys' dot products with q and k: the key tile [M, 128] int8 is the A operand (rows = slots),
       // the B fragments are those of the state pass (the 8-bit layout: the key tile holds bytes)
@@ -378,9 +499,11 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? SQB_MMA_MINB_FOLD : (BITS == 4
 #pragma unroll
       for (int r = 0; r < 8; r++) bf8[r] = Bfw[(BITS == 8 ? 0 : 256) + r * 32 + lane];
       SQB_STAMP(2);
+      asm volatile("bar.sync 1, 64;" ::: "memory");           // warp 2 has armed the key tile's barrier
       const bool landed = mbar_wait(&bars[nst], 0, A.wait_ns);
       SQB_STAMP(15);
       if (lane == 0) misc[2] = landed ? 0.f : 1.f;          // "a copy never arrived" flag
+      const float ksl = ksv[lane];                          // scale of buffered key `lane`
       const float iq1 = fq.i1, iq2 = fq.i2, ik1 = fk.i1, ik2 = fk.i2;
       for (int sb = 0; sb < M; sb += 16) {
         int acc[4] = {MAGIC_I, MAGIC_I, MAGIC_I, MAGIC_I};
@@ -394,7 +517,7 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? SQB_MMA_MINB_FOLD : (BITS == 4
           mma_i8<false>(acc, m[0], m[1], m[2], m[3], bf8[2 * j], bf8[2 * j + 1]);
         }
         const int i8 = lane >> 2, t = lane & 3;
-        const float k0s = __shfl_sync(0xffffffffu, ksv, (sb + i8) & 31), k1s = __shfl_sync(0xffffffffu, ksv, (sb + i8 + 8) & 31);
+        const float k0s = __shfl_sync(0xffffffffu, ksl, (sb + i8) & 31), k1s = __shfl_sync(0xffffffffu, ksl, (sb + i8 + 8) & 31);
         float p[4] = {(__int_as_float(acc[0]) - 12582912.0f) * k0s, (__int_as_float(acc[1]) - 12582912.0f) * k0s,
                       (__int_as_float(acc[2]) - 12582912.0f) * k1s, (__int_as_float(acc[3]) - 12582912.0f) * k1s};
         float T = join_digits(p, t);          // t = 0: q, slot sb + i8; t = 1: q, slot sb + i8 + 8; t = 2, 3: k
@@ -406,17 +529,15 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? SQB_MMA_MINB_FOLD : (BITS == 4
         }
       }
     }
-  } else if (warp == 3) {
-    start_stage(1);
+  } else {
+    // warp 3
     load_v();
     float qr[CW], kr[CW];
     cvt4_raw(rq, A.dt_qk, qr);
     cvt4_raw(rk, A.dt_qk, kr);
     if constexpr (!VDEC) {
-      // round and append the key at slot n0; its rounded value is what the fold uses for slot M - 1.  The
-      // normalisation is redone here (same arithmetic as warp 0, so the same bits)
-      const int n0 = NPseq[h0] & (M - 1);
-      const bool FOLD = CANFOLD && n0 == M - 1;
+      // the key that goes into the buffer, rounded: its normalisation is redone here (the arithmetic of warp 0, so
+      // the same bits)
       float s1 = 0.f;
 #pragma unroll
       for (int j = 0; j < CW; j++) s1 += kr[j] * kr[j];
@@ -429,27 +550,12 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? SQB_MMA_MINB_FOLD : (BITS == 4
       float mx = 0.f;
 #pragma unroll
       for (int j = 0; j < CW; j++) mx = fmaxf(mx, fabsf(kr[j]));
-      mx = warp_max(mx);
-      const float ksc = fp16_scale(mx, 127.0f);
-      uint32_t w = 0;
-#pragma unroll
-      for (int j = 0; j < CW; j++) {
-        const float cc = rq_exact(kr[j], ksc, 127.0f);
-        w |= (static_cast<uint32_t>(static_cast<int>(cc)) & 0xFFu) << (8 * j);
-        if (FOLD) Rf[(M - 1) * 160 + ((lane * CW + j) >> 4) * 20 + ((lane * CW + j) & 15)] = cc * ksc;
-      }
-      if (first) {
-        *reinterpret_cast<uint32_t*>(KBh + (long long)n0 * DK + lane * 4) = w;
-        if (lane == 0) KBSh[n0] = f2h(ksc);
-      }
+      mx = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(mx)));
+      round_key(kr, mx);
     } else {
       // KDA: dot products of the buffered keys (times their per-channel decay ratios) with q and k, in fp32, from
       // this warp's own copy of the normalised vectors (same arithmetic as warp 0, so the same bits)
       constexpr int QD = DK / 4;
-      fetch_key_tile();
-      const int n0 = NPseq[h0] & (M - 1);
-      float ksv = 0.f;
-      if (lane < M) ksv = h2f(KBSh[lane]);
       float gnr[CW];
       float s0 = 0.f, s1 = 0.f;
 #pragma unroll
@@ -468,11 +574,14 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? SQB_MMA_MINB_FOLD : (BITS == 4
         wg[lane * CW + j] = gnr[j];
       }
       __syncwarp();
+      asm volatile("bar.sync 1, 64;" ::: "memory");           // warp 2 has armed the key tile's barrier
       const bool landed = mbar_wait(&bars[nst], 0, A.wait_ns);
       if (lane == 0) misc[2] = landed ? 0.f : 1.f;          // "a copy never arrived" flag
+      const int n0 = __float_as_int(misc[1]);
+      const float ksl = ksv[lane];
       for (int i0 = 0; i0 < M; i0 += 8) {
         const int i = i0 + (lane >> 2), part = lane & 3;
-        const float ks_i = __shfl_sync(0xffffffffu, ksv, i & 31);
+        const float ks_i = __shfl_sync(0xffffffffu, ksl, i & 31);
         float dq = 0.f, dk = 0.f;
         if (i < n0) {
 #pragma unroll
@@ -496,52 +605,6 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? SQB_MMA_MINB_FOLD : (BITS == 4
         dk += __shfl_xor_sync(0xffffffffu, dk, 1); dk += __shfl_xor_sync(0xffffffffu, dk, 2);
         if (part == 0 && i < M) dqk[i] = make_float2(dq, dk);
       }
-    }
-  } else {
-    // warp 1, per value head: gates and the scalars derived from them (one lane per head)
-    start_stage(2);
-    load_v();
-    if (lane < gqa) {
-      const int hi = lane, h = h0 + hi;
-      const float gcur = VDEC ? 0.f : GCseq[h];
-      float g4[4];
-      if (KIND == K_GDN) {
-        if (A.gate) {
-          g4[0] = cvt_raw(rg[0], A.dt_ab); g4[1] = cvt_raw(rg[1], A.dt_dtb); g4[2] = cvt_raw(rg[2], A.dt_alog); g4[3] = cvt_raw(rg[3], A.dt_ab);
-        } else {
-          g4[0] = cvt_raw(rg[0], A.dt_g); g4[1] = cvt_raw(rg[1], A.dt_g); g4[2] = g4[3] = 0.f;
-        }
-      } else if (KIND == K_M2) {
-        g4[0] = cvt_raw(rg[0], A.dt_g); g4[1] = A.dt_bias ? cvt_raw(rg[1], A.dt_dtb) : 0.f;
-        g4[2] = cvt_raw(rg[2], A.dt_alog); g4[3] = A.beta ? cvt_raw(rg[3], A.dt_beta) : 0.f;
-      } else {
-        g4[0] = cvt_raw(rg[0], A.dt_beta); g4[1] = g4[2] = g4[3] = 0.f;
-      }
-      float g = 0.f, bt = 0.f, Dv = 0.f;
-      if (KIND == K_GDN) {
-        if (A.gate) {
-          const float x = g4[0] + g4[1];
-          const float sp = x <= 20.0f ? logf(1.0f + expf(x)) : x;
-          g = -expf(g4[2]) * sp;
-          bt = __fdiv_rn(1.0f, 1.0f + expf(-g4[3]));
-        } else {
-          g = g4[0];
-          bt = g4[1];
-        }
-      } else if (KIND == K_M2) {
-        float dtv = g4[0];
-        if (A.dt_bias) dtv = dtv + g4[1];
-        if (A.dt_softplus) dtv = dtv <= 20.0f ? logf(1.0f + expf(dtv)) : dtv;
-        if (A.dt_clamp) dtv = fminf(fmaxf(dtv, A.dt_min), A.dt_max);
-        g = __fmul_rn(g4[2], dtv);
-        bt = dtv;
-        Dv = g4[3];
-      } else {
-        bt = g4[0];
-      }
-      float* o = hd + hi * HD_W;
-      o[0] = g; o[1] = bt; o[2] = gcur; o[3] = VDEC ? 1.0f : expf(gcur); o[4] = VDEC ? 1.0f : expf(g);
-      o[5] = gcur + g; o[6] = Dv;
     }
   }
   SQB_STAMP(3);
@@ -568,6 +631,23 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? SQB_MMA_MINB_FOLD : (BITS == 4
   const float kq = misc[0];
   const int n0 = __float_as_int(misc[1]);                       // live buffer entries of this slot
   const bool FOLD = CANFOLD && n0 == M - 1;                     // this token fills the buffer: fold after the read-out
+  if (warp == KEY_WARP) {
+    // the key goes into the buffer at slot n0 (one CTA per key head stores it); its rounded value is what the fold
+    // uses for slot M - 1
+    if (first) {
+      *reinterpret_cast<uint32_t*>(KBh + (long long)n0 * DK + lane * 4) = kword;
+      if (lane == 0) KBSh[n0] = f2h(kscale);
+    }
+    if (FOLD) {
+      if (TFOLD) {                            // the tensor-pipe fold takes the codes and the scale
+        *reinterpret_cast<uint32_t*>(smraw + P.kcur + lane * 4) = kword;
+        if (lane == 0) misc[8] = kscale;
+      } else {
+#pragma unroll
+        for (int j = 0; j < CW; j++) Rf[(M - 1) * 160 + ((lane * CW + j) >> 4) * 20 + ((lane * CW + j) & 15)] = kdeq[j];
+      }
+    }
+  }
   const float iq1 = misc[4], iq2 = misc[5], ik1 = misc[6], ik2 = misc[7];
   const float2 dq01 = dqk[0];
   bool lost = false;
@@ -647,16 +727,50 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? SQB_MMA_MINB_FOLD : (BITS == 4
 
     if (CANFOLD && FOLD) {
       // append and fold the heads of this stage from the staged tile, then hand the stage back
-      float* Lf = fsm + P.L;
-      float* fdec = fsm + P.fdec;
       float* ksf = fsm + P.ksf;
-      const int LM = fold_lm(M);
       if (__syncthreads_or(lost)) { bail(); return; }         // (a barrier: u and its maxima are complete)
       const float udq = append_row(sh);
       if (VDEC) {
         GBseq[((long long)h * M + n0) * DK + tid] = ga[tid];
         GCseq[(long long)h * DK + tid] = 0.f;
       }
+      if (TFMT && TFOLD) {
+        if constexpr (TFMT) {
+          // ---- the fold on the tensor pipe (fold_mma.cuh) ----
+          uint32_t* KBf = reinterpret_cast<uint32_t*>(smraw + P.kbf);
+          float* tab = fsm + P.tab;
+          us[hi * DV + rv] = udq;                               // this token's values as stored
+          if (sh == 0) {
+            mbar_wait(&bars[nst], 0, A.wait_ns);                // the key tile has landed (warp 0 saw it before)
+            if (tid < 7) ksf[tid] = h2f(KBSh[tid]);
+            if (tid == 7) ksf[7] = misc[8];
+            build_key_frags<BITS>(KBf, reinterpret_cast<const int8_t*>(kbt), reinterpret_cast<const int8_t*>(smraw + P.kcur), tid);
+          }
+          if (tid < HPS * 8) {                                  // per head of the stage: decays and value scales of the slots
+            const int hq = tid >> 3, i = tid & 7, hf = sh * HPS + hq;
+            const float gnew = hd[hf * HD_W + 5];
+            tab[hq * 20 + i] = i == 7 ? 1.0f : expf(gnew - fsm[P.gbs + hf * 8 + i]);
+            tab[hq * 20 + 8 + i] = dcu[hf * 8 + i].y;
+            if (i == 0) tab[hq * 20 + 16] = expf(gnew);
+          }
+          __syncthreads();
+          fold_stage_mma<BITS, UPG, DV>(smem_u32(st), reinterpret_cast<unsigned short*>(st + P.sc_off),
+                                        reinterpret_cast<const int8_t*>(st + P.ub_off), us + sh * HPS * DV, tab, ksf, KBf, warp, lane);
+          __syncthreads();
+          if (warp == 0) {
+            // the stage goes back to the slot: eight pieces of codes and the scales, as bulk copies
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            const long long row0 = (long long)h0 * DV + sh * 128;
+            if (lane < 8) bulk_s2g(Sseq + (row0 + lane * 16) * ROWB, st + lane * PITCH, 16 * ROWB);
+            else if (lane == 8) bulk_s2g(SCseq + row0 * NG * 2, st + P.sc_off, 128 * NG * 2);
+            bulk_commit();
+            if (sh + nst < NSH || sh + 1 == NSH) bulk_wait_read();   // before the stage is refilled, and before leaving
+          }
+        }
+      } else {
+      float* Lf = fsm + P.L;
+      float* fdec = fsm + P.fdec;
+      const int LM = fold_lm(M);
       if (sh == 0) {
         // R: the keys of slots 0 .. M - 2 (KDA: times their decay ratio); row M - 1 was written by the key append
         if (tid < M) ksf[tid] = h2f(KBSh[tid]);
@@ -693,6 +807,7 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? SQB_MMA_MINB_FOLD : (BITS == 4
                                              alphan, DV, G, M, nullptr, Sseq + (long long)hg * DV * ROWB,
                                              reinterpret_cast<unsigned short*>(SCseq) + (long long)hg * DV * NG, warp, lane, tid,
                                              [] { __syncthreads(); return true; });
+      }
       }
       if (sh + nst < NSH) {
         __syncthreads();

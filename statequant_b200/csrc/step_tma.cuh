@@ -54,15 +54,17 @@ __device__ __forceinline__ unsigned long long global_ns() {
   return t;
 }
 constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;     // a wait gives up after one second
-// Bounded wait: gives up after WAIT_LIMIT_NS (try_wait itself may block for a hardware-defined time, so the bound is
-// on the clock, not on the iteration count), records nothing itself and lets the caller bail out.
+// Bounded wait: gives up after about limit_ns (try_wait itself may block for a hardware-defined time, so the bound is on
+// a clock, not on the iteration count: the SM's cycle counter, taken as 2 cycles per nanosecond, which is cheap to read),
+// records nothing itself and lets the caller bail out.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns = WAIT_LIMIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_ns();
+  const long long t0 = clock64();
+  const long long limit = static_cast<long long>(limit_ns) * 2;
   for (int it = 0;; it++) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (it > 64) __nanosleep(100);
-    if ((it & 15) == 15 && global_ns() - t0 > limit_ns) return false;
+    if (it > 256) __nanosleep(64);
+    if ((it & 15) == 15 && clock64() - t0 > limit) return false;
   }
 }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
