@@ -383,6 +383,7 @@ def cpu_baseline(batch, steps, warmup, preset='int8k'):
     q, k, v, a, b = make_inputs(batch, gen, 'cpu')
     A_log, dtb = torch.randn(HV, generator=gen) * 0.3, torch.randn(HV, generator=gen)
     out = torch.empty(batch, HV, DV, dtype=torch.bfloat16)
+    oracle.set_num_threads(os.cpu_count() or 1)        # all host cores, whatever OMP_NUM_THREADS a launcher exported
     for _ in range(warmup):
         oracle.gdn_step(lay, V, idx, q, k, v, out, DK ** -0.5, gate=(a, b, A_log, dtb))
     t0 = time.perf_counter()
@@ -392,16 +393,69 @@ def cpu_baseline(batch, steps, warmup, preset='int8k'):
     return steps / dt, oracle.num_threads(), dt
 
 
-# DRAM bytes (read + write) per layer-step from ncu captures at batch 256 (profiles/): the step kernel of a non-fold
-# step, and on every 8th step the fold kernel on top; traffic grows in proportion to the batch.
-NCU_TRAFFIC_B256 = {'int8k': (160.0e6 + 5.2e6, 155.8e6 + 84.3e6)}
-
-
 def ncu_traffic(preset, batch):
-    if preset not in NCU_TRAFFIC_B256:
+    """DRAM bytes (read + write) per layer-step from the ncu captures summarised under profiles/ (traffic.json, written
+    next to the summaries: per preset the bytes of a launch that does not fold and of one in which every head folds,
+    at batch 256); averaged over the fold period and scaled to the batch (traffic grows in proportion to it)."""
+    try:
+        t = json.load(open(os.path.join(ROOT, 'profiles', 'traffic.json')))[preset]
+        return (t['step_bytes'] * (M - 1) + t['fold_step_bytes']) / M * batch / t.get('batch', 256)
+    except Exception:
         return None
-    step, fold = NCU_TRAFFIC_B256[preset]
-    return (step + fold / M) * batch / 256
+
+
+def run_config4(args, rank, world, device, barrier, max_over_ranks, table=8192, batches=(64, 256, 1024, 4096), layers=4):
+    """The slot-scaling sweep: one GDN layer stack on the GGA mixed-width state (per-layer widths 4,6,4,4,6,... with the
+    pure-write window), a state table of `table` slots, and ONE global batch of 64 / 256 / 1024 / 4096 rows drawn as
+    the prefix of a seeded random permutation of slots 1 .. table - 1 (slot 0 is padding).  On N GPUs the table is
+    sharded (slot s lives on rank (s - 1) mod N, statequant_b200/sharding.py), every rank serves the rows whose
+    slots it owns, and the time of a layer-step is the slowest rank's: strong scaling, with the imbalance of a
+    random batch across the shards reported next to it.  No collective on the data path."""
+    global LAYERS
+    from statequant_b200 import sharding
+    from statequant_b200.kernels import GGAPacked
+    from statequant_b200.kernels.gga import StepPlan
+    gen = torch.Generator().manual_seed(99)                        # the same on every rank
+    widths = [4, 6, 4, 4, 6, 4]
+    plan = StepPlan({l: (torch.full((HV,), widths[l % 6]), torch.rand(HV, DK, generator=gen) + 0.5) for l in range(layers)},
+                    32, name='config4')
+    lay = GGAPacked(plan, HV, HK, DK, DV, pw=True, m=M)
+    nloc = sharding.local_slots(table, rank, world)
+    blobs = [lay.alloc(nloc, device) for _ in range(layers)]
+    views = [lay.views(b) for b in blobs]
+    perm = torch.randperm(table - 1, generator=gen) + 1
+    A_log, dtb = (torch.randn(HV, generator=gen) * 0.3).to(device), torch.randn(HV, generator=gen).to(device)
+    out = {'table_slots': table, 'layers': layers, 'slot_bytes': lay.nbytes, 'scaling': 'strong', 'batches': {}}
+    for B in batches:
+        gidx = perm[:B].to(torch.int32)
+        rows = sharding.rows_of(gidx, rank, world)
+        lidx = sharding.to_local(gidx, rank, world)[rows].contiguous().to(device)
+        nb = int(rows.numel())
+        ins = [make_inputs(max(nb, 1), gen, device) for _ in range(layers)]
+        outs = [torch.empty(max(nb, 1), HV, DV, dtype=torch.bfloat16, device=device) for _ in range(layers)]
+
+        def step():
+            if nb:
+                for l in range(layers):
+                    q, k, v, a, b = ins[l]
+                    lay.step(views[l], lidx, q, k, v, outs[l], DK ** -0.5, gate=(a, b, A_log, dtb), layer=l)
+        for _ in range(3):
+            step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        nrep = 4
+        e0.record()
+        for _ in range(nrep):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = max_over_ranks(e0.elapsed_time(e1))
+        most = max_over_ranks(float(nb))
+        out['batches'][str(B)] = {'us_per_layer_step': ms * 1e3 / (nrep * layers), 'rows_on_busiest_rank': int(most),
+                                  'imbalance': most * world / B}
+    del blobs, views
+    torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -439,8 +493,8 @@ def main():
     if args.impl == 'reference':
         if rank != 0:
             return
-        import __graft_entry__ as ge
-        ge.build()
+        from oracle import oracle
+        oracle.build()                                        # the CPU oracle only: this arm loads no CUDA library
         steps = max(1, args.steps)
         val, cores, dt = cpu_baseline(args.batch, steps, max(1, min(args.warmup, 8)), args.preset)
         sample = f'one layer of the stack, batch {args.batch}, {steps} layer-steps, {dt:.1f} s wall'
@@ -483,40 +537,50 @@ def main():
         config['workload'] = (f'{WORKLOAD_TEXT[args.workload]}, state preset {args.preset}, batch {args.batch} slots per '
                               f'GPU, bf16 activations')
     presets = [args.preset] + ([] if args.no_variants else [p for p in PRESETS if p != args.preset])
+    # The state is folded every M = 8 tokens and a fold step costs several plain steps, so only whole fold periods are
+    # timed: the requested step count is rounded up to a multiple of 8.
+    steps_timed = -(-args.steps // M) * M
+    config['fold_period_steps'] = M
+    config['steps_timed'] = steps_timed
     clocks = None
     launches = 0
     e2e = None
-    for pi, preset in enumerate(presets):
-        stack = WORKLOADS[args.workload](preset, args.batch, device, seed=1234 + rank)
+
+    def time_stack(stack, steps, sample_clocks=False):
         stack.prewarm(args.prewarm, torch.Generator().manual_seed(4321 + rank))
         if not args.eager:
             stack.capture()
         stack.timed(max(3, args.warmup))
         barrier()
-        sampler = ClockSampler(local) if (pi == 0 and rank == 0) else None
+        sampler = ClockSampler(local) if (sample_clocks and rank == 0) else None
         t0 = time.time()
         l0 = _cabi.launch_count()
-        ms = stack.timed(args.steps)
+        ms = stack.timed(steps)
         barrier()
         t1 = time.time()
         ms = max_over_ranks(ms)
-        if sampler is not None:
-            clocks = sampler.stop(t0, t1)
+        clk = sampler.stop(t0, t1) if sampler is not None else None
         total, state = stack.bytes_per_slot()
-        lsteps = args.steps * LAYERS
+        lsteps = steps * LAYERS
         per_launch_s = ms * 1e-3 / lsteps
-        results[preset] = {'layer_steps_per_s': world * lsteps / (ms * 1e-3), 'us_per_layer_step': per_launch_s * 1e6,
-                           'ms_per_step': ms / args.steps,
-                           'total_gbs_per_gpu': args.batch * total / per_launch_s / 1e9,
-                           'state_gbs_per_gpu': args.batch * state / per_launch_s / 1e9,
-                           'bytes_per_slot_layer_step': total}
+        res = {'layer_steps_per_s': world * lsteps / (ms * 1e-3), 'us_per_layer_step': per_launch_s * 1e6,
+               'ms_per_step': ms / steps, 'layers': LAYERS, 'steps_timed': steps,
+               'total_gbs_per_gpu': args.batch * total / per_launch_s / 1e9,
+               'state_gbs_per_gpu': args.batch * state / per_launch_s / 1e9,
+               'bytes_per_slot_layer_step': total}
+        nl = (stack.launches_per_step * steps if stack.launches_per_step is not None else _cabi.launch_count() - l0)
+        return res, clk, nl
+
+    for pi, preset in enumerate(presets):
+        stack = WORKLOADS[args.workload](preset, args.batch, device, seed=1234 + rank)
+        res, clk, nl = time_stack(stack, steps_timed, sample_clocks=pi == 0)
+        results[preset] = res
         if pi == 0:
-            launches = (stack.launches_per_step * args.steps if stack.launches_per_step is not None
-                        else _cabi.launch_count() - l0)
+            clocks, launches = clk, nl
         if pi == 0 and not args.no_e2e and not args.eager:
             barrier()
-            ems, h2d, d2h = run_e2e(stack, max(1, min(args.steps, 32)), 3)
-            esteps = max(1, min(args.steps, 32))
+            esteps = max(M, min(steps_timed, 32))
+            ems, h2d, d2h = run_e2e(stack, esteps, 3)
             ems = max_over_ranks(ems)
             e2e = {'value': world * esteps * LAYERS / (ems * 1e-3), 'unit': UNIT, 'h2d_bytes_per_step': h2d,
                    'd2h_bytes_per_step': d2h, 'steps': esteps,
@@ -525,6 +589,23 @@ def main():
         del stack
         torch.cuda.empty_cache()
 
+    if args.workload == 'gdn' and not args.no_variants:
+        # the other kernel families on their own shapes (8-layer stacks: far above L2), and the slot-scaling sweep
+        saved = LAYERS
+        LAYERS = min(8, saved)
+        for name, wl, preset in (('mamba2_int8k', 'mamba2', 'int8k'), ('kda_pace4', 'kda', 'pace4'), ('gga_pw', 'gga', 'pace4')):
+            stack = WORKLOADS[wl](preset, args.batch, device, seed=1234 + rank)
+            keep = args.prewarm
+            args.prewarm = min(args.prewarm, 64)
+            res, _, _ = time_stack(stack, max(M, min(steps_timed, 32)))
+            args.prewarm = keep
+            res['workload'] = WORKLOAD_TEXT[wl]
+            results[name] = res
+            del stack
+            torch.cuda.empty_cache()
+        LAYERS = saved
+        results['config4_gga_slot_scaling'] = run_config4(args, rank, world, device, barrier, max_over_ranks)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -532,7 +613,7 @@ def main():
     head = results[args.preset]
     peak, which = measured_peak_gbs()
     line = {
-        'metric': METRIC if args.workload == 'gdn' else f'decode layer-steps/s ({args.workload} stack)', 'value': head['layer_steps_per_s'], 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
+        'metric': METRIC if args.workload == 'gdn' else f'decode layer-steps/s ({args.workload} stack)', 'value': head['layer_steps_per_s'], 'unit': UNIT, 'n_gpus': world, 'steps': args.steps, 'steps_timed': steps_timed,
         'warmup': max(3, args.warmup), 'ms_per_step': head['ms_per_step'], 'higher_is_better': True, 'scaling': 'weak',
         'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic', 'config': config,
         'us_per_layer_step': head['us_per_layer_step'],
@@ -541,14 +622,14 @@ def main():
         'roofline': {'bound': 'hbm', 'achieved': head['total_gbs_per_gpu'], 'peak': peak, 'unit': 'GB/s',
                      'frac': head['total_gbs_per_gpu'] / peak, 'traffic': ncu_traffic(args.preset, args.batch) if args.workload == 'gdn' else None,
                      'peak_source': which,
-                     'kernel': 'step_tma_kernel<GDN> + fold_kernel: the two launches of one layer-step (one C-ABI call), '
-                               'averaged over the fold period of 8 steps',
+                     'kernel': 'step_mma_kernel<GDN>: the one launch of a layer-step (one C-ABI call; on a slot\'s 8th token it '
+                               'also folds), averaged over whole fold periods of 8 steps',
                      'algorithmic_bytes_per_launch': args.batch * head['bytes_per_slot_layer_step']},
         'variants': results, 'clocks': clocks, 'e2e': e2e, 'gpu_launches': launches,
     }
     if world == 1 and not args.no_cpu:
-        import __graft_entry__ as ge
-        ge.build()
+        from oracle import oracle
+        oracle.build()
         v, cores, dt = cpu_baseline(args.batch, 16, 4, args.preset)
         line['cpu_baseline'] = {'value': v, 'unit': UNIT, 'cores': cores, 'kind': 'port',
                                 'sample': f'one layer of the stack, batch {args.batch}, 16 layer-steps after 4 warm-up, {dt:.1f} s wall'}

@@ -54,6 +54,11 @@ def num_threads():
     return int(lib().sqo_num_threads())
 
 
+def set_num_threads(n):
+    """Threads of the oracle's parallel loops from now on (overrides OMP_NUM_THREADS)."""
+    lib().sqo_set_num_threads(int(n))
+
+
 def pack_vk(x, bits, axis_k, group):
     """fp32 [n, dv, dk] -> (codes, scales) with the oracle's packer."""
     x = x.float().contiguous()

@@ -603,6 +603,17 @@ int sqo_slot_write(const sqb_state_t *st, int kind, const int64_t *slots, int64_
   return 0;
 }
 
+/* threads the oracle's parallel loops use from now on (the benchmark's CPU legs set this to the host's core count
+ * themselves: launchers such as torchrun export OMP_NUM_THREADS=1) */
+void sqo_set_num_threads(int n) {
+#ifdef _OPENMP
+  extern void omp_set_num_threads(int);
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int sqo_num_threads(void) {
 #ifdef _OPENMP
   extern int omp_get_max_threads(void);

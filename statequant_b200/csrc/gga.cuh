@@ -391,7 +391,7 @@ __host__ __device__ inline GgaSmem gga_smem(int dk, int dv, int M, int group) {
   s.rs = o; o += dk * (dv / group > 0 ? dv / group : 1);
   s.rrs = o; o += dk;
   s.cs = o; o += dv; s.ps = o; o += 2 * GNT; s.wsm = o; o += dk;
-  s.Pw = o; o += M * dk; s.Vw = o; o += M * dv; s.r0 = o; o += dk; s.coef = o; o += 32; s.red = o; o += 32;
+  s.Pw = o; o += M * dk; s.Vw = o; o += M * dv; s.r0 = o; o += dk; s.coef = o; o += (M > 32 ? M : 32); s.red = o; o += 32;
   s.total = o;
   return s;
 }
@@ -582,6 +582,7 @@ __global__ void __launch_bounds__(GNT) gga_store_kernel(const __grid_constant__ 
   const int dk = A.DK, dv = A.DV, HV = A.HV;
   const int ph = blockIdx.x, p = ph / HV, h = ph - p * HV;
   const long long seq = A.idx[p];
+  if (seq <= 0) return;                      // a padding row (0, or an engine's -1): nothing is written
   const GgaSmem P = gga_smem(dk, dv, A.M, A.group);
   float* T = gsm + P.T;
   const float* x = A.X + (long long)ph * dk * dv;
@@ -600,11 +601,15 @@ __global__ void __launch_bounds__(GNT) gga_load_kernel(const __grid_constant__ G
   const int dk = A.DK, dv = A.DV, HV = A.HV;
   const int ph = blockIdx.x, p = ph / HV, h = ph - p * HV;
   const long long seq = A.idx[p];
+  float* y = A.Y + (long long)ph * dk * dv;
+  if (seq <= 0) {                            // a padding row: its output is zeroed, no slot is read
+    for (int e = tid; e < dk * dv; e += GNT) y[e] = 0.f;
+    return;
+  }
   const GgaSmem P = gga_smem(dk, dv, A.M, A.group);
   float* T = gsm + P.T;
   gga_decode_head(A.blob + seq * A.stride + A.offs[h], A.bits[h], dk, dv, A.group, T, P.LD);
   __syncthreads();
-  float* y = A.Y + (long long)ph * dk * dv;
   for (int e = tid; e < dk * dv; e += GNT) y[e] = T[(e / dv) * P.LD + (e % dv)];
 }
 

@@ -25,12 +25,14 @@ inline bool mma_shape_ok(const StepArgs& a, int bits, bool axk, bool kda) {
 }
 
 // stages resident per CTA and the plan; false if the CTA does not fit
-// value heads a CTA takes: a whole key head's, unless told otherwise (a.hpc set by the caller: a divisor of the key
-// head's value heads that fills whole stages)
+// value heads a CTA takes (a.hpc set by the caller, if it is a divisor of the key head's value heads that fills whole
+// stages; else the default below)
 inline int mma_hpc(const StepArgs& a) {
   const int gqa = a.HV / a.HK, hps = 128 / a.DV;
   if (a.hpc > 0 && gqa % a.hpc == 0 && a.hpc % hps == 0) return a.hpc;
-  return gqa;
+  // two stages per CTA where the key head has them (Qwen GDN: both value heads of the key head; Nemotron-H Mamba2: 4 of
+  // the group's 16 heads, measured 113 us per layer-step against 158 us with all 16 and 133 us with 2)
+  return gqa % (2 * hps) == 0 ? 2 * hps : gqa;
 }
 
 template <int KIND>

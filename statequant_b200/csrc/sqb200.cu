@@ -271,6 +271,7 @@ int sqb_slot_read(const sqb_state_t* st, int kind, const int32_t* idx, int32_t r
   sqb::StepArgs a;
   if (int rc = slot_io_args(st, kind, idx, rows, a)) return rc;
   if (!out) return fail(SQB_EINVAL, "out is NULL");
+  if (reinterpret_cast<uintptr_t>(out) & 15) return fail(SQB_EINVAL, "out must be 16-byte aligned (it is written in 16-byte pieces)");
   if (rows == 0) return 0;
   return sub_rc(sqb::launch_read(kind, a, st->bits, st->axis_k, out, static_cast<cudaStream_t>(stream)));
 }
@@ -279,6 +280,7 @@ int sqb_slot_write(const sqb_state_t* st, int kind, const int32_t* idx, int32_t 
   sqb::StepArgs a;
   if (int rc = slot_io_args(st, kind, idx, rows, a)) return rc;
   if (!S) return fail(SQB_EINVAL, "S is NULL");
+  if (reinterpret_cast<uintptr_t>(S) & 15) return fail(SQB_EINVAL, "S must be 16-byte aligned (it is read in 16-byte pieces)");
   if (rows == 0) return 0;
   return sub_rc(sqb::launch_write(kind, a, st->bits, st->axis_k, S, static_cast<cudaStream_t>(stream)));
 }
@@ -384,12 +386,14 @@ void fill_gga(sqb::GgaArgs& a, const sqb_gga_layout_t* L) {
   a.HV = L->hv; a.HK = L->hk; a.DK = L->dk; a.DV = L->dv; a.M = L->pw ? L->m : 1; a.pw = L->pw; a.group = L->group;
 }
 
-template <typename K>
+// TAG: one instantiation (and so one cached shared-memory limit per device) per kernel
+template <int TAG, typename K>
 int launch_gga(K kern, const sqb::GgaArgs& a, long long ctas, cudaStream_t stream) {
   const sqb::GgaSmem plan = sqb::gga_smem(a.DK, a.DV, a.M, a.group);
   const int smem = plan.total * static_cast<int>(sizeof(float));
   if (smem > 200 * 1024) return fail(SQB_EINVAL, "GGA tile needs %d bytes of shared memory", smem);
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static sqb::SmemLimit limit;
+  cudaError_t e = limit.ensure(kern, smem);
   if (e != cudaSuccess) return fail(SQB_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   if (ctas <= 0) return 0;
   kern<<<static_cast<unsigned>(ctas), sqb::GNT, smem, stream>>>(a);
@@ -421,9 +425,9 @@ int sqb_gga_step(const sqb_gga_layout_t* L, const sqb_gdn_inputs_t* in, void* st
   a.dt_dtb = in->dtb_dtype; a.dt_out = in->out_dtype; a.scale = in->scale;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (L->dk == 128 && L->dv == 128) {
-    if (int rc = launch_gga(sqb::gga_step_kernel<128, 128>, a, static_cast<long long>(in->rows) * L->hv, st)) return rc;
+    if (int rc = launch_gga<0>(sqb::gga_step_kernel<128, 128>, a, static_cast<long long>(in->rows) * L->hv, st)) return rc;
   } else {
-    if (int rc = launch_gga(sqb::gga_step_kernel<0, 0>, a, static_cast<long long>(in->rows) * L->hv, st)) return rc;
+    if (int rc = launch_gga<1>(sqb::gga_step_kernel<0, 0>, a, static_cast<long long>(in->rows) * L->hv, st)) return rc;
   }
   if (L->pw) {
     sqb::gga_advance_kernel<<<(in->rows + 127) / 128, 128, 0, st>>>(a.blob, a.stride, a.idx, in->rows, L->m);
@@ -441,7 +445,7 @@ int sqb_gga_store(const sqb_gga_layout_t* L, const int32_t* idx, int64_t P, cons
   sqb::GgaArgs a;
   fill_gga(a, L);
   a.idx = idx; a.X = X; a.P = P;
-  return launch_gga(sqb::gga_store_kernel, a, P * L->hv, static_cast<cudaStream_t>(stream));
+  return launch_gga<2>(sqb::gga_store_kernel, a, P * L->hv, static_cast<cudaStream_t>(stream));
 }
 
 int sqb_gga_load(const sqb_gga_layout_t* L, const int32_t* idx, int64_t P, float* Y, void* stream) {
@@ -451,7 +455,7 @@ int sqb_gga_load(const sqb_gga_layout_t* L, const int32_t* idx, int64_t P, float
   sqb::GgaArgs a;
   fill_gga(a, L);
   a.idx = idx; a.Y = Y; a.P = P;
-  return launch_gga(sqb::gga_load_kernel, a, P * L->hv, static_cast<cudaStream_t>(stream));
+  return launch_gga<3>(sqb::gga_load_kernel, a, P * L->hv, static_cast<cudaStream_t>(stream));
 }
 
 int sqb_stepquant_fit(const float* x, float* y, const int32_t* bits, const float* w, int64_t B, int32_t H, int32_t dk,
@@ -463,7 +467,7 @@ int sqb_stepquant_fit(const float* x, float* y, const int32_t* bits, const float
   sqb::GgaArgs a;
   memset(&a, 0, sizeof a);
   a.bits = bits; a.w = w; a.HV = H; a.HK = H; a.DK = dk; a.DV = dv; a.M = 1; a.group = group; a.X = x; a.Y = y;
-  return launch_gga(sqb::stepquant_fit_kernel, a, B * H, static_cast<cudaStream_t>(stream));
+  return launch_gga<4>(sqb::stepquant_fit_kernel, a, B * H, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -87,6 +87,8 @@ class GGAPacked:
         self.QSZ = m * (dk + dv + 8)
         self.nbytes = self.QOFF + (hv * self.QSZ if pw else 0)
         self._dev = {}
+        if torch.cuda.is_available():       # stage the plans now: a copy inside a CUDA-graph capture would fail
+            self.prepare(torch.device('cuda', torch.cuda.current_device()))
 
     def __repr__(self):
         return (f'GGAPacked({self.method.name}{"+PW-S%d" % self.m if self.pw else ""}, hv={self.HV}, hk={self.HK}, '

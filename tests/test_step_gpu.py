@@ -23,9 +23,10 @@ def kernel_path(request):
     not take a shape falls through to the next one."""
     from statequant_b200 import _cabi
     _cabi.set_option('kernel_path', {'generic': 1, 'staged': 2, 'mma': 3, 'fused': 4}[request.param])
+    base = _cabi.device_status()
     yield request.param
     _cabi.set_option('kernel_path', 0)
-    assert _cabi.device_status() == 0, 'a bounded wait ran out on the device'
+    assert _cabi.device_status() == base, 'a bounded wait ran out on the device'
 
 
 @pytest.mark.parametrize('name', list(CASES))
@@ -572,3 +573,140 @@ def test_extreme_read_out_vectors(name, kernel_path):
     assert st['worst'] < 2e-5, st
     assert st['buf'] <= max(1, 1e-4 * st['nbuf']), st
     assert st['codes'] <= max(1, 1e-4 * st['ncodes']), st
+
+
+@pytest.mark.parametrize('preset,fmt', [('int8k', (8, 'k', 32)), ('int4v', (4, 'v', 32))])
+def test_full_batch_properties_gdn_presets(preset, fmt):
+    """The benchmark's headline preset (int8k) and its int4v variant at the benchmark's shapes (32 value heads, 16 key
+    heads, d 128, batch 256, bf16 activations, in-kernel gate): determinism, padding rows, a sample of rows against the
+    oracle from their pre-step bytes, across one fold period."""
+    hv, hk, D = 32, 16, 128
+    lay = SlotLayout(sq.Quantizer(*fmt), hv, hk, D, D, m=8)
+    g1 = torch.Generator().manual_seed(17)
+    A_log, dtb = torch.randn(hv, generator=g1) * 0.3, torch.randn(hv, generator=g1)
+    A_logd, dtbd = A_log.to(DEV), dtb.to(DEV)
+
+    def make(B, g):
+        f = lambda *s: torch.randn(*s, generator=g)                                      # noqa: E731
+        return [f(B, hk, D).bfloat16(), f(B, hk, D).bfloat16(), f(B, hv, D).bfloat16(), (f(B, hv) + 2.0).bfloat16(),
+                f(B, hv).bfloat16()]
+
+    _full_batch(lay, 9, make,
+                lambda V, i, x, o: lay.step(V, i, x[0], x[1], x[2], o, D ** -0.5, gate=(x[3], x[4], A_logd, dtbd)),
+                lambda V, i, x, o: oracle.gdn_step(lay, V, i, x[0], x[1], x[2], o, D ** -0.5, gate=(x[3], x[4], A_log, dtb)),
+                sample_n=3, hv=hv, dv=D)
+
+
+def _hand_built_gdn_inputs(idx, q, k, v, out, scale, g, beta):
+    """``sqb_gdn_inputs_t`` filled in by the test itself, field by field from the tensors' own pointers and strides
+    (not by the package's marshalling code), for the oracle side of the strided-input check."""
+    from statequant_b200 import _cabi
+    code = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+    a = _cabi.GdnInputs()
+    a.idx = idx.data_ptr()
+    a.q, a.sq = q.data_ptr(), q.stride(0) * q.element_size()
+    a.k, a.sk = k.data_ptr(), k.stride(0) * k.element_size()
+    a.v, a.sv = v.data_ptr(), v.stride(0) * v.element_size()
+    a.g, a.sg = g.data_ptr(), g.stride(0) * g.element_size()
+    a.beta, a.sbeta = beta.data_ptr(), beta.stride(0) * beta.element_size()
+    a.out, a.so = out.data_ptr(), out.stride(0) * out.element_size()
+    a.scale, a.rows, a.qk_per_key_head, a.gate = float(scale), out.shape[0], 1, 0
+    a.qk_dtype, a.v_dtype, a.gb_dtype, a.out_dtype = code[q.dtype], code[v.dtype], code[g.dtype], code[out.dtype]
+    return a
+
+
+@pytest.mark.parametrize('name', ['gdn_pace4_qwen', 'gdn_int4k32_m8_b8'])
+def test_strided_inputs_replay_reference_golden(name, kernel_path):
+    """vLLM-style inputs: q, k, v are column slices of ONE [rows, 2 hk dk + hv dv] tensor (the conv output), g and beta
+    column slices of one [rows, 2 hv] tensor, with padding rows in between (reference: tests/test_slots.py:174-207,
+    integrations/vllm_plugin.py:395-397).  The CUDA step on them replays the reference's golden record; the oracle is
+    stepped on the same strided host tensors through an argument struct the test fills in itself."""
+    import ctypes as C
+    from harness import load_golden
+    c = CASES[name]
+    G = load_golden(name)
+    inp = make_inputs(c)
+    lay = layout_of(c)
+    B, hv, hk, dk, dv, m, T = c['B'], c['hv'], c['hk'], c['dk'], c['dv'], c['m'], c['T']
+    rows = B + 2                                            # a padding row before and after
+    blob_h = torch.zeros(B + 2, lay.nbytes, dtype=torch.uint8)
+    sl = torch.arange(1, B + 1)
+    lay.write(lay.views(blob_h), sl, inp['S0'].view(B, hv, dv, dk))
+    blob_d = blob_h.to(DEV)
+    Vh, Vd = lay.views(blob_h), lay.views(blob_d)
+    idx = torch.tensor([0] + list(range(1, B + 1)) + [-1], dtype=torch.int32)
+    worst = 0.
+    for t in range(T):
+        mixed = torch.zeros(rows, 2 * hk * dk + hv * dv)
+        mixed[1:B + 1, :hk * dk] = inp['q'][t].reshape(B, -1)
+        mixed[1:B + 1, hk * dk:2 * hk * dk] = inp['k'][t].reshape(B, -1)
+        mixed[1:B + 1, 2 * hk * dk:] = inp['v'][t].reshape(B, -1)
+        gb = torch.zeros(rows, 2 * hv)
+        gb[1:B + 1, :hv], gb[1:B + 1, hv:] = inp['g'][t], inp['beta'][t]
+        outs = []
+        for dev, V in ((DEV, Vd), ('cpu', Vh)):
+            mx, gx = mixed.to(dev), gb.to(dev)
+            q = mx[:, :hk * dk].unflatten(-1, (hk, dk))
+            k = mx[:, hk * dk:2 * hk * dk].unflatten(-1, (hk, dk))
+            v = mx[:, 2 * hk * dk:].unflatten(-1, (hv, dv))
+            g, beta = gx[:, :hv], gx[:, hv:]
+            assert not q.is_contiguous() and not g.is_contiguous()
+            out = torch.full((rows, hv, dv), 7., device=dev)
+            if dev == 'cpu':
+                a = _hand_built_gdn_inputs(idx, q, k, v, out, dk ** -0.5, g, beta)
+                assert oracle.lib().sqo_gdn_step(C.byref(lay._struct(V)), C.byref(a)) == 0
+            else:
+                lay.step(V, idx.to(dev), q, k, v, out, dk ** -0.5, g=g, beta=beta)
+            outs.append(out.cpu())
+        want = torch.from_numpy(G['o'][t]).view(B, hv, dv)
+        for o in outs:
+            assert torch.equal(o[0], torch.zeros(hv, dv)) and torch.equal(o[-1], torch.zeros(hv, dv))
+            worst = max(worst, ((o[1:B + 1] - want).abs().max() / want.abs().max()).item())
+        d = field_diff(lay, blob_d.cpu(), blob_h, sl.tolist())
+        assert d['NPTR'] == 0 and d['GB'] == 0 and d['S'] + d['KB'] + d['UB'] <= 2, (t, d)
+        blob_h.copy_(blob_d.cpu())                           # re-sync on the device's bytes
+    assert worst < 2e-5, worst
+
+
+def test_bounded_wait_runs_out_and_is_reported():
+    """The device-side waits for bulk copies are bounded: with a stage barrier made to expect more bytes than are ever
+    copied (a test switch of the library; nothing faults, the copies themselves complete) and the bound shortened to
+    a few milliseconds, every CTA gives up, the call returns, the health word counts the CTAs, the outputs of the
+    rows are zeroed, and the slots' state is left as it was.  Afterwards the library works as before."""
+    from statequant_b200 import _cabi
+    hv, hk, D, B = 4, 2, 128, 3
+    lay = SlotLayout(sq.Quantizer(8, 'k', 32), hv, hk, D, D, m=8)
+    g0 = torch.Generator().manual_seed(21)
+    blob = lay.alloc(B + 1, DEV)
+    V = lay.views(blob)
+    idx = torch.arange(1, B + 1, dtype=torch.int32, device=DEV)
+    lay.write(V, idx, (torch.randn(B, hv, D, D, generator=g0) * 0.3).to(DEV))
+    q, k = (torch.randn(B, hk, D, generator=g0).to(DEV) for _ in range(2))
+    v = torch.randn(B, hv, D, generator=g0).to(DEV)
+    gg = (-torch.rand(B, hv, generator=g0) * 0.1).to(DEV)
+    beta = torch.rand(B, hv, generator=g0).to(DEV)
+    out = torch.full((B, hv, D), 7., device=DEV)
+    lay.step(V, idx, q, k, v, out, D ** -0.5, g=gg, beta=beta)               # a healthy step first
+    torch.cuda.synchronize()
+    base = _cabi.device_status()
+    before = blob.clone()
+    _cabi.set_option('kernel_path', 4)
+    _cabi.set_option('wait_limit_us', 2000)
+    _cabi.set_option('test_extra_tx', 64)
+    try:
+        out.fill_(7.)
+        lay.step(V, idx, q, k, v, out, D ** -0.5, g=gg, beta=beta)
+        torch.cuda.synchronize()
+        assert _cabi.device_status() - base == B * hk                    # one count per CTA
+        assert torch.equal(out, torch.zeros_like(out))
+        d = field_diff(lay, blob.cpu(), before.cpu(), list(range(1, B + 1)))
+        assert d['S'] == 0 and d['SC'] == 0 and d['UB'] == 0 and d['NPTR'] == 0 and d['GCUR'] == 0, d
+    finally:
+        _cabi.set_option('test_extra_tx', 0)
+        _cabi.set_option('wait_limit_us', 1000000)
+        _cabi.set_option('kernel_path', 0)
+    blob.copy_(before)
+    o2 = torch.empty_like(out)
+    lay.step(V, idx, q, k, v, o2, D ** -0.5, g=gg, beta=beta)
+    torch.cuda.synchronize()
+    assert _cabi.device_status() - base == B * hk and torch.isfinite(o2).all() and o2.abs().max() > 0
