@@ -18,21 +18,31 @@ import torch
 from ..quantizer import FP16_TINY, FloatCast, Quantizer
 
 
+_QUANTIZER_FIELDS = ('bits', 'axis', 'group', 'affine', 'rotation', 'rounding', 'scale_bits')
+
+
+def _need(ok, why):
+    if not ok:
+        raise AssertionError(why)
+
+
 def packed_format(fmt):
-    """The format a packed store holds for ``fmt``: the same quantizer with fp16 scales, or ``None`` for a bf16
-    state ('bf16', ``FloatCast('bf16')`` or None).  Anything a packed store cannot hold is refused
-    (reference: ``fold.py:91-104``).  ``fmt`` may be this package's ``Quantizer`` or any dataclass with the same
-    fields (the reference's own)."""
-    if fmt is None or (isinstance(fmt, str) and fmt == 'bf16'):
+    """What a packed store keeps for ``fmt``.  'bf16', ``FloatCast('bf16')`` (not stochastic) and None mean a bf16
+    state and give None; a quantizer gives the same quantizer with fp16 scales.  The kernels implement symmetric
+    round-to-nearest int4 / int8 with one 16-bit scale per group along d_k or d_v and nothing else, so every other
+    quantizer is refused here rather than stored wrongly (reference: ``fold.py:91-104``).  ``fmt`` may be this
+    package's ``Quantizer`` or any dataclass with the same fields (the reference's own)."""
+    if fmt is None or fmt == 'bf16':
         return None
-    if getattr(fmt, 'dtype', None) == 'bf16' and hasattr(fmt, 'stochastic') and not fmt.stochastic:
+    if getattr(fmt, 'dtype', None) == 'bf16' and getattr(fmt, 'stochastic', True) is False:
         return None
-    need = ('bits', 'axis', 'group', 'affine', 'rotation', 'rounding', 'scale_bits')
-    assert all(hasattr(fmt, a) for a in need), f'packed storage needs a Quantizer or bf16, got {fmt!r}'
-    assert fmt.bits in (4, 8) and fmt.axis in ('k', 'v'), (fmt.bits, fmt.axis)
-    assert not fmt.affine and fmt.rotation is None and fmt.rounding == 'rtn' and fmt.scale_bits == 16, \
-        'packed storage implements symmetric RTN with 16-bit scales and no rotation'
-    assert fmt.group % 2 == 0
+    missing = [f for f in _QUANTIZER_FIELDS if not hasattr(fmt, f)]
+    _need(not missing, f'a packed store holds a Quantizer or bf16; {fmt!r} lacks {missing}')
+    _need(fmt.bits in (4, 8), f'state codes are 4 or 8 bits wide, not {fmt.bits}')
+    _need(fmt.axis in ('k', 'v'), f"scale groups run along 'k' or 'v', not {fmt.axis!r}")
+    _need(fmt.group % 2 == 0, f'group {fmt.group}: two int4 codes share a byte, so groups are even')
+    for field, want in (('affine', False), ('rotation', None), ('rounding', 'rtn'), ('scale_bits', 16)):
+        _need(getattr(fmt, field) == want, f'{field}={getattr(fmt, field)!r} is not stored packed (only {want!r})')
     return dataclasses.replace(fmt, scale_dtype='fp16')
 
 
@@ -46,16 +56,18 @@ def pow2(n):
 
 
 def check_dims(fmt, dk, dv):
-    """Head dims and groups a packed GDN store accepts (reference: ``fold.py:63-76``)."""
-    assert dk >= 16 and dk % 2 == 0, f'd_k must be even and >= 16, got {dk}'
-    assert dv % 32 == 0, f'd_v must be a multiple of 32, got {dv}'
-    if fmt is not None:
-        g = fmt.group
-        assert g >= 2 and g & (g - 1) == 0, f'group {g} must be a power of two'
-        if fmt.axis == 'k':
-            assert g <= pow2(dk) and pow2(dk) // g <= 8, f'key group {g} on d_k {dk}: 1 .. 8 groups'
-        else:
-            assert dv % g == 0, f'value group {g} must divide d_v {dv}'
+    """Refuse head dims and groups the kernels have no tiling for (reference: ``fold.py:63-76``): a key row is
+    padded to a power of two and cut into at most 8 scale groups; the value rows are dealt out 32 at a time."""
+    _need(dk % 2 == 0 and dk >= 16, f'd_k = {dk}: need an even width of at least 16')
+    _need(dv % 32 == 0, f'd_v = {dv}: need a multiple of 32')
+    if fmt is None:
+        return
+    g, width = fmt.group, pow2(dk)
+    _need(g >= 2 and g == pow2(g), f'group = {g}: need a power of two')
+    if fmt.axis == 'k':
+        _need(g <= width and width <= 8 * g, f'group = {g} along d_k = {dk}: need between 1 and 8 groups per row')
+    else:
+        _need(dv % g == 0, f'group = {g} along d_v = {dv}: the groups must tile the rows exactly')
 
 
 def _scale_of(amax, qmax):

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import ctypes as C
 import dataclasses
+import itertools
 
 import torch
 
@@ -29,12 +30,14 @@ class StepPlan:
 
 
 def head_bytes(b, dk, dv, group=32):
-    """Stored bytes of one head at width b: codes + row factors (2 bit: per 32-column group) + column factors."""
+    """Stored bytes of one head at width b.  A packed head is its d_k x d_v codes, one fp16 column factor per value
+    channel, and fp16 row factors: one per key row, except at 2 bits where every ``group`` columns of a row have
+    their own.  Width 16 is the fp16 pivot: the values themselves, no factors."""
+    cells = dk * dv
     if b == 16:
-        return 2 * dk * dv
-    if b == 2:
-        return dk * dv // 4 + 2 * dk * (dv // group) + 2 * dv
-    return dk * dv * b // 8 + 2 * dk + 2 * dv
+        return 2 * cells
+    row_factors = dk * (dv // group if b == 2 else 1)
+    return cells * b // 8 + 2 * (row_factors + dv)
 
 
 def _al(n):
@@ -69,47 +72,55 @@ class GGAPacked:
     its own offset table; an engine sizes one slot for all layers, so ``nbytes`` is the largest layer's."""
     per_layer = True
 
+    WIDTHS = (2, 4, 6, 8, 16)
+    COUNTERS = 16                   # bytes in front of the first head: (count, ring head) of the window, padding
+
     def __init__(self, method, hv, hk, dk, dv, pw=False, m=8):
-        assert dk & (dk - 1) == 0 and dv & (dv - 1) == 0 and dv % 32 == 0, (dk, dv)
-        self.method, self.HV, self.HK, self.DK, self.DV = method, hv, hk, dk, dv
-        self.pw, self.m, self.gqa = pw, m, hv // hk
+        for d in (dk, dv):
+            assert d > 0 and d & (d - 1) == 0, f'head dims are powers of two, got {dk} x {dv}'
+        assert dv % 32 == 0 and hv % hk == 0, (dv, hv, hk)
+        self.method, self.pw, self.m = method, pw, m
+        self.HV, self.HK, self.DK, self.DV, self.gqa = hv, hk, dk, dv, hv // hk
+        # per layer: every head's byte offset in the slot (heads back to back, each padded to the alignment), its
+        # width, the impact factors; ``tables`` / ``bytes_per_layer`` are the reference's names for them
         self.tables, self.bytes_per_layer = {}, {}
-        for layer, (b, w) in method.plan.items():
-            b = [int(x) for x in b]
-            assert len(b) == hv and set(b) <= {2, 4, 6, 8, 16}, b
-            offs, off = [], 16                                  # the counters come first
-            for x in b:
-                offs.append(off)
-                off += _al(head_bytes(x, dk, dv, method.group))
-            self.tables[layer] = (offs, b, w)
-            self.bytes_per_layer[layer] = off
+        for layer, (widths, impact) in method.plan.items():
+            widths = [int(x) for x in widths]
+            assert len(widths) == hv and all(x in self.WIDTHS for x in widths), widths
+            sizes = [_al(head_bytes(x, dk, dv, method.group)) for x in widths]
+            ends = list(itertools.accumulate(sizes, initial=self.COUNTERS))
+            self.tables[layer] = (ends[:-1], widths, impact)
+            self.bytes_per_layer[layer] = ends[-1]
+        # the window queue (per head: m key rows + m value rows of e4m3, 2 m fp32 scales) follows the largest layer
         self.QOFF = _al(max(self.bytes_per_layer.values()))
-        self.QSZ = m * (dk + dv + 8)
+        self.QSZ = m * (dk + dv) + 2 * m * 4
         self.nbytes = self.QOFF + (hv * self.QSZ if pw else 0)
         self._dev = {}
         if torch.cuda.is_available():       # stage the plans now: a copy inside a CUDA-graph capture would fail
             self.prepare(torch.device('cuda', torch.cuda.current_device()))
 
     def __repr__(self):
-        return (f'GGAPacked({self.method.name}{"+PW-S%d" % self.m if self.pw else ""}, hv={self.HV}, hk={self.HK}, '
-                f'dk={self.DK}, dv={self.DV}, {self.nbytes} B/slot = max over layers; mean '
-                f'{self.bits_per_value():.3f} b/value)')
+        widths = sorted({x for t in self.tables.values() for x in t[1]})
+        win = f' + window of {self.m}' if self.pw else ''
+        return (f'<GGAPacked {self.method.name}{win} | widths {widths} over {len(self.tables)} layers, '
+                f'{self.bits_per_value():.2f} bits per value | hv={self.HV}, hk={self.HK}, dk={self.DK}, dv={self.DV} | '
+                f'{self.nbytes} B per slot>')
 
     def bits_per_value(self):
         """Mean stored bits per state value over the layers (without the 16-byte counters), window included."""
-        n = self.HV * self.DK * self.DV
-        st = sum(sum(head_bytes(x, self.DK, self.DV, self.method.group) for x in t[1]) for t in self.tables.values())
-        q = self.HV * self.QSZ * len(self.tables) if self.pw else 0
-        return 8 * (st + q) / (n * len(self.tables))
+        per_layer = [sum(head_bytes(x, self.DK, self.DV, self.method.group) for x in widths) +
+                     (self.HV * self.QSZ if self.pw else 0) for _, widths, _ in self.tables.values()]
+        return 8. * sum(per_layer) / (len(per_layer) * self.HV * self.DK * self.DV)
 
     def _plan(self, layer, dev):
-        key = (layer, str(dev))
-        if key not in self._dev:
-            offs, b, w = self.tables[layer]
-            self._dev[key] = (torch.tensor(offs, dtype=torch.int32, device=dev),
-                              torch.tensor(b, dtype=torch.int32, device=dev),
-                              w.to(dev, torch.float32).contiguous())
-        return self._dev[key]
+        """(offsets int32 [HV], widths int32 [HV], impact factors fp32 [HV, d_k]) of a layer on device ``dev``."""
+        have = self._dev.get((layer, str(dev)))
+        if have is None:
+            offsets, widths, impact = self.tables[layer]
+            have = tuple(torch.tensor(x, dtype=torch.int32, device=dev) for x in (offsets, widths)) + \
+                (impact.to(device=dev, dtype=torch.float32).contiguous(),)
+            self._dev[(layer, str(dev))] = have
+        return have
 
     def prepare(self, device):
         """Move every layer's plan to the device now (so that nothing is copied during graph capture)."""
@@ -167,32 +178,37 @@ class GGAPacked:
     @torch.no_grad()
     def window(self, views, idx):
         """The queued pairs of slots idx as reconstructed fp32 (P [n, m, HV, d_k], V [n, m, HV, d_v]) in ring order
-        from the oldest, and the counts; dead entries zeroed (torch; reference: ``vllm_gga.py:275-293``)."""
-        li = idx.long()
-        blob = views['blob'][li]
+        from the oldest, and the counts; dead entries zeroed (torch; reference: ``vllm_gga.py:275-293``).
+
+        A head's queue record is, in this order: m key rows and m value rows of e4m3 codes, then m fp32 key scales
+        and m fp32 value scales; the slot's first 16 bytes hold (count, head of the ring) as int32."""
+        rows = views['blob'][idx.long()]
         m, HV, DK, DV = self.m, self.HV, self.DK, self.DV
-        ct = blob[:, :16].view(torch.int32)
-        n, hd = ct[:, 0], ct[:, 1]
-        Qb = blob[:, self.QOFF:self.QOFF + HV * self.QSZ].reshape(-1, HV, self.QSZ)
-        Pc = Qb[..., :m * DK].contiguous().view(torch.float8_e4m3fn).float().view(-1, HV, m, DK)
-        Vc = Qb[..., m * DK:m * (DK + DV)].contiguous().view(torch.float8_e4m3fn).float().view(-1, HV, m, DV)
-        sc = Qb[..., m * (DK + DV):].contiguous().view(torch.float32).view(-1, HV, 2, m)
-        Pf, Vf = Pc * sc[:, :, 0, :, None], Vc * sc[:, :, 1, :, None]
-        order = (hd[:, None] + torch.arange(m, device=li.device)[None, :]) % m
-        Pf = torch.gather(Pf, 2, order[:, None, :, None].expand(-1, HV, -1, DK)).transpose(1, 2)
-        Vf = torch.gather(Vf, 2, order[:, None, :, None].expand(-1, HV, -1, DV)).transpose(1, 2)
-        live = (torch.arange(m, device=li.device)[None, :] < n[:, None])[:, :, None, None]
-        return torch.where(live, Pf, 0.), torch.where(live, Vf, 0.), n
+        count, head = rows[:, :8].view(torch.int32).unbind(1)
+        rec = rows[:, self.QOFF:self.QOFF + HV * self.QSZ].unflatten(1, (HV, self.QSZ))
+        kc, vc, ks, vs = rec.split([m * DK, m * DV, 4 * m, 4 * m], dim=-1)
+
+        def entries(codes, scales, d):          # -> [n, m (ring position), HV, d]
+            x = codes.contiguous().view(torch.float8_e4m3fn).float().unflatten(-1, (m, d))
+            return (x * scales.contiguous().view(torch.float32)[..., None]).transpose(1, 2)
+
+        age = torch.arange(m, device=rows.device)
+        ring = (head[:, None] + age) % m                                  # position of the j-th oldest entry
+        live = (age < count[:, None])[..., None, None]
+        who = torch.arange(rows.shape[0], device=rows.device)[:, None]
+        P, V = entries(kc, ks, DK)[who, ring], entries(vc, vs, DV)[who, ring]
+        return P.where(live, 0.), V.where(live, 0.), count        # not a product: a dead entry may decode to NaN
 
     @torch.no_grad()
     def read(self, views, idx, layer=None):
-        """Logical state (stored + window), value-major fp32 [P, HV, d_v, d_k]."""
+        """Logical state (stored + window), value-major fp32 [P, HV, d_v, d_k].  The window adds the outer products
+        of its live pairs to every packed head; a pivot head (width 16) takes its writes at once and has none
+        pending."""
         S = self.stored(views, idx, layer)
-        if self.pw and idx.shape[0]:
-            P, V, _ = self.window(views, idx)
-            _, bits, _ = self._plan(layer, idx.device)
-            nonp = (bits != 16)[None, :, None, None].float()
-            S = S + torch.einsum('bmhk,bmhv->bhkv', P, V) * nonp
+        if self.pw and idx.numel():
+            keys, values, _ = self.window(views, idx)
+            packed = self._plan(layer, idx.device)[1] != 16
+            S[:, packed] += torch.einsum('bmhk,bmhv->bhkv', keys, values)[:, packed]
         return S.transpose(-1, -2)
 
     @torch.no_grad()

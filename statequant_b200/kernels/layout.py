@@ -77,11 +77,52 @@ def state_struct(tables, strides, *, bits, axis_k, group, buffer_bits, m, hv, hk
     return st
 
 
+def set_shape(obj, fmt, hv, hk, dk, dv, m, buffer_bits, *, gdn_dims, float_group):
+    """Store on ``obj`` the attributes every layout and container carries (fmt, bits, HV, HK, DK, DV, m, gqa,
+    buffer_bits, qbuf, axk, group) after checking that the kernels have a tiling for them.
+
+    gdn_dims     True: the Gated DeltaNet rules of ``check_dims`` (padded key rows, at most 8 groups per row, any m);
+                 False: the Mamba2 / KDA rules (the groups tile the quantised axis exactly, m <= 32)
+    float_group  the group written into the state struct when the state is a float one (never read by a kernel)"""
+    from .formats import _need, check_dims, packed_format, pow2, state_bits
+    obj.fmt = packed_format(fmt)
+    obj.bits = state_bits(obj.fmt)
+    _need(hk >= 1 and hv % hk == 0, f'{hv} value heads do not divide over {hk} key heads')
+    _need(m >= 1 and m == pow2(m) and (gdn_dims or m <= 32),
+          f'm = {m}: the buffer length is a power of two' + ('' if gdn_dims else ' of at most 32'))
+    _need(buffer_bits in (8, 16), f'buffer_bits = {buffer_bits}: the decode buffer is int8 or bf16')
+    if gdn_dims:
+        check_dims(obj.fmt, dk, dv)
+    else:
+        _need(dk % 2 == 0 and dk >= 16, f'd_k = {dk}: need an even width of at least 16')
+        if obj.fmt is not None:
+            g, along = obj.fmt.group, dk if obj.fmt.axis == 'k' else dv
+            _need(g >= 2 and g == pow2(g), f'group = {g}: need a power of two')
+            _need(along % g == 0, f'group = {g} does not tile d_{obj.fmt.axis} = {along}')
+    obj.HV, obj.HK, obj.DK, obj.DV, obj.m, obj.gqa = hv, hk, dk, dv, m, hv // hk
+    obj.buffer_bits, obj.qbuf = buffer_bits, buffer_bits == 8
+    obj.axk = obj.fmt is not None and obj.fmt.axis == 'k'
+    obj.group = obj.fmt.group if obj.fmt is not None else float_group
+
+
+def describe_format(obj):
+    """'int4 x k/32' style tag of a layout's state format."""
+    if obj.fmt is None:
+        return 'fp32' if getattr(obj, 'state_dtype', None) == torch.float32 else 'bf16'
+    return f'int{obj.bits} x {obj.fmt.axis}/{obj.group}'
+
+
 class BlobLayout:
     """Common part of the slot layouts: field table, typed views, allocation, the ``sqb_state_t`` of a blob and
     the torch read / write used around prefill."""
 
     kind = KIND_GDN
+    _head_words = ('hv', 'hk', 'dk', 'dv')          # how the subclass names HV, HK, DK, DV in its constructor
+
+    def __repr__(self):
+        dims = ', '.join(f'{w}={x}' for w, x in zip(self._head_words, (self.HV, self.HK, self.DK, self.DV)) if w)
+        buf = 'int8' if self.qbuf else 'bf16'
+        return f'<{type(self).__name__} {describe_format(self)} | {dims} | {self.m} x {buf} buffer | {self.nbytes} B per slot>'
 
     def _finish(self, decay_width=1, ragged=True):
         self.fields, self.nbytes = field_table(state_specs(

@@ -10,31 +10,13 @@ from __future__ import annotations
 import torch
 
 from .. import _cabi
-from .formats import pack_vk, packed_format, state_bits, unpack_vk
-from .layout import KIND_M2, BlobLayout, state_struct
-
-
-def _check_dims(fmt, dk, dv):
-    assert dk >= 16 and dk % 2 == 0, dk
-    if fmt is not None:
-        g = fmt.group
-        assert g & (g - 1) == 0, f'group {g} must be a power of two'
-        assert (dk if fmt.axis == 'k' else dv) % g == 0, f'group {g} must divide d_{fmt.axis} ({dk}, {dv})'
+from .layout import KIND_M2, BlobLayout, set_shape
+from .lockstep import LockstepTables
 
 
 def _common(st, fmt, hv, hk, dk, dv, m, buffer_bits):
-    st.fmt = packed_format(fmt)
-    st.bits = state_bits(st.fmt)
     st.state_dtype = torch.bfloat16
-    st.HV, st.HK, st.DK, st.DV, st.m = hv, hk, dk, dv, m
-    assert hv % hk == 0, (hv, hk)
-    st.gqa = hv // hk
-    assert m >= 1 and m & (m - 1) == 0 and m <= 32, 'm must be a power of two <= 32'
-    _check_dims(st.fmt, dk, dv)
-    assert buffer_bits in (8, 16)
-    st.buffer_bits, st.qbuf = buffer_bits, buffer_bits == 8
-    st.axk = st.fmt is not None and st.fmt.axis == 'k'
-    st.group = st.fmt.group if st.fmt is not None else 16
+    set_shape(st, fmt, hv, hk, dk, dv, m, buffer_bits, gdn_dims=False, float_group=16)
 
 
 def _inputs(st, idx, x, dt, B, Cm, out, A, D, dt_bias, dt_softplus, dt_limit):
@@ -80,7 +62,7 @@ def mamba2_recurrence(S, x, dt, B, C, A, D=None, dt_bias=None, dt_softplus=False
     return y if D is None else y + D.float()[:, None] * x.float()
 
 
-class PackedMamba2State:
+class PackedMamba2State(LockstepTables):
     """One Mamba2 layer's packed state and decode buffer for B sequences in lockstep.
 
     S [B, H, d_v, d_k] (or [B*H, d_v, d_k]); fmt, m, hv (= H), hk (= G groups), buffer_bits as the slot layout;
@@ -89,72 +71,13 @@ class PackedMamba2State:
 
     def __init__(self, S, fmt, m=8, hv=None, hk=None, buffer_bits=8, out_dtype=torch.bfloat16, sbv=None, fbv=None,
                  warps=None):
-        S = S.float().reshape(-1, S.shape[-2], S.shape[-1])
+        S = self._vk(S)
         BH, DV, DK = S.shape
         hv = hv or BH
-        hk = hk or hv
         assert BH % hv == 0
-        _common(self, fmt, hv, hk, DK, DV, m, buffer_bits)
+        _common(self, fmt, hv, hk or hv, DK, DV, m, buffer_bits)
         self.BH, self.B = BH, BH // hv
-        dev = S.device
-        c, s = pack_vk(S, self.fmt)
-        bdt = torch.int8 if self.qbuf else torch.bfloat16
-        self.T = dict(S=c.clone(), SC=s.clone(),
-                      KB=torch.zeros(self.B * hk, m, DK, device=dev, dtype=bdt),
-                      UB=torch.zeros(BH, m, DV, device=dev, dtype=bdt),
-                      KBS=torch.zeros(self.B * hk, m, device=dev, dtype=torch.float16),
-                      UBS=torch.zeros(BH, m, device=dev, dtype=torch.float16),
-                      GB=torch.zeros(BH, m, device=dev), GCUR=torch.zeros(BH, device=dev),
-                      NPTR=torch.zeros(self.B, hv, device=dev, dtype=torch.int32))
-        self.O = torch.zeros(self.B, hv, DV, device=dev, dtype=out_dtype)
-        T = self.T
-        per_seq = dict(S=hv * T['S'][0].numel() * T['S'].element_size(),
-                       SC=hv * T['SC'][0].numel() * 2 if self.fmt is not None else 0,
-                       KB=hk * m * DK * T['KB'].element_size(), KBS=hk * m * 2,
-                       UB=hv * m * DV * T['UB'].element_size(), UBS=hv * m * 2, GB=hv * m * 4, GCUR=hv * 4, NPTR=hv * 4)
-        tabs = dict(T)
-        if self.fmt is None:
-            tabs['SC'] = None
-        self._st = state_struct(tabs, per_seq, bits=self.bits, axis_k=self.axk, group=self.group,
-                                buffer_bits=buffer_bits, m=m, hv=hv, hk=hk, dk=DK, dv=DV)
-
-    def __getattr__(self, name):
-        T = self.__dict__.get('T')
-        if T is not None and name in T:
-            return T[name]
-        raise AttributeError(name)
-
-    @property
-    def codes(self):
-        return self.T['S']
-
-    @property
-    def scales(self):
-        return self.T['SC']
-
-    @property
-    def n(self):
-        return int(self.T['NPTR'].reshape(-1)[0])
-
-    @torch.no_grad()
-    def load(self, S):
-        c, s = pack_vk(S.float().reshape(self.BH, self.DV, self.DK), self.fmt)
-        self.T['S'].copy_(c)
-        self.T['SC'].copy_(s)
-        for k in ('KB', 'UB', 'KBS', 'UBS', 'GB', 'GCUR', 'NPTR'):
-            self.T[k].zero_()
-
-    def dequantize(self):
-        return unpack_vk(self.T['S'], self.T['SC'], self.fmt, self.DK)
-
-    def stored_bytes(self):
-        nb = lambda t: t.numel() * t.element_size()          # noqa: E731
-        T = self.T
-        per = dict(state=nb(T['S']) + (nb(T['SC']) if self.fmt is not None else 0),
-                   buffer=nb(T['KB']) + nb(T['UB']) + ((nb(T['KBS']) + nb(T['UBS'])) if self.qbuf else 0),
-                   decay=nb(T['GB']) + nb(T['GCUR']) + nb(T['NPTR']))
-        per['total'] = sum(per.values())
-        return per
+        self._allocate(S, 1, out_dtype)
 
     def step(self, x, dt, B, C, A, D=None, dt_bias=None, dt_softplus=False, dt_limit=None):
         Bn, HV, HK = self.B, self.HV, self.HK
@@ -181,10 +104,7 @@ class Mamba2SlotLayout(BlobLayout):
         self.fused = True
         self._finish(ragged=False)
 
-    def __repr__(self):
-        f = 'bf16' if self.fmt is None else f'int{self.bits}-{self.fmt.axis}-g{self.group}'
-        return (f'Mamba2SlotLayout({f}, heads={self.HV}, groups={self.HK}, d_state={self.DK}, head_dim={self.DV}, '
-                f'm={self.m}, buffer_bits={self.buffer_bits}, {self.nbytes} B/slot)')
+    _head_words = ('heads', 'groups', 'd_state', 'head_dim')
 
     def step(self, views, idx, x, dt, B, C, out, A, D=None, dt_bias=None, dt_softplus=True,
              dt_limit=(0., float('inf'))):

@@ -10,8 +10,8 @@ from __future__ import annotations
 import torch
 
 from .. import _cabi
-from .formats import check_dims, packed_format, pow2, state_bits
-from .layout import KIND_GDN, BlobLayout
+from .formats import pow2
+from .layout import KIND_GDN, BlobLayout, set_shape
 
 
 def _gdn_inputs(idx, q, k, v, out, scale, g, beta, gate, per_key_head):
@@ -57,27 +57,11 @@ class SlotLayout(BlobLayout):
 
     def __init__(self, fmt, hv, hk, dk, dv, m=8, buffer_bits=8, fused=None):
         self.fused = fused
-        self.state_dtype = torch.float32 if (isinstance(fmt, str) and fmt == 'fp32') else torch.bfloat16
-        fmt = 'bf16' if (isinstance(fmt, str) and fmt == 'fp32') else fmt
-        self.fmt = packed_format(fmt)
-        self.bits = state_bits(self.fmt)
-        self.HV, self.HK, self.DK, self.DV, self.m = hv, hk, dk, dv, m
-        assert hv % hk == 0
-        self.gqa = hv // hk
-        assert m >= 1 and m & (m - 1) == 0, 'm must be a power of two'
-        check_dims(self.fmt, dk, dv)
+        full = fmt == 'fp32' if isinstance(fmt, str) else False
+        self.state_dtype = torch.float32 if full else torch.bfloat16
+        set_shape(self, 'bf16' if full else fmt, hv, hk, dk, dv, m, buffer_bits, gdn_dims=True, float_group=32)
         self.DKP, self.DVP = pow2(dk), pow2(dv)
-        assert buffer_bits in (8, 16)
-        self.buffer_bits, self.qbuf = buffer_bits, buffer_bits == 8
-        self.axk = self.fmt is not None and self.fmt.axis == 'k'
-        self.group = self.fmt.group if self.fmt is not None else 32
         self._finish()
-
-    def __repr__(self):
-        f = ('bf16' if self.state_dtype == torch.bfloat16 else 'fp32') if self.fmt is None else \
-            f'int{self.bits}-{self.fmt.axis}-g{self.group}'
-        return (f'SlotLayout({f}, hv={self.HV}, hk={self.HK}, dk={self.DK}, dv={self.DV}, m={self.m}, '
-                f'buffer_bits={self.buffer_bits}, {self.nbytes} B/slot)')
 
     def step(self, views, idx, q, k, v, out, scale, *, g=None, beta=None, gate=None, fused='layout'):
         """One decode token for every batch row b, on slot ``idx[b]`` (int32 [B]; <= 0 = padding row: the output
