@@ -44,6 +44,10 @@ __device__ __forceinline__ void split3(float x, float& p1, float& p2, float& p3)
   p3 = __bfloat162float(__float2bfloat16_rn(r1 - p2));
 }
 
+// rint(x / s) + mb by the IEEE division: the rare path of the fold's rounding, kept out of line so that the hot loop
+// stays small in the instruction cache
+static __device__ __noinline__ float div_round_cold(float x, float s, float mb) { return rintf(__fdiv_rn(x, s)) + mb; }
+
 // Column of the head that accumulator column n (0..7) of N-block q of span j stands for.
 template <int BITS>
 __host__ __device__ __forceinline__ int fold_col(int j, int q, int n) {
@@ -111,27 +115,64 @@ __device__ __forceinline__ void fold_stage_mma(uint32_t st_addr, unsigned short*
       const int gi = BITS == 8 ? j : j;                // scale group of the span (one group per span)
       const float sc0 = h2f(scs[row0 * NG + gi]), sc1 = h2f(scs[(row0 + 1) * NG + gi]);
       float acc[NQ][4];
-      // ---- start values: (code * scale) * alpha, two roundings ----
+      // ---- start values: (code * scale) * alpha; code * scale is exact in fp32, so this rounds once, as the
+      // reference's two multiplications do ----
+      const float2 al2 = make_float2(alphan, alphan);
       if constexpr (BITS == 8) {
-        const uint32_t x0 = m[0] ^ 0x80808080u, x1 = m[1] ^ 0x80808080u, x2 = m[2] ^ 0x80808080u, x3 = m[3] ^ 0x80808080u;
-        acc[0][0] = byte_to_f<0>(x0); acc[0][1] = byte_to_f<1>(x0); acc[0][2] = byte_to_f<0>(x1); acc[0][3] = byte_to_f<1>(x1);
-        acc[1][0] = byte_to_f<2>(x0); acc[1][1] = byte_to_f<3>(x0); acc[1][2] = byte_to_f<2>(x1); acc[1][3] = byte_to_f<3>(x1);
-        acc[2][0] = byte_to_f<0>(x2); acc[2][1] = byte_to_f<1>(x2); acc[2][2] = byte_to_f<0>(x3); acc[2][3] = byte_to_f<1>(x3);
-        acc[3][0] = byte_to_f<2>(x2); acc[3][1] = byte_to_f<3>(x2); acc[3][2] = byte_to_f<2>(x3); acc[3][3] = byte_to_f<3>(x3);
-      } else {
+        // byte u = code + 128 lands in bits 8..15 of 2^23's mantissa: the float is 2^23 + 256 u, and
+        // fma(that, scale / 256, -(2^23 + 2^15) scale / 256) is code * scale with every intermediate exact
+        const float q0 = sc0 * 0.00390625f, q1 = sc1 * 0.00390625f;
+        const float2 m0 = make_float2(q0, q0), m1 = make_float2(q1, q1);
+        const float2 c0 = make_float2(-8421376.0f * q0, -8421376.0f * q0), c1 = make_float2(-8421376.0f * q1, -8421376.0f * q1);
+        const uint32_t x[4] = {m[0] ^ 0x80808080u, m[1] ^ 0x80808080u, m[2] ^ 0x80808080u, m[3] ^ 0x80808080u};
 #pragma unroll
-        for (int q = 0; q < 8; q++) {
-          const uint32_t w0 = m[2 * (q >> 2)] >> (8 * (q & 3)), w1 = m[2 * (q >> 2) + 1] >> (8 * (q & 3));
-          acc[q][0] = __uint_as_float((w0 & 15u) | 0x4B000000u) - 8388616.0f;            // 2^23 + 8
-          acc[q][1] = __uint_as_float(((w0 >> 4) & 15u) | 0x4B000000u) - 8388616.0f;
-          acc[q][2] = __uint_as_float((w1 & 15u) | 0x4B000000u) - 8388616.0f;
-          acc[q][3] = __uint_as_float(((w1 >> 4) & 15u) | 0x4B000000u) - 8388616.0f;
+        for (int q = 0; q < 4; q++) {
+          const uint32_t wa = x[2 * (q >> 1)], wb = x[2 * (q >> 1) + 1];
+          float2 a, c;
+          if (q & 1) {
+            a = make_float2(__uint_as_float(__byte_perm(wa, 0x4B000000u, 0x7424)), __uint_as_float(__byte_perm(wa, 0x4B000000u, 0x7434)));
+            c = make_float2(__uint_as_float(__byte_perm(wb, 0x4B000000u, 0x7424)), __uint_as_float(__byte_perm(wb, 0x4B000000u, 0x7434)));
+          } else {
+            a = make_float2(__uint_as_float(__byte_perm(wa, 0x4B000000u, 0x7404)), __uint_as_float(__byte_perm(wa, 0x4B000000u, 0x7414)));
+            c = make_float2(__uint_as_float(__byte_perm(wb, 0x4B000000u, 0x7404)), __uint_as_float(__byte_perm(wb, 0x4B000000u, 0x7414)));
+          }
+          a = __fmul2_rn(__ffma2_rn(a, m0, c0), al2);
+          c = __fmul2_rn(__ffma2_rn(c, m1, c1), al2);
+          acc[q][0] = a.x; acc[q][1] = a.y; acc[q][2] = c.x; acc[q][3] = c.y;
         }
-      }
+      } else {
+        // nibble n of a word is masked IN PLACE into 2^23's mantissa (n <= 4; nibbles 5, 6, 7 from the word shifted down
+        // by 20): the float is 2^23 + u 16^e, minus (2^23 + 8 16^e) gives (u - 8) 16^e exactly, and the power of
+        // sixteen goes into the scale.  Byte i of a word holds the pair (e, e') = (0,1), (2,3), (4,0), (1,2).
+        constexpr float E0[4] = {1.0f, 256.0f, 65536.0f, 16.0f}, E1[4] = {16.0f, 4096.0f, 1.0f, 256.0f};
+        float2 f0[4], f1[4], bias[4];
 #pragma unroll
-      for (int q = 0; q < NQ; q++) {
-        acc[q][0] = (acc[q][0] * sc0) * alphan; acc[q][1] = (acc[q][1] * sc0) * alphan;
-        acc[q][2] = (acc[q][2] * sc1) * alphan; acc[q][3] = (acc[q][3] * sc1) * alphan;
+        for (int i = 0; i < 4; i++) {
+          f0[i] = make_float2(sc0 / E0[i], sc0 / E1[i]);             // divisions by constants: powers of two, exact
+          f1[i] = make_float2(sc1 / E0[i], sc1 / E1[i]);
+          bias[i] = make_float2(-(8388608.0f + 8.0f * E0[i]), -(8388608.0f + 8.0f * E1[i]));
+        }
+#pragma unroll
+        for (int hx = 0; hx < 2; hx++) {
+          const uint32_t w0 = m[2 * hx], w1 = m[2 * hx + 1], w0s = w0 >> 20, w1s = w1 >> 20;
+          const uint32_t K = 0x4B000000u;
+          float2 a[4], c[4];
+          a[0] = make_float2(nib_f<0x0000000Fu>(w0, K), nib_f<0x000000F0u>(w0, K));
+          a[1] = make_float2(nib_f<0x00000F00u>(w0, K), nib_f<0x0000F000u>(w0, K));
+          a[2] = make_float2(nib_f<0x000F0000u>(w0, K), nib_f<0x0000000Fu>(w0s, K));
+          a[3] = make_float2(nib_f<0x000000F0u>(w0s, K), nib_f<0x00000F00u>(w0s, K));
+          c[0] = make_float2(nib_f<0x0000000Fu>(w1, K), nib_f<0x000000F0u>(w1, K));
+          c[1] = make_float2(nib_f<0x00000F00u>(w1, K), nib_f<0x0000F000u>(w1, K));
+          c[2] = make_float2(nib_f<0x000F0000u>(w1, K), nib_f<0x0000000Fu>(w1s, K));
+          c[3] = make_float2(nib_f<0x000000F0u>(w1s, K), nib_f<0x00000F00u>(w1s, K));
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const float2 av = __fmul2_rn(__fmul2_rn(__fadd2_rn(a[i], bias[i]), f0[i]), al2);
+            const float2 cv = __fmul2_rn(__fmul2_rn(__fadd2_rn(c[i], bias[i]), f1[i]), al2);
+            const int q = hx * 4 + i;
+            acc[q][0] = av.x; acc[q][1] = av.y; acc[q][2] = cv.x; acc[q][3] = cv.y;
+          }
+        }
       }
       // ---- the eight buffer slots ----
 #pragma unroll
@@ -150,34 +191,40 @@ __device__ __forceinline__ void fold_stage_mma(uint32_t st_addr, unsigned short*
       am0 = fmaxf(am0, __shfl_xor_sync(0xffffffffu, am0, 1)); am1 = fmaxf(am1, __shfl_xor_sync(0xffffffffu, am1, 1));
       am0 = fmaxf(am0, __shfl_xor_sync(0xffffffffu, am0, 2)); am1 = fmaxf(am1, __shfl_xor_sync(0xffffffffu, am1, 2));
       const float s0 = fp16_scale(am0, QMAX), s1 = fp16_scale(am1, QMAX);
-      const float r0 = rcp_approx(s0), r1 = rcp_approx(s1);
-      // ---- round: candidate by reciprocal multiply, verified by the exact residual (see round_fast) ----
+      // ---- round: rint(x / s) lies between the roundings of x r- and x r+ for any r- < 1 / s < r+ (rounding is
+      // monotone, and so is the division's own rounding, which moves the quotient by 2^-24 of itself, well inside
+      // the bracket).  r+- = r (1 +- 2^-22) around the approximate reciprocal r (error below 2^-23 of itself).
+      // Where the two agree, that is the answer; where they differ (the quotient within 1e-4 of a tie) divide. ----
+      const float ra0 = rcp_approx(s0), ra1 = rcp_approx(s1);
+      const float2 lo0 = make_float2(fmaf(-ra0, 0x1p-22f, ra0), fmaf(-ra0, 0x1p-22f, ra0));
+      const float2 hi0 = make_float2(fmaf(ra0, 0x1p-22f, ra0), fmaf(ra0, 0x1p-22f, ra0));
+      const float2 lo1 = make_float2(fmaf(-ra1, 0x1p-22f, ra1), fmaf(-ra1, 0x1p-22f, ra1));
+      const float2 hi1 = make_float2(fmaf(ra1, 0x1p-22f, ra1), fmaf(ra1, 0x1p-22f, ra1));
+      const float2 mb2 = make_float2(MB, MB);
       float tv[NQ][4];
-      float worst0 = 0.f, worst1 = 0.f;
+      uint32_t differ = 0;
 #pragma unroll
       for (int q = 0; q < NQ; q++) {
-#pragma unroll
-        for (int e = 0; e < 2; e++) {
-          tv[q][e] = fmaf(acc[q][e], r0, MB);
-          worst0 = fmaxf(worst0, fabsf(fmaf(-(tv[q][e] - MB), s0, acc[q][e])));
-          tv[q][2 + e] = fmaf(acc[q][2 + e], r1, MB);
-          worst1 = fmaxf(worst1, fabsf(fmaf(-(tv[q][2 + e] - MB), s1, acc[q][2 + e])));
-        }
+        const float2 xa = make_float2(acc[q][0], acc[q][1]), xc = make_float2(acc[q][2], acc[q][3]);
+        const float2 la = __ffma2_rn(xa, lo0, mb2), ha = __ffma2_rn(xa, hi0, mb2);
+        const float2 lc = __ffma2_rn(xc, lo1, mb2), hc = __ffma2_rn(xc, hi1, mb2);
+        tv[q][0] = la.x; tv[q][1] = la.y; tv[q][2] = lc.x; tv[q][3] = lc.y;
+        differ |= (__float_as_uint(la.x) ^ __float_as_uint(ha.x)) | (__float_as_uint(la.y) ^ __float_as_uint(ha.y));
+        differ |= (__float_as_uint(lc.x) ^ __float_as_uint(hc.x)) | (__float_as_uint(lc.y) ^ __float_as_uint(hc.y));
       }
-      // A verified candidate is the right UNCLAMPED integer whatever the scale; only a scale in fp16's subnormal range
-      // (rounded far from absmax / qmax) lets a quotient pass qmax, and then clamping the candidate is what
-      // clamp(rint(div_rn(x, s))) does.
-      const bool ok0 = worst0 < s0 * 0.49998474f, ok1 = worst1 < s1 * 0.49998474f;
-      if (!ok0 || !ok1) {                             // rare: an element close to a tie
+      if (differ != 0) {                              // rare: some element of this thread is close to a tie
 #pragma unroll
         for (int q = 0; q < NQ; q++) {
 #pragma unroll
           for (int e = 0; e < 2; e++) {
-            if (!ok0) tv[q][e] = rintf(__fdiv_rn(acc[q][e], s0)) + MB;
-            if (!ok1) tv[q][2 + e] = rintf(__fdiv_rn(acc[q][2 + e], s1)) + MB;
+            tv[q][e] = div_round_cold(acc[q][e], s0, MB);
+            tv[q][2 + e] = div_round_cold(acc[q][2 + e], s1, MB);
           }
         }
       }
+      // The candidate is the right UNCLAMPED integer whatever the scale; only a scale in fp16's subnormal range
+      // (rounded far from absmax / qmax) lets a quotient pass qmax, and then clamping the candidate is what
+      // clamp(rint(div_rn(x, s))) does.
       if (s0 < FP16_MIN_NORMAL || s1 < FP16_MIN_NORMAL) {
 #pragma unroll
         for (int q = 0; q < NQ; q++) {
@@ -187,24 +234,23 @@ __device__ __forceinline__ void fold_stage_mma(uint32_t st_addr, unsigned short*
       }
       // ---- repack into the fragment registers ----
       uint32_t o[4];
+      auto two = [](uint32_t a, uint32_t c) { return __byte_perm(a, c, 0x0040); };   // bytes (a, c)
       if constexpr (BITS == 8) {
-        auto two = [](float a, float c) { return __byte_perm(__float_as_uint(a), __float_as_uint(c), 0x0040); };   // bytes (a, c)
-        o[0] = __byte_perm(two(tv[0][0], tv[0][1]), two(tv[1][0], tv[1][1]), 0x5410);
-        o[1] = __byte_perm(two(tv[0][2], tv[0][3]), two(tv[1][2], tv[1][3]), 0x5410);
-        o[2] = __byte_perm(two(tv[2][0], tv[2][1]), two(tv[3][0], tv[3][1]), 0x5410);
-        o[3] = __byte_perm(two(tv[2][2], tv[2][3]), two(tv[3][2], tv[3][3]), 0x5410);
+        auto u = [](float f) { return __float_as_uint(f); };
+        o[0] = __byte_perm(two(u(tv[0][0]), u(tv[0][1])), two(u(tv[1][0]), u(tv[1][1])), 0x5410);
+        o[1] = __byte_perm(two(u(tv[0][2]), u(tv[0][3])), two(u(tv[1][2]), u(tv[1][3])), 0x5410);
+        o[2] = __byte_perm(two(u(tv[2][0]), u(tv[2][1])), two(u(tv[3][0]), u(tv[3][1])), 0x5410);
+        o[3] = __byte_perm(two(u(tv[2][2]), u(tv[2][3])), two(u(tv[3][2]), u(tv[3][3])), 0x5410);
       } else {
+        // a candidate's low 4 bits are code + 8 and the next 4 are zero, so lo + 16 hi has the packed byte at the bottom
+        auto by = [](float lo, float hi) { return __float_as_uint(lo) + (__float_as_uint(hi) << 4); };
 #pragma unroll
         for (int hx = 0; hx < 2; hx++) {
-          uint32_t a = 0, c = 0;
-#pragma unroll
-          for (int i = 0; i < 4; i++) {
-            const int q = hx * 4 + i;
-            a |= ((__float_as_uint(tv[q][0]) & 15u) | ((__float_as_uint(tv[q][1]) & 15u) << 4)) << (8 * i);
-            c |= ((__float_as_uint(tv[q][2]) & 15u) | ((__float_as_uint(tv[q][3]) & 15u) << 4)) << (8 * i);
-          }
-          o[2 * hx] = a;
-          o[2 * hx + 1] = c;
+          const int q = hx * 4;
+          o[2 * hx] = __byte_perm(two(by(tv[q][0], tv[q][1]), by(tv[q + 1][0], tv[q + 1][1])),
+                                  two(by(tv[q + 2][0], tv[q + 2][1]), by(tv[q + 3][0], tv[q + 3][1])), 0x5410);
+          o[2 * hx + 1] = __byte_perm(two(by(tv[q][2], tv[q][3]), by(tv[q + 1][2], tv[q + 1][3])),
+                                      two(by(tv[q + 2][2], tv[q + 2][3]), by(tv[q + 3][2], tv[q + 3][3])), 0x5410);
         }
       }
       __syncwarp();                                     // every lane has read the span's codes and old scales
