@@ -54,6 +54,7 @@ struct StepArgs {
   int m_log2, gqa_full;      // tensor-core kernels: log2(m), value heads per key head
   int prefetch_dist;         // tensor-core kernels: a CTA prefetches into L2 for the CTA this many blocks later (0: off)
   int test_extra_tx;         // test hook: bytes a stage barrier expects beyond what is copied (so its wait runs out)
+  int axv;                   // tensor-core kernels: the scale groups run along d_v (32 rows per group)
 };
 
 // shared-memory plan (floats)

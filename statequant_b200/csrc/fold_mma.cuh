@@ -263,4 +263,163 @@ __device__ __forceinline__ void fold_stage_mma(uint32_t st_addr, unsigned short*
   }
 }
 
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], uint32_t saddr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(saddr));
+}
+__device__ __forceinline__ void stsm_x2(uint32_t saddr, uint32_t r0, uint32_t r1) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x2.shared.b16 [%0], {%1, %2};" ::"r"(saddr), "r"(r0), "r"(r1) : "memory");
+}
+
+// The same fold for 4-bit codes scaled along v in groups of 32 rows (one scale per column and group).  Warp w owns
+// group w of the stage (the rows of tile_pass_v, mma_pass.cuh), so a column's absolute maximum over the group is a
+// reduction inside the warp.  The row is walked in four chunks of 32 columns (16 bytes: one ldmatrix.x2 per 16-row
+// block); a thread holds 8 columns of 4 rows per chunk.  After the reduction lane (i, t) computes the fresh scale of
+// ONE column (the i-th of the quad's eight) and the quad's lanes exchange them.
+//   scs: the stage's scales [4][128] fp16, rewritten in place; the other arguments as fold_stage_mma.
+template <int DV>
+__device__ __forceinline__ void fold_stage_mma_v4(uint32_t st_addr, unsigned short* scs, const int8_t* ubt, const float* udq,
+                                                  const float* tab, const float* ksf, const uint32_t* KBf, int w, int lane) {
+  constexpr int ROWB = 64, PITCH = 16 * ROWB + 16, TABW = 20;
+  constexpr float QMAX = 7.0f, MB = MAGIC + 8.0f;
+  const int i = lane >> 2, t = lane & 3;
+  const uint32_t lrow = st_addr + (2 * w + (lane & 1)) * PITCH + (((lane & 7) >> 1) + 4 * ((lane >> 3) & 1)) * ROWB;
+  const int hh = (32 * w) / DV;                        // the warp's 32 rows lie in one head
+  const float* tb = tab + hh * TABW;
+  const float2 al2 = make_float2(tb[16], tb[16]);
+  // ---- A fragments: L of the thread's four rows (fragment rows i, i + 8 of blocks 0, 1) at slots 2t, 2t + 1 ----
+  uint32_t A1[2][2], A2[2][2], A3[2][2];
+#pragma unroll
+  for (int bb = 0; bb < 2; bb++) {
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      const int rv0 = (32 * w + 16 * (i & 1) + (i >> 1) + 4 * r + 8 * bb) % DV;
+      float p1[2], p2[2], p3[2];
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        const int sl = 2 * t + e;
+        float L;
+        if (sl < 7) L = tb[sl] * (static_cast<float>(ubt[(hh * 8 + sl) * DV + rv0]) * tb[8 + sl]);
+        else L = udq[hh * DV + rv0];
+        split3(L * ksf[sl], p1[e], p2[e], p3[e]);
+      }
+      A1[bb][r] = bf2(p1[0], p1[1]); A2[bb][r] = bf2(p2[0], p2[1]); A3[bb][r] = bf2(p3[0], p3[1]);
+    }
+  }
+  constexpr float E0[4] = {1.0f, 256.0f, 65536.0f, 16.0f}, E1[4] = {16.0f, 4096.0f, 1.0f, 256.0f};   // see fold_stage_mma
+#pragma unroll 1
+  for (int c4 = 0; c4 < 4; c4++) {
+    uint32_t wd[2][2];                                 // [block][fragment row i / i + 8]: 8 nibbles = this thread's 8 columns
+    ldsm_x2(wd[0], lrow + 16 * c4);
+    ldsm_x2(wd[1], lrow + 8 * ROWB + 16 * c4);
+    unsigned short* scol = scs + w * 128 + 32 * c4 + 8 * t;                  // the thread's 8 column scales
+    const uint4 sw = *reinterpret_cast<const uint4*>(scol);
+    const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sw.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&sw.y));
+    const float2 s45 = __half22float2(*reinterpret_cast<const __half2*>(&sw.z)), s67 = __half22float2(*reinterpret_cast<const __half2*>(&sw.w));
+    const float2 so[4] = {s01, s23, s45, s67};
+    float acc[2][4][4];
+    // ---- start values: (code * scale) * alpha ----
+#pragma unroll
+    for (int bb = 0; bb < 2; bb++) {
+      const uint32_t w0 = wd[bb][0], w1 = wd[bb][1], w0s = w0 >> 20, w1s = w1 >> 20;
+      const uint32_t K = 0x4B000000u;
+      float2 a[4], c[4];
+      a[0] = make_float2(nib_f<0x0000000Fu>(w0, K), nib_f<0x000000F0u>(w0, K));
+      a[1] = make_float2(nib_f<0x00000F00u>(w0, K), nib_f<0x0000F000u>(w0, K));
+      a[2] = make_float2(nib_f<0x000F0000u>(w0, K), nib_f<0x0000000Fu>(w0s, K));
+      a[3] = make_float2(nib_f<0x000000F0u>(w0s, K), nib_f<0x00000F00u>(w0s, K));
+      c[0] = make_float2(nib_f<0x0000000Fu>(w1, K), nib_f<0x000000F0u>(w1, K));
+      c[1] = make_float2(nib_f<0x00000F00u>(w1, K), nib_f<0x0000F000u>(w1, K));
+      c[2] = make_float2(nib_f<0x000F0000u>(w1, K), nib_f<0x0000000Fu>(w1s, K));
+      c[3] = make_float2(nib_f<0x000000F0u>(w1s, K), nib_f<0x00000F00u>(w1s, K));
+#pragma unroll
+      for (int b4 = 0; b4 < 4; b4++) {
+        const float2 f = make_float2(so[b4].x / E0[b4], so[b4].y / E1[b4]);     // powers of two: exact
+        const float2 bias = make_float2(-(8388608.0f + 8.0f * E0[b4]), -(8388608.0f + 8.0f * E1[b4]));
+        const float2 av = __fmul2_rn(__fmul2_rn(__fadd2_rn(a[b4], bias), f), al2);
+        const float2 cv = __fmul2_rn(__fmul2_rn(__fadd2_rn(c[b4], bias), f), al2);
+        acc[bb][b4][0] = av.x; acc[bb][b4][1] = av.y; acc[bb][b4][2] = cv.x; acc[bb][b4][3] = cv.y;
+      }
+    }
+    // ---- the eight buffer slots ----
+#pragma unroll
+    for (int b4 = 0; b4 < 4; b4++) {
+      const uint32_t kw = KBf[(c4 * 4 + b4) * 32 + lane];
+#pragma unroll
+      for (int bb = 0; bb < 2; bb++) {
+        mma_bf16(acc[bb][b4], A1[bb][0], A1[bb][1], A2[bb][0], A2[bb][1], kw, kw);
+        mma_bf16(acc[bb][b4], A3[bb][0], A3[bb][1], 0u, 0u, kw, kw);
+      }
+    }
+    // ---- fresh scales: a column's absolute maximum over the group's 32 rows ----
+    float cm[8];
+#pragma unroll
+    for (int b4 = 0; b4 < 4; b4++) {
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        float m = fmaxf(fmaxf(fabsf(acc[0][b4][e]), fabsf(acc[0][b4][2 + e])), fmaxf(fabsf(acc[1][b4][e]), fabsf(acc[1][b4][2 + e])));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+        cm[2 * b4 + e] = m;
+      }
+    }
+    float mine = (i & 4) ? ((i & 2) ? ((i & 1) ? cm[7] : cm[6]) : ((i & 1) ? cm[5] : cm[4]))
+                         : ((i & 2) ? ((i & 1) ? cm[3] : cm[2]) : ((i & 1) ? cm[1] : cm[0]));
+    const float sc_mine = fp16_scale(mine, QMAX), rc_mine = rcp_approx(sc_mine);
+    __syncwarp();                                      // every lane has read the chunk's old scales
+    scol[i] = f2h(sc_mine);
+    float sn[8], rn[8];
+    float smin = 1.0f;
+#pragma unroll
+    for (int x = 0; x < 8; x++) {
+      sn[x] = __shfl_sync(0xffffffffu, sc_mine, 4 * x + t);
+      rn[x] = __shfl_sync(0xffffffffu, rc_mine, 4 * x + t);
+      smin = fminf(smin, sn[x]);
+    }
+    // ---- round (the bracket of fold_stage_mma, one reciprocal per column) and repack ----
+    uint32_t o[2][2];
+#pragma unroll
+    for (int bb = 0; bb < 2; bb++) {
+      float tv[4][4];
+      uint32_t differ = 0;
+#pragma unroll
+      for (int b4 = 0; b4 < 4; b4++) {
+        const float2 lo = make_float2(fmaf(-rn[2 * b4], 0x1p-22f, rn[2 * b4]), fmaf(-rn[2 * b4 + 1], 0x1p-22f, rn[2 * b4 + 1]));
+        const float2 hi = make_float2(fmaf(rn[2 * b4], 0x1p-22f, rn[2 * b4]), fmaf(rn[2 * b4 + 1], 0x1p-22f, rn[2 * b4 + 1]));
+        const float2 mb2 = make_float2(MB, MB);
+        const float2 xa = make_float2(acc[bb][b4][0], acc[bb][b4][1]), xc = make_float2(acc[bb][b4][2], acc[bb][b4][3]);
+        const float2 la = __ffma2_rn(xa, lo, mb2), ha = __ffma2_rn(xa, hi, mb2);
+        const float2 lc = __ffma2_rn(xc, lo, mb2), hc = __ffma2_rn(xc, hi, mb2);
+        tv[b4][0] = la.x; tv[b4][1] = la.y; tv[b4][2] = lc.x; tv[b4][3] = lc.y;
+        differ |= (__float_as_uint(la.x) ^ __float_as_uint(ha.x)) | (__float_as_uint(la.y) ^ __float_as_uint(ha.y));
+        differ |= (__float_as_uint(lc.x) ^ __float_as_uint(hc.x)) | (__float_as_uint(lc.y) ^ __float_as_uint(hc.y));
+      }
+      if (differ != 0) {                               // rare: some element of this thread is close to a tie
+#pragma unroll
+        for (int b4 = 0; b4 < 4; b4++) {
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            tv[b4][e] = div_round_cold(acc[bb][b4][e], sn[2 * b4 + e], MB);
+            tv[b4][2 + e] = div_round_cold(acc[bb][b4][2 + e], sn[2 * b4 + e], MB);
+          }
+        }
+      }
+      if (smin < FP16_MIN_NORMAL) {                    // only a scale in fp16's subnormal range lets a quotient pass qmax
+#pragma unroll
+        for (int b4 = 0; b4 < 4; b4++) {
+#pragma unroll
+          for (int e = 0; e < 4; e++) tv[b4][e] = fminf(fmaxf(tv[b4][e], MB - QMAX), MB + QMAX);
+        }
+      }
+      auto two = [](uint32_t a, uint32_t c) { return __byte_perm(a, c, 0x0040); };
+      auto by = [](float lo, float hi) { return __float_as_uint(lo) + (__float_as_uint(hi) << 4); };
+      o[bb][0] = __byte_perm(two(by(tv[0][0], tv[0][1]), by(tv[1][0], tv[1][1])), two(by(tv[2][0], tv[2][1]), by(tv[3][0], tv[3][1])), 0x5410);
+      o[bb][1] = __byte_perm(two(by(tv[0][2], tv[0][3]), by(tv[1][2], tv[1][3])), two(by(tv[2][2], tv[2][3]), by(tv[3][2], tv[3][3])), 0x5410);
+    }
+    __syncwarp();                                      // every lane has read the chunk's codes
+    stsm_x2(lrow + 16 * c4, o[0][0], o[0][1]);
+    stsm_x2(lrow + 8 * ROWB + 16 * c4, o[1][0], o[1][1]);
+  }
+}
+
 }  // namespace sqb

@@ -9,10 +9,14 @@ namespace sqb {
 // Shapes the tensor-core kernels take: 4 / 8-bit codes scaled along k in groups of 32, 64 or 128, d_k 128, d_v 64 or
 // 128 (whole stages of 128 rows per key head), int8 buffer, q / k per key head, every per-head chunk and table
 // stride a multiple of 16 bytes.
-inline bool mma_shape_ok(const StepArgs& a, int bits, bool axk, bool kda) {
-  if ((bits != 4 && bits != 8) || !axk || a.DK != 128 || !a.qbuf) return false;
+// Scaled along v: 4-bit codes in groups of 32 rows, Gated DeltaNet, buffer length 8 (the fold inside the step kernel
+// is the tensor-pipe one).
+inline bool mma_shape_ok(const StepArgs& a, int bits, bool axk, bool kda, int kind = K_GDN) {
+  if ((bits != 4 && bits != 8) || a.DK != 128 || !a.qbuf) return false;
   if (a.DV != 64 && a.DV != 128) return false;
-  if (a.group != 32 && a.group != 64 && a.group != 128) return false;
+  if (!axk) {
+    if (bits != 4 || a.group != 32 || kind != K_GDN || a.M != 8 || a.DV != 128) return false;
+  } else if (a.group != 32 && a.group != 64 && a.group != 128) return false;
   if (!a.per_key_head && a.HV != a.HK) return false;
   const int gqa = a.HV / a.HK, hps = 128 / a.DV;
   if (gqa % hps) return false;
@@ -37,19 +41,19 @@ inline int mma_hpc(const StepArgs& a) {
 
 template <int KIND>
 inline bool mma_plan(const StepArgs& a, int bits, int mode, SmemM& plan, int& nst) {
-  const int gqa = mma_hpc(a), nsh = gqa / (128 / a.DV), upg = a.group / 32;
+  const int gqa = mma_hpc(a), nsh = gqa / (128 / a.DV), upg = a.axv ? 1 : a.group / 32;
   nst = nsh < 4 ? nsh : 4;
-  plan = smemm_plan(KIND, bits, upg, a.DV, a.M, nst, gqa, mode == 3);
+  plan = smemm_plan(KIND, bits, upg, a.DV, a.M, nst, gqa, mode == 3, a.axv != 0);
   while (nst > 1 && plan.total > 96 * 1024) {
     nst--;
-    plan = smemm_plan(KIND, bits, upg, a.DV, a.M, nst, gqa, mode == 3);
+    plan = smemm_plan(KIND, bits, upg, a.DV, a.M, nst, gqa, mode == 3, a.axv != 0);
   }
   return plan.total <= 220 * 1024;
 }
 
-template <int KIND, int BITS, int UPG, int DV, int MODE>
+template <int KIND, int BITS, int UPG, int DV, int MODE, bool AXV = false>
 int launch_mma_one(const StepArgs& a, cudaStream_t stream) {
-  auto kern = step_mma_kernel<KIND, BITS, UPG, DV, MODE>;
+  auto kern = step_mma_kernel<KIND, BITS, UPG, DV, MODE, AXV>;
   SmemM plan;
   int nst;
   if (!mma_plan<KIND>(a, BITS, MODE, plan, nst)) return 1;
@@ -89,6 +93,10 @@ int launch_mma_one(const StepArgs& a, cudaStream_t stream) {
 
 template <int KIND, int DV, int MODE>
 int launch_mma_fmt(const StepArgs& a, int bits, cudaStream_t stream) {
+  if (a.axv) {
+    if constexpr (KIND == K_GDN && DV == 128) return launch_mma_one<KIND, 4, 1, DV, MODE, true>(a, stream);
+    else return 1;
+  }
   const int upg = a.group / 32;
   if (bits == 4) {
     if (upg == 1) return launch_mma_one<KIND, 4, 1, DV, MODE>(a, stream);

@@ -201,4 +201,71 @@ __device__ __forceinline__ void tile_pass(uint32_t codes, const unsigned short* 
   tk = t < 2 ? recv : T[1];
 }
 
+// ---- states scaled along v (one scale per column for every group of 32 rows) ------------------------------------------
+// The scale varies along the contraction, so it goes into the read-out vectors: group G of a head is read against
+// q * scale_G and k * scale_G, in fixed point as above, and the integer sums need no scale afterwards.  A warp takes
+// exactly one group: rows 32 w .. 32 w + 31 of the stage = pieces 2w and 2w + 1, and builds its own B fragments for it.
+// Block bb (16 rows): fragment row f = row (f >> 1) + 8 bb of piece 2w + (f & 1).  With 64-byte rows (4-bit codes) the
+// eight row addresses of an ldmatrix tile then fall on four distinct 16-byte bank groups (a two-way conflict); with
+// 128-byte rows they would all collide, so 8-bit codes scaled along v do not come this way.
+// On return lane (i, t) holds the sums of stage row 32 w + 16 (i & 1) + (i >> 1) + 4 (t & 1) + 8 (t >> 1).
+
+// This lane's stage row in the layout above.
+__device__ __forceinline__ int tile_row_v(int w, int lane) {
+  const int i = lane >> 2, t = lane & 3;
+  return 32 * w + 16 * (i & 1) + (i >> 1) + 4 * (t & 1) + 8 * (t >> 1);
+}
+
+// The warp's B fragments for its group: sg = the group's 128 column scales (fp16), vq / vk = the read-out vectors
+// (fp32, 128 each; vk unused if !TWO).  Bf: the warp's own 1 KB of shared memory.  Returns the fixed-point scales.
+template <int BITS, bool TWO>
+__device__ __forceinline__ void build_b_v(uint32_t* Bf, const unsigned short* sg, const float* vq, const float* vk, int lane,
+                                          uint32_t (&bf)[8], FxScale& fq, FxScale& fk) {
+  const uint2 sw = *reinterpret_cast<const uint2*>(sg + 4 * lane);
+  const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sw.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&sw.y));
+  const float4 q4 = *reinterpret_cast<const float4*>(vq + 4 * lane);
+  float eq[4] = {q4.x * s01.x, q4.y * s01.y, q4.z * s23.x, q4.w * s23.y};
+  float ek[4] = {0.f, 0.f, 0.f, 0.f};
+  if constexpr (TWO) {
+    const float4 k4 = *reinterpret_cast<const float4*>(vk + 4 * lane);
+    ek[0] = k4.x * s01.x; ek[1] = k4.y * s01.y; ek[2] = k4.z * s23.x; ek[3] = k4.w * s23.y;
+  }
+  float mq = fmaxf(fmaxf(fabsf(eq[0]), fabsf(eq[1])), fmaxf(fabsf(eq[2]), fabsf(eq[3])));
+  float mk = fmaxf(fmaxf(fabsf(ek[0]), fabsf(ek[1])), fmaxf(fabsf(ek[2]), fabsf(ek[3])));
+  mq = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(mq)));
+  if constexpr (TWO) mk = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(mk)));
+  fq = fx30_scale(mq);
+  fk = fx30_scale(mk);
+  uint32_t yq[4], yk[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) { yq[j] = fx30_digits(eq[j], fq); yk[j] = TWO ? fx30_digits(ek[j], fk) : 0u; }
+  __syncwarp();                                        // the fragments of the previous stage have been read
+  put_b_words<BITS>(Bf, lane, 0, yq[0], yq[1], yq[2], yq[3]);
+  put_b_words<BITS>(Bf, lane, 1, yk[0], yk[1], yk[2], yk[3]);
+  __syncwarp();
+#pragma unroll
+  for (int r = 0; r < 8; r++) bf[r] = Bf[r * 32 + lane];
+}
+
+// one: shared address of a word holding the fp16 pair (1, 1) (the blocks carry no scale of their own)
+template <int BITS>
+__device__ __forceinline__ void tile_pass_v(uint32_t codes, const unsigned short* one, const uint32_t (&bf)[8], int w,
+                                            int lane, float& tq, float& tk) {
+  constexpr int ROWB = 128 * BITS / 8, PITCH = 16 * ROWB + 16;
+  const int t = lane & 3;
+  int ci[1][2];
+  acc_start<BITS, 4>(bf, ci);
+  const uint32_t lrow = codes + (2 * w + (lane & 1)) * PITCH + (((lane & 7) >> 1) + 4 * ((lane >> 3) & 1)) * ROWB + (lane >> 4) * 16;
+  float T[2];
+#pragma unroll
+  for (int bb = 0; bb < 2; bb++) {
+    float p[4] = {0.f, 0.f, 0.f, 0.f};
+    block_pass<BITS, 4>(lrow + 8 * bb * ROWB, one, bf, ci, p);
+    T[bb] = join_digits(p, t);
+  }
+  const float recv = __shfl_xor_sync(0xffffffffu, t < 2 ? T[1] : T[0], 2);
+  tq = t < 2 ? T[0] : recv;
+  tk = t < 2 ? recv : T[1];
+}
+
 }  // namespace sqb

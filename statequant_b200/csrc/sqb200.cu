@@ -181,12 +181,15 @@ bool fold_fits(const sqb::StepArgs& a, int bits, bool axk, bool kda) {
 }
 
 template <int KIND>
-int launch(const sqb::StepArgs& a, int bits, bool axk, cudaStream_t stream) {
+int launch(const sqb::StepArgs& a0, int bits, bool axk, cudaStream_t stream) {
+  const sqb::StepArgs& a = a0;
   const int path = g_force_generic.load(std::memory_order_relaxed) ? 1 : g_kernel_path.load(std::memory_order_relaxed);
   constexpr bool kda = KIND == sqb::K_KDA;
   // Every check that could refuse a launch is made before the first one: a positive "shape not taken" code after a
   // step kernel has appended would leave the slot between two states.
-  if ((path == 0 || path >= 3) && sqb::mma_shape_ok(a, bits, axk, kda)) {
+  if ((path == 0 || path >= 3) && sqb::mma_shape_ok(a0, bits, axk, kda, KIND)) {
+    sqb::StepArgs a = a0;
+    a.axv = axk ? 0 : 1;
     sqb::SmemM plan;
     int nst;
     if (path == 4 || path == 0) {

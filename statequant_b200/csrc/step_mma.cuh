@@ -38,16 +38,19 @@ __device__ long long g_mma_trace[64 * 4 * 16];
 #endif
 
 struct SmemM {
-  int bars, stage0, stage_bytes, sc_off, ub_off, kb, gbt, bf, kbf, kcur, f0, total;
+  int bars, stage0, stage_bytes, sc_off, ub_off, kb, gbt, bf, bfv, kbf, kcur, f0, total;
   int hd, dcu, gbs, dqk, ksv, us, red, misc, ga, ae, wq, wk, wg, tab, R, L, fdec, ksf;     // float offsets from f0
 };
 // The fold of the m-th token runs on the tensor pipe (fold_mma.cuh) for decays per head, a buffer of 8 and one scale
 // group per 32-byte span of a row; otherwise in fp32 (fold_rows.cuh), which needs the R / L tiles.
-__host__ __device__ inline bool fold_on_tensor_pipe(int kind, int bits, int upg, int M) {
+// (axv: 4-bit codes scaled along v in groups of 32 rows, fold_stage_mma_v4.)
+__host__ __device__ inline bool fold_on_tensor_pipe(int kind, int bits, int upg, int M, bool axv = false) {
+  if (axv) return kind != K_KDA && M == 8 && bits == 4;
   return kind != K_KDA && M == 8 && ((bits == 8 && upg == 1) || (bits == 4 && upg == 2));
 }
-__host__ __device__ inline SmemM smemm_plan(int kind, int bits, int upg, int DV, int M, int nst, int gqa, bool fold) {
-  const bool simt = fold && !fold_on_tensor_pipe(kind, bits, upg, M), tens = fold && !simt;
+__host__ __device__ inline SmemM smemm_plan(int kind, int bits, int upg, int DV, int M, int nst, int gqa, bool fold,
+                                            bool axv = false) {
+  const bool simt = fold && !fold_on_tensor_pipe(kind, bits, upg, M, axv), tens = fold && !simt;
   SmemM s;
   const int rowb = 128 * bits / 8, pitch = 16 * rowb + 16, ng = 4 / upg;
   s.sc_off = 8 * pitch;
@@ -59,6 +62,7 @@ __host__ __device__ inline SmemM smemm_plan(int kind, int bits, int upg, int DV,
   s.kb = o; o += al16i(M * 128);
   s.gbt = o; o += (kind == K_KDA ? M * 128 * 4 : 0);
   s.bf = o; o += (bits == 4 && kind != K_KDA) ? 2048 : 1024;   // B fragments: the state's layout (+ the byte layout for the key tile)
+  s.bfv = o; o += axv ? 4096 : 0;    // states scaled along v: every warp's own B fragments
   s.kbf = o; o += tens ? 2048 : 0;   // the fold's key fragments
   s.kcur = o; o += tens ? 128 : 0;   // the codes of the key appended by this token
   s.f0 = o;
@@ -73,8 +77,8 @@ __host__ __device__ inline SmemM smemm_plan(int kind, int bits, int upg, int DV,
   s.misc = f; f += 16;
   s.ga = f; f += (kind == K_KDA ? 128 : 0);
   s.ae = f; f += (kind == K_KDA ? 128 : 0);
-  s.wq = f; f += (kind == K_KDA ? 128 : 0);
-  s.wk = f; f += (kind == K_KDA ? 128 : 0);
+  s.wq = f; f += (kind == K_KDA || axv ? 128 : 0);
+  s.wk = f; f += (kind == K_KDA || axv ? 128 : 0);
   s.wg = f; f += (kind == K_KDA ? 128 : 0);
   f = (f + 3) & ~3;
   s.tab = f; f += tens ? 2 * 20 : 0;
@@ -156,8 +160,8 @@ __device__ __forceinline__ void prefetch_l2_line(const void* p) {
 #define SQB_MMA_MINB_TFOLD 5
 #endif
 
-template <int KIND, int BITS, int UPG, int DV, int MODE>
-__global__ void __launch_bounds__(NT, MODE == 3 ? (KIND != K_KDA && ((BITS == 8 && UPG == 1) || (BITS == 4 && UPG == 2)) ? SQB_MMA_MINB_TFOLD : SQB_MMA_MINB_FOLD)
+template <int KIND, int BITS, int UPG, int DV, int MODE, bool AXV = false>
+__global__ void __launch_bounds__(NT, MODE == 3 ? (!AXV && KIND != K_KDA && ((BITS == 8 && UPG == 1) || (BITS == 4 && UPG == 2)) ? SQB_MMA_MINB_TFOLD : SQB_MMA_MINB_FOLD)
                                                : (BITS == 4 ? SQB_MMA_MINB4 : SQB_MMA_MINB8))
     step_mma_kernel(const __grid_constant__ StepArgs A, const __grid_constant__ SmemM P, const int nst) {
   constexpr int DK = 128, NG = 4 / UPG, G = 32 * UPG;
@@ -165,8 +169,10 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (KIND != K_KDA && ((BITS == 8 
   constexpr int HPS = 128 / DV;                  // heads per stage
   constexpr int CW = 4;                          // columns per lane in the prologue
   constexpr bool TWO = KIND != K_M2, VDEC = KIND == K_KDA, CANFOLD = MODE == 3;
-  constexpr bool TFMT = !VDEC && ((BITS == 8 && UPG == 1) || (BITS == 4 && UPG == 2));
+  constexpr bool TFMT = !VDEC && (AXV ? BITS == 4 : ((BITS == 8 && UPG == 1) || (BITS == 4 && UPG == 2)));
   static_assert(DV == 64 || DV == 128, "a stage is 128 rows: one or two heads");
+  static_assert(!AXV || (BITS == 4 && UPG == 1 && !VDEC && (MODE == 0 || TFMT)),
+                "scales along v: 4-bit codes, groups of 32 rows (the stage's scales are [4][128], as many bytes as UPG = 1)");
 
   extern __shared__ __align__(128) uint8_t smraw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -226,7 +232,7 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (KIND != K_KDA && ((BITS == 8 
   // a loaded word already waits for it), and a wait never sits in front of fetches that do not depend on it:
   //   warps 0 and 3 need q and k first and the slot only later: their q / k loads leave before the slot index;
   //   warps 1 and 2 issue the bulk copies, which need nothing but the slot index: they load it alone.
-  const int rho = (lane >> 2) * 16 + 4 * warp + (lane & 3);     // this lane's row within a stage
+  const int rho = AXV ? tile_row_v(warp, lane) : (lane >> 2) * 16 + 4 * warp + (lane & 3);     // this lane's row within a stage
   const int hh = rho / DV, rv = rho % DV;                        // head within the stage, row within the head
   Raw4 rq, rk;
   rq.v = make_uint4(0u, 0u, 0u, 0u); rk.v = rq.v; rq.vec = false; rk.vec = false;
@@ -477,8 +483,14 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (KIND != K_KDA && ((BITS == 8 
     uint32_t yq[CW], yk[CW];
 #pragma unroll
     for (int j = 0; j < CW; j++) { yq[j] = fx30_digits(eq[j], fq); yk[j] = TWO ? fx30_digits(ek[j], fk) : 0u; }
-    put_b_words<BITS>(Bfw, lane, 0, yq[0], yq[1], yq[2], yq[3]);
-    put_b_words<BITS>(Bfw, lane, 1, yk[0], yk[1], yk[2], yk[3]);
+    if constexpr (AXV) {                    // every warp scales the vectors by its group's column scales, per stage
+      *reinterpret_cast<float4*>(wq + lane * CW) = make_float4(eq[0], eq[1], eq[2], eq[3]);
+      *reinterpret_cast<float4*>(wk + lane * CW) = make_float4(ek[0], ek[1], ek[2], ek[3]);
+      if (lane == 0) misc[9] = __uint_as_float(0x3C003C00u);      // the fp16 pair (1, 1): the blocks carry no scale
+    } else {
+      put_b_words<BITS>(Bfw, lane, 0, yq[0], yq[1], yq[2], yq[3]);
+      put_b_words<BITS>(Bfw, lane, 1, yk[0], yk[1], yk[2], yk[3]);
+    }
     if (BITS == 4 && !VDEC) {               // the key tile holds bytes: its product takes the byte layout
       put_b_words<8>(Bfw + 256, lane, 0, yq[0], yq[1], yq[2], yq[3]);
       put_b_words<8>(Bfw + 256, lane, 1, yk[0], yk[1], yk[2], yk[3]);
@@ -624,10 +636,12 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (KIND != K_KDA && ((BITS == 8 
 
   // ---- the stages of this key head ----------------------------------------------------------------------------------
   uint32_t bf[8];
-#pragma unroll
-  for (int r = 0; r < 8; r++) bf[r] = Bfw[r * 32 + lane];
   int ci[NG][2];
-  acc_start<BITS, UPG>(bf, ci);
+  if constexpr (!AXV) {
+#pragma unroll
+    for (int r = 0; r < 8; r++) bf[r] = Bfw[r * 32 + lane];
+    acc_start<BITS, UPG>(bf, ci);
+  }
   const float kq = misc[0];
   const int n0 = __float_as_int(misc[1]);                       // live buffer entries of this slot
   const bool FOLD = CANFOLD && n0 == M - 1;                     // this token fills the buffer: fold after the read-out
@@ -692,10 +706,18 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (KIND != K_KDA && ((BITS == 8 
     SQB_STAMP(5 + 3 * (sh & 1));
 
     float tq, tk;
-    tile_pass<BITS, UPG, 16>(smem_u32(st), scs, bf, ci, warp, lane, tq, tk);
+    if constexpr (AXV) {
+      FxScale fq, fk;
+      build_b_v<BITS, TWO>(reinterpret_cast<uint32_t*>(smraw + P.bfv) + warp * 256, scs + warp * 128, wq, wk, lane, bf, fq, fk);
+      tile_pass_v<BITS>(smem_u32(st), reinterpret_cast<const unsigned short*>(misc + 9), bf, warp, lane, tq, tk);
+      tq = (tq * fq.i1) * fq.i2;
+      if (TWO) tk = (tk * fk.i1) * fk.i2;
+    } else {
+      tile_pass<BITS, UPG, 16>(smem_u32(st), scs, bf, ci, warp, lane, tq, tk);
+      tq = (tq * iq1) * iq2;                                  // powers of two: exact
+      if (TWO) tk = (tk * ik1) * ik2;
+    }
     SQB_STAMP(6 + 3 * (sh & 1));
-    tq = (tq * iq1) * iq2;                                    // powers of two: exact
-    if (TWO) tk = (tk * ik1) * ik2;
     if (!VDEC) { tq = alpha * tq; tk = alpha * tk; }
     for (int i = 0; i < n0; i++) {                             // live slots only; dead ones may hold garbage
       const float2 du = dcf[i];
@@ -754,8 +776,12 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (KIND != K_KDA && ((BITS == 8 
             if (i == 0) tab[hq * 20 + 16] = expf(gnew);
           }
           __syncthreads();
-          fold_stage_mma<BITS, UPG, DV>(smem_u32(st), reinterpret_cast<unsigned short*>(st + P.sc_off),
-                                        reinterpret_cast<const int8_t*>(st + P.ub_off), us + sh * HPS * DV, tab, ksf, KBf, warp, lane);
+          if constexpr (AXV)
+            fold_stage_mma_v4<DV>(smem_u32(st), reinterpret_cast<unsigned short*>(st + P.sc_off),
+                                  reinterpret_cast<const int8_t*>(st + P.ub_off), us + sh * HPS * DV, tab, ksf, KBf, warp, lane);
+          else
+            fold_stage_mma<BITS, UPG, DV>(smem_u32(st), reinterpret_cast<unsigned short*>(st + P.sc_off),
+                                          reinterpret_cast<const int8_t*>(st + P.ub_off), us + sh * HPS * DV, tab, ksf, KBf, warp, lane);
           __syncthreads();
           if (warp == 0) {
             // the stage goes back to the slot: eight pieces of codes and the scales, as bulk copies
@@ -767,7 +793,7 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (KIND != K_KDA && ((BITS == 8 
             if (sh + nst < NSH || sh + 1 == NSH) bulk_wait_read();   // before the stage is refilled, and before leaving
           }
         }
-      } else {
+      } else if constexpr (!AXV) {
       float* Lf = fsm + P.L;
       float* fdec = fsm + P.fdec;
       const int LM = fold_lm(M);
