@@ -162,8 +162,10 @@ typedef struct sqb_gga_layout {
   int32_t m;           /* window length */
   int32_t pw;          /* 1: pure-write window on */
   int32_t group;       /* column group of 2-bit row factors (32) */
-  int32_t reserved;
+  int32_t flags;       /* bit 0 (SQB_GGA_ALL_PACKED, a hint that may be left 0): every head of this layer is 4, 6 or 8
+                          bits wide, so the step needs no launch for 2-bit heads and fp16 pivots */
 } sqb_gga_layout_t;
+#define SQB_GGA_ALL_PACKED 1
 
 /* replaces `_fused_step[(BH,)]`, src/statequant/kernels/fold.py:401-407 and slots.py:180-186 */
 int sqb_gdn_step(const sqb_state_t *st, const sqb_gdn_inputs_t *in, void *cuda_stream);

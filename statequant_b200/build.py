@@ -18,7 +18,7 @@ SRC = os.path.join(HERE, 'csrc')
 OUT_DIR = os.path.join(HERE, 'lib')
 OUT = os.path.join(OUT_DIR, 'libstatequant_b200.so')
 UNITS = ['sqb200.cu', 'staged_gdn.cu', 'staged_m2.cu', 'staged_kda.cu', 'fold_launch.cu', 'mma_gdn.cu', 'mma_m2.cu',
-         'mma_kda.cu']
+         'mma_kda.cu', 'gga_reg.cu']
 
 
 def _nvcc():

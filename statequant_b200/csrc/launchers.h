@@ -23,6 +23,9 @@ struct SmemLimit {
     return e;
   }
 };
+struct GgaArgs;
+// the GGA step with the tile in registers (gga_reg.cuh): 0, 1 = shape not taken, -1000 - cudaError
+int launch_gga_reg(const GgaArgs& a, long long ctas, cudaStream_t stream);
 int launch_staged_gdn(const StepArgs& a, int bits, bool axk, cudaStream_t stream);
 int launch_staged_m2(const StepArgs& a, int bits, bool axk, cudaStream_t stream);
 int launch_staged_kda(const StepArgs& a, int bits, bool axk, cudaStream_t stream);

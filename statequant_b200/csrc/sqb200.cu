@@ -427,10 +427,25 @@ int sqb_gga_step(const sqb_gga_layout_t* L, const sqb_gdn_inputs_t* in, void* st
   a.dt_qk = in->qk_dtype; a.dt_v = in->v_dtype; a.dt_ab = in->ab_dtype; a.dt_alog = in->alog_dtype;
   a.dt_dtb = in->dtb_dtype; a.dt_out = in->out_dtype; a.scale = in->scale;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (L->dk == 128 && L->dv == 128) {
-    if (int rc = launch_gga<0>(sqb::gga_step_kernel<128, 128>, a, static_cast<long long>(in->rows) * L->hv, st)) return rc;
-  } else {
-    if (int rc = launch_gga<1>(sqb::gga_step_kernel<0, 0>, a, static_cast<long long>(in->rows) * L->hv, st)) return rc;
+  const long long ctas = static_cast<long long>(in->rows) * L->hv;
+  a.status = status_ptr();
+  if (!a.status) return fail(SQB_ECUDA, "the device status word is not reachable (cudaGetSymbolAddress failed)");
+  // heads of width 4 / 6 / 8 (128 x 128): the register-tile kernel; 2-bit heads, pivots and other shapes: the tile kernel
+  bool reg = L->dk == 128 && L->dv == 128 && g_kernel_path.load(std::memory_order_relaxed) != 1 &&
+             !g_force_generic.load(std::memory_order_relaxed);
+  if (reg) {
+    const int rc = sqb::launch_gga_reg(a, ctas, st);
+    if (rc < 0) return fail(SQB_ECUDA, "kernel launch: %s", cudaGetErrorString(static_cast<cudaError_t>(-rc - 1000)));
+    if (rc == 0) g_launches.fetch_add(1, std::memory_order_relaxed);
+    else reg = false;
+  }
+  a.skip_packed = reg ? 1 : 0;
+  if (!(reg && (L->flags & SQB_GGA_ALL_PACKED))) {
+    if (L->dk == 128 && L->dv == 128) {
+      if (int rc = launch_gga<0>(sqb::gga_step_kernel<128, 128>, a, ctas, st)) return rc;
+    } else {
+      if (int rc = launch_gga<1>(sqb::gga_step_kernel<0, 0>, a, ctas, st)) return rc;
+    }
   }
   if (L->pw) {
     sqb::gga_advance_kernel<<<(in->rows + 127) / 128, 128, 0, st>>>(a.blob, a.stride, a.idx, in->rows, L->m);

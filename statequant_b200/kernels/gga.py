@@ -49,7 +49,7 @@ class GgaLayoutStruct(C.Structure):
     _fields_ = [('blob', C.c_void_p), ('stride', C.c_int64), ('offs', C.c_void_p), ('bits', C.c_void_p),
                 ('w', C.c_void_p), ('qoff', C.c_int64), ('qsz', C.c_int32), ('hv', C.c_int32), ('hk', C.c_int32),
                 ('dk', C.c_int32), ('dv', C.c_int32), ('m', C.c_int32), ('pw', C.c_int32), ('group', C.c_int32),
-                ('reserved', C.c_int32)]
+                ('flags', C.c_int32)]
 
 
 def fit(x, bits, w, group=32, has_two=None):
@@ -144,6 +144,7 @@ class GGAPacked:
         st.qoff, st.qsz = self.QOFF, self.QSZ
         st.hv, st.hk, st.dk, st.dv, st.m, st.pw, st.group = self.HV, self.HK, self.DK, self.DV, self.m, int(self.pw), \
             self.method.group
+        st.flags = int(all(x in (4, 6, 8) for x in self.tables[layer][1]))         # SQB_GGA_ALL_PACKED
         return st
 
     def step(self, views, idx, q, k, v, out, scale, *, g=None, beta=None, gate=None, layer=None, fused=None):
