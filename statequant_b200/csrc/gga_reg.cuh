@@ -316,26 +316,22 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
     if (lane == 0) (warp == 0 ? PS : VS)[jn] = sc;
   }
   // ---- the fit: row factors r = half(sqrt(max(mean |x|, 1e-20) / w)) ----
-  // Range check for div_h16 on the way: every row sum below 1e14 (so every |x| is), and the smallest non-zero |x|
-  // above 1e-30 (compared on the bit patterns shifted left by one, zero wrapping around to the largest value).
+  // Range check for div_h16 on the way: every row sum below 1e14 (so every |x| is).  No lower bound is needed here: a
+  // quotient x / r that is an ulp off can only come from |x| < 1e-30, and such an element weighs nothing in what
+  // follows: its code is 0 whatever the last bit (|x / r / c| < 1e-15 with factors of at least 2^-24), it adds zero to
+  // the refit's sums, and a column whose maximum it is gets the smallest factor 2^-24 either way.
   bool bad;
   {
     float s[16];
-    uint32_t lou = 0xFFFFFFFFu;
 #pragma unroll
-    for (int r = 0; r < 16; r++) {
-      s[r] = (fabsf(x[r][0].x) + fabsf(x[r][0].y)) + (fabsf(x[r][1].x) + fabsf(x[r][1].y));
-      lou = min(lou, min(min((__float_as_uint(x[r][0].x) << 1) - 1u, (__float_as_uint(x[r][0].y) << 1) - 1u),
-                         min((__float_as_uint(x[r][1].x) << 1) - 1u, (__float_as_uint(x[r][1].y) << 1) - 1u)));
-    }
+    for (int r = 0; r < 16; r++) s[r] = (fabsf(x[r][0].x) + fabsf(x[r][0].y)) + (fabsf(x[r][1].x) + fabsf(x[r][1].y));
     const float tot = transpose_sum16(s, lane);
     const int rr_ = row0 + transpose_row16(lane);
     const float rf = halfc(__fsqrt_rn(__fdiv_rn(fmaxf(tot * (1.0f / RD), 1e-20f), C.w[rr_])));
     if (!(lane & 1)) { C.rs[rr_] = rf; C.rrs[rr_] = __frcp_rn(rf); }
-    bad = !(tot < 1e14f) || lou <= ((__float_as_uint(1e-30f) << 1) - 1u);
+    bad = !(tot < 1e14f);
   }
   bad = __syncthreads_or(bad);
-  uint32_t pk[16];                                     // this lane's packed codes, row by row
   if (!bad) {
     // ---- column factors c = half(max |x / r| / qmax) ----
     {
@@ -350,33 +346,43 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
       *reinterpret_cast<float4*>(C.pa + warp * RD + col0) = make_float4(m0, m1, m2, m3);
     }
     __syncthreads();
+    bool big = false;
     if (tid < RD) {
       float mm = C.pa[tid];
 #pragma unroll
       for (int w = 1; w < RNW; w++) mm = fmaxf(mm, C.pa[w * RD + tid]);
-      const float c0 = halfc(__fdiv_rn(mm, qmax));
+      const float cq = __fdiv_rn(mm, qmax);
+      const float c0 = halfc(cq);
       C.cs[tid] = c0;
       C.rcs[tid] = __frcp_rn(c0);
+      big = !(cq <= 65504.0f);                         // the factor is cut at fp16's largest value: quotients pass qmax
     }
-    __syncthreads();
-    // ---- one weighted least-squares refit of c with the codes fixed ----
+    // Unless a column factor was cut, |x / r / c| <= qmax (1 + 2^-10) for every element and the refit's codes need no clamp.
+    bad = __syncthreads_or(big);
+  }
+  if (!bad) {
+    // ---- one weighted least-squares refit of c with the codes fixed; x / r replaces x on the way ----
     {
       const float4 c4 = *reinterpret_cast<const float4*>(C.cs + col0), rc4 = *reinterpret_cast<const float4*>(C.rcs + col0);
       const float2 ca = make_float2(c4.x, c4.y), cb = make_float2(c4.z, c4.w), nca = make_float2(-c4.x, -c4.y),
                    ncb = make_float2(-c4.z, -c4.w), rca = make_float2(rc4.x, rc4.y), rcb = make_float2(rc4.z, rc4.w);
+      const float2 mg = make_float2(MAGIC, MAGIC), nmg = make_float2(-MAGIC, -MAGIC);
       float2 n0 = make_float2(0.f, 0.f), n1 = n0, d0 = n0, d1 = n0;
 #pragma unroll
       for (int r = 0; r < 16; r++) {
         const float rv = C.rs[row0 + r], ri = C.rrs[row0 + r], wv = C.w[row0 + r];
         const float ww = wv * wv;
         const float2 d = make_float2(rv, rv), nd = make_float2(-rv, -rv), rd = make_float2(ri, ri), w2 = make_float2(ww, ww);
-        const float2 z0 = rint_clamp2(div_h16x2(div_h16x2(x[r][0], d, nd, rd), ca, nca, rca), qmax);
-        const float2 z1 = rint_clamp2(div_h16x2(div_h16x2(x[r][1], d, nd, rd), cb, ncb, rcb), qmax);
+        const float2 y0 = div_h16x2(x[r][0], d, nd, rd), y1 = div_h16x2(x[r][1], d, nd, rd);
+        const float2 z0 = __fadd2_rn(__fadd2_rn(div_h16x2(y0, ca, nca, rca), mg), nmg);      // rint
+        const float2 z1 = __fadd2_rn(__fadd2_rn(div_h16x2(y1, cb, ncb, rcb), mg), nmg);
         const float2 v0 = __fmul2_rn(d, z0), v1 = __fmul2_rn(d, z1);
         n0 = __fadd2_rn(n0, __fmul2_rn(__fmul2_rn(w2, v0), x[r][0]));
         n1 = __fadd2_rn(n1, __fmul2_rn(__fmul2_rn(w2, v1), x[r][1]));
         d0 = __fadd2_rn(d0, __fmul2_rn(w2, __fmul2_rn(v0, v0)));
         d1 = __fadd2_rn(d1, __fmul2_rn(w2, __fmul2_rn(v1, v1)));
+        x[r][0] = y0;
+        x[r][1] = y1;
       }
       *reinterpret_cast<float4*>(C.pa + warp * RD + col0) = make_float4(n0.x, n0.y, n1.x, n1.y);
       *reinterpret_cast<float4*>(C.pb + warp * RD + col0) = make_float4(d0.x, d0.y, d1.x, d1.y);
@@ -392,7 +398,8 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
     }
     __syncthreads();
     // ---- the codes with the refitted c: clamp, then round by adding 1.5 * 2^23 + 2^(B-1) (an even constant, so
-    // ties still go to even codes): the sum's low B bits are code + qmax + 1, the bits above them up to bit 15 clear ----
+    // ties still go to even codes): the sum's low B bits are code + qmax + 1, the bits above them up to bit 15 clear.
+    // They go straight into the head's bytes (every thread is long past reading them). ----
     {
       const float4 c4 = *reinterpret_cast<const float4*>(C.cs + col0), rc4 = *reinterpret_cast<const float4*>(C.rcs + col0);
       const float2 ca = make_float2(c4.x, c4.y), cb = make_float2(c4.z, c4.w), nca = make_float2(-c4.x, -c4.y),
@@ -401,20 +408,21 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
       const float2 mg = make_float2(MG, MG);
 #pragma unroll
       for (int r = 0; r < 16; r++) {
-        const float rv = C.rs[row0 + r], ri = C.rrs[row0 + r];
-        const float2 d = make_float2(rv, rv), nd = make_float2(-rv, -rv), rd = make_float2(ri, ri);
-        float2 y0 = div_h16x2(div_h16x2(x[r][0], d, nd, rd), ca, nca, rca);
-        float2 y1 = div_h16x2(div_h16x2(x[r][1], d, nd, rd), cb, ncb, rcb);
+        float2 y0 = div_h16x2(x[r][0], ca, nca, rca), y1 = div_h16x2(x[r][1], cb, ncb, rcb);     // x holds x / r by now
         y0 = make_float2(fminf(fmaxf(y0.x, -qmax), qmax), fminf(fmaxf(y0.y, -qmax), qmax));
         y1 = make_float2(fminf(fmaxf(y1.x, -qmax), qmax), fminf(fmaxf(y1.y, -qmax), qmax));
         const float2 t0 = __fadd2_rn(y0, mg), t1 = __fadd2_rn(y1, mg);
         const uint32_t b0 = __float_as_uint(t0.x), b1 = __float_as_uint(t0.y), b2 = __float_as_uint(t1.x), b3 = __float_as_uint(t1.y);
         if constexpr (B == 8) {
-          pk[r] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410) - 0x01010101u;
+          *reinterpret_cast<uint32_t*>(C.raw + (row0 + r) * 128 + 4 * lane) =
+              __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410) - 0x01010101u;
         } else if constexpr (B == 4) {
-          pk[r] = (b0 + (b1 << 4) + (b2 << 8) + (b3 << 12)) - 0x1111u;
+          *reinterpret_cast<unsigned short*>(C.raw + (row0 + r) * 64 + 2 * lane) =
+              static_cast<unsigned short>((b0 + (b1 << 4) + (b2 << 8) + (b3 << 12)) - 0x1111u);
         } else {
-          pk[r] = ((b0 & 0xFFFFu) + (b1 << 6) + (b2 << 12) + (b3 << 18)) - 0x41041u;
+          const uint32_t wd = ((b0 & 0xFFFFu) + (b1 << 6) + (b2 << 12) + (b3 << 18)) - 0x41041u;
+          uint8_t* t = C.raw + (row0 + r) * 96 + 3 * lane;
+          t[0] = static_cast<uint8_t>(wd & 255u); t[1] = static_cast<uint8_t>((wd >> 8) & 255u); t[2] = static_cast<uint8_t>((wd >> 16) & 255u);
         }
       }
     }
@@ -424,26 +432,16 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
 #pragma unroll
     for (int r = 0; r < 16; r++) { xc[4 * r] = x[r][0].x; xc[4 * r + 1] = x[r][0].y; xc[4 * r + 2] = x[r][1].x; xc[4 * r + 3] = x[r][1].y; }
     gga_reg_fit_cold<B>(xc, uc, C.rs, C.w, C.cs, C.pa, C.pb, warp, lane);
-#pragma unroll
-    for (int r = 0; r < 16; r++)
-      pk[r] = uc[4 * r] | (static_cast<uint32_t>(uc[4 * r + 1]) << B) | (static_cast<uint32_t>(uc[4 * r + 2]) << (2 * B)) |
-              (static_cast<uint32_t>(uc[4 * r + 3]) << (3 * B));
-  }
-  // ---- the head's bytes, rebuilt in place: codes, row factors, column factors ----
-#pragma unroll
-  for (int r = 0; r < 16; r++) {
-    if constexpr (B == 8) *reinterpret_cast<uint32_t*>(C.raw + (row0 + r) * 128 + 4 * lane) = pk[r];
-    else if constexpr (B == 4) *reinterpret_cast<unsigned short*>(C.raw + (row0 + r) * 64 + 2 * lane) = static_cast<unsigned short>(pk[r]);
-    else {
-      uint8_t* t = C.raw + (row0 + r) * 96 + 3 * lane;
-      t[0] = static_cast<uint8_t>(pk[r] & 255u); t[1] = static_cast<uint8_t>((pk[r] >> 8) & 255u); t[2] = static_cast<uint8_t>((pk[r] >> 16) & 255u);
-    }
+    for (int r = 0; r < 16; r++) gga_reg_put<B>(C.raw, row0 + r, lane, uc[4 * r], uc[4 * r + 1], uc[4 * r + 2], uc[4 * r + 3]);
   }
   unsigned short* Rw = reinterpret_cast<unsigned short*>(C.raw + RD * ROWB);
   if (tid < RD) { Rw[tid] = f2h(C.rs[tid]); Rw[RD + tid] = f2h(C.cs[tid]); }
 }
 
-__global__ void __launch_bounds__(RNT, 2) gga_step_reg_kernel(const __grid_constant__ GgaArgs A) {
+#ifndef SQB_GGA_REG_MINB
+#define SQB_GGA_REG_MINB 2
+#endif
+__global__ void __launch_bounds__(RNT, SQB_GGA_REG_MINB) gga_step_reg_kernel(const __grid_constant__ GgaArgs A) {
   extern __shared__ __align__(128) uint8_t rsm[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int HV = A.HV, M = A.M;
