@@ -178,12 +178,13 @@ def register():
         from . import binding
         binding.bind_reference()
         from statequant.integrations import vllm_plugin as ref_plugin
-    except ImportError:
-        patch_calculators()
-        _STATE['registered'] = 'calculators-only'
-        raise NotImplementedError(
-            'statequant_b200: the packed slot sizes are registered with vLLM, but the layer forward hooks are the '
-            "reference package's Python (statequant.integrations.vllm_plugin, vLLM >= 0.32); install it next to this "
-            'package and its plugin will run on these kernels') from None
+    except ImportError as err:
+        # The layer forward hooks are the reference package's own Python (statequant.integrations.vllm_plugin); without
+        # it nothing of vLLM is touched: no calculator is patched, the engine runs its stock state.
+        import warnings
+        warnings.warn('statequant_b200: STATEQUANT_VLLM is set but the statequant package, whose vLLM layer hooks run '
+                      f'on these kernels, cannot be imported ({err}); vLLM is left unchanged', RuntimeWarning, stacklevel=2)
+        _STATE['registered'] = 'skipped'
+        return
     ref_plugin.register()
     _STATE['registered'] = True

@@ -100,3 +100,25 @@ def test_bind_reference_rebinds_a_package(tmp_path, monkeypatch):
     assert FK.PackedGDNState is sq.kernels.PackedGDNState and FS.SlotLayout is SlotLayout
     assert FG.GGAPacked is GGAPacked and fit is our_fit
     assert ('fakeref.kernels', 'pack_vk') in done and binding.bind_reference('fakeref') is done
+
+
+def test_register_without_the_reference_package_leaves_vllm_alone():
+    """STATEQUANT_VLLM set, `statequant` not importable: a warning, no calculator patched, no exception."""
+    import subprocess
+    import sys
+    code = (
+        "import sys, warnings\n"
+        "sys.modules['statequant'] = None\n"                      # import statequant -> ImportError
+        "from statequant_b200.integrations import vllm_plugin as p\n"
+        "with warnings.catch_warnings(record=True) as w:\n"
+        "    warnings.simplefilter('always')\n"
+        "    p.register()\n"
+        "assert any('left unchanged' in str(x.message) for x in w), [str(x.message) for x in w]\n"
+        "assert p._STATE.get('registered') == 'skipped'\n"
+        "p.register()\n"                                          # idempotent
+        "print('ok')\n")
+    env = dict(os.environ, STATEQUANT_VLLM='pace4')
+    env.pop('STATEQUANT_REF_SRC', None)
+    r = subprocess.run([sys.executable, '-c', code], capture_output=True, text=True, env=env,
+                       cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0 and 'ok' in r.stdout, r.stdout + r.stderr
