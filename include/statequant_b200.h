@@ -208,14 +208,22 @@ const char *sqb_last_error(void);
 int sqb_abi_version(void);
 /* number of kernel launches issued by this library in this process (all threads) */
 int64_t sqb_launch_count(void);
-/* tuning / test switches.  "kernel_path" selects the kernel of the decode steps: 0 the best one for the shape
-   (default), 1 the generic kernel (direct loads, folds inside its own launch; any supported shape), 2 the staged
-   kernel (one CTA per batch row and key head, the state staged through shared memory by bulk async copies) followed
-   by the fold launch, falling back to 1 for shapes it does not take.  "force_generic_kernel" = 1 is the same as
-   kernel_path 1.  All give the same bytes. */
+/* tuning / test switches.
+   "kernel_path" selects the kernel of the decode steps: 0 the best one for the shape (default); 1 the generic kernel
+   (direct loads, folds inside its own launch; any supported shape); 2 the staged SIMT kernel (one CTA per batch row
+   and key head, the state staged through shared memory by bulk async copies) followed by the fold launch; 3 the
+   tensor-core kernel (the state pass as integer mma.sync products) followed by the fold launch; 4 the tensor-core
+   kernel with the fold of a slot's m-th token inside its launch (what 0 picks wherever the shape allows).  A path
+   that does not take a shape falls through to the next lower one.  "force_generic_kernel" = 1 is the same as
+   kernel_path 1 (and sends every GGA head to the tile kernel).  The paths agree up to the order of fp32 sums.
+   "wait_limit_us": how long a device-side wait for a bulk copy may last before the CTA gives up (default 1 s).
+   "mma_heads_per_cta": value heads a CTA of the tensor-core kernels takes (0: the default, two stages of 128 rows).
+   "mma_prefetch_dist": L2 prefetch distance in CTAs for the tensor-core kernels (0: off, the default; -1: one wave).
+   "test_extra_tx": test hook; bytes a stage barrier is told to expect beyond what is copied, so that its wait runs
+   out (a multiple of 16; 0 in any real run). */
 int sqb_set_option(const char *name, int value);
 /* Device-side health word of the current device (synchronises): the number of CTAs whose wait for a bulk copy ran
-   out of its iteration budget since the library was loaded.  0 in a healthy run. */
+   out of its time limit since the library was loaded (such a CTA zeroes its output rows and touches no slot).  0 in a healthy run. */
 int sqb_device_status(int *wait_timeouts);
 
 #ifdef __cplusplus

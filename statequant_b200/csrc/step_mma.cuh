@@ -272,6 +272,14 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (!AXV && KIND != K_KDA && ((BI
   float* GBseq = reinterpret_cast<float*>(A.GB + seq * A.sGB);
   float* GCseq = reinterpret_cast<float*>(A.GCUR + seq * A.sGC);
   const uint32_t stage_tx = 128 * ROWB + 128 * NG * 2 + M * 128 + A.test_extra_tx;
+  // KDA: this token's log decays and the slot's running ones, the lane's four channels (warps 0 and 3), as raw bits
+  Raw4 rgk;
+  rgk.v = make_uint4(0u, 0u, 0u, 0u); rgk.vec = false;
+  float4 gck = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (VDEC && (warp == 0 || warp == 3)) {
+    rgk = ld4_raw(A.g + (long long)b * A.sg, A.dt_g, (long long)h0 * DK + lane * CW);
+    gck = *reinterpret_cast<const float4*>(GCseq + (long long)h0 * DK + lane * CW);
+  }
 
   // the copies of stage `sh` into ring position s, one per lane (lanes 0..9 of the calling warp)
   auto issue_stage = [&](int s, int sh, int l) {
@@ -437,14 +445,17 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (!AXV && KIND != K_KDA && ((BI
     float qr[CW], kr[CW];
     cvt4_raw(rq, A.dt_qk, qr);
     cvt4_raw(rk, A.dt_qk, kr);
-    float gnr[CW];
+    float gnr[CW] = {0.f, 0.f, 0.f, 0.f};
     float s0 = 0.f, s1 = 0.f;
+    if constexpr (VDEC) {
+      float gin[CW];
+      cvt4_raw(rgk, A.dt_g, gin);
+      gnr[0] = gck.x + gin[0]; gnr[1] = gck.y + gin[1]; gnr[2] = gck.z + gin[2]; gnr[3] = gck.w + gin[3];
+    }
 #pragma unroll
     for (int j = 0; j < CW; j++) {
       s0 += qr[j] * qr[j];
       s1 += kr[j] * kr[j];
-      if (VDEC) gnr[j] = GCseq[(long long)h0 * DK + lane * CW + j] +
-                         ldf(A.g + (long long)b * A.sg, A.dt_g, (long long)h0 * DK + lane * CW + j);
     }
     SQB_STAMP(1);
     if (KIND != K_M2) {
@@ -567,14 +578,15 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (!AXV && KIND != K_KDA && ((BI
     } else {
       // KDA: dot products of the buffered keys (times their per-channel decay ratios) with q and k, in fp32, from
       // this warp's own copy of the normalised vectors (same arithmetic as warp 0, so the same bits)
-      constexpr int QD = DK / 4;
-      float gnr[CW];
+      float gnr[CW], gin[CW];
+      cvt4_raw(rgk, A.dt_g, gin);
+      const float gcu[CW] = {gck.x, gck.y, gck.z, gck.w};
       float s0 = 0.f, s1 = 0.f;
 #pragma unroll
       for (int j = 0; j < CW; j++) {
         s0 += qr[j] * qr[j];
         s1 += kr[j] * kr[j];
-        gnr[j] = GCseq[(long long)h0 * DK + lane * CW + j] + ldf(A.g + (long long)b * A.sg, A.dt_g, (long long)h0 * DK + lane * CW + j);
+        gnr[j] = gcu[j] + gin[j];
       }
       s0 = warp_sum(s0);
       s1 = warp_sum(s1);
@@ -586,37 +598,8 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (!AXV && KIND != K_KDA && ((BI
         wg[lane * CW + j] = gnr[j];
       }
       __syncwarp();
-      asm volatile("bar.sync 1, 64;" ::: "memory");           // warp 2 has armed the key tile's barrier
-      const bool landed = mbar_wait(&bars[nst], 0, A.wait_ns);
-      if (lane == 0) misc[2] = landed ? 0.f : 1.f;          // "a copy never arrived" flag
-      const int n0 = __float_as_int(misc[1]);
-      const float ksl = ksv[lane];
-      for (int i0 = 0; i0 < M; i0 += 8) {
-        const int i = i0 + (lane >> 2), part = lane & 3;
-        const float ks_i = __shfl_sync(0xffffffffu, ksl, i & 31);
-        float dq = 0.f, dk = 0.f;
-        if (i < n0) {
-#pragma unroll
-          for (int j0 = 0; j0 < QD; j0 += 4) {
-            const int k = part * QD + j0;
-            float kv[4];
-            const uint32_t wx = *reinterpret_cast<const uint32_t*>(kbt + i * DK + k) ^ 0x80808080u;
-            kv[0] = byte_to_f<0>(wx) * ks_i; kv[1] = byte_to_f<1>(wx) * ks_i;
-            kv[2] = byte_to_f<2>(wx) * ks_i; kv[3] = byte_to_f<3>(wx) * ks_i;
-            const float4 q4 = *reinterpret_cast<const float4*>(wq + k);
-            const float4 k4 = *reinterpret_cast<const float4*>(wk + k);
-            const float4 g4v = *reinterpret_cast<const float4*>(wg + k);
-            const float4 b4 = *reinterpret_cast<const float4*>(gbt + i * DK + k);
-            kv[0] = kv[0] * expf(g4v.x - b4.x); kv[1] = kv[1] * expf(g4v.y - b4.y);
-            kv[2] = kv[2] * expf(g4v.z - b4.z); kv[3] = kv[3] * expf(g4v.w - b4.w);
-            dq = fmaf(kv[0], q4.x, dq); dq = fmaf(kv[1], q4.y, dq); dq = fmaf(kv[2], q4.z, dq); dq = fmaf(kv[3], q4.w, dq);
-            dk = fmaf(kv[0], k4.x, dk); dk = fmaf(kv[1], k4.y, dk); dk = fmaf(kv[2], k4.z, dk); dk = fmaf(kv[3], k4.w, dk);
-          }
-        }
-        dq += __shfl_xor_sync(0xffffffffu, dq, 1); dq += __shfl_xor_sync(0xffffffffu, dq, 2);
-        dk += __shfl_xor_sync(0xffffffffu, dk, 1); dk += __shfl_xor_sync(0xffffffffu, dk, 2);
-        if (part == 0 && i < M) dqk[i] = make_float2(dq, dk);
-      }
+      asm volatile("bar.sync 1, 64;" ::: "memory");           // pairs with warp 2's arrival
+      if (lane == 0) misc[2] = 0.f;                          // (the key tile's wait follows the block barrier)
     }
   }
   SQB_STAMP(3);
@@ -633,6 +616,41 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (!AXV && KIND != K_KDA && ((BI
     }
   };
   if (misc[2] != 0.f) { bail(); return; }
+  if constexpr (VDEC) {
+    // KDA: dot products of the buffered keys (times their per-channel decay ratios) with q and k, in fp32: two slots
+    // per warp and pass, sixteen lanes per slot, eight channels per lane
+    constexpr int QD = 8;
+    const bool landed = mbar_wait(&bars[nst], 0, A.wait_ns);
+    const int nlive = __float_as_int(misc[1]);
+    for (int i0 = 0; i0 < M; i0 += 8) {
+      const int i = i0 + 2 * warp + (lane >> 4), k = (lane & 15) * QD;
+      float dq = 0.f, dk = 0.f;
+      if (landed && i < nlive) {
+        const float ks_i = ksv[i];
+        const uint2 cw = *reinterpret_cast<const uint2*>(kbt + i * DK + k);
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+          const uint32_t wx = (hf ? cw.y : cw.x) ^ 0x80808080u;
+          float kv[4] = {byte_to_f<0>(wx) * ks_i, byte_to_f<1>(wx) * ks_i, byte_to_f<2>(wx) * ks_i, byte_to_f<3>(wx) * ks_i};
+          const float4 q4 = *reinterpret_cast<const float4*>(wq + k + 4 * hf);
+          const float4 k4 = *reinterpret_cast<const float4*>(wk + k + 4 * hf);
+          const float4 g4v = *reinterpret_cast<const float4*>(wg + k + 4 * hf);
+          const float4 b4 = *reinterpret_cast<const float4*>(gbt + i * DK + k + 4 * hf);
+          kv[0] = kv[0] * expf(g4v.x - b4.x); kv[1] = kv[1] * expf(g4v.y - b4.y);
+          kv[2] = kv[2] * expf(g4v.z - b4.z); kv[3] = kv[3] * expf(g4v.w - b4.w);
+          dq = fmaf(kv[0], q4.x, dq); dq = fmaf(kv[1], q4.y, dq); dq = fmaf(kv[2], q4.z, dq); dq = fmaf(kv[3], q4.w, dq);
+          dk = fmaf(kv[0], k4.x, dk); dk = fmaf(kv[1], k4.y, dk); dk = fmaf(kv[2], k4.z, dk); dk = fmaf(kv[3], k4.w, dk);
+        }
+      }
+#pragma unroll
+      for (int o = 1; o < 16; o <<= 1) {
+        dq += __shfl_xor_sync(0xffffffffu, dq, o);
+        dk += __shfl_xor_sync(0xffffffffu, dk, o);
+      }
+      if ((lane & 15) == 0 && i < M) dqk[i] = make_float2(dq, dk);
+    }
+    if (__syncthreads_or(!landed)) { bail(); return; }
+  }
 
   // ---- the stages of this key head ----------------------------------------------------------------------------------
   uint32_t bf[8];
