@@ -71,13 +71,42 @@ __device__ __forceinline__ void build_key_frags(uint32_t* KBf, const int8_t* kbt
   }
 }
 
+
+// KDA: the fold's right factor is the buffered key times its per-channel decay ratio, an fp32 value:
+//     Kd_i[k] = (code_i[k] ks_i) exp(gnew[k] - G_i[k])          (slot 7: this token's key, ratio 1)
+// cut into three bf16 pieces like L.  Three planes of fragments, KBf[p * NSPAN * NQ * 32 + x], x as in build_key_frags.
+// gbt: the slot's buffered log decays [8][128] fp32; ga: gnew [128]; ksf: key scales of slots 0..6, [7] = this token's.
+template <int BITS>
+__device__ __forceinline__ void build_key_frags_kda(uint32_t* KBf, const int8_t* kbt, const int8_t* kcur, const float* gbt,
+                                                    const float* ga, const float* ksf, int tid) {
+  constexpr int NQ = BITS == 8 ? 4 : 8, NSPAN = BITS == 8 ? 4 : 2, PLANE = NSPAN * NQ * 32;
+  for (int x = tid; x < PLANE; x += NT) {
+    const int l = x & 31, q = (x >> 5) % NQ, j = x / (32 * NQ);
+    const int col = fold_col<BITS>(j, q, l >> 2), s0 = 2 * (l & 3);
+    const float g = ga[col];
+    const float k0 = (static_cast<float>(kbt[s0 * 128 + col]) * ksf[s0]) * expf(g - gbt[s0 * 128 + col]);
+    const float k1 = s0 + 1 == 7 ? static_cast<float>(kcur[col]) * ksf[7]
+                                 : (static_cast<float>(kbt[(s0 + 1) * 128 + col]) * ksf[s0 + 1]) * expf(g - gbt[(s0 + 1) * 128 + col]);
+    float a1, a2, a3, b1, b2, b3;
+    split3(k0, a1, a2, a3);
+    split3(k1, b1, b2, b3);
+    KBf[x] = bf2(a1, b1);
+    KBf[PLANE + x] = bf2(a2, b2);
+    KBf[2 * PLANE + x] = bf2(a3, b3);
+  }
+}
+
 // Folds the 32 rows of warp w (row blocks 2w and 2w + 1) of a stage.  HPS heads of d_v = 128 / HPS rows per stage.
 //   st_addr / scs: the stage's codes (padded pieces) and scales [row][NG] in shared memory, both rewritten in place
 //   ubt: the stage's buffered values [HPS][8][DV] int8 (slots 0..6); udq: this token's rounded values [HPS][DV]
 //   tab: per head of the stage 8 floats dec_i (dec_7 unused), 8 floats value scales, then alpha; ksf: key scales [8]
-template <int BITS, int UPG, int DV>
+// VDEC (KDA): decays per key channel: the start value is (code scale) ae[k], ae = exp(gnew); L carries no decay and no
+// key scale (both are in the key fragments, three bf16 planes: build_key_frags_kda), and a product L Kd is taken as
+// p1 r1 + p1 r2 + p2 r1 + p1 r3 + p2 r2 + p3 r1 (the three terms left out are below 2^-24 of it).
+template <int BITS, int UPG, int DV, bool VDEC = false>
 __device__ __forceinline__ void fold_stage_mma(uint32_t st_addr, unsigned short* scs, const int8_t* ubt, const float* udq,
-                                               const float* tab, const float* ksf, const uint32_t* KBf, int w, int lane) {
+                                               const float* tab, const float* ksf, const uint32_t* KBf, int w, int lane,
+                                               const float* ae = nullptr) {
   constexpr int NG = 4 / UPG, ROWB = 128 * BITS / 8, PITCH = 16 * ROWB + 16;
   constexpr int NQ = BITS == 8 ? 4 : 8, NSPAN = BITS == 8 ? 4 : 2, TABW = 20;
   constexpr float QMAX = BITS == 4 ? 7.0f : 127.0f, MB = BITS == 4 ? MAGIC + 8.0f : MAGIC;
@@ -103,7 +132,7 @@ __device__ __forceinline__ void fold_stage_mma(uint32_t st_addr, unsigned short*
         float L;
         if (s < 7) L = tb[s] * (static_cast<float>(ubt[(hh * 8 + s) * DV + rv0 + r]) * tb[8 + s]);
         else L = udq[hh * DV + rv0 + r];
-        split3(L * ksf[s], p1[e], p2[e], p3[e]);
+        split3(VDEC ? L : L * ksf[s], p1[e], p2[e], p3[e]);
       }
       A1[r] = bf2(p1[0], p1[1]); A2[r] = bf2(p2[0], p2[1]); A3[r] = bf2(p3[0], p3[1]);
     }
@@ -118,6 +147,11 @@ __device__ __forceinline__ void fold_stage_mma(uint32_t st_addr, unsigned short*
       // ---- start values: (code * scale) * alpha; code * scale is exact in fp32, so this rounds once, as the
       // reference's two multiplications do ----
       const float2 al2 = make_float2(alphan, alphan);
+      // the decay of N-block q's column pair: per head, or (KDA) per key channel
+      auto decay_of = [&](int q) -> float2 {
+        if constexpr (VDEC) return *reinterpret_cast<const float2*>(ae + fold_col<BITS>(j, q, 2 * t));
+        else return al2;
+      };
       if constexpr (BITS == 8) {
         // byte u = code + 128 lands in bits 8..15 of 2^23's mantissa: the float is 2^23 + 256 u, and
         // fma(that, scale / 256, -(2^23 + 2^15) scale / 256) is code * scale with every intermediate exact
@@ -136,8 +170,8 @@ __device__ __forceinline__ void fold_stage_mma(uint32_t st_addr, unsigned short*
             a = make_float2(__uint_as_float(__byte_perm(wa, 0x4B000000u, 0x7404)), __uint_as_float(__byte_perm(wa, 0x4B000000u, 0x7414)));
             c = make_float2(__uint_as_float(__byte_perm(wb, 0x4B000000u, 0x7404)), __uint_as_float(__byte_perm(wb, 0x4B000000u, 0x7414)));
           }
-          a = __fmul2_rn(__ffma2_rn(a, m0, c0), al2);
-          c = __fmul2_rn(__ffma2_rn(c, m1, c1), al2);
+          a = __fmul2_rn(__ffma2_rn(a, m0, c0), decay_of(q));
+          c = __fmul2_rn(__ffma2_rn(c, m1, c1), decay_of(q));
           acc[q][0] = a.x; acc[q][1] = a.y; acc[q][2] = c.x; acc[q][3] = c.y;
         }
       } else {
@@ -167,9 +201,9 @@ __device__ __forceinline__ void fold_stage_mma(uint32_t st_addr, unsigned short*
           c[3] = make_float2(nib_f<0x000000F0u>(w1s, K), nib_f<0x00000F00u>(w1s, K));
 #pragma unroll
           for (int i = 0; i < 4; i++) {
-            const float2 av = __fmul2_rn(__fmul2_rn(__fadd2_rn(a[i], bias[i]), f0[i]), al2);
-            const float2 cv = __fmul2_rn(__fmul2_rn(__fadd2_rn(c[i], bias[i]), f1[i]), al2);
             const int q = hx * 4 + i;
+            const float2 av = __fmul2_rn(__fmul2_rn(__fadd2_rn(a[i], bias[i]), f0[i]), decay_of(q));
+            const float2 cv = __fmul2_rn(__fmul2_rn(__fadd2_rn(c[i], bias[i]), f1[i]), decay_of(q));
             acc[q][0] = av.x; acc[q][1] = av.y; acc[q][2] = cv.x; acc[q][3] = cv.y;
           }
         }
@@ -177,9 +211,18 @@ __device__ __forceinline__ void fold_stage_mma(uint32_t st_addr, unsigned short*
       // ---- the eight buffer slots ----
 #pragma unroll
       for (int q = 0; q < NQ; q++) {
-        const uint32_t kw = KBf[(j * NQ + q) * 32 + lane];
-        mma_bf16(acc[q], A1[0], A1[1], A2[0], A2[1], kw, kw);
-        mma_bf16(acc[q], A3[0], A3[1], 0u, 0u, kw, kw);
+        if constexpr (VDEC) {
+          constexpr int PLANE = NSPAN * NQ * 32;
+          const uint32_t r1 = KBf[(j * NQ + q) * 32 + lane], r2 = KBf[PLANE + (j * NQ + q) * 32 + lane],
+                         r3 = KBf[2 * PLANE + (j * NQ + q) * 32 + lane];
+          mma_bf16(acc[q], A1[0], A1[1], A1[0], A1[1], r1, r2);      // p1 r1 + p1 r2
+          mma_bf16(acc[q], A2[0], A2[1], A1[0], A1[1], r1, r3);      // p2 r1 + p1 r3
+          mma_bf16(acc[q], A2[0], A2[1], A3[0], A3[1], r2, r1);      // p2 r2 + p3 r1
+        } else {
+          const uint32_t kw = KBf[(j * NQ + q) * 32 + lane];
+          mma_bf16(acc[q], A1[0], A1[1], A2[0], A2[1], kw, kw);
+          mma_bf16(acc[q], A3[0], A3[1], 0u, 0u, kw, kw);
+        }
       }
       // ---- fresh scales: absmax over the group = this span, over the quad ----
       float am0 = 0.f, am1 = 0.f;

@@ -46,7 +46,7 @@ struct SmemM {
 // (axv: 4-bit codes scaled along v in groups of 32 rows, fold_stage_mma_v4.)
 __host__ __device__ inline bool fold_on_tensor_pipe(int kind, int bits, int upg, int M, bool axv = false) {
   if (axv) return kind != K_KDA && M == 8 && bits == 4;
-  return kind != K_KDA && M == 8 && ((bits == 8 && upg == 1) || (bits == 4 && upg == 2));
+  return M == 8 && ((bits == 8 && upg == 1) || (bits == 4 && upg == 2));
 }
 __host__ __device__ inline SmemM smemm_plan(int kind, int bits, int upg, int DV, int M, int nst, int gqa, bool fold,
                                             bool axv = false) {
@@ -63,7 +63,7 @@ __host__ __device__ inline SmemM smemm_plan(int kind, int bits, int upg, int DV,
   s.gbt = o; o += (kind == K_KDA ? M * 128 * 4 : 0);
   s.bf = o; o += (bits == 4 && kind != K_KDA) ? 2048 : 1024;   // B fragments: the state's layout (+ the byte layout for the key tile)
   s.bfv = o; o += axv ? 4096 : 0;    // states scaled along v: every warp's own B fragments
-  s.kbf = o; o += tens ? 2048 : 0;   // the fold's key fragments
+  s.kbf = o; o += tens ? (kind == K_KDA ? 3 * 2048 : 2048) : 0;   // the fold's key fragments (KDA: three bf16 planes)
   s.kcur = o; o += tens ? 128 : 0;   // the codes of the key appended by this token
   s.f0 = o;
   int f = 0;
@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (!AXV && KIND != K_KDA && ((BI
   constexpr int HPS = 128 / DV;                  // heads per stage
   constexpr int CW = 4;                          // columns per lane in the prologue
   constexpr bool TWO = KIND != K_M2, VDEC = KIND == K_KDA, CANFOLD = MODE == 3;
-  constexpr bool TFMT = !VDEC && (AXV ? BITS == 4 : ((BITS == 8 && UPG == 1) || (BITS == 4 && UPG == 2)));
+  constexpr bool TFMT = AXV ? BITS == 4 : ((BITS == 8 && UPG == 1) || (BITS == 4 && UPG == 2));
   static_assert(DV == 64 || DV == 128, "a stage is 128 rows: one or two heads");
   static_assert(!AXV || (BITS == 4 && UPG == 1 && !VDEC && (MODE == 0 || TFMT)),
                 "scales along v: 4-bit codes, groups of 32 rows (the stage's scales are [4][128], as many bytes as UPG = 1)");
@@ -784,12 +784,18 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (!AXV && KIND != K_KDA && ((BI
             mbar_wait(&bars[nst], 0, A.wait_ns);                // the key tile has landed (warp 0 saw it before)
             if (tid < 7) ksf[tid] = h2f(KBSh[tid]);
             if (tid == 7) ksf[7] = misc[8];
-            build_key_frags<BITS>(KBf, reinterpret_cast<const int8_t*>(kbt), reinterpret_cast<const int8_t*>(smraw + P.kcur), tid);
+            if constexpr (VDEC) {
+              __syncthreads();                                  // the key scales (and ga, ae of the prologue) for everybody
+              build_key_frags_kda<BITS>(KBf, reinterpret_cast<const int8_t*>(kbt), reinterpret_cast<const int8_t*>(smraw + P.kcur),
+                                        gbt, ga, ksf, tid);
+            } else {
+              build_key_frags<BITS>(KBf, reinterpret_cast<const int8_t*>(kbt), reinterpret_cast<const int8_t*>(smraw + P.kcur), tid);
+            }
           }
           if (tid < HPS * 8) {                                  // per head of the stage: decays and value scales of the slots
             const int hq = tid >> 3, i = tid & 7, hf = sh * HPS + hq;
             const float gnew = hd[hf * HD_W + 5];
-            tab[hq * 20 + i] = i == 7 ? 1.0f : expf(gnew - fsm[P.gbs + hf * 8 + i]);
+            tab[hq * 20 + i] = (VDEC || i == 7) ? 1.0f : expf(gnew - fsm[P.gbs + hf * 8 + i]);
             tab[hq * 20 + 8 + i] = dcu[hf * 8 + i].y;
             if (i == 0) tab[hq * 20 + 16] = expf(gnew);
           }
@@ -798,8 +804,9 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (!AXV && KIND != K_KDA && ((BI
             fold_stage_mma_v4<DV>(smem_u32(st), reinterpret_cast<unsigned short*>(st + P.sc_off),
                                   reinterpret_cast<const int8_t*>(st + P.ub_off), us + sh * HPS * DV, tab, ksf, KBf, warp, lane);
           else
-            fold_stage_mma<BITS, UPG, DV>(smem_u32(st), reinterpret_cast<unsigned short*>(st + P.sc_off),
-                                          reinterpret_cast<const int8_t*>(st + P.ub_off), us + sh * HPS * DV, tab, ksf, KBf, warp, lane);
+            fold_stage_mma<BITS, UPG, DV, VDEC>(smem_u32(st), reinterpret_cast<unsigned short*>(st + P.sc_off),
+                                                reinterpret_cast<const int8_t*>(st + P.ub_off), us + sh * HPS * DV, tab, ksf, KBf,
+                                                warp, lane, ae);
           __syncthreads();
           if (warp == 0) {
             // the stage goes back to the slot: eight pieces of codes and the scales, as bulk copies
