@@ -143,6 +143,17 @@ class Stack:
             self.step()
         torch.cuda.synchronize()
 
+    def stagger(self):
+        """Spread the slots' buffer positions uniformly over the fold period: row r takes r mod m extra tokens (the other
+        rows sit out as padding rows), so that afterwards every step folds an m-th of the slots."""
+        keep = self.idx
+        rows = torch.arange(self.batch, device=self.device) % M
+        for j in range(1, M):
+            self.idx = torch.where(rows >= j, keep, torch.zeros_like(keep))
+            self.step()
+        self.idx = keep
+        torch.cuda.synchronize()
+
     def capture(self):
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
@@ -546,8 +557,10 @@ def main():
     launches = 0
     e2e = None
 
-    def time_stack(stack, steps, sample_clocks=False):
+    def time_stack(stack, steps, sample_clocks=False, stagger=False):
         stack.prewarm(args.prewarm, torch.Generator().manual_seed(4321 + rank))
+        if stagger:
+            stack.stagger()
         if not args.eager:
             stack.capture()
         stack.timed(max(3, args.warmup))
@@ -603,6 +616,17 @@ def main():
             results[name] = res
             del stack
             torch.cuda.empty_cache()
+        # the headline stack with the slots at different buffer positions, as a serving engine has them (the
+        # headline itself keeps the baseline's protocol: all slots in lockstep, one step in eight folds everything)
+        stack = WORKLOADS['gdn'](args.preset, args.batch, device, seed=1234 + rank)
+        keep = args.prewarm
+        args.prewarm = min(args.prewarm, 64)
+        res, _, _ = time_stack(stack, max(M, min(steps_timed, 32)), stagger=True)
+        args.prewarm = keep
+        res['workload'] = 'the headline stack (8 layers) with the slots\' buffer positions spread uniformly over the fold period'
+        results[args.preset + '_staggered'] = res
+        del stack
+        torch.cuda.empty_cache()
         LAYERS = saved
         results['config4_gga_slot_scaling'] = run_config4(args, rank, world, device, barrier, max_over_ranks)
 
