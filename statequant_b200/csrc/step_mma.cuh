@@ -1,24 +1,26 @@
-// The fused packed-state decode step with the state pass on the tensor pipe (mma_pass.cuh): integer states scaled
-// along k in groups of 32, 64 or 128, head dim d_k = 128, d_v 64 or 128, int8 decode buffer.
+// The fused packed-state decode step with the state pass on the tensor pipe (mma_pass.cuh): 4- and 8-bit states scaled
+// along k in groups of 32, 64 or 128 (and 4-bit states scaled along v in groups of 32 rows), head dim d_k = 128, d_v 64
+// or 128, int8 decode buffer.
 //
-// One CTA (128 threads) per (batch row, KEY head) walks the value heads that share the key head in STAGES of 128
+// One CTA (128 threads) per (batch row, KEY head, part of its value heads) walks its value heads in STAGES of 128
 // state rows (one head of d_v 128, two heads of d_v 64).  A stage -- codes as 8 padded pieces, scales, buffered
 // values -- arrives by bulk async copies on one mbarrier; the copies of the first stages and of the key tile are
-// issued by the lanes of one warp in the CTA's first instructions.  Per stage each warp takes a tile of 32 rows
-// through the tensor-core pass and finishes one row per lane (buffer term, u, o); the appends follow after the last
-// stage (MODE 0) or per stage, together with the fold of the stage's heads (MODE 2).
+// issued by the lanes of warps 2 and 1 in the CTA's first instructions.  Per stage each warp takes a tile of 32 rows
+// through the tensor-core pass and finishes one row per lane (buffer term, u, o).
 //
-// MODE 0: every token is stepped and appended; on a slot's m-th token the head's counter is left at m for the fold
-//         launch that follows (fold_kernel.cuh).
+// MODE 0: every token is stepped and appended (after the last stage); on a slot's m-th token the head's counter is
+//         left at m for the fold launch that follows (fold_kernel.cuh).
 // MODE 3: the same, and a slot on its m-th token is folded right here from the staged tile (the stored state is read
-//         once per token, fold or not): per stage the append and the fold of the stage's heads follow the read-out.
+//         once per token, fold or not): per stage the append and the fold of the stage's heads follow the read-out
+//         (on the tensor pipe, fold_mma.cuh, where the format allows; else in fp32, fold_rows.cuh).
 //         Nothing a CTA fetches depends on the slot's counter, so every copy and every scalar load leaves in the
 //         CTA's first instructions.
 //
 // Prologue by role: warp 0 normalises q and k, builds the fixed-point B fragments and (GDN, Mamba2) takes the
 // buffered keys' dot products on the tensor pipe; warp 1 the gates; warp 2 issues the copies and computes decay
-// factors and value scales of every (head, slot); warp 3 rounds and appends the key (KDA: takes the buffered keys'
-// dot products, whose per-channel decays keep them in fp32, while warp 0 appends the key).
+// factors and value scales of every (head, slot); warp 3 rounds the key that goes into the buffer (KDA: prepares the
+// normalised vectors and log decays for the buffered keys' products, which all four warps take in fp32 after the
+// block barrier, their decay ratios being per channel; warp 0 rounds the key).
 //
 // Arithmetic is that of delta_step.cuh (same rounding of scales, payloads and buffer entries); only the order of the
 // reductions differs, and the read-out vectors pass through 30-bit fixed point (mma_pass.cuh).
