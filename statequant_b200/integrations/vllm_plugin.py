@@ -41,9 +41,16 @@ def config():
     from ..quantizer import Quantizer
     _STATE.pop('gga', None)
     if mode.startswith('external:'):
-        raise NotImplementedError(f'{ENV}=external:... (a Python quantizer called at every rounding point) is an '
-                                  'evaluation hook of the reference and is not part of the packed decode path')
-    if mode.startswith('gga:'):
+        # An external state quantizer fn(S, layer) applied to the stored state after every fold and prefill chunk: the
+        # slot then holds an UNPACKED state (fp32, or bf16 by STATEQUANT_VLLM_EXTERNAL_DTYPE) that the decode step of
+        # this package advances like any other; fn itself is imported and called by the reference's forward hook
+        # (vllm_plugin.py:400-410 there), on the slot layout's 'S' view.
+        spec = raw[len('external:'):]
+        src, _, fn = spec.rpartition(':')
+        assert src and fn, f'{ENV}=external:<file.py or module>:<function>, got {spec!r}'
+        fmt = os.environ.get('STATEQUANT_VLLM_EXTERNAL_DTYPE', 'fp32').strip().lower()
+        assert fmt in ('fp32', 'bf16'), f'STATEQUANT_VLLM_EXTERNAL_DTYPE={fmt!r}: use fp32 or bf16'
+    elif mode.startswith('gga:'):
         rest = raw[len('gga:'):]
         pw = rest.endswith(':pw')
         path = rest[:-3] if pw else rest

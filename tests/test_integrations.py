@@ -122,3 +122,21 @@ def test_register_without_the_reference_package_leaves_vllm_alone():
     r = subprocess.run([sys.executable, '-c', code], capture_output=True, text=True, env=env,
                        cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     assert r.returncode == 0 and 'ok' in r.stdout, r.stdout + r.stderr
+
+
+def test_external_quantizer_mode_is_an_unpacked_slot(monkeypatch):
+    """STATEQUANT_VLLM=external:<src>:<fn>: the reference's forward hook applies fn to the stored state; here the mode
+    means an fp32 (or bf16) slot, whose 'S' view is the [slots, HV, d_v, d_k] tensor that hook reads and writes."""
+    monkeypatch.setenv('STATEQUANT_VLLM', 'external:my_pkg.quant:fake_quant')
+    fmt, m, bb, fused = P.config()
+    assert (fmt, m, bb, fused) == ('fp32', 8, 8, None)
+    monkeypatch.setenv('STATEQUANT_VLLM_EXTERNAL_DTYPE', 'bf16')
+    assert P.config()[0] == 'bf16'
+    monkeypatch.setenv('STATEQUANT_VLLM', 'external:nofunction')
+    with pytest.raises(AssertionError):
+        P.config()
+    lay = SlotLayout('fp32', 4, 2, 128, 128, m=8)
+    views = lay.views(torch.zeros(3, lay.nbytes, dtype=torch.uint8))
+    assert views['S'].dtype == torch.float32 and tuple(views['S'].shape) == (3, 4, 128, 128)
+    views['S'][torch.tensor([1])] = 0.5                       # what the hook does: an indexed write through the view
+    assert float(lay.read(views, torch.tensor([1], dtype=torch.int32)).mean()) == 0.5
