@@ -20,9 +20,14 @@
 
 namespace sqb {
 
-constexpr int RNT = 256;   // threads per CTA
-constexpr int RNW = 8;
-constexpr int RD = 128;    // d_k = d_v
+#ifndef SQB_GGA_RPW
+#define SQB_GGA_RPW 16
+#endif
+constexpr int RD = 128;            // d_k = d_v
+constexpr int RPW = SQB_GGA_RPW;   // tile rows per warp: 16 (256 threads, 64 elements per thread) or 8 (512 threads, 32)
+constexpr int RNW = RD / RPW;
+constexpr int RNT = 32 * RNW;      // threads per CTA
+static_assert(RPW == 16 || RPW == 8, "rows per warp");
 
 // shared-memory plan (bytes)
 struct GgaRegSmem { int bar, raw, win, f0, total; int q, k, bk, v, o, w, rs, rrs, cs, rcs, pa, pb, Pw, Vw, coef, red; };
@@ -55,37 +60,35 @@ __device__ __forceinline__ float block_reduce_r(float v, float* red) {
   return r;
 }
 
-// Sixteen per-lane values -> their sums over the warp, one row per lane pair: on return lane l holds the total of
-// value ((l >> 4) & 1) * 8 + ((l >> 3) & 1) * 4 + ((l >> 2) & 1) * 2 + ((l >> 1) & 1).  16 shuffles.
-__device__ __forceinline__ float transpose_sum16(float (&v)[16], int lane) {
+// RPW per-lane values -> their sums over the warp, one row per group of lanes: the rounds halve the number of values a
+// lane carries (it keeps one half and sends the other to its partner), so RPW - 1 shuffles do the job, plus one per
+// remaining level for the lanes that end up with the same row.  On return lane l holds the total of row
+// transpose_row(l).
+__device__ __forceinline__ float transpose_sum(float (&v)[RPW], int lane) {
+  int n = RPW, bit = 16;
 #pragma unroll
-  for (int j = 0; j < 8; j++) {
-    const bool up = lane & 16;
-    const float send = up ? v[j] : v[j + 8], keep = up ? v[j + 8] : v[j];
-    v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
-  }
+  for (int level = 0; level < (RPW == 16 ? 4 : 3); level++) {
+    n >>= 1;
 #pragma unroll
-  for (int j = 0; j < 4; j++) {
-    const bool up = lane & 8;
-    const float send = up ? v[j] : v[j + 4], keep = up ? v[j + 4] : v[j];
-    v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    for (int j = 0; j < RPW / 2; j++) {
+      if (j < n) {
+        const bool up = lane & bit;
+        const float send = up ? v[j] : v[j + n], keep = up ? v[j + n] : v[j];
+        v[j] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+      }
+    }
+    bit >>= 1;
   }
+  float t = v[0];
 #pragma unroll
-  for (int j = 0; j < 2; j++) {
-    const bool up = lane & 4;
-    const float send = up ? v[j] : v[j + 2], keep = up ? v[j + 2] : v[j];
-    v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-  }
-  {
-    const bool up = lane & 2;
-    const float send = up ? v[0] : v[1], keep = up ? v[1] : v[0];
-    v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
-  }
-  return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
+  for (int o = RPW == 16 ? 1 : 2; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return t;
 }
-__device__ __forceinline__ int transpose_row16(int lane) {
-  return ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
+__device__ __forceinline__ int transpose_row(int lane) {
+  if (RPW == 16) return ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
+  return ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
 }
+constexpr int ROW_LANES = RPW == 16 ? 2 : 4;       // lanes that end up with the same row's total
 
 // x / d for a pair, d an fp16 value with rd = RN(1 / d) (see div_h16)
 __device__ __forceinline__ float2 div_h16x2(float2 x, float2 d, float2 nd, float2 rd) {
@@ -108,8 +111,8 @@ __device__ __noinline__ void gga_reg_fit_cold(const float* x, uint8_t* u, const 
   constexpr float qmax = static_cast<float>((1 << (B - 1)) - 1);
   const int tid = warp * 32 + lane;
   float m[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int r = 0; r < 16; r++)
-    for (int c = 0; c < 4; c++) m[c] = fmaxf(m[c], fabsf(__fdiv_rn(x[r * 4 + c], rs[16 * warp + r])));
+  for (int r = 0; r < RPW; r++)
+    for (int c = 0; c < 4; c++) m[c] = fmaxf(m[c], fabsf(__fdiv_rn(x[r * 4 + c], rs[RPW * warp + r])));
   for (int c = 0; c < 4; c++) pa[warp * RD + 4 * lane + c] = m[c];
   __syncthreads();
   if (tid < RD) {
@@ -119,8 +122,8 @@ __device__ __noinline__ void gga_reg_fit_cold(const float* x, uint8_t* u, const 
   }
   __syncthreads();
   float num[4] = {0.f, 0.f, 0.f, 0.f}, den[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int r = 0; r < 16; r++) {
-    const float rf = rs[16 * warp + r], ww = wsm[16 * warp + r] * wsm[16 * warp + r];
+  for (int r = 0; r < RPW; r++) {
+    const float rf = rs[RPW * warp + r], ww = wsm[RPW * warp + r] * wsm[RPW * warp + r];
     for (int c = 0; c < 4; c++) {
       const float xv = x[r * 4 + c];
       const float z = fminf(fmaxf(rintf(__fdiv_rn(__fdiv_rn(xv, rf), cs[4 * lane + c])), -qmax), qmax);
@@ -137,9 +140,9 @@ __device__ __noinline__ void gga_reg_fit_cold(const float* x, uint8_t* u, const 
     cs[tid] = halfc(d > 0.f ? __fdiv_rn(n, fmaxf(d, 1e-30f)) : cs[tid]);
   }
   __syncthreads();
-  for (int r = 0; r < 16; r++)
+  for (int r = 0; r < RPW; r++)
     for (int c = 0; c < 4; c++) {
-      const float z = fminf(fmaxf(rintf(__fdiv_rn(__fdiv_rn(x[r * 4 + c], rs[16 * warp + r]), cs[4 * lane + c])), -qmax), qmax);
+      const float z = fminf(fmaxf(rintf(__fdiv_rn(__fdiv_rn(x[r * 4 + c], rs[RPW * warp + r]), cs[4 * lane + c])), -qmax), qmax);
       u[r * 4 + c] = static_cast<uint8_t>(static_cast<int>(z) + static_cast<int>(qmax));
     }
 }
@@ -188,18 +191,18 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
   constexpr int iq = (1 << (B - 1)) - 1;
   constexpr int ROWB = RD * B / 8;
   const int tid = warp * 32 + lane, M = C.M;
-  const int row0 = 16 * warp, col0 = 4 * lane;
+  const int row0 = RPW * warp, col0 = 4 * lane;
   const unsigned short* Rf = reinterpret_cast<const unsigned short*>(C.raw + RD * ROWB);
   const unsigned short* Cf = Rf + RD;
 
   // ---- decode: x = (r c) (code - qmax), pairs (columns 0,1) and (2,3) ----
-  float2 x[16][2];
+  float2 x[RPW][2];
   {
     const uint2 cw = *reinterpret_cast<const uint2*>(Cf + col0);
     const float2 c01 = __half22float2(*reinterpret_cast<const __half2*>(&cw.x)), c23 = __half22float2(*reinterpret_cast<const __half2*>(&cw.y));
     const float2 off = make_float2(-(8388608.0f + qmax), -(8388608.0f + qmax));
 #pragma unroll
-    for (int r = 0; r < 16; r++) {
+    for (int r = 0; r < RPW; r++) {
       uint32_t u[4];
       gga_reg_codes<B>(C.raw, row0 + r, lane, u);
       const float rr = h2f(Rf[row0 + r]);
@@ -213,7 +216,7 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
   {
     float2 s0 = make_float2(0.f, 0.f), s1 = s0;
 #pragma unroll
-    for (int r = 0; r < 16; r++) {
+    for (int r = 0; r < RPW; r++) {
       const float kv = C.k[row0 + r];
       s0 = __ffma2_rn(make_float2(kv, kv), x[r][0], s0);
       s1 = __ffma2_rn(make_float2(kv, kv), x[r][1], s1);
@@ -232,7 +235,7 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
     const float2 a2 = make_float2(C.a, C.a);
     float2 o0 = make_float2(0.f, 0.f), o1 = o0;
 #pragma unroll
-    for (int r = 0; r < 16; r++) {
+    for (int r = 0; r < RPW; r++) {
       const float nb = -C.bk[row0 + r], qv = C.q[row0 + r];
       // O - bk kO as O + (-(bk kO)): the product is rounded first, as in the tile kernel
       x[r][0] = __fmul2_rn(a2, __fadd2_rn(x[r][0], __fmul2_rn(make_float2(nb, nb), make_float2(t.x, t.y))));
@@ -296,7 +299,7 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
     const float* lf = C.window ? C.Pw : C.bk;
     const float4 rv = *reinterpret_cast<const float4*>((C.window ? C.Vw : C.v) + col0);
 #pragma unroll
-    for (int r = 0; r < 16; r++) {
+    for (int r = 0; r < RPW; r++) {
       const float pi = lf[row0 + r];
       x[r][0] = __fadd2_rn(x[r][0], __fmul2_rn(make_float2(pi, pi), make_float2(rv.x, rv.y)));
       x[r][1] = __fadd2_rn(x[r][1], __fmul2_rn(make_float2(pi, pi), make_float2(rv.z, rv.w)));
@@ -322,13 +325,13 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
   // the refit's sums, and a column whose maximum it is gets the smallest factor 2^-24 either way.
   bool bad;
   {
-    float s[16];
+    float s[RPW];
 #pragma unroll
-    for (int r = 0; r < 16; r++) s[r] = (fabsf(x[r][0].x) + fabsf(x[r][0].y)) + (fabsf(x[r][1].x) + fabsf(x[r][1].y));
-    const float tot = transpose_sum16(s, lane);
-    const int rr_ = row0 + transpose_row16(lane);
+    for (int r = 0; r < RPW; r++) s[r] = (fabsf(x[r][0].x) + fabsf(x[r][0].y)) + (fabsf(x[r][1].x) + fabsf(x[r][1].y));
+    const float tot = transpose_sum(s, lane);
+    const int rr_ = row0 + transpose_row(lane);
     const float rf = halfc(__fsqrt_rn(__fdiv_rn(fmaxf(tot * (1.0f / RD), 1e-20f), C.w[rr_])));
-    if (!(lane & 1)) { C.rs[rr_] = rf; C.rrs[rr_] = __frcp_rn(rf); }
+    if (!(lane & (ROW_LANES - 1))) { C.rs[rr_] = rf; C.rrs[rr_] = __frcp_rn(rf); }
     bad = !(tot < 1e14f);
   }
   bad = __syncthreads_or(bad);
@@ -337,7 +340,7 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
     {
       float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
 #pragma unroll
-      for (int r = 0; r < 16; r++) {
+      for (int r = 0; r < RPW; r++) {
         const float rv = C.rs[row0 + r], ri = C.rrs[row0 + r];
         const float2 d = make_float2(rv, rv), nd = make_float2(-rv, -rv), rd = make_float2(ri, ri);
         const float2 y0 = div_h16x2(x[r][0], d, nd, rd), y1 = div_h16x2(x[r][1], d, nd, rd);
@@ -369,7 +372,7 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
       const float2 mg = make_float2(MAGIC, MAGIC), nmg = make_float2(-MAGIC, -MAGIC);
       float2 n0 = make_float2(0.f, 0.f), n1 = n0, d0 = n0, d1 = n0;
 #pragma unroll
-      for (int r = 0; r < 16; r++) {
+      for (int r = 0; r < RPW; r++) {
         const float rv = C.rs[row0 + r], ri = C.rrs[row0 + r], wv = C.w[row0 + r];
         const float ww = wv * wv;
         const float2 d = make_float2(rv, rv), nd = make_float2(-rv, -rv), rd = make_float2(ri, ri), w2 = make_float2(ww, ww);
@@ -407,7 +410,7 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
       constexpr float MG = MAGIC + static_cast<float>(iq + 1);
       const float2 mg = make_float2(MG, MG);
 #pragma unroll
-      for (int r = 0; r < 16; r++) {
+      for (int r = 0; r < RPW; r++) {
         float2 y0 = div_h16x2(x[r][0], ca, nca, rca), y1 = div_h16x2(x[r][1], cb, ncb, rcb);     // x holds x / r by now
         y0 = make_float2(fminf(fmaxf(y0.x, -qmax), qmax), fminf(fmaxf(y0.y, -qmax), qmax));
         y1 = make_float2(fminf(fmaxf(y1.x, -qmax), qmax), fminf(fmaxf(y1.y, -qmax), qmax));
@@ -427,12 +430,12 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
       }
     }
   } else {
-    float xc[64];
-    uint8_t uc[64];
+    float xc[4 * RPW];
+    uint8_t uc[4 * RPW];
 #pragma unroll
-    for (int r = 0; r < 16; r++) { xc[4 * r] = x[r][0].x; xc[4 * r + 1] = x[r][0].y; xc[4 * r + 2] = x[r][1].x; xc[4 * r + 3] = x[r][1].y; }
+    for (int r = 0; r < RPW; r++) { xc[4 * r] = x[r][0].x; xc[4 * r + 1] = x[r][0].y; xc[4 * r + 2] = x[r][1].x; xc[4 * r + 3] = x[r][1].y; }
     gga_reg_fit_cold<B>(xc, uc, C.rs, C.w, C.cs, C.pa, C.pb, warp, lane);
-    for (int r = 0; r < 16; r++) gga_reg_put<B>(C.raw, row0 + r, lane, uc[4 * r], uc[4 * r + 1], uc[4 * r + 2], uc[4 * r + 3]);
+    for (int r = 0; r < RPW; r++) gga_reg_put<B>(C.raw, row0 + r, lane, uc[4 * r], uc[4 * r + 1], uc[4 * r + 2], uc[4 * r + 3]);
   }
   unsigned short* Rw = reinterpret_cast<unsigned short*>(C.raw + RD * ROWB);
   if (tid < RD) { Rw[tid] = f2h(C.rs[tid]); Rw[RD + tid] = f2h(C.cs[tid]); }
