@@ -249,3 +249,63 @@ def test_full_batch_properties_gga_qwen_shapes():
         flips = ((Sd - Sh).abs() > 1e-3 * Sh.abs().amax()).float().mean().item()
         assert flips < 2e-3, (t, flips)
         assert torch.equal(blob.cpu()[sl.long(), :8], hb[sl.long(), :8])               # window counters
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('pw', [True, False])
+def test_mixed_widths_at_128_split_between_the_two_step_kernels(pw):
+    """A 128 x 128 layer that mixes the widths: 4 / 6 / 8-bit heads go to the register-tile kernel, the 2-bit head and the
+    fp16 pivot to the tile kernel (the layout carries no all-packed hint here), every step from the oracle's bytes,
+    across a window wrap (m = 4), with padding rows; then the same layer with the generic path forced (tile kernel for
+    every head) must give the device's own bytes again up to refit flips."""
+    from statequant_b200 import _cabi
+    hv, hk, D, m, B = 6, 3, 128, 4, 3
+    g0 = torch.Generator().manual_seed(77)
+    widths = torch.tensor([8, 16, 2, 4, 6, 8])
+    plan = StepPlan({0: (widths, torch.rand(hv, D, generator=g0) + 0.5)}, 32, name='mixed')
+    pk = GGAPacked(plan, hv, hk, D, D, pw=pw, m=m)
+    assert pk._struct(pk.views(torch.zeros(1, pk.nbytes, dtype=torch.uint8)), 0).flags == 0
+    idx = torch.tensor([2, 0, 1], dtype=torch.int32)
+    ok = idx > 0
+    hb = torch.zeros(B + 1, pk.nbytes, dtype=torch.uint8)
+    Vh = pk.views(hb)
+    oracle.gga_store(pk, Vh, idx[ok], torch.randn(int(ok.sum()), hv, D, D, generator=g0) * 0.3, 0)
+    db = hb.clone().to(DEV)
+    Vd = pk.views(db)
+    A_log, dtb = torch.randn(hv, generator=g0) * 0.3, torch.randn(hv, generator=g0)
+    packed = (widths != 16) & (widths != 2)
+    for t in range(2 * m + 1):
+        f = lambda *s: torch.randn(*s, generator=g0)                                     # noqa: E731
+        q, k, v = f(B, hk, D), f(B, hk, D), f(B, hv, D)
+        a, b = f(B, hv) + 2.0, f(B, hv)
+        db.copy_(hb)                                             # both start from the master's bytes
+        oh = torch.full((B, hv, D), 7.)
+        od = torch.full((B, hv, D), 7., device=DEV)
+        oracle.gga_step(pk, Vh, idx, q, k, v, oh, D ** -0.5, (a, b, A_log, dtb), 0)
+        gate = tuple(x.to(DEV) for x in (a, b, A_log, dtb))
+        pk.step(Vd, idx.to(DEV), q.to(DEV), k.to(DEV), v.to(DEV), od, D ** -0.5, gate=gate, layer=0)
+        od = od.cpu()
+        assert torch.equal(od[~ok], torch.zeros_like(od[~ok]))
+        assert ((od - oh).norm() / oh.norm()).item() < 1e-5, t
+        Sd, Sh = pk.stored(Vd, idx[ok].to(DEV), 0).cpu(), oracle.gga_load(pk, Vh, idx[ok], 0)
+        flips = ((Sd - Sh).abs() > 1e-3 * Sh.abs().amax()).float().mean().item()
+        assert flips < 2e-3, (t, flips)
+        if pw:
+            Pd, Vwd, nd = pk.window(Vd, idx[ok].to(DEV))
+            Ph, Vwh, nh = pk.window(Vh, idx[ok])
+            assert torch.equal(nd.cpu(), nh) and torch.equal(Vwd.cpu(), Vwh), t
+            assert ((Pd.cpu() - Ph).abs() > 1e-6 * Ph.abs().amax()).float().mean().item() < 1e-3, t
+        assert torch.equal(db.cpu()[0], hb[0])                   # the padding slot is untouched
+    # the tile kernel alone on the last step's inputs gives the same outputs
+    db.copy_(hb)
+    o1 = torch.empty(B, hv, D, device=DEV)
+    pk.step(Vd, idx.to(DEV), q.to(DEV), k.to(DEV), v.to(DEV), o1, D ** -0.5, gate=gate, layer=0)
+    db.copy_(hb)
+    o2 = torch.empty(B, hv, D, device=DEV)
+    _cabi.set_option('kernel_path', 1)
+    try:
+        pk.step(Vd, idx.to(DEV), q.to(DEV), k.to(DEV), v.to(DEV), o2, D ** -0.5, gate=gate, layer=0)
+    finally:
+        _cabi.set_option('kernel_path', 0)
+    assert ((o1 - o2).norm() / o2.norm()).item() < 1e-5
+    assert torch.equal(o1[:, ~packed], o2[:, ~packed])           # heads the tile kernel serves either way: identical
