@@ -309,3 +309,42 @@ def test_mixed_widths_at_128_split_between_the_two_step_kernels(pw):
         _cabi.set_option('kernel_path', 0)
     assert ((o1 - o2).norm() / o2.norm()).item() < 1e-5
     assert torch.equal(o1[:, ~packed], o2[:, ~packed])           # heads the tile kernel serves either way: identical
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('scale', [1e16, 3e13])
+def test_register_tile_kernel_outside_the_fast_quotient_range(scale):
+    """Values for which the fit's three-FMA quotients are not proved exact: the register-tile kernel must take its IEEE
+    path for the head.  A value vector of 1e16 drives a head's row sums past 1e14; one of 3e13 in a single column cuts a column factor at
+    fp16's maximum (quotients pass the code range; the row sums stay below 1e14).  No window, so the write lands in the state at once."""
+    hv, hk, D, B = 2, 1, 128, 2
+    g0 = torch.Generator().manual_seed(5)
+    plan = StepPlan({0: (torch.tensor([4, 8]), torch.rand(hv, D, generator=g0) + 0.5)}, 32, name='range')
+    pk = GGAPacked(plan, hv, hk, D, D, pw=False, m=8)
+    idx = torch.tensor([1, 2], dtype=torch.int32)
+    hb = torch.zeros(B + 1, pk.nbytes, dtype=torch.uint8)
+    Vh = pk.views(hb)
+    oracle.gga_store(pk, Vh, idx, torch.randn(B, hv, D, D, generator=g0) * 0.3, 0)
+    db = hb.clone().to(DEV)
+    Vd = pk.views(db)
+    A_log, dtb = torch.randn(hv, generator=g0) * 0.3, torch.randn(hv, generator=g0)
+    for t in range(3):
+        f = lambda *s: torch.randn(*s, generator=g0)                                     # noqa: E731
+        q, k, v = f(B, hk, D), f(B, hk, D), f(B, hv, D)
+        v[0, 1] *= scale                                          # row 0, head 1: out of range; the others stay in it
+        if scale < 1e15:
+            v[0, 1, 1:] = 0.                                      # one huge column only
+        a, b = f(B, hv) + 2.0, f(B, hv)
+        db.copy_(hb)
+        oh, od = torch.empty(B, hv, D), torch.empty(B, hv, D, device=DEV)
+        oracle.gga_step(pk, Vh, idx, q, k, v, oh, D ** -0.5, (a, b, A_log, dtb), 0)
+        pk.step(Vd, idx.to(DEV), q.to(DEV), k.to(DEV), v.to(DEV), od, D ** -0.5,
+                gate=tuple(x.to(DEV) for x in (a, b, A_log, dtb)), layer=0)
+        assert torch.isfinite(od).all()
+        assert ((od.cpu() - oh).norm() / oh.norm()).item() < 1e-5, t
+        Sd, Sh = pk.stored(Vd, idx.to(DEV), 0).cpu(), oracle.gga_load(pk, Vh, idx, 0)
+        for h in range(hv):
+            for r in range(B):
+                ref = Sh[r, h]
+                flips = ((Sd[r, h] - ref).abs() > 1e-3 * ref.abs().amax()).float().mean().item()
+                assert flips < 2e-3, (t, r, h, flips)
