@@ -18,6 +18,8 @@ struct GgaArgs {
   // store / load / fit
   const float* X; float* Y; long long P;
   int* status;        // device health word: [0] counts CTAs whose bounded wait ran out
+  unsigned long long wait_ns;   // register-tile kernel: how long the wait for its bulk copies may take
+  int test_extra_tx;  // test hook: bytes its barrier expects beyond what is copied (so that its wait runs out)
   int skip_packed;    // gga_step_kernel: leave the heads of width 4 / 6 / 8 to the register-tile kernel (gga_reg.cuh)
 };
 

@@ -468,7 +468,7 @@ __global__ void __launch_bounds__(RNT, SQB_GGA_REG_MINB) gga_step_reg_kernel(con
   if (tid == 0) {
     mbar_init(bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    mbar_expect_tx(bar, head_bytes + (window ? A.qsz : 0));
+    mbar_expect_tx(bar, head_bytes + (window ? A.qsz : 0) + A.test_extra_tx);
     bulk_g2s(rsm + P.raw, S, head_bytes, bar);
     if (window) bulk_g2s(rsm + P.win, qb, A.qsz, bar);
   }
@@ -507,7 +507,9 @@ __global__ void __launch_bounds__(RNT, SQB_GGA_REG_MINB) gga_step_reg_kernel(con
   C.bq = block_reduce_r<false>(bqp, red);                   // (beta k) . q; also publishes q, k, bk, v, w
   C.a = a; C.n = n; C.hd = hd;
   // the head's bytes and the window's
-  if (!mbar_wait(bar, 0)) {
+  // (a bounded wait; the verdict is taken by the whole CTA together, since threads poll on their own clocks.  Both copies
+  // complete on this one barrier, so after a wait that ran out there is nothing further to drain.)
+  if (__syncthreads_or(!mbar_wait(bar, 0, A.wait_ns))) {
     for (int v = tid; v < RD; v += RNT) stf(orow, A.dt_out, v, 0.0f);
     if (tid == 0 && A.status) atomicAdd(&A.status[0], 1);
     return;

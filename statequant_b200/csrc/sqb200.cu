@@ -430,6 +430,8 @@ int sqb_gga_step(const sqb_gga_layout_t* L, const sqb_gdn_inputs_t* in, void* st
   const long long ctas = static_cast<long long>(in->rows) * L->hv;
   a.status = status_ptr();
   if (!a.status) return fail(SQB_ECUDA, "the device status word is not reachable (cudaGetSymbolAddress failed)");
+  a.wait_ns = static_cast<unsigned long long>(g_wait_ns.load(std::memory_order_relaxed));
+  a.test_extra_tx = g_test_extra_tx.load(std::memory_order_relaxed);
   // heads of width 4 / 6 / 8 (128 x 128): the register-tile kernel; 2-bit heads, pivots and other shapes: the tile kernel
   bool reg = L->dk == 128 && L->dv == 128 && g_kernel_path.load(std::memory_order_relaxed) != 1 &&
              !g_force_generic.load(std::memory_order_relaxed);

@@ -348,3 +348,44 @@ def test_register_tile_kernel_outside_the_fast_quotient_range(scale):
                 ref = Sh[r, h]
                 flips = ((Sd[r, h] - ref).abs() > 1e-3 * ref.abs().amax()).float().mean().item()
                 assert flips < 2e-3, (t, r, h, flips)
+
+
+@pytest.mark.gpu
+def test_register_tile_kernel_bounded_wait_runs_out_and_is_reported():
+    """The register-tile kernel's wait for its two bulk copies is bounded like the step kernels': with the barrier told
+    to expect more bytes than are copied (test switch) and a short limit, every CTA gives up together, the health word
+    counts them, the output rows are zero and the slots are untouched; afterwards the library works as before."""
+    from statequant_b200 import _cabi
+    hv, hk, D, B = 4, 2, 128, 2
+    g0 = torch.Generator().manual_seed(9)
+    plan = StepPlan({0: (torch.tensor([4, 6, 8, 4]), torch.rand(hv, D, generator=g0) + 0.5)}, 32, name='wait')
+    pk = GGAPacked(plan, hv, hk, D, D, pw=True, m=4)
+    blob = pk.alloc(B + 1, DEV)
+    V = pk.views(blob)
+    idx = torch.arange(1, B + 1, dtype=torch.int32, device=DEV)
+    pk.write(V, idx, (torch.randn(B, hv, D, D, generator=g0) * 0.3).to(DEV), layer=0)
+    f = lambda *s: torch.randn(*s, generator=g0).to(DEV)                                 # noqa: E731
+    q, k, v, a, b = f(B, hk, D), f(B, hk, D), f(B, hv, D), f(B, hv) + 2.0, f(B, hv)
+    gate = (a, b, f(hv) * 0.3, f(hv))
+    out = torch.full((B, hv, D), 7., device=DEV)
+    pk.step(V, idx, q, k, v, out, D ** -0.5, gate=gate, layer=0)                         # a healthy step first
+    torch.cuda.synchronize()
+    base = _cabi.device_status()
+    before = blob.clone()
+    _cabi.set_option('wait_limit_us', 2000)
+    _cabi.set_option('test_extra_tx', 64)
+    try:
+        out.fill_(7.)
+        pk.step(V, idx, q, k, v, out, D ** -0.5, gate=gate, layer=0)
+        torch.cuda.synchronize()
+        assert _cabi.device_status() - base == B * hv                                    # one count per CTA
+        assert torch.equal(out, torch.zeros_like(out))
+        assert torch.equal(blob[:, 16:], before[:, 16:])                                 # heads and windows untouched
+    finally:
+        _cabi.set_option('test_extra_tx', 0)
+        _cabi.set_option('wait_limit_us', 1000000)
+    blob.copy_(before)
+    o2 = torch.empty_like(out)
+    pk.step(V, idx, q, k, v, o2, D ** -0.5, gate=gate, layer=0)
+    torch.cuda.synchronize()
+    assert _cabi.device_status() - base == B * hv and torch.isfinite(o2).all() and o2.abs().sum() > 0
