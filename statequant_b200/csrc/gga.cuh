@@ -378,7 +378,7 @@ __global__ void __launch_bounds__(GNT) gga_step_kernel(const __grid_constant__ G
   const GgaSmem P = gga_smem(dk, dv, M, A.group);
   const int LD = dv + 1;
   float *T = gsm + P.T, *q = gsm + P.q, *k = gsm + P.k, *bk = gsm + P.bk, *v = gsm + P.v, *o = gsm + P.o,
-        *kO = gsm + P.kO, *Pw = gsm + P.Pw, *Vw = gsm + P.Vw, *r0 = gsm + P.r0, *coef = gsm + P.coef, *red = gsm + P.red;
+        *kO = gsm + P.kO, *Pw = gsm + P.Pw, *Vw = gsm + P.Vw, *coef = gsm + P.coef, *red = gsm + P.red;
   uint8_t* base = A.blob + seq * A.stride;
   const int bits = A.bits[h];
   uint8_t* S = base + A.offs[h];

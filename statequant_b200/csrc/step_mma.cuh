@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (KIN
 
   extern __shared__ __align__(128) uint8_t smraw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int M = A.M, HV = A.HV;
+  const int M = A.M;
   // grid: x = batch row, y = (key head, part of its value heads); no division on the way to the first fetch
   const int gqa = A.hpc;                          // value heads of this CTA: all heads of a key head, or a part of them
   const int gqf = A.gqa_full;                     // value heads per key head
@@ -317,7 +317,7 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (KIN
   // The key tile (and KDA's decay tile) is fetched by warp 2; the warp that takes the buffered keys' dot products
   // (warp 0; KDA: warp 3) meets warp 2 at named barrier 1 (64 threads) before it waits for the tile, so that its wait
   // can never meet a barrier that is not initialised yet; by then the key scales and the slot's counter are published.
-  constexpr int DOTS_WARP = VDEC ? 3 : 0, KEY_WARP = VDEC ? 0 : 3;
+  constexpr int KEY_WARP = VDEC ? 0 : 3;
   // the key as it goes into the buffer, rounded by KEY_WARP before the block barrier and stored after it
   uint32_t kword = 0;
   float kscale = 0.f;

@@ -268,14 +268,11 @@ __global__ void __launch_bounds__(NT, AXK ? (KIND == K_M2 ? SQB_MINB_K_M2 : SQB_
                                                                 const int nst) {
   constexpr int DK = LPR * 16;
   constexpr int RPP = 32 / LPR;                  // rows per warp pass
-  constexpr int CB = 16 * BITS / 8;              // bytes of a lane chunk
-  constexpr int ROWB = DK * BITS / 8;
   constexpr int CW = DK / 32;                    // columns per lane in the prologue
   constexpr int QD = DK / 4;                     // columns per lane in the buffered-key dot products
   constexpr bool TWO = KIND != K_M2;
   constexpr bool VDEC = KIND == K_KDA;
   constexpr bool FX = AXK && LPR == 8;            // integer dot products against fixed-point q, k
-  constexpr float QMAX = BITS == 4 ? 7.0f : 127.0f;
 
   extern __shared__ __align__(128) uint8_t smraw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -682,7 +679,7 @@ __global__ void __launch_bounds__(NT, AXK ? (KIND == K_M2 ? SQB_MINB_K_M2 : SQB_
     const uint8_t* ubt = st + P.codes_b + P.scales_b;
     uint8_t* orow = A.out + (long long)b * A.so + (long long)h * DV * osz;
     const float* hdv = hd + hi * HD_W;
-    const float beta = hdv[1], alpha = hdv[3], a = hdv[4], gnew = hdv[5], Dv = hdv[6];
+    const float beta = hdv[1], alpha = hdv[3], a = hdv[4], Dv = hdv[6];
     const int n = __float_as_int(hdv[7]);
     const float* dcf = decf + hi * M;
     const float* usf = ubsf + hi * M;
