@@ -34,6 +34,55 @@ __device__ __forceinline__ void stf(void* p, int dt, long long i, float v) {
 }
 __host__ __device__ __forceinline__ int dt_size(int dt) { return dt == DT_F32 ? 4 : 2; }
 
+// Activation loads in two steps, so that a group of loads is in flight together: the raw bits first (nothing waits
+// for them), the conversion to fp32 where the values are needed.  (ldf converts at once, which makes every load of a
+// sequence wait for the one before.)
+__device__ __forceinline__ uint32_t ld1_raw(const void* p, int dt, long long i) {
+  if (dt == DT_F32) return reinterpret_cast<const uint32_t*>(p)[i];
+  return reinterpret_cast<const unsigned short*>(p)[i];
+}
+__device__ __forceinline__ float cvt_raw(uint32_t w, int dt) {
+  if (dt == DT_F32) return __uint_as_float(w);
+  if (dt == DT_BF16) return __uint_as_float(w << 16);
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(w)));
+}
+// Elements i .. i + 3 (i a multiple of 4) as loaded, untouched: unpacking a loaded word is already a use that waits
+// for the load, so it is left to cvt4_raw.  vec: the row is read by one 8- or 16-byte load (the address allows it).
+struct Raw4 { uint4 v; bool vec; };
+__device__ __forceinline__ Raw4 ld4_raw(const uint8_t* p, int dt, long long i) {
+  Raw4 r;
+  r.v = make_uint4(0u, 0u, 0u, 0u);
+  if (dt == DT_F32) {
+    const uint8_t* q = p + 4 * i;
+    r.vec = (reinterpret_cast<uintptr_t>(q) & 15) == 0;
+    if (r.vec) {
+      r.v = *reinterpret_cast<const uint4*>(q);
+    } else {
+      r.v.x = reinterpret_cast<const uint32_t*>(q)[0]; r.v.y = reinterpret_cast<const uint32_t*>(q)[1];
+      r.v.z = reinterpret_cast<const uint32_t*>(q)[2]; r.v.w = reinterpret_cast<const uint32_t*>(q)[3];
+    }
+  } else {
+    const uint8_t* q = p + 2 * i;
+    r.vec = (reinterpret_cast<uintptr_t>(q) & 7) == 0;
+    if (r.vec) {
+      const uint2 t = *reinterpret_cast<const uint2*>(q);
+      r.v.x = t.x; r.v.y = t.y;
+    } else {
+      r.v.x = reinterpret_cast<const unsigned short*>(q)[0]; r.v.y = reinterpret_cast<const unsigned short*>(q)[1];
+      r.v.z = reinterpret_cast<const unsigned short*>(q)[2]; r.v.w = reinterpret_cast<const unsigned short*>(q)[3];
+    }
+  }
+  return r;
+}
+__device__ __forceinline__ void cvt4_raw(const Raw4& r, int dt, float (&f)[4]) {
+  if (dt == DT_F32 || !r.vec) {
+    f[0] = cvt_raw(r.v.x, dt); f[1] = cvt_raw(r.v.y, dt); f[2] = cvt_raw(r.v.z, dt); f[3] = cvt_raw(r.v.w, dt);
+  } else {
+    f[0] = cvt_raw(r.v.x & 0xFFFFu, dt); f[1] = cvt_raw(r.v.x >> 16, dt);
+    f[2] = cvt_raw(r.v.y & 0xFFFFu, dt); f[3] = cvt_raw(r.v.y >> 16, dt);
+  }
+}
+
 __device__ __forceinline__ float h2f(unsigned short h) { return __half2float(__ushort_as_half(h)); }
 __device__ __forceinline__ unsigned short f2h(float f) { return __half_as_ushort(__float2half_rn(f)); }
 __device__ __forceinline__ float bf2f(unsigned short b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }

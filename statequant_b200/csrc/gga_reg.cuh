@@ -14,6 +14,7 @@
 // values leave the range in which div_h16 is exact takes the IEEE divisions instead (the cold path below).
 // Heads of other widths (2-bit, fp16 pivots) are left to gga_step_kernel: this kernel's CTA returns at once for them.
 #pragma once
+#include <cuda_fp8.h>
 #include "gga_common.cuh"
 #include "step_tma.cuh"
 #include "fold_mma.cuh"
@@ -48,18 +49,6 @@ __host__ __device__ inline GgaRegSmem gga_reg_smem(int M, int qsz) {
   return s;
 }
 
-template <bool MAX>
-__device__ __forceinline__ float block_reduce_r(float v, float* red) {
-  v = MAX ? warp_max(v) : warp_sum(v);
-  __syncthreads();
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-  __syncthreads();
-  float r = red[0];
-#pragma unroll
-  for (int w = 1; w < RNW; w++) r = MAX ? fmaxf(r, red[w]) : r + red[w];
-  return r;
-}
-
 // RPW per-lane values -> their sums over the warp, one row per group of lanes: the rounds halve the number of values a
 // lane carries (it keeps one half and sends the other to its partner), so RPW - 1 shuffles do the job, plus one per
 // remaining level for the lanes that end up with the same row.  On return lane l holds the total of row
@@ -89,6 +78,16 @@ __device__ __forceinline__ int transpose_row(int lane) {
   return ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
 }
 constexpr int ROW_LANES = RPW == 16 ? 2 : 4;       // lanes that end up with the same row's total
+
+// E4M3 through the conversion instructions (round to nearest even, saturating at 448, subnormals down to 2^-9: what
+// e4m3_round / e4m3_byte / e4m3_val of gga_common.cuh spell out), two values at a time
+__device__ __forceinline__ float2 e4m3x2_val(uint32_t b0, uint32_t b1) {
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(b0 | (b1 << 8)), __NV_E4M3);
+  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
+__device__ __forceinline__ uint32_t e4m3x2_byte(float a, float b) {
+  return __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+}
 
 // x / d for a pair, d an fp16 value with rd = RN(1 / d) (see div_h16)
 __device__ __forceinline__ float2 div_h16x2(float2 x, float2 d, float2 nd, float2 rd) {
@@ -255,28 +254,37 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
       if (live) {
         const int jj = (C.hd + i) % M;
         const float ps_ = PS[jj], vs_ = VS[jj];
+        uint8_t *pp = PP + jj * RD, *vp = VP + jj * RD;
+        float* pw = C.Pw + i * RD;
+        // this lane's channels: lane, lane + 32, lane + 64, lane + 96
+        const float2 p01 = e4m3x2_val(pp[lane], pp[lane + 32]), p23 = e4m3x2_val(pp[lane + 64], pp[lane + 96]);
+        const float2 v01 = e4m3x2_val(vp[lane], vp[lane + 32]), v23 = e4m3x2_val(vp[lane + 64], vp[lane + 96]);
+        float pv[4] = {p01.x * ps_, p01.y * ps_, p23.x * ps_, p23.y * ps_};
+        C.Vw[i * RD + lane] = v01.x * vs_; C.Vw[i * RD + lane + 32] = v01.y * vs_;
+        C.Vw[i * RD + lane + 64] = v23.x * vs_; C.Vw[i * RD + lane + 96] = v23.y * vs_;
         float kp = 0.f;
-        for (int t = lane; t < RD; t += 32) {
-          const float pv = e4m3_val(PP[jj * RD + t]) * ps_;
-          C.Pw[i * RD + t] = pv;
-          kp = fmaf(C.k[t], pv, kp);
-          C.Vw[i * RD + t] = e4m3_val(VP[jj * RD + t]) * vs_;
-        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) kp = fmaf(C.k[lane + 32 * j], pv[j], kp);
         kp = warp_sum(kp);
         float am = 0.f;
-        for (int t = lane; t < RD; t += 32) {
-          const float ap = C.a * (C.Pw[i * RD + t] - C.bk[t] * kp);
-          C.Pw[i * RD + t] = ap;
-          am = fmaxf(am, fabsf(ap));
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          pv[j] = C.a * (pv[j] - C.bk[lane + 32 * j] * kp);
+          am = fmaxf(am, fabsf(pv[j]));
         }
         am = warp_max(am);
         const float sc = __fdiv_rn(am, 448.0f), safe = sc > 0.f ? sc : 1.0f;
-        for (int t = lane; t < RD; t += 32) {
-          const float y = e4m3_round(fminf(fmaxf(__fdiv_rn(C.Pw[i * RD + t], safe), -448.0f), 448.0f));
-          PP[jj * RD + t] = e4m3_byte(y);
-          const float r = sc > 0.f ? y * safe : 0.f;
-          C.Pw[i * RD + t] = r;
-          cf = fmaf(r, C.q[t], cf);
+        const uint32_t e01 = e4m3x2_byte(__fdiv_rn(pv[0], safe), __fdiv_rn(pv[1], safe));
+        const uint32_t e23 = e4m3x2_byte(__fdiv_rn(pv[2], safe), __fdiv_rn(pv[3], safe));
+        pp[lane] = static_cast<uint8_t>(e01 & 255u); pp[lane + 32] = static_cast<uint8_t>(e01 >> 8);
+        pp[lane + 64] = static_cast<uint8_t>(e23 & 255u); pp[lane + 96] = static_cast<uint8_t>(e23 >> 8);
+        const float2 y01 = e4m3x2_val(e01 & 255u, e01 >> 8), y23 = e4m3x2_val(e23 & 255u, e23 >> 8);
+        const float yv[4] = {y01.x, y01.y, y23.x, y23.y};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          const float r = sc > 0.f ? yv[j] * safe : 0.f;
+          pw[lane + 32 * j] = r;
+          cf = fmaf(r, C.q[lane + 32 * j], cf);
         }
         if (lane == 0) PS[jj] = sc;
         cf = warp_sum(cf);
@@ -314,8 +322,10 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
     am = warp_max(am);
     const float sc = __fdiv_rn(am, 448.0f), safe = sc > 0.f ? sc : 1.0f;
     uint8_t* dst = (warp == 0 ? PP : VP) + jn * RD;
-    for (int t = lane; t < RD; t += 32)
-      dst[t] = e4m3_byte(e4m3_round(fminf(fmaxf(__fdiv_rn(src[t], safe), -448.0f), 448.0f)));
+    const uint32_t e01 = e4m3x2_byte(__fdiv_rn(src[lane], safe), __fdiv_rn(src[lane + 32], safe));
+    const uint32_t e23 = e4m3x2_byte(__fdiv_rn(src[lane + 64], safe), __fdiv_rn(src[lane + 96], safe));
+    dst[lane] = static_cast<uint8_t>(e01 & 255u); dst[lane + 32] = static_cast<uint8_t>(e01 >> 8);
+    dst[lane + 64] = static_cast<uint8_t>(e23 & 255u); dst[lane + 96] = static_cast<uint8_t>(e23 >> 8);
     if (lane == 0) (warp == 0 ? PS : VS)[jn] = sc;
   }
   // ---- the fit: row factors r = half(sqrt(max(mean |x|, 1e-20) / w)) ----
@@ -478,34 +488,48 @@ __global__ void __launch_bounds__(RNT, SQB_GGA_REG_MINB) gga_step_reg_kernel(con
   C.rs = fs + P.rs; C.rrs = fs + P.rrs; C.cs = fs + P.cs; C.rcs = fs + P.rcs; C.pa = fs + P.pa; C.pb = fs + P.pb;
   C.Pw = fs + P.Pw; C.Vw = fs + P.Vw; C.coef = fs + P.coef;
   C.M = M; C.window = window; C.orow = orow; C.dt_out = A.dt_out;
-  float* red = fs + P.red;
-  // q, k (fla's normalisation), gates: as gga_step_kernel
-  float sq = 0.f, sk = 0.f, qv = 0.f, kv = 0.f;
-  if (tid < RD) {
-    qv = ldf(A.q + (long long)b * A.sq, A.dt_qk, (long long)hk * RD + tid);
-    kv = ldf(A.k + (long long)b * A.sk, A.dt_qk, (long long)hk * RD + tid);
-    C.v[tid] = ldf(A.v + (long long)b * A.sv, A.dt_v, (long long)h * RD + tid);
-    C.w[tid] = A.w[(long long)h * RD + tid];
-    sq = qv * qv; sk = kv * kv;
+  // q, k (fla's normalisation), gates: gga_step_kernel's arithmetic, on ONE warp (four channels per lane, sums by
+  // shuffles), while the other warps bring in v and w; the block barrier below publishes it all
+  float* sc = fs + P.red;                                   // a, (beta k) . q, window count, ring head
+  if (warp == 0) {
+    const Raw4 rq = ld4_raw(A.q + (long long)b * A.sq, A.dt_qk, (long long)hk * RD + 4 * lane);
+    const Raw4 rk = ld4_raw(A.k + (long long)b * A.sk, A.dt_qk, (long long)hk * RD + 4 * lane);
+    const uint32_t ra = ld1_raw(A.a + (long long)b * A.sa, A.dt_ab, h), rdb = ld1_raw(A.dt_bias, A.dt_dtb, h);
+    const uint32_t ral = ld1_raw(A.A_log, A.dt_alog, h), rb = ld1_raw(A.b + (long long)b * A.sb, A.dt_ab, h);
+    int n = 0, hd = 0;
+    if (window && lane == 0) { const int* ct = reinterpret_cast<const int*>(base); n = ct[0]; hd = ct[1]; }
+    float qv[4], kv[4];
+    cvt4_raw(rq, A.dt_qk, qv);
+    cvt4_raw(rk, A.dt_qk, kv);
+    float sq = (qv[0] * qv[0] + qv[1] * qv[1]) + (qv[2] * qv[2] + qv[3] * qv[3]);
+    float sk = (kv[0] * kv[0] + kv[1] * kv[1]) + (kv[2] * kv[2] + kv[3] * kv[3]);
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    const float nq = __fsqrt_rn(sq + 1e-6f), nk = __fsqrt_rn(sk + 1e-6f);
+    const float xg = cvt_raw(ra, A.dt_ab) + cvt_raw(rdb, A.dt_dtb);
+    const float sp = xg <= 20.0f ? logf(1.0f + expf(xg)) : xg;
+    const float a = expf(-expf(cvt_raw(ral, A.dt_alog)) * sp);
+    const float beta = __fdiv_rn(1.0f, 1.0f + expf(-cvt_raw(rb, A.dt_ab)));
+    float qn[4], kn[4], bkv[4], bqp = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      qn[j] = __fdiv_rn(qv[j], nq) * A.scale;
+      kn[j] = __fdiv_rn(kv[j], nk);
+      bkv[j] = beta * kn[j];
+      bqp += bkv[j] * qn[j];
+    }
+    bqp = warp_sum(bqp);
+    *reinterpret_cast<float4*>(C.q + 4 * lane) = make_float4(qn[0], qn[1], qn[2], qn[3]);
+    *reinterpret_cast<float4*>(C.k + 4 * lane) = make_float4(kn[0], kn[1], kn[2], kn[3]);
+    *reinterpret_cast<float4*>(C.bk + 4 * lane) = make_float4(bkv[0], bkv[1], bkv[2], bkv[3]);
+    if (lane == 0) { sc[0] = a; sc[1] = bqp; sc[2] = __int_as_float(n); sc[3] = __int_as_float(hd); }
+  } else {
+    for (int i = tid - 32; i < RD; i += RNT - 32) {
+      C.v[i] = ldf(A.v + (long long)b * A.sv, A.dt_v, (long long)h * RD + i);
+      C.w[i] = A.w[(long long)h * RD + i];
+    }
   }
-  const float xg = ldf(A.a + (long long)b * A.sa, A.dt_ab, h) + ldf(A.dt_bias, A.dt_dtb, h);
-  const float alog = ldf(A.A_log, A.dt_alog, h), bg = ldf(A.b + (long long)b * A.sb, A.dt_ab, h);
-  int n = 0, hd = 0;
-  if (window) { const int* ct = reinterpret_cast<const int*>(base); n = ct[0]; hd = ct[1]; }
-  sq = block_reduce_r<false>(sq, red);
-  sk = block_reduce_r<false>(sk, red);
-  const float nq = __fsqrt_rn(sq + 1e-6f), nk = __fsqrt_rn(sk + 1e-6f);
-  const float sp = xg <= 20.0f ? logf(1.0f + expf(xg)) : xg;
-  const float a = expf(-expf(alog) * sp);
-  const float beta = __fdiv_rn(1.0f, 1.0f + expf(-bg));
-  float bqp = 0.f;
-  if (tid < RD) {
-    const float qn = __fdiv_rn(qv, nq) * A.scale, kn = __fdiv_rn(kv, nk);
-    C.q[tid] = qn; C.k[tid] = kn; C.bk[tid] = beta * kn;
-    bqp = (beta * kn) * qn;
-  }
-  C.bq = block_reduce_r<false>(bqp, red);                   // (beta k) . q; also publishes q, k, bk, v, w
-  C.a = a; C.n = n; C.hd = hd;
+  __syncthreads();                                          // (also: nobody looks at the barrier before thread 0 has set it up)
   // the head's bytes and the window's
   // (a bounded wait; the verdict is taken by the whole CTA together, since threads poll on their own clocks.  Both copies
   // complete on this one barrier, so after a wait that ran out there is nothing further to drain.)
@@ -514,6 +538,7 @@ __global__ void __launch_bounds__(RNT, SQB_GGA_REG_MINB) gga_step_reg_kernel(con
     if (tid == 0 && A.status) atomicAdd(&A.status[0], 1);
     return;
   }
+  C.a = sc[0]; C.bq = sc[1]; C.n = __float_as_int(sc[2]); C.hd = __float_as_int(sc[3]);
   if (bits == 4) gga_reg_head<4>(C, warp, lane);
   else if (bits == 6) gga_reg_head<6>(C, warp, lane);
   else gga_reg_head<8>(C, warp, lane);
