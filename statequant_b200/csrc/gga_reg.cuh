@@ -183,9 +183,57 @@ struct GgaRegCtx {
   uint8_t* orow; int dt_out;
 };
 
+// q, k (fla's normalisation) and the gates of one head: gga_step_kernel's arithmetic on ONE warp (four channels per
+// lane, sums by shuffles), while the other warps bring in v and w.  Results in shared memory: C.q, C.k, C.bk, C.v, C.w
+// and sc = (a, (beta k) . q, window count, ring head); a block barrier must follow before anybody reads them.
+__device__ __forceinline__ void gga_reg_prologue(const GgaArgs& A, const GgaRegCtx& C, float* sc, int b, int h, int hk,
+                                                 const uint8_t* base, bool window, int warp, int lane) {
+  const int tid = warp * 32 + lane;
+  if (warp == 0) {
+    const Raw4 rq = ld4_raw(A.q + (long long)b * A.sq, A.dt_qk, (long long)hk * RD + 4 * lane);
+    const Raw4 rk = ld4_raw(A.k + (long long)b * A.sk, A.dt_qk, (long long)hk * RD + 4 * lane);
+    const uint32_t ra = ld1_raw(A.a + (long long)b * A.sa, A.dt_ab, h), rdb = ld1_raw(A.dt_bias, A.dt_dtb, h);
+    const uint32_t ral = ld1_raw(A.A_log, A.dt_alog, h), rb = ld1_raw(A.b + (long long)b * A.sb, A.dt_ab, h);
+    int n = 0, hd = 0;
+    if (window && lane == 0) { const int* ct = reinterpret_cast<const int*>(base); n = ct[0]; hd = ct[1]; }
+    float qv[4], kv[4];
+    cvt4_raw(rq, A.dt_qk, qv);
+    cvt4_raw(rk, A.dt_qk, kv);
+    float sq = (qv[0] * qv[0] + qv[1] * qv[1]) + (qv[2] * qv[2] + qv[3] * qv[3]);
+    float sk = (kv[0] * kv[0] + kv[1] * kv[1]) + (kv[2] * kv[2] + kv[3] * kv[3]);
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    const float nq = __fsqrt_rn(sq + 1e-6f), nk = __fsqrt_rn(sk + 1e-6f);
+    const float xg = cvt_raw(ra, A.dt_ab) + cvt_raw(rdb, A.dt_dtb);
+    const float sp = xg <= 20.0f ? logf(1.0f + expf(xg)) : xg;
+    const float a = expf(-expf(cvt_raw(ral, A.dt_alog)) * sp);
+    const float beta = __fdiv_rn(1.0f, 1.0f + expf(-cvt_raw(rb, A.dt_ab)));
+    float qn[4], kn[4], bkv[4], bqp = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      qn[j] = __fdiv_rn(qv[j], nq) * A.scale;
+      kn[j] = __fdiv_rn(kv[j], nk);
+      bkv[j] = beta * kn[j];
+      bqp += bkv[j] * qn[j];
+    }
+    bqp = warp_sum(bqp);
+    *reinterpret_cast<float4*>(C.q + 4 * lane) = make_float4(qn[0], qn[1], qn[2], qn[3]);
+    *reinterpret_cast<float4*>(C.k + 4 * lane) = make_float4(kn[0], kn[1], kn[2], kn[3]);
+    *reinterpret_cast<float4*>(C.bk + 4 * lane) = make_float4(bkv[0], bkv[1], bkv[2], bkv[3]);
+    if (lane == 0) { sc[0] = a; sc[1] = bqp; sc[2] = __int_as_float(n); sc[3] = __int_as_float(hd); }
+  } else {
+    for (int i = tid - 32; i < RD; i += RNT - 32) {
+      C.v[i] = ldf(A.v + (long long)b * A.sv, A.dt_v, (long long)h * RD + i);
+      C.w[i] = A.w[(long long)h * RD + i];
+    }
+  }
+}
+
 // Everything between the arrival of the head's bytes and their departure, for width B.
+// Returns false if the wait for the head's bytes ran out (the verdict of the whole CTA): nothing has been written then.
 template <int B>
-__device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int lane) {
+__device__ __forceinline__ bool gga_reg_head(GgaRegCtx& C, const GgaArgs& A, float* sc, uint64_t* bar, int b, int h, int hk,
+                                             const uint8_t* base, int warp, int lane) {
   constexpr float qmax = static_cast<float>((1 << (B - 1)) - 1);
   constexpr int iq = (1 << (B - 1)) - 1;
   constexpr int ROWB = RD * B / 8;
@@ -194,6 +242,10 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
   const unsigned short* Rf = reinterpret_cast<const unsigned short*>(C.raw + RD * ROWB);
   const unsigned short* Cf = Rf + RD;
 
+  // ---- the head's prologue on warp 0; meanwhile the other warps fetch v and w and, once the head's bytes have landed,
+  // decode their part of the tile (which needs nothing of the prologue): warp 0 follows when it is done ----
+  gga_reg_prologue(A, C, sc, b, h, hk, base, C.window, warp, lane);
+  const bool landed = mbar_wait(bar, 0, A.wait_ns);
   // ---- decode: x = (r c) (code - qmax), pairs (columns 0,1) and (2,3) ----
   float2 x[RPW][2];
   {
@@ -211,6 +263,10 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
       x[r][1] = __fmul2_rn(__fmul2_rn(make_float2(rr, rr), c23), z23);
     }
   }
+  // (a bounded wait: the verdict is taken by the whole CTA together, since threads poll on their own clocks; the barrier
+  // also publishes the prologue's results)
+  if (__syncthreads_or(!landed)) return false;
+  C.a = sc[0]; C.bq = sc[1]; C.n = __float_as_int(sc[2]); C.hd = __float_as_int(sc[3]);
   // ---- kO = k^T O: this warp's 16 rows, then the 8 warps ----
   {
     float2 s0 = make_float2(0.f, 0.f), s1 = s0;
@@ -449,6 +505,7 @@ __device__ __forceinline__ void gga_reg_head(const GgaRegCtx& C, int warp, int l
   }
   unsigned short* Rw = reinterpret_cast<unsigned short*>(C.raw + RD * ROWB);
   if (tid < RD) { Rw[tid] = f2h(C.rs[tid]); Rw[RD + tid] = f2h(C.cs[tid]); }
+  return true;
 }
 
 #ifndef SQB_GGA_REG_MINB
@@ -488,60 +545,18 @@ __global__ void __launch_bounds__(RNT, SQB_GGA_REG_MINB) gga_step_reg_kernel(con
   C.rs = fs + P.rs; C.rrs = fs + P.rrs; C.cs = fs + P.cs; C.rcs = fs + P.rcs; C.pa = fs + P.pa; C.pb = fs + P.pb;
   C.Pw = fs + P.Pw; C.Vw = fs + P.Vw; C.coef = fs + P.coef;
   C.M = M; C.window = window; C.orow = orow; C.dt_out = A.dt_out;
-  // q, k (fla's normalisation), gates: gga_step_kernel's arithmetic, on ONE warp (four channels per lane, sums by
-  // shuffles), while the other warps bring in v and w; the block barrier below publishes it all
+  __syncthreads();                                          // nobody looks at the barrier before thread 0 has set it up
   float* sc = fs + P.red;                                   // a, (beta k) . q, window count, ring head
-  if (warp == 0) {
-    const Raw4 rq = ld4_raw(A.q + (long long)b * A.sq, A.dt_qk, (long long)hk * RD + 4 * lane);
-    const Raw4 rk = ld4_raw(A.k + (long long)b * A.sk, A.dt_qk, (long long)hk * RD + 4 * lane);
-    const uint32_t ra = ld1_raw(A.a + (long long)b * A.sa, A.dt_ab, h), rdb = ld1_raw(A.dt_bias, A.dt_dtb, h);
-    const uint32_t ral = ld1_raw(A.A_log, A.dt_alog, h), rb = ld1_raw(A.b + (long long)b * A.sb, A.dt_ab, h);
-    int n = 0, hd = 0;
-    if (window && lane == 0) { const int* ct = reinterpret_cast<const int*>(base); n = ct[0]; hd = ct[1]; }
-    float qv[4], kv[4];
-    cvt4_raw(rq, A.dt_qk, qv);
-    cvt4_raw(rk, A.dt_qk, kv);
-    float sq = (qv[0] * qv[0] + qv[1] * qv[1]) + (qv[2] * qv[2] + qv[3] * qv[3]);
-    float sk = (kv[0] * kv[0] + kv[1] * kv[1]) + (kv[2] * kv[2] + kv[3] * kv[3]);
-    sq = warp_sum(sq);
-    sk = warp_sum(sk);
-    const float nq = __fsqrt_rn(sq + 1e-6f), nk = __fsqrt_rn(sk + 1e-6f);
-    const float xg = cvt_raw(ra, A.dt_ab) + cvt_raw(rdb, A.dt_dtb);
-    const float sp = xg <= 20.0f ? logf(1.0f + expf(xg)) : xg;
-    const float a = expf(-expf(cvt_raw(ral, A.dt_alog)) * sp);
-    const float beta = __fdiv_rn(1.0f, 1.0f + expf(-cvt_raw(rb, A.dt_ab)));
-    float qn[4], kn[4], bkv[4], bqp = 0.f;
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-      qn[j] = __fdiv_rn(qv[j], nq) * A.scale;
-      kn[j] = __fdiv_rn(kv[j], nk);
-      bkv[j] = beta * kn[j];
-      bqp += bkv[j] * qn[j];
-    }
-    bqp = warp_sum(bqp);
-    *reinterpret_cast<float4*>(C.q + 4 * lane) = make_float4(qn[0], qn[1], qn[2], qn[3]);
-    *reinterpret_cast<float4*>(C.k + 4 * lane) = make_float4(kn[0], kn[1], kn[2], kn[3]);
-    *reinterpret_cast<float4*>(C.bk + 4 * lane) = make_float4(bkv[0], bkv[1], bkv[2], bkv[3]);
-    if (lane == 0) { sc[0] = a; sc[1] = bqp; sc[2] = __int_as_float(n); sc[3] = __int_as_float(hd); }
-  } else {
-    for (int i = tid - 32; i < RD; i += RNT - 32) {
-      C.v[i] = ldf(A.v + (long long)b * A.sv, A.dt_v, (long long)h * RD + i);
-      C.w[i] = A.w[(long long)h * RD + i];
-    }
-  }
-  __syncthreads();                                          // (also: nobody looks at the barrier before thread 0 has set it up)
-  // the head's bytes and the window's
-  // (a bounded wait; the verdict is taken by the whole CTA together, since threads poll on their own clocks.  Both copies
-  // complete on this one barrier, so after a wait that ran out there is nothing further to drain.)
-  if (__syncthreads_or(!mbar_wait(bar, 0, A.wait_ns))) {
+  bool done;
+  if (bits == 4) done = gga_reg_head<4>(C, A, sc, bar, b, h, hk, base, warp, lane);
+  else if (bits == 6) done = gga_reg_head<6>(C, A, sc, bar, b, h, hk, base, warp, lane);
+  else done = gga_reg_head<8>(C, A, sc, bar, b, h, hk, base, warp, lane);
+  if (!done) {
+    // both copies complete on the one barrier, so after a wait that ran out there is nothing further to drain
     for (int v = tid; v < RD; v += RNT) stf(orow, A.dt_out, v, 0.0f);
     if (tid == 0 && A.status) atomicAdd(&A.status[0], 1);
     return;
   }
-  C.a = sc[0]; C.bq = sc[1]; C.n = __float_as_int(sc[2]); C.hd = __float_as_int(sc[3]);
-  if (bits == 4) gga_reg_head<4>(C, warp, lane);
-  else if (bits == 6) gga_reg_head<6>(C, warp, lane);
-  else gga_reg_head<8>(C, warp, lane);
   // back to the slot
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncthreads();
