@@ -552,6 +552,10 @@ LONG_TAIL = [
     # the fold launch's shared-memory plan does not fit: the whole step must fall to the generic kernel BEFORE anything
     # is appended (a step kernel that ran ahead of a refused fold would leave the slot between two states)
     dict(kind='gdn', fmt=(8, 'k', 32), B=1, hv=2, hk=1, dk=128, dv=512, m=32, bb=8, seed=69),
+    # 4-bit codes scaled along v at the tensor-core kernel's shapes (per-warp scale-folded read-out vectors, the fold with
+    # in-warp column maxima), fp32 and bf16 buffers
+    dict(kind='gdn', fmt=(4, 'v', 32), B=2, hv=4, hk=2, dk=128, dv=128, m=8, bb=8, seed=71),
+    dict(kind='gdn', fmt=(4, 'v', 32), B=1, hv=6, hk=2, dk=128, dv=128, m=8, bb=8, seed=72),
 ]
 
 
@@ -567,11 +571,14 @@ def test_long_tail_shapes_match_oracle(c, kernel_path):
     assert st['scal'] <= max(1, 1e-4 * st['ncodes']), st
 
 
-@pytest.mark.parametrize('name', ['gdn_pace4_qwen', 'm2_int8k32_m8_b8', 'kda_pace4'])
+INT4V_128 = dict(kind='gdn', fmt=(4, 'v', 32), B=1, hv=4, hk=2, dk=128, dv=128, m=8, bb=8, T=17, seed=73)
+
+
+@pytest.mark.parametrize('name', ['gdn_pace4_qwen', 'm2_int8k32_m8_b8', 'kda_pace4', 'gdn_int4v_128'])
 def test_extreme_read_out_vectors(name, kernel_path):
     """Read-out vectors that are all zero, tiny (1e-30) or huge (1e20) on alternating steps: the staged kernels hold
     them as fixed point with a per-vector power-of-two scale, which must cover the whole float range."""
-    c = dict(CASES[name], extreme=True)
+    c = dict(INT4V_128 if name == 'gdn_int4v_128' else CASES[name], extreme=True)
     st = _oracle_lockstep(c, T=2 * c['m'] + 3, act_dtype=torch.float32)
     assert st['worst'] < 2e-5, st
     assert st['buf'] <= max(1, 1e-4 * st['nbuf']), st
