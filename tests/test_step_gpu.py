@@ -556,6 +556,11 @@ LONG_TAIL = [
     # in-warp column maxima), fp32 and bf16 buffers
     dict(kind='gdn', fmt=(4, 'v', 32), B=2, hv=4, hk=2, dk=128, dv=128, m=8, bb=8, seed=71),
     dict(kind='gdn', fmt=(4, 'v', 32), B=1, hv=6, hk=2, dk=128, dv=128, m=8, bb=8, seed=72),
+    # key groups for which the tensor-core kernel folds in fp32 (more than one scale group, or less than one, per span)
+    dict(kind='gdn', fmt=(8, 'k', 64), B=1, hv=4, hk=2, dk=128, dv=128, m=8, bb=8, seed=74),
+    dict(kind='gdn', fmt=(4, 'k', 32), B=1, hv=4, hk=2, dk=128, dv=128, m=8, bb=8, seed=75),
+    dict(kind='gdn', fmt=(4, 'k', 128), B=1, hv=4, hk=2, dk=128, dv=128, m=8, bb=8, seed=76),
+    dict(kind='m2', fmt=(8, 'k', 128), B=1, hv=8, hk=2, dk=128, dv=64, m=8, bb=8, seed=77),
 ]
 
 
