@@ -36,6 +36,7 @@ import torch  # noqa: E402
 HV, HK, DK, DV, M = 32, 16, 128, 128, 8
 LAYERS = 24          # overridden by --layers (profiling runs use fewer)
 PRESETS = {'int8k': (8, 'k', 32), 'int4v': (4, 'v', 32), 'pace4': (4, 'k', 64)}
+EXTRA_PRESETS = {'int8v': (8, 'v', 32)}             # not in the default run: --preset int8v --no-variants
 METRIC = 'decode layer-steps/s (24-layer GDN stack, batch 256 slots per GPU)'
 UNIT = 'layer-steps/s'
 
@@ -113,7 +114,7 @@ class Stack:
     def __init__(self, preset, batch, device, seed):
         import statequant_b200 as sq
         from statequant_b200.kernels import SlotLayout
-        self.lay = SlotLayout(sq.Quantizer(*PRESETS[preset]), HV, HK, DK, DV, m=M, buffer_bits=8)
+        self.lay = SlotLayout(sq.Quantizer(*{**PRESETS, **EXTRA_PRESETS}[preset]), HV, HK, DK, DV, m=M, buffer_bits=8)
         self.batch, self.device = batch, device
         gen = torch.Generator().manual_seed(seed)
         self.blobs = [self.lay.alloc(batch + 1, device) for _ in range(LAYERS)]
@@ -477,7 +478,7 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--batch', type=int, default=256)
     ap.add_argument('--prewarm', type=int, default=512)
-    ap.add_argument('--preset', default='int8k', choices=list(PRESETS) + ['int8k128'])
+    ap.add_argument('--preset', default='int8k', choices=list(PRESETS) + list(EXTRA_PRESETS) + ['int8k128'])
     ap.add_argument('--no-variants', action='store_true', help='time the headline preset only')
     ap.add_argument('--layers', type=int, default=24, help='layers of the stack (24 = the benchmark; fewer for ncu captures)')
     ap.add_argument('--no-e2e', action='store_true', help='skip the host-buffer leg')

@@ -465,4 +465,149 @@ __device__ __forceinline__ void fold_stage_mma_v4(uint32_t st_addr, unsigned sho
   }
 }
 
+// The same for 8-bit codes scaled along v (pieces of four rows, see tile_row_v<8>): a chunk is 32 columns = 32 bytes of
+// a row, one ldmatrix.x4 per 16-row block; a thread holds columns 4t .. 4t + 3 and 16 + 4t .. 16 + 4t + 3 of the chunk
+// (N-block q: half q >> 1, byte pair q & 1) of four rows.
+template <int DV>
+__device__ __forceinline__ void fold_stage_mma_v8(uint32_t st_addr, unsigned short* scs, const int8_t* ubt, const float* udq,
+                                                  const float* tab, const float* ksf, const uint32_t* KBf, int w, int lane) {
+  constexpr int TABW = 20;
+  constexpr float QMAX = 127.0f, MB = MAGIC;
+  const int i = lane >> 2, t = lane & 3;
+  const int hh = (32 * w) / DV;
+  const float* tb = tab + hh * TABW;
+  const float2 al2 = make_float2(tb[16], tb[16]);
+  uint32_t A1[2][2], A2[2][2], A3[2][2];
+#pragma unroll
+  for (int bb = 0; bb < 2; bb++) {
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      const int rv0 = (32 * w + 4 * i + 2 * bb + r) % DV;
+      float p1[2], p2[2], p3[2];
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        const int sl = 2 * t + e;
+        float L;
+        if (sl < 7) L = tb[sl] * (static_cast<float>(ubt[(hh * 8 + sl) * DV + rv0]) * tb[8 + sl]);
+        else L = udq[hh * DV + rv0];
+        split3(L * ksf[sl], p1[e], p2[e], p3[e]);
+      }
+      A1[bb][r] = bf2(p1[0], p1[1]); A2[bb][r] = bf2(p2[0], p2[1]); A3[bb][r] = bf2(p3[0], p3[1]);
+    }
+  }
+#pragma unroll 1
+  for (int c4 = 0; c4 < 4; c4++) {
+    uint32_t m[2][4];
+    ldsm_x4(m[0], tile_lrow_v<8>(st_addr, w, lane, 0) + 32 * c4);
+    ldsm_x4(m[1], tile_lrow_v<8>(st_addr, w, lane, 1) + 32 * c4);
+    // the thread's 8 column scales: columns 4t .. 4t + 3 and 16 + 4t .. 16 + 4t + 3 of the chunk
+    unsigned short* scol = scs + w * 128 + 32 * c4 + 4 * t;
+    const uint2 swa = *reinterpret_cast<const uint2*>(scol), swb = *reinterpret_cast<const uint2*>(scol + 16);
+    const float2 so[4] = {__half22float2(*reinterpret_cast<const __half2*>(&swa.x)), __half22float2(*reinterpret_cast<const __half2*>(&swa.y)),
+                          __half22float2(*reinterpret_cast<const __half2*>(&swb.x)), __half22float2(*reinterpret_cast<const __half2*>(&swb.y))};
+    float acc[2][4][4];
+    // ---- start values: (code * scale) * alpha (fold_stage_mma's exact byte-in-mantissa product, one scale per column) ----
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+      const float2 mq = make_float2(so[q].x * 0.00390625f, so[q].y * 0.00390625f);
+      const float2 cq = make_float2(-8421376.0f * mq.x, -8421376.0f * mq.y);
+#pragma unroll
+      for (int bb = 0; bb < 2; bb++) {
+        const uint32_t wa = m[bb][2 * (q >> 1)] ^ 0x80808080u, wb = m[bb][2 * (q >> 1) + 1] ^ 0x80808080u;
+        float2 a, c;
+        if (q & 1) {
+          a = make_float2(__uint_as_float(__byte_perm(wa, 0x4B000000u, 0x7424)), __uint_as_float(__byte_perm(wa, 0x4B000000u, 0x7434)));
+          c = make_float2(__uint_as_float(__byte_perm(wb, 0x4B000000u, 0x7424)), __uint_as_float(__byte_perm(wb, 0x4B000000u, 0x7434)));
+        } else {
+          a = make_float2(__uint_as_float(__byte_perm(wa, 0x4B000000u, 0x7404)), __uint_as_float(__byte_perm(wa, 0x4B000000u, 0x7414)));
+          c = make_float2(__uint_as_float(__byte_perm(wb, 0x4B000000u, 0x7404)), __uint_as_float(__byte_perm(wb, 0x4B000000u, 0x7414)));
+        }
+        a = __fmul2_rn(__ffma2_rn(a, mq, cq), al2);
+        c = __fmul2_rn(__ffma2_rn(c, mq, cq), al2);
+        acc[bb][q][0] = a.x; acc[bb][q][1] = a.y; acc[bb][q][2] = c.x; acc[bb][q][3] = c.y;
+      }
+    }
+    // ---- the eight buffer slots ----
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+      const uint32_t kw = KBf[(c4 * 4 + q) * 32 + lane];
+#pragma unroll
+      for (int bb = 0; bb < 2; bb++) {
+        mma_bf16(acc[bb][q], A1[bb][0], A1[bb][1], A2[bb][0], A2[bb][1], kw, kw);
+        mma_bf16(acc[bb][q], A3[bb][0], A3[bb][1], 0u, 0u, kw, kw);
+      }
+    }
+    // ---- fresh scales: a column's absolute maximum over the group's 32 rows ----
+    float cm[8];
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        float mx = fmaxf(fmaxf(fabsf(acc[0][q][e]), fabsf(acc[0][q][2 + e])), fmaxf(fabsf(acc[1][q][e]), fabsf(acc[1][q][2 + e])));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+        cm[2 * q + e] = mx;
+      }
+    }
+    float mine = (i & 4) ? ((i & 2) ? ((i & 1) ? cm[7] : cm[6]) : ((i & 1) ? cm[5] : cm[4]))
+                         : ((i & 2) ? ((i & 1) ? cm[3] : cm[2]) : ((i & 1) ? cm[1] : cm[0]));
+    const float sc_mine = fp16_scale(mine, QMAX), rc_mine = rcp_approx(sc_mine);
+    __syncwarp();                                      // every lane has read the chunk's old scales
+    scol[(i >> 2) * 16 + (i & 3)] = f2h(sc_mine);      // column i of the thread's eight: (q, e) = (i >> 1, i & 1)
+    float sn[8], rn[8];
+    float smin = 1.0f;
+#pragma unroll
+    for (int x = 0; x < 8; x++) {
+      sn[x] = __shfl_sync(0xffffffffu, sc_mine, 4 * x + t);
+      rn[x] = __shfl_sync(0xffffffffu, rc_mine, 4 * x + t);
+      smin = fminf(smin, sn[x]);
+    }
+    // ---- round (the bracket of fold_stage_mma, one reciprocal per column) and repack ----
+#pragma unroll
+    for (int bb = 0; bb < 2; bb++) {
+      float tv[4][4];
+      uint32_t differ = 0;
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        const float2 lo = make_float2(fmaf(-rn[2 * q], 0x1p-22f, rn[2 * q]), fmaf(-rn[2 * q + 1], 0x1p-22f, rn[2 * q + 1]));
+        const float2 hi = make_float2(fmaf(rn[2 * q], 0x1p-22f, rn[2 * q]), fmaf(rn[2 * q + 1], 0x1p-22f, rn[2 * q + 1]));
+        const float2 mb2 = make_float2(MB, MB);
+        const float2 xa = make_float2(acc[bb][q][0], acc[bb][q][1]), xc = make_float2(acc[bb][q][2], acc[bb][q][3]);
+        const float2 la = __ffma2_rn(xa, lo, mb2), ha = __ffma2_rn(xa, hi, mb2);
+        const float2 lc = __ffma2_rn(xc, lo, mb2), hc = __ffma2_rn(xc, hi, mb2);
+        tv[q][0] = la.x; tv[q][1] = la.y; tv[q][2] = lc.x; tv[q][3] = lc.y;
+        differ |= (__float_as_uint(la.x) ^ __float_as_uint(ha.x)) | (__float_as_uint(la.y) ^ __float_as_uint(ha.y));
+        differ |= (__float_as_uint(lc.x) ^ __float_as_uint(hc.x)) | (__float_as_uint(lc.y) ^ __float_as_uint(hc.y));
+      }
+      if (differ != 0) {                               // rare: some element of this thread is close to a tie
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            tv[q][e] = div_round_cold(acc[bb][q][e], sn[2 * q + e], MB);
+            tv[q][2 + e] = div_round_cold(acc[bb][q][2 + e], sn[2 * q + e], MB);
+          }
+        }
+      }
+      if (smin < FP16_MIN_NORMAL) {                    // only a scale in fp16's subnormal range lets a quotient pass qmax
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+#pragma unroll
+          for (int e = 0; e < 4; e++) tv[q][e] = fminf(fmaxf(tv[q][e], MB - QMAX), MB + QMAX);
+        }
+      }
+      auto two = [](uint32_t a, uint32_t c) { return __byte_perm(a, c, 0x0040); };
+      auto u = [](float f) { return __float_as_uint(f); };
+      uint32_t o[4];
+      o[0] = __byte_perm(two(u(tv[0][0]), u(tv[0][1])), two(u(tv[1][0]), u(tv[1][1])), 0x5410);
+      o[1] = __byte_perm(two(u(tv[0][2]), u(tv[0][3])), two(u(tv[1][2]), u(tv[1][3])), 0x5410);
+      o[2] = __byte_perm(two(u(tv[2][0]), u(tv[2][1])), two(u(tv[3][0]), u(tv[3][1])), 0x5410);
+      o[3] = __byte_perm(two(u(tv[2][2]), u(tv[2][3])), two(u(tv[3][2]), u(tv[3][3])), 0x5410);
+      __syncwarp();                                    // every lane has read the block's codes of this chunk
+      stsm_x4(tile_lrow_v<8>(st_addr, w, lane, bb) + 32 * c4, o);
+    }
+  }
+}
+
 }  // namespace sqb

@@ -9,13 +9,13 @@ namespace sqb {
 // Shapes the tensor-core kernels take: 4 / 8-bit codes scaled along k in groups of 32, 64 or 128, d_k 128, d_v 64 or
 // 128 (whole stages of 128 rows per key head), int8 buffer, q / k per key head, every per-head chunk and table
 // stride a multiple of 16 bytes.
-// Scaled along v: 4-bit codes in groups of 32 rows, Gated DeltaNet, buffer length 8 (the fold inside the step kernel
+// Scaled along v: 4- or 8-bit codes in groups of 32 rows, Gated DeltaNet, buffer length 8 (the fold inside the step kernel
 // is the tensor-pipe one).
 inline bool mma_shape_ok(const StepArgs& a, int bits, bool axk, bool kda, int kind = K_GDN) {
   if ((bits != 4 && bits != 8) || a.DK != 128 || !a.qbuf) return false;
   if (a.DV != 64 && a.DV != 128) return false;
   if (!axk) {
-    if (bits != 4 || a.group != 32 || kind != K_GDN || a.M != 8 || a.DV != 128) return false;
+    if (a.group != 32 || kind != K_GDN || a.M != 8 || a.DV != 128) return false;
   } else if (a.group != 32 && a.group != 64 && a.group != 128) return false;
   if (!a.per_key_head && a.HV != a.HK) return false;
   const int gqa = a.HV / a.HK, hps = 128 / a.DV;
@@ -94,7 +94,8 @@ int launch_mma_one(const StepArgs& a, cudaStream_t stream) {
 template <int KIND, int DV, int MODE>
 int launch_mma_fmt(const StepArgs& a, int bits, cudaStream_t stream) {
   if (a.axv) {
-    if constexpr (KIND == K_GDN && DV == 128) return launch_mma_one<KIND, 4, 1, DV, MODE, true>(a, stream);
+    if constexpr (KIND == K_GDN && DV == 128)
+      return bits == 4 ? launch_mma_one<KIND, 4, 1, DV, MODE, true>(a, stream) : launch_mma_one<KIND, 8, 1, DV, MODE, true>(a, stream);
     else return 1;
   }
   const int upg = a.group / 32;

@@ -207,13 +207,28 @@ __device__ __forceinline__ void tile_pass(uint32_t codes, const unsigned short* 
 // exactly one group: rows 32 w .. 32 w + 31 of the stage = pieces 2w and 2w + 1, and builds its own B fragments for it.
 // Block bb (16 rows): fragment row f = row (f >> 1) + 8 bb of piece 2w + (f & 1).  With 64-byte rows (4-bit codes) the
 // eight row addresses of an ldmatrix tile then fall on four distinct 16-byte bank groups (a two-way conflict); with
-// 128-byte rows they would all collide, so 8-bit codes scaled along v do not come this way.
+// 128-byte rows they would all collide, so 8-bit codes scaled along v are staged in smaller pieces (below).
 // On return lane (i, t) holds the sums of stage row 32 w + 16 (i & 1) + (i >> 1) + 4 (t & 1) + 8 (t >> 1).
 
-// This lane's stage row in the layout above.
+// 8-bit codes (128-byte rows) scaled along v come in 32 pieces of FOUR rows instead (pitch 4 * 128 + 16): a group is
+// then eight pieces, fragment row i < 8 is row 2 bb of piece 8 w + i and fragment row 8 + i its row 2 bb + 1, and the
+// eight row addresses of an ldmatrix tile fall on distinct banks again.  On return lane (i, t) holds stage row
+// 32 w + 4 i + t.
+constexpr int V8_PIECE_ROWS = 4, V8_PITCH = V8_PIECE_ROWS * 128 + 16;
+
+// This lane's stage row in the layouts above.
+template <int BITS>
 __device__ __forceinline__ int tile_row_v(int w, int lane) {
   const int i = lane >> 2, t = lane & 3;
+  if (BITS == 8) return 32 * w + 4 * i + t;
   return 32 * w + 16 * (i & 1) + (i >> 1) + 4 * (t & 1) + 8 * (t >> 1);
+}
+// shared address of the ldmatrix row this lane supplies for block bb of warp w's group (first 32 bytes of the rows)
+template <int BITS>
+__device__ __forceinline__ uint32_t tile_lrow_v(uint32_t codes, int w, int lane, int bb) {
+  if (BITS == 8) return codes + (8 * w + (lane & 7)) * V8_PITCH + (2 * bb + ((lane >> 3) & 1)) * 128 + (lane >> 4) * 16;
+  constexpr int ROWB = 64, PITCH = 16 * ROWB + 16;
+  return codes + (2 * w + (lane & 1)) * PITCH + (((lane & 7) >> 1) + 4 * ((lane >> 3) & 1) + 8 * bb) * ROWB + (lane >> 4) * 16;
 }
 
 // The warp's B fragments for its group: sg = the group's 128 column scales (fp16), vq / vk = the read-out vectors
@@ -251,16 +266,14 @@ __device__ __forceinline__ void build_b_v(uint32_t* Bf, const unsigned short* sg
 template <int BITS>
 __device__ __forceinline__ void tile_pass_v(uint32_t codes, const unsigned short* one, const uint32_t (&bf)[8], int w,
                                             int lane, float& tq, float& tk) {
-  constexpr int ROWB = 128 * BITS / 8, PITCH = 16 * ROWB + 16;
   const int t = lane & 3;
   int ci[1][2];
   acc_start<BITS, 4>(bf, ci);
-  const uint32_t lrow = codes + (2 * w + (lane & 1)) * PITCH + (((lane & 7) >> 1) + 4 * ((lane >> 3) & 1)) * ROWB + (lane >> 4) * 16;
   float T[2];
 #pragma unroll
   for (int bb = 0; bb < 2; bb++) {
     float p[4] = {0.f, 0.f, 0.f, 0.f};
-    block_pass<BITS, 4>(lrow + 8 * bb * ROWB, one, bf, ci, p);
+    block_pass<BITS, 4>(tile_lrow_v<BITS>(codes, w, lane, bb), one, bf, ci, p);
     T[bb] = join_digits(p, t);
   }
   const float recv = __shfl_xor_sync(0xffffffffu, t < 2 ? T[1] : T[0], 2);

@@ -1,6 +1,6 @@
 // The fused packed-state decode step with the state pass on the tensor pipe (mma_pass.cuh): 4- and 8-bit states scaled
-// along k in groups of 32, 64 or 128 (and 4-bit states scaled along v in groups of 32 rows), head dim d_k = 128, d_v 64
-// or 128, int8 decode buffer.
+// along k in groups of 32, 64 or 128 (and 4- / 8-bit states scaled along v in groups of 32 rows), head dim d_k = 128,
+// d_v 64 or 128, int8 decode buffer.
 //
 // One CTA (128 threads) per (batch row, KEY head, part of its value heads) walks its value heads in STAGES of 128
 // state rows (one head of d_v 128, two heads of d_v 64).  A stage -- codes as 8 padded pieces, scales, buffered
@@ -47,15 +47,17 @@ struct SmemM {
 // group per 32-byte span of a row; otherwise in fp32 (fold_rows.cuh), which needs the R / L tiles.
 // (axv: 4-bit codes scaled along v in groups of 32 rows, fold_stage_mma_v4.)
 __host__ __device__ inline bool fold_on_tensor_pipe(int kind, int bits, int upg, int M, bool axv = false) {
-  if (axv) return kind != K_KDA && M == 8 && bits == 4;
+  if (axv) return kind != K_KDA && M == 8 && (bits == 4 || bits == 8);
   return M == 8 && ((bits == 8 && upg == 1) || (bits == 4 && upg == 2));
 }
 __host__ __device__ inline SmemM smemm_plan(int kind, int bits, int upg, int DV, int M, int nst, int gqa, bool fold,
                                             bool axv = false) {
   const bool simt = fold && !fold_on_tensor_pipe(kind, bits, upg, M, axv), tens = fold && !simt;
   SmemM s;
-  const int rowb = 128 * bits / 8, pitch = 16 * rowb + 16, ng = 4 / upg;
-  s.sc_off = 8 * pitch;
+  const int rowb = 128 * bits / 8, ng = 4 / upg;
+  const bool v8 = axv && bits == 8;                  // 8-bit codes scaled along v: 32 pieces of 4 rows (mma_pass.cuh)
+  const int pitch = v8 ? V8_PITCH : 16 * rowb + 16;
+  s.sc_off = (v8 ? 32 : 8) * pitch;
   s.ub_off = s.sc_off + 128 * ng * 2;
   s.stage_bytes = s.ub_off + al16i(M * 128);
   int o = 0;
@@ -121,14 +123,14 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (KIN
                                                : (BITS == 4 ? SQB_MMA_MINB4 : SQB_MMA_MINB8))
     step_mma_kernel(const __grid_constant__ StepArgs A, const __grid_constant__ SmemM P, const int nst) {
   constexpr int DK = 128, NG = 4 / UPG, G = 32 * UPG;
-  constexpr int ROWB = DK * BITS / 8, PITCH = 16 * ROWB + 16;
+  constexpr bool V8 = AXV && BITS == 8;          // 32 pieces of 4 rows instead of 8 pieces of 16
+  constexpr int ROWB = DK * BITS / 8, PROWS = V8 ? V8_PIECE_ROWS : 16, NPIECE = 128 / PROWS, PITCH = PROWS * ROWB + 16;
   constexpr int HPS = 128 / DV;                  // heads per stage
   constexpr int CW = 4;                          // columns per lane in the prologue
   constexpr bool TWO = KIND != K_M2, VDEC = KIND == K_KDA, CANFOLD = MODE == 3;
-  constexpr bool TFMT = AXV ? BITS == 4 : ((BITS == 8 && UPG == 1) || (BITS == 4 && UPG == 2));
+  constexpr bool TFMT = AXV || (BITS == 8 && UPG == 1) || (BITS == 4 && UPG == 2);
   static_assert(DV == 64 || DV == 128, "a stage is 128 rows: one or two heads");
-  static_assert(!AXV || (BITS == 4 && UPG == 1 && !VDEC && (MODE == 0 || TFMT)),
-                "scales along v: 4-bit codes, groups of 32 rows (the stage's scales are [4][128], as many bytes as UPG = 1)");
+  static_assert(!AXV || (UPG == 1 && !VDEC), "scales along v: groups of 32 rows (the stage's scales are [4][128], as many bytes as UPG = 1)");
 
   extern __shared__ __align__(128) uint8_t smraw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -188,7 +190,7 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (KIN
   // a loaded word already waits for it), and a wait never sits in front of fetches that do not depend on it:
   //   warps 0 and 3 need q and k first and the slot only later: their q / k loads leave before the slot index;
   //   warps 1 and 2 issue the bulk copies, which need nothing but the slot index: they load it alone.
-  const int rho = AXV ? tile_row_v(warp, lane) : (lane >> 2) * 16 + 4 * warp + (lane & 3);     // this lane's row within a stage
+  const int rho = AXV ? tile_row_v<BITS>(warp, lane) : (lane >> 2) * 16 + 4 * warp + (lane & 3);     // this lane's row within a stage
   const int hh = rho / DV, rv = rho % DV;                        // head within the stage, row within the head
   Raw4 rq, rk;
   rq.v = make_uint4(0u, 0u, 0u, 0u); rk.v = rq.v; rq.vec = false; rk.vec = false;
@@ -241,9 +243,10 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (KIN
   auto issue_stage = [&](int s, int sh, int l) {
     uint8_t* st = smraw + P.stage0 + s * P.stage_bytes;
     const long long row0 = (long long)h0 * DV + sh * 128;
-    if (l < 8) bulk_g2s(st + l * PITCH, Sseq + (row0 + l * 16) * ROWB, 16 * ROWB, &bars[s]);
-    else if (l == 8) bulk_g2s(st + P.sc_off, SCseq + row0 * NG * 2, 128 * NG * 2, &bars[s]);
-    else if (l == 9) bulk_g2s(st + P.ub_off, UBseq + (long long)(h0 + sh * HPS) * M * DV, M * 128, &bars[s]);
+    if (l < NPIECE) bulk_g2s(st + l * PITCH, Sseq + (row0 + l * PROWS) * ROWB, PROWS * ROWB, &bars[s]);
+    const int x = V8 ? l + 32 : l;                           // (32 pieces take every lane: two of them copy twice)
+    if (x == NPIECE) bulk_g2s(st + P.sc_off, SCseq + row0 * NG * 2, 128 * NG * 2, &bars[s]);
+    else if (x == NPIECE + 1) bulk_g2s(st + P.ub_off, UBseq + (long long)(h0 + sh * HPS) * M * DV, M * 128, &bars[s]);
   };
   // A stage barrier of the first fill is initialised, armed and its copies issued by ONE warp (a warp's copies leave
   // one after the other, so the stages are spread over warps 2 and 1); everybody else meets it after the block barrier.
@@ -454,6 +457,10 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (KIN
       *reinterpret_cast<float4*>(wq + lane * CW) = make_float4(eq[0], eq[1], eq[2], eq[3]);
       *reinterpret_cast<float4*>(wk + lane * CW) = make_float4(ek[0], ek[1], ek[2], ek[3]);
       if (lane == 0) misc[9] = __uint_as_float(0x3C003C00u);      // the fp16 pair (1, 1): the blocks carry no scale
+      if (BITS == 8) {                      // the key tile's product still takes the plain vectors, in the byte layout
+        put_b_words<8>(Bfw, lane, 0, yq[0], yq[1], yq[2], yq[3]);
+        put_b_words<8>(Bfw, lane, 1, yk[0], yk[1], yk[2], yk[3]);
+      }
     } else {
       put_b_words<BITS>(Bfw, lane, 0, yq[0], yq[1], yq[2], yq[3]);
       put_b_words<BITS>(Bfw, lane, 1, yk[0], yk[1], yk[2], yk[3]);
@@ -756,7 +763,10 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (KIN
             if (i == 0) tab[hq * 20 + 16] = expf(gnew);
           }
           __syncthreads();
-          if constexpr (AXV)
+          if constexpr (AXV && BITS == 8)
+            fold_stage_mma_v8<DV>(smem_u32(st), reinterpret_cast<unsigned short*>(st + P.sc_off),
+                                  reinterpret_cast<const int8_t*>(st + P.ub_off), us + sh * HPS * DV, tab, ksf, KBf, warp, lane);
+          else if constexpr (AXV)
             fold_stage_mma_v4<DV>(smem_u32(st), reinterpret_cast<unsigned short*>(st + P.sc_off),
                                   reinterpret_cast<const int8_t*>(st + P.ub_off), us + sh * HPS * DV, tab, ksf, KBf, warp, lane);
           else
@@ -768,8 +778,8 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (KIN
             // the stage goes back to the slot: eight pieces of codes and the scales, as bulk copies
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             const long long row0 = (long long)h0 * DV + sh * 128;
-            if (lane < 8) bulk_s2g(Sseq + (row0 + lane * 16) * ROWB, st + lane * PITCH, 16 * ROWB);
-            else if (lane == 8) bulk_s2g(SCseq + row0 * NG * 2, st + P.sc_off, 128 * NG * 2);
+            if (lane < NPIECE) bulk_s2g(Sseq + (row0 + lane * PROWS) * ROWB, st + lane * PITCH, PROWS * ROWB);
+            if (lane == (V8 ? 0 : NPIECE)) bulk_s2g(SCseq + row0 * NG * 2, st + P.sc_off, 128 * NG * 2);
             bulk_commit();
             if (sh + nst < NSH || sh + 1 == NSH) bulk_wait_read();   // before the stage is refilled, and before leaving
           }

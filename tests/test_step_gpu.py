@@ -556,6 +556,7 @@ LONG_TAIL = [
     # in-warp column maxima), fp32 and bf16 buffers
     dict(kind='gdn', fmt=(4, 'v', 32), B=2, hv=4, hk=2, dk=128, dv=128, m=8, bb=8, seed=71),
     dict(kind='gdn', fmt=(4, 'v', 32), B=1, hv=6, hk=2, dk=128, dv=128, m=8, bb=8, seed=72),
+    dict(kind='gdn', fmt=(8, 'v', 32), B=2, hv=4, hk=2, dk=128, dv=128, m=8, bb=8, seed=78),   # pieces of four rows
     # key groups for which the tensor-core kernel folds in fp32 (more than one scale group, or less than one, per span)
     dict(kind='gdn', fmt=(8, 'k', 64), B=1, hv=4, hk=2, dk=128, dv=128, m=8, bb=8, seed=74),
     dict(kind='gdn', fmt=(4, 'k', 32), B=1, hv=4, hk=2, dk=128, dv=128, m=8, bb=8, seed=75),
@@ -579,18 +580,19 @@ def test_long_tail_shapes_match_oracle(c, kernel_path):
 INT4V_128 = dict(kind='gdn', fmt=(4, 'v', 32), B=1, hv=4, hk=2, dk=128, dv=128, m=8, bb=8, T=17, seed=73)
 
 
-@pytest.mark.parametrize('name', ['gdn_pace4_qwen', 'm2_int8k32_m8_b8', 'kda_pace4', 'gdn_int4v_128'])
+@pytest.mark.parametrize('name', ['gdn_pace4_qwen', 'm2_int8k32_m8_b8', 'kda_pace4', 'gdn_int4v_128', 'gdn_int8v_128'])
 def test_extreme_read_out_vectors(name, kernel_path):
     """Read-out vectors that are all zero, tiny (1e-30) or huge (1e20) on alternating steps: the staged kernels hold
     them as fixed point with a per-vector power-of-two scale, which must cover the whole float range."""
-    c = dict(INT4V_128 if name == 'gdn_int4v_128' else CASES[name], extreme=True)
+    c = dict(INT4V_128 if name == 'gdn_int4v_128' else dict(INT4V_128, fmt=(8, 'v', 32), seed=79) if name == 'gdn_int8v_128'
+             else CASES[name], extreme=True)
     st = _oracle_lockstep(c, T=2 * c['m'] + 3, act_dtype=torch.float32)
     assert st['worst'] < 2e-5, st
     assert st['buf'] <= max(1, 1e-4 * st['nbuf']), st
     assert st['codes'] <= max(1, 1e-4 * st['ncodes']), st
 
 
-@pytest.mark.parametrize('preset,fmt', [('int8k', (8, 'k', 32)), ('int4v', (4, 'v', 32))])
+@pytest.mark.parametrize('preset,fmt', [('int8k', (8, 'k', 32)), ('int4v', (4, 'v', 32)), ('int8v', (8, 'v', 32))])
 def test_full_batch_properties_gdn_presets(preset, fmt):
     """The benchmark's headline preset (int8k) and its int4v variant at the benchmark's shapes (32 value heads, 16 key
     heads, d 128, batch 256, bf16 activations, in-kernel gate): determinism, padding rows, a sample of rows against the
