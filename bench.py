@@ -405,6 +405,45 @@ def cpu_baseline(batch, steps, warmup, preset='int8k'):
     return steps / dt, oracle.num_threads(), dt
 
 
+def time_slot_io(preset, batch, device, layers=4, reps=5):
+    """The prefill boundary of the same layout (the device kernels behind ``SlotLayout.read`` / ``write``): one call
+    reads `batch` slots' current state as fp32 (stored state advanced across the pending buffer), one call packs fp32
+    states into the slots.  Rotating over `layers` blobs (far above L2), CUDA events, microseconds per call and
+    algorithmic GB/s (fp32 states + the slots' packed bytes)."""
+    import statequant_b200 as sq
+    from statequant_b200.kernels import SlotLayout
+    lay = SlotLayout(sq.Quantizer(*{**PRESETS, **EXTRA_PRESETS}[preset]), HV, HK, DK, DV, m=M, buffer_bits=8)
+    gen = torch.Generator().manual_seed(3)
+    blobs = [lay.alloc(batch + 1, device) for _ in range(layers)]
+    views = [lay.views(b) for b in blobs]
+    idx = (torch.randperm(batch, generator=gen) + 1).to(torch.int32).to(device)
+    S = [(torch.randn(batch, HV, DV, DK, generator=gen) * 0.3).to(device) for _ in range(2)]
+    for v in views:
+        lay.write(v, idx, S[0])
+    bd = lay.breakdown()
+    packed = bd['S'] + bd.get('SC', 0)
+    f32 = HV * DV * DK * 4
+    out = {}
+    for name, fn, nbytes in (('write', lambda v, i: lay.write(v, idx, S[i & 1]), f32 + packed),
+                             ('read', lambda v, i: lay.read(v, idx), f32 + packed + bd['KB'] + bd['UB'])):
+        for i, v in enumerate(views):
+            fn(v, i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for r in range(reps):
+            for i, v in enumerate(views):
+                fn(v, i)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (reps * layers)
+        out[name + '_us_per_call'] = us
+        out[name + '_gbs'] = batch * nbytes / (us * 1e-6) / 1e9
+    out['slots_per_call'] = batch
+    out['workload'] = f'SlotLayout.read / write of {batch} slots ({preset}), fp32 states in HBM'
+    return out
+
+
 def ncu_traffic(preset, batch):
     """DRAM bytes (read + write) per layer-step from the ncu captures summarised under profiles/ (traffic.json, written
     next to the summaries: per preset the bytes of a launch that does not fold and of one in which every head folds,
@@ -629,6 +668,7 @@ def main():
         del stack
         torch.cuda.empty_cache()
         LAYERS = saved
+        results['slot_io_' + args.preset] = time_slot_io(args.preset, args.batch, device)
         results['config4_gga_slot_scaling'] = run_config4(args, rank, world, device, barrier, max_over_ranks)
 
     if rank != 0:

@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (KIN
     step_mma_kernel(const __grid_constant__ StepArgs A, const __grid_constant__ SmemM P, const int nst) {
   constexpr int DK = 128, NG = 4 / UPG, G = 32 * UPG;
   constexpr bool V8 = AXV && BITS == 8;          // 32 pieces of 4 rows instead of 8 pieces of 16
-  constexpr int ROWB = DK * BITS / 8, PROWS = V8 ? V8_PIECE_ROWS : 16, NPIECE = 128 / PROWS, PITCH = PROWS * ROWB + 16;
+  constexpr int ROWB = DK * BITS / 8, PROWS = V8 ? V8_PIECE_ROWS : 16, PITCH = PROWS * ROWB + 16;
   constexpr int HPS = 128 / DV;                  // heads per stage
   constexpr int CW = 4;                          // columns per lane in the prologue
   constexpr bool TWO = KIND != K_M2, VDEC = KIND == K_KDA, CANFOLD = MODE == 3;
@@ -243,10 +243,15 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (KIN
   auto issue_stage = [&](int s, int sh, int l) {
     uint8_t* st = smraw + P.stage0 + s * P.stage_bytes;
     const long long row0 = (long long)h0 * DV + sh * 128;
-    if (l < NPIECE) bulk_g2s(st + l * PITCH, Sseq + (row0 + l * PROWS) * ROWB, PROWS * ROWB, &bars[s]);
-    const int x = V8 ? l + 32 : l;                           // (32 pieces take every lane: two of them copy twice)
-    if (x == NPIECE) bulk_g2s(st + P.sc_off, SCseq + row0 * NG * 2, 128 * NG * 2, &bars[s]);
-    else if (x == NPIECE + 1) bulk_g2s(st + P.ub_off, UBseq + (long long)(h0 + sh * HPS) * M * DV, M * 128, &bars[s]);
+    if constexpr (V8) {                                      // 32 pieces take every lane: two of them copy twice
+      bulk_g2s(st + l * PITCH, Sseq + (row0 + l * PROWS) * ROWB, PROWS * ROWB, &bars[s]);
+      if (l == 0) bulk_g2s(st + P.sc_off, SCseq + row0 * NG * 2, 128 * NG * 2, &bars[s]);
+      else if (l == 1) bulk_g2s(st + P.ub_off, UBseq + (long long)(h0 + sh * HPS) * M * DV, M * 128, &bars[s]);
+    } else {
+      if (l < 8) bulk_g2s(st + l * PITCH, Sseq + (row0 + l * 16) * ROWB, 16 * ROWB, &bars[s]);
+      else if (l == 8) bulk_g2s(st + P.sc_off, SCseq + row0 * NG * 2, 128 * NG * 2, &bars[s]);
+      else if (l == 9) bulk_g2s(st + P.ub_off, UBseq + (long long)(h0 + sh * HPS) * M * DV, M * 128, &bars[s]);
+    }
   };
   // A stage barrier of the first fill is initialised, armed and its copies issued by ONE warp (a warp's copies leave
   // one after the other, so the stages are spread over warps 2 and 1); everybody else meets it after the block barrier.
@@ -778,8 +783,13 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (KIN
             // the stage goes back to the slot: eight pieces of codes and the scales, as bulk copies
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             const long long row0 = (long long)h0 * DV + sh * 128;
-            if (lane < NPIECE) bulk_s2g(Sseq + (row0 + lane * PROWS) * ROWB, st + lane * PITCH, PROWS * ROWB);
-            if (lane == (V8 ? 0 : NPIECE)) bulk_s2g(SCseq + row0 * NG * 2, st + P.sc_off, 128 * NG * 2);
+            if constexpr (V8) {
+              bulk_s2g(Sseq + (row0 + lane * PROWS) * ROWB, st + lane * PITCH, PROWS * ROWB);
+              if (lane == 0) bulk_s2g(SCseq + row0 * NG * 2, st + P.sc_off, 128 * NG * 2);
+            } else {
+              if (lane < 8) bulk_s2g(Sseq + (row0 + lane * 16) * ROWB, st + lane * PITCH, 16 * ROWB);
+              else if (lane == 8) bulk_s2g(SCseq + row0 * NG * 2, st + P.sc_off, 128 * NG * 2);
+            }
             bulk_commit();
             if (sh + nst < NSH || sh + 1 == NSH) bulk_wait_read();   // before the stage is refilled, and before leaving
           }
