@@ -158,13 +158,17 @@ __device__ __forceinline__ void block_pass(uint32_t a_addr, const unsigned short
       mma_i8<true>(acc[(2 * J + 1) / UPG], l2, l3, h2, h3, bf[4 * J + 2], bf[4 * J + 3]);
     }
   }
+  // (the accumulators of a row are a register pair: packed f32x2 arithmetic, same roundings)
+  float2 p01 = make_float2(p[0], p[1]), p23 = make_float2(p[2], p[3]);
+  const float2 nm = make_float2(-12582912.0f, -12582912.0f);
 #pragma unroll
   for (int g = 0; g < NG; g++) {
-    p[0] = fmaf(__int_as_float(acc[g][0]) - 12582912.0f, s0[g], p[0]);
-    p[1] = fmaf(__int_as_float(acc[g][1]) - 12582912.0f, s0[g], p[1]);
-    p[2] = fmaf(__int_as_float(acc[g][2]) - 12582912.0f, s1[g], p[2]);
-    p[3] = fmaf(__int_as_float(acc[g][3]) - 12582912.0f, s1[g], p[3]);
+    const float2 a01 = __fadd2_rn(make_float2(__int_as_float(acc[g][0]), __int_as_float(acc[g][1])), nm);
+    const float2 a23 = __fadd2_rn(make_float2(__int_as_float(acc[g][2]), __int_as_float(acc[g][3])), nm);
+    p01 = __ffma2_rn(a01, make_float2(s0[g], s0[g]), p01);
+    p23 = __ffma2_rn(a23, make_float2(s1[g], s1[g]), p23);
   }
+  p[0] = p01.x; p[1] = p01.y; p[2] = p23.x; p[3] = p23.y;
 }
 
 // Recombine the digit pair of a thread: after this, lane t = 0 holds vector 0 of row0, t = 1 vector 0 of row1,
