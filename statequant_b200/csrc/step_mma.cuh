@@ -119,7 +119,7 @@ __device__ __forceinline__ void prefetch_l2_line(const void* p) {
 #endif
 
 template <int KIND, int BITS, int UPG, int DV, int MODE, bool AXV = false>
-__global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (KIND != K_KDA && ((BITS == 8 && UPG == 1) || (BITS == 4 && UPG == 2)) ? SQB_MMA_MINB_TFOLD : SQB_MMA_MINB_FOLD))
+__global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((BITS == 8 && UPG == 1) || (BITS == 4 && UPG == 2)) ? SQB_MMA_MINB_TFOLD : SQB_MMA_MINB_FOLD))
                                                : (BITS == 4 ? SQB_MMA_MINB4 : SQB_MMA_MINB8))
     step_mma_kernel(const __grid_constant__ StepArgs A, const __grid_constant__ SmemM P, const int nst) {
   constexpr int DK = 128, NG = 4 / UPG, G = 32 * UPG;
