@@ -444,6 +444,46 @@ def time_slot_io(preset, batch, device, layers=4, reps=5):
     return out
 
 
+def time_conv_update(batch, device, layers=24, reps=6):
+    """The short causal convolution in front of the step (`causal_conv1d_update`, one token per row): the GDN layer's
+    mixed q | k | v row of 2 HK DK + HV DV channels, width 4, bf16, SiLU, the cache as vLLM lays it out
+    ([lines, 3, dim]).  One cache per layer (24 x 12.6 MB: above L2), a CUDA graph of one call per layer, CUDA events.
+    Algorithmic bytes per row and channel: 3 state elements read and written, x read, the result written."""
+    from statequant_b200.kernels import causal_conv1d_update
+    gen = torch.Generator().manual_seed(5)
+    dim, width = 2 * HK * DK + HV * DV, 4
+    caches = [torch.randn(batch + 1, width - 1, dim, generator=gen).to(torch.bfloat16).to(device) for _ in range(layers)]
+    xs = [torch.randn(batch, dim, generator=gen).to(torch.bfloat16).to(device) for _ in range(layers)]
+    w = (torch.randn(dim, width, generator=gen) * 0.5).to(torch.bfloat16).to(device)
+    b = (torch.randn(dim, generator=gen) * 0.1).to(torch.bfloat16).to(device)
+    idx = (torch.randperm(batch, generator=gen) + 1).to(torch.int32).to(device)
+
+    def step():
+        for c, x in zip(caches, xs):
+            causal_conv1d_update(x, c.transpose(1, 2), w, b, 'silu', idx)
+
+    step()
+    torch.cuda.synchronize()
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        step()
+    for _ in range(3):
+        gr.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        gr.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (reps * layers)
+    nbytes = batch * dim * 2 * (2 * (width - 1) + 2)
+    peak, _ = measured_peak_gbs()
+    return {'us_per_call': us, 'gbs': nbytes / (us * 1e-6) / 1e9, 'frac_of_peak': nbytes / (us * 1e-6) / 1e9 / peak,
+            'algorithmic_bytes_per_call': nbytes, 'rows': batch, 'dim': dim,
+            'workload': f'causal_conv1d_update, {batch} rows x {dim} channels, width {width}, bf16, SiLU, {layers} caches in rotation'}
+
+
 def ncu_traffic(preset, batch):
     """DRAM bytes (read + write) per layer-step from the ncu captures summarised under profiles/ (traffic.json, written
     next to the summaries: per preset the bytes of a launch that does not fold and of one in which every head folds,
@@ -529,6 +569,8 @@ def main():
     ap.add_argument('--mma-hpc', type=int, default=0, help='tensor-core kernels: value heads per CTA (0: a whole key head)')
     ap.add_argument('--kernel-path', type=int, default=0, choices=[0, 1, 2, 3, 4],
                     help='0 best kernel for the shape; 1 generic; 2 staged + fold launch (profiling / comparison)')
+    ap.add_argument('--conv-only', action='store_true',
+                    help='time only the causal conv update in front of the step (--layers caches in rotation) and print its figures')
     args = ap.parse_args()
     global LAYERS
     LAYERS = args.layers
@@ -566,6 +608,10 @@ def main():
     if args.mma_hpc:
         _cabi.set_option('mma_heads_per_cta', args.mma_hpc)
     device = f'cuda:{local}'
+    if args.conv_only:
+        if rank == 0:
+            print(json.dumps({'conv_update': time_conv_update(args.batch, device, layers=args.layers, reps=max(1, args.steps))}))
+        return
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group('nccl', device_id=torch.device(device))
@@ -669,6 +715,7 @@ def main():
         torch.cuda.empty_cache()
         LAYERS = saved
         results['slot_io_' + args.preset] = time_slot_io(args.preset, args.batch, device)
+        results['conv_update'] = time_conv_update(args.batch, device)
         results['config4_gga_slot_scaling'] = run_config4(args, rank, world, device, barrier, max_over_ranks)
 
     if rank != 0:

@@ -203,6 +203,35 @@ int sqb_stepquant_fit(const float *x, float *y, const int32_t *bits, const float
 int sqb_slot_read(const sqb_state_t *st, int kind, const int32_t *idx, int32_t rows, float *out, void *stream);
 int sqb_slot_write(const sqb_state_t *st, int kind, const int32_t *idx, int32_t rows, const float *S, void *stream);
 
+/*
+ * The short causal convolution that feeds the decode step (one token per sequence): the op the reference's vLLM
+ * forward calls right before `lay.step` (src/statequant/integrations/vllm_plugin.py:379-381,
+ * `causal_conv1d_update(mixed_qkv, conv_state, w, bias, activation, conv_state_indices=...)`, vLLM's
+ * model_executor/layers/mamba/ops/causal_conv1d.py), whose output rows are the q | k | v the step reads as column
+ * slices.  Per row r with line = idx[r] (idx NULL: line = r; line == null_line or line < 0: the row is left alone)
+ * and per channel c:
+ *     window = state[line, c, 0 .. width-2], x[r, c]
+ *     acc    = bias[c] (fp32; 0 without bias);  acc += x_j * w[c, j] for j = 0 .. width-1, in this order
+ *              (x and w of the same 16-bit type: the product is rounded to that type first, as the Triton kernel's
+ *              typed multiply does; otherwise the product is fused into the fp32 sum)
+ *     out[r, c] = silu ? acc / (1 + exp(-acc)) : acc      rounded to x's type
+ *     state[line, c, t] = state[line, c, t+1] for t < state_len-1;  state[line, c, state_len-1] = x[r, c]
+ * x, out and the state share one element type; out may be x itself (vLLM's kernel works in place).
+ */
+typedef struct sqb_conv_update {
+  void *x;          int64_t sx;            /* [rows, dim], row stride in bytes, unit inner stride */
+  void *out;        int64_t so;            /* [rows, dim]; may alias x */
+  void *state;      int64_t s_line, s_dim, s_tok;   /* conv state [lines, dim, state_len], strides in bytes */
+  const void *w;    int64_t sw_dim, sw_tap;         /* weights [dim, width], strides in bytes */
+  const void *bias;                        /* [dim], type of w; may be NULL */
+  const int32_t *idx;                      /* [rows] cache lines; may be NULL */
+  int32_t rows, dim, width, state_len;     /* width 2 .. 4; state_len >= width - 1 */
+  int32_t x_dtype, w_dtype;                /* SQB_F32 / SQB_BF16 / SQB_F16 */
+  int32_t silu;
+  int32_t null_line;                       /* rows with this line are skipped (vLLM's null block, 0); -1: none */
+} sqb_conv_update_t;
+int sqb_conv1d_update(const sqb_conv_update_t *a, void *cuda_stream);
+
 const char *sqb_last_error(void);
 /* ABI version of this header; bumped whenever a struct changes */
 int sqb_abi_version(void);

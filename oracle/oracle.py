@@ -23,7 +23,7 @@ _lib = None
 
 
 def build(force=False):
-    srcs = [os.path.join(HERE, f) for f in ('sq_oracle.c', 'sq_oracle_gga.c', 'Makefile')]
+    srcs = [os.path.join(HERE, f) for f in ('sq_oracle.c', 'sq_oracle_gga.c', 'sq_oracle_conv.c', 'Makefile')]
     srcs.append(os.path.join(HERE, '..', 'include', 'statequant_b200.h'))
     if force or not os.path.exists(LIB) or any(os.path.getmtime(s) > os.path.getmtime(LIB) for s in srcs):
         subprocess.run(['make', '-C', HERE, '-B', 'liboracle.so'], check=True, capture_output=True)
@@ -40,6 +40,8 @@ def lib():
             getattr(L, n).restype = C.c_int
             getattr(L, n).argtypes = [C.c_void_p, C.c_void_p]
         L.sqo_num_threads.restype = C.c_int
+        L.sqo_conv1d_update.restype = C.c_int
+        L.sqo_conv1d_update.argtypes = [C.c_void_p]
         L.sqo_gga_step.restype = L.sqo_gga_store.restype = L.sqo_gga_load.restype = C.c_int
         _lib = L
     return _lib
@@ -172,3 +174,26 @@ def gga_load(pk, views, idx, layer):
                             C.c_void_p(Y.data_ptr()))
     assert rc == 0
     return Y
+
+
+def conv1d_update(x, conv_state, weight, bias=None, activation=None, conv_state_indices=None, null_block_id=0):
+    """The oracle's causal conv update on host tensors, in place on x and conv_state (arguments as
+    ``statequant_b200.kernels.conv.causal_conv1d_update``); returns x."""
+    _cpu(x, conv_state, weight, bias, conv_state_indices)
+    assert x.dim() == 2 and x.stride(1) == 1 and x.dtype == conv_state.dtype
+    rows, dim = x.shape
+    es, ws = x.element_size(), weight.element_size()
+    idx = conv_state_indices
+    if idx is not None:
+        idx = idx.to(torch.int32).contiguous()
+    a = _cabi.ConvUpdate(
+        x=x.data_ptr(), sx=x.stride(0) * es, out=x.data_ptr(), so=x.stride(0) * es,
+        state=conv_state.data_ptr(), s_line=conv_state.stride(0) * es, s_dim=conv_state.stride(1) * es,
+        s_tok=conv_state.stride(2) * es, w=weight.data_ptr(), sw_dim=weight.stride(0) * ws,
+        sw_tap=weight.stride(1) * ws, bias=_cabi.ptr(bias), idx=_cabi.ptr(idx), rows=rows, dim=dim,
+        width=weight.size(1), state_len=conv_state.size(2), x_dtype=_cabi.dtype_code(x),
+        w_dtype=_cabi.dtype_code(weight), silu=int(bool(activation)),
+        null_line=-1 if null_block_id is None else int(null_block_id))
+    rc = lib().sqo_conv1d_update(C.byref(a))
+    assert rc == 0, f'sqo_conv1d_update: {rc}'
+    return x

@@ -56,6 +56,14 @@ class KdaInputs(C.Structure):
                 ('beta_dtype', i32), ('out_dtype', i32), ('reserved', i32)]
 
 
+class ConvUpdate(C.Structure):
+    """``sqb_conv_update_t``"""
+    _fields_ = [('x', vp), ('sx', i64), ('out', vp), ('so', i64), ('state', vp), ('s_line', i64), ('s_dim', i64),
+                ('s_tok', i64), ('w', vp), ('sw_dim', i64), ('sw_tap', i64), ('bias', vp), ('idx', vp),
+                ('rows', i32), ('dim', i32), ('width', i32), ('state_len', i32), ('x_dtype', i32), ('w_dtype', i32),
+                ('silu', i32), ('null_line', i32)]
+
+
 def dtype_code(t):
     """SQB_* element type of a tensor (fp32, bf16 or fp16)."""
     try:
@@ -98,6 +106,8 @@ def lib():
         L.sqb_slot_read.restype = L.sqb_slot_write.restype = C.c_int
         L.sqb_slot_read.argtypes = [vp, i32, vp, i32, vp, vp]
         L.sqb_slot_write.argtypes = [vp, i32, vp, i32, vp, vp]
+        L.sqb_conv1d_update.restype = C.c_int
+        L.sqb_conv1d_update.argtypes = [vp, vp]
         L.sqb_set_option.restype = C.c_int
         L.sqb_set_option.argtypes = [C.c_char_p, C.c_int]
         L.sqb_device_status.restype = C.c_int

@@ -10,6 +10,7 @@
 #include "fold_kernel.cuh"
 #include "launch_mma.cuh"
 #include "gga.cuh"
+#include "conv_update.cuh"
 
 namespace sqb {
 __device__ int g_step_status[4];   // [0]: number of CTAs whose bounded wait ran out (0 in a healthy run)
@@ -286,6 +287,33 @@ int sqb_slot_write(const sqb_state_t* st, int kind, const int32_t* idx, int32_t 
   if (reinterpret_cast<uintptr_t>(S) & 15) return fail(SQB_EINVAL, "S must be 16-byte aligned (it is read in 16-byte pieces)");
   if (rows == 0) return 0;
   return sub_rc(sqb::launch_write(kind, a, st->bits, st->axis_k, S, static_cast<cudaStream_t>(stream)));
+}
+
+int sqb_conv1d_update(const sqb_conv_update_t* c, void* stream) {
+  if (!c) return fail(SQB_EINVAL, "arguments are NULL");
+  if (c->rows <= 0) return c->rows == 0 ? 0 : fail(SQB_EINVAL, "rows %d < 0", c->rows);
+  if (!c->x || !c->out || !c->state || !c->w) return fail(SQB_EINVAL, "x, out, state or w is NULL");
+  if (check_dtype(c->x_dtype, "x") || check_dtype(c->w_dtype, "w")) return SQB_EINVAL;
+  if (c->width < 2 || c->width > 4) return fail(SQB_EINVAL, "width %d: expected 2, 3 or 4", c->width);
+  if (c->state_len < c->width - 1) return fail(SQB_EINVAL, "state_len %d is shorter than width - 1 = %d", c->state_len, c->width - 1);
+  if (c->dim <= 0) return fail(SQB_EINVAL, "dim %d <= 0", c->dim);
+  const int esz = c->x_dtype == SQB_F32 ? 4 : 2, wsz = c->w_dtype == SQB_F32 ? 4 : 2;
+  if (esz == 2 && wsz == 2 && c->x_dtype != c->w_dtype) return fail(SQB_EINVAL, "x and w are different 16-bit types");
+  if (c->sx % esz || c->so % esz || c->s_line % esz || c->s_dim % esz || c->s_tok % esz || c->sw_dim % wsz || c->sw_tap % wsz)
+    return fail(SQB_EINVAL, "a stride is not a multiple of its element size");
+  if ((reinterpret_cast<uintptr_t>(c->x) | reinterpret_cast<uintptr_t>(c->out) | reinterpret_cast<uintptr_t>(c->state)) % esz ||
+      (reinterpret_cast<uintptr_t>(c->w) | reinterpret_cast<uintptr_t>(c->bias)) % wsz)
+    return fail(SQB_EINVAL, "a pointer is not aligned to its element size");
+  sqb::ConvArgs a;
+  a.x = static_cast<const uint8_t*>(c->x); a.sx = c->sx;
+  a.out = static_cast<uint8_t*>(c->out); a.so = c->so;
+  a.state = static_cast<uint8_t*>(c->state); a.s_line = c->s_line; a.s_dim = c->s_dim; a.s_tok = c->s_tok;
+  a.w = static_cast<const uint8_t*>(c->w); a.sw_dim = c->sw_dim; a.sw_tap = c->sw_tap;
+  a.bias = static_cast<const uint8_t*>(c->bias); a.idx = c->idx;
+  a.rows = c->rows; a.dim = c->dim; a.width = c->width; a.state_len = c->state_len;
+  a.dt_x = c->x_dtype; a.dt_w = c->w_dtype; a.silu = c->silu != 0; a.null_line = c->null_line;
+  a.pmode = (esz == 2 && wsz == 2) ? (c->x_dtype == SQB_BF16 ? 1 : 2) : 0;
+  return sub_rc(sqb::launch_conv_update(a, static_cast<cudaStream_t>(stream)));
 }
 
 int sqb_gdn_step(const sqb_state_t* st, const sqb_gdn_inputs_t* in, void* stream) {

@@ -65,3 +65,28 @@ def bind_reference(package='statequant'):
     _BOUND[package] = done
     ref._statequant_b200_bound = True
     return done
+
+
+def bind_conv_update(module, name='causal_conv1d_update'):
+    """Route the plain decode case of ``module.<name>`` -- the vLLM model module's ``causal_conv1d_update``, which the
+    reference's forward calls right before the packed step (``integrations/vllm_plugin.py:379-381``) -- to this
+    package's kernel.  Calls the kernel does not take (speculative decoding, varlen batches, prefix-cache block
+    indices, host tensors) go to the original.  Idempotent; returns the original function."""
+    from ..kernels.conv import causal_conv1d_update as ours
+    orig = getattr(module, name)
+    if getattr(orig, '_statequant_b200', False):
+        return orig._original
+
+    def causal_conv1d_update(x, conv_state, weight, bias=None, activation=None, conv_state_indices=None, **kw):
+        plain = (x.is_cuda and x.dim() == 2 and 2 <= weight.size(1) <= 4
+                 and all(kw.get(k) is None for k in ('num_accepted_tokens', 'query_start_loc',
+                                                     'block_idx_last_scheduled_token', 'initial_state_idx')))
+        if not plain:
+            return orig(x, conv_state, weight, bias, activation, conv_state_indices=conv_state_indices, **kw)
+        return ours(x, conv_state, weight, bias, activation, conv_state_indices,
+                    null_block_id=kw.get('null_block_id', 0))
+
+    causal_conv1d_update._statequant_b200 = True
+    causal_conv1d_update._original = orig
+    setattr(module, name, causal_conv1d_update)
+    return orig

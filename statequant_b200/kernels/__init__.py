@@ -9,7 +9,9 @@ from .slots import SlotLayout
 from .mamba2 import Mamba2SlotLayout, PackedMamba2State, mamba2_recurrence
 from .kda import KDASlotLayout, PackedKDAState, kda_recurrence
 from .gga import GGAPacked, StepPlan, head_bytes
+from .conv import causal_conv1d_update, split_qkv
 
 __all__ = ['PackedGDNState', 'SlotLayout', 'pack', 'unpack', 'pack_vk', 'unpack_vk', 'packed_format',
            'PackedMamba2State', 'Mamba2SlotLayout', 'mamba2_recurrence',
-           'PackedKDAState', 'KDASlotLayout', 'kda_recurrence', 'GGAPacked', 'StepPlan', 'head_bytes']
+           'PackedKDAState', 'KDASlotLayout', 'kda_recurrence', 'GGAPacked', 'StepPlan', 'head_bytes',
+           'causal_conv1d_update', 'split_qkv']

@@ -140,3 +140,22 @@ def test_external_quantizer_mode_is_an_unpacked_slot(monkeypatch):
     assert views['S'].dtype == torch.float32 and tuple(views['S'].shape) == (3, 4, 128, 128)
     views['S'][torch.tensor([1])] = 0.5                       # what the hook does: an indexed write through the view
     assert float(lay.read(views, torch.tensor([1], dtype=torch.int32)).mean()) == 0.5
+
+
+def test_bind_conv_update_routes_only_the_plain_decode_case():
+    """Host tensors, speculative decoding and varlen calls keep going to the module's own function."""
+    import types
+    from statequant_b200.integrations import binding
+    calls = []
+
+    def original(x, conv_state, weight, bias=None, activation=None, conv_state_indices=None, **kw):
+        calls.append(sorted(kw))
+        return x
+
+    mod = types.SimpleNamespace(causal_conv1d_update=original)
+    assert binding.bind_conv_update(mod) is original
+    assert binding.bind_conv_update(mod) is original                  # idempotent
+    x, st, w = torch.zeros(2, 8), torch.zeros(3, 8, 3), torch.zeros(8, 4)
+    assert mod.causal_conv1d_update(x, st, w) is x                    # host tensors
+    assert mod.causal_conv1d_update(x, st, w, num_accepted_tokens=torch.ones(2)) is x
+    assert calls == [[], ['num_accepted_tokens']]
