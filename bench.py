@@ -713,6 +713,18 @@ def main():
         results[args.preset + '_staggered'] = res
         del stack
         torch.cuda.empty_cache()
+        # the same with the fold as its own, balanced launch behind a step kernel that only appends (kernel_path 3):
+        # what an engine whose slots sit at different buffer positions should select
+        _cabi.set_option('kernel_path', 3)
+        stack = WORKLOADS['gdn'](args.preset, args.batch, device, seed=1234 + rank)
+        args.prewarm = min(args.prewarm, 64)
+        res, _, _ = time_stack(stack, max(M, min(steps_timed, 32)), stagger=True)
+        args.prewarm = keep
+        _cabi.set_option('kernel_path', args.kernel_path)
+        res['workload'] = 'the staggered stack with kernel_path 3: tensor-core step kernel that only appends + the fold launch'
+        results[args.preset + '_staggered_fold_launch'] = res
+        del stack
+        torch.cuda.empty_cache()
         LAYERS = saved
         results['slot_io_' + args.preset] = time_slot_io(args.preset, args.batch, device)
         results['conv_update'] = time_conv_update(args.batch, device)

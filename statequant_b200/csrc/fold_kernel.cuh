@@ -7,7 +7,7 @@
 // re-rounds it, and resets the counter and GCUR to 0 -- the same arithmetic, on the same rounded buffer entries, as
 // the fused fold of the reference (kernels/_fused_triton.py:279-394), so the bytes after the call are identical.
 //
-// It is persistent: a CTA takes a contiguous share of the (batch row, value head) pairs, its threads test 128 pairs
+// It is persistent: a CTA takes every gridDim.x-th of the (batch row, value head) pairs, its threads test 128 pairs
 // at a time (slot index -> counter, two dependent loads, all in flight together), and the heads found are folded one
 // after the other with the next head's codes, scales and buffer tiles already on their way (two stages of bulk
 // async copies).  A launch in which no head is due costs one such scan.
@@ -88,10 +88,10 @@ __global__ void __launch_bounds__(NT, 4) fold_kernel(const __grid_constant__ Fol
     mbar_init(&bars[1], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  // pair q of this CTA is pair q * gridDim.x + blockIdx.x of the launch: the heads of one batch row go to as many
+  // CTAs, so that a launch in which only some rows are due (slots at different buffer positions) is still balanced
   const long long pairs = static_cast<long long>(A.rows) * HV;
-  const long long chunk = (pairs + gridDim.x - 1) / gridDim.x;
-  const long long p_begin = chunk * blockIdx.x;
-  const long long p_end = p_begin + chunk < pairs ? p_begin + chunk : pairs;
+  const long long per_cta = (pairs + gridDim.x - 1) / gridDim.x;
   uint32_t phases = 0;                         // bit s: parity of the next phase of stage s's barrier
   bool failed = false;
 
@@ -114,14 +114,14 @@ __global__ void __launch_bounds__(NT, 4) fold_kernel(const __grid_constant__ Fol
     }
   };
 
-  for (long long base = p_begin; base < p_end && !failed; base += NT) {
+  for (long long base = 0; base < per_cta && !failed; base += NT) {
     // ---- scan 128 pairs: which heads have a full buffer? ----
     __syncthreads();                           // the list of the previous round is no longer read
     if (tid == 0) *lcount = 0;
     __syncthreads();
-    const long long pr = base + tid;
+    const long long pr = (base + tid) * gridDim.x + blockIdx.x;
     bool due = false;
-    if (pr < p_end) {
+    if (base + tid < per_cta && pr < pairs) {
       const int b = static_cast<int>(pr / HV), h = static_cast<int>(pr - (long long)b * HV);
       long long seq = b;
       bool live = true;

@@ -8,6 +8,10 @@ Environment (the reference's surface, ``src/statequant/integrations/vllm_plugin.
     STATEQUANT_VLLM_LAYERS=gdn,mamba2,kda
     STATEQUANT_VLLM_PW_M=8            window length of gga:...:pw
     STATEQUANT_VLLM_FUSED, STATEQUANT_GGA_WARPS   parsed and ignored (one code path here)
+    STATEQUANT_B200_FOLD=launch|inline   (this package only) where a slot's m-th token is folded: in a balanced launch
+                                      of its own behind the step kernel (default under vLLM: the slots of a serving
+                                      batch sit at different buffer positions, and a launch that mixes folding and
+                                      plain rows ends on the long-running folding CTAs), or inside the step kernel
 
 ``register()`` is the ``vllm.general_plugins`` entry point.  The engine glue -- replacing the state-shape calculators
 and the layers' ``_forward_core`` -- is Python that lives in the reference's plugin and depends on vLLM >= 0.32
@@ -175,6 +179,20 @@ def unpatch_calculators():
         mu.MambaStateDtypeCalculator.gated_delta_net_state_dtype = dtype0
 
 
+def fold_policy():
+    """'launch' or 'inline' from STATEQUANT_B200_FOLD (default 'launch': continuous batching)."""
+    pol = os.environ.get('STATEQUANT_B200_FOLD', 'launch').strip().lower()
+    assert pol in ('launch', 'inline'), f'STATEQUANT_B200_FOLD={pol!r}: use launch or inline'
+    return pol
+
+
+def apply_fold_policy():
+    """Select the device code path of the decode steps for this process: kernel_path 3 (step kernel that only appends +
+    the fold launch) for 'launch', 0 (the fold inside the step kernel wherever the shape allows) for 'inline'."""
+    from .. import _cabi
+    _cabi.set_option('kernel_path', 3 if fold_policy() == 'launch' else 0)
+
+
 def register():
     """``vllm.general_plugins`` entry point.  Idempotent; a no-op unless STATEQUANT_VLLM is set."""
     cfg = config()
@@ -194,4 +212,5 @@ def register():
         _STATE['registered'] = 'skipped'
         return
     ref_plugin.register()
+    apply_fold_policy()
     _STATE['registered'] = True

@@ -159,3 +159,14 @@ def test_bind_conv_update_routes_only_the_plain_decode_case():
     assert mod.causal_conv1d_update(x, st, w) is x                    # host tensors
     assert mod.causal_conv1d_update(x, st, w, num_accepted_tokens=torch.ones(2)) is x
     assert calls == [[], ['num_accepted_tokens']]
+
+
+def test_fold_policy_env(monkeypatch):
+    from statequant_b200.integrations import vllm_plugin as vp
+    monkeypatch.delenv('STATEQUANT_B200_FOLD', raising=False)
+    assert vp.fold_policy() == 'launch'
+    monkeypatch.setenv('STATEQUANT_B200_FOLD', 'inline')
+    assert vp.fold_policy() == 'inline'
+    monkeypatch.setenv('STATEQUANT_B200_FOLD', 'sometimes')
+    with pytest.raises(AssertionError):
+        vp.fold_policy()
