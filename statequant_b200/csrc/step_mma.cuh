@@ -118,6 +118,23 @@ __device__ __forceinline__ void prefetch_l2_line(const void* p) {
 #define SQB_MMA_MINB_AXV 5
 #endif
 
+// Cold paths kept out of line (they are never taken in a healthy run, and inlined at every use they were an eighth of
+// the kernel's code): the zero fill of a CTA's output rows, and the exit of a CTA whose copy never completed.
+// clamp(rint(x / s), +-127) by the IEEE division: the rare exact path of a buffer entry's rounding
+static __device__ __noinline__ float rq_exact_cold(float x, float s) { return rq_exact(x, s, 127.0f); }
+static __device__ __noinline__ void zero_out_rows(uint8_t* orow, int dt, int n) {
+  for (int v = threadIdx.x; v < n; v += NT) stf(orow, dt, v, 0.0f);
+}
+static __device__ __noinline__ void mma_bail(uint8_t* orow, int dt, int n, uint64_t* bars, int narmed, int nst,
+                                             unsigned long long wait_ns, int* status) {
+  zero_out_rows(orow, dt, n);
+  if (threadIdx.x == 0) {       // wait (bounded) for what may still be in flight, count it, leave
+    for (int s = 0; s < narmed; s++) mbar_wait(&bars[s], 0, wait_ns);
+    mbar_wait(&bars[nst], 0, wait_ns);
+    atomicAdd(&status[0], 1);
+  }
+}
+
 template <int KIND, int BITS, int UPG, int DV, int MODE, bool AXV = false>
 __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((BITS == 8 && UPG == 1) || (BITS == 4 && UPG == 2)) ? SQB_MMA_MINB_TFOLD : SQB_MMA_MINB_FOLD))
                                                : (BITS == 4 ? SQB_MMA_MINB4 : SQB_MMA_MINB8))
@@ -202,8 +219,7 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
   if (A.idx != nullptr) {
     seq = A.idx[b];
     if (seq <= 0) {
-      uint8_t* orow = A.out + (long long)b * A.so + (long long)h0 * DV * osz;
-      for (int v = tid; v < gqa * DV; v += NT) stf(orow, A.dt_out, v, 0.0f);
+      zero_out_rows(A.out + (long long)b * A.so + (long long)h0 * DV * osz, A.dt_out, gqa * DV);
       return;
     }
   }
@@ -575,13 +591,8 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
   SQB_STAMP(4);
   // a copy that never completed: wait (bounded) for what may still be in flight, count it, leave
   auto bail = [&]() {
-    uint8_t* orow = A.out + (long long)b * A.so + (long long)h0 * DV * osz;
-    for (int v = tid; v < gqa * DV; v += NT) stf(orow, A.dt_out, v, 0.0f);
-    if (tid == 0) {
-      for (int s = 0; s < nst && s < NSH; s++) mbar_wait(&bars[s], 0, A.wait_ns);     // the barriers that were armed
-      mbar_wait(&bars[nst], 0, A.wait_ns);
-      atomicAdd(&A.status[0], 1);
-    }
+    mma_bail(A.out + (long long)b * A.so + (long long)h0 * DV * osz, A.dt_out, gqa * DV, bars, min(nst, NSH), nst, A.wait_ns,
+             A.status);
   };
   if (misc[2] != 0.f) { bail(); return; }
   if constexpr (VDEC) {
@@ -862,7 +873,40 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
     // ---- append the values of all heads at slot n0, every lane its own rows ----
     if (__syncthreads_or(lost)) { bail(); return; }
     SQB_STAMP(11);
-    for (int sh = 0; sh < NSH; sh++) append_row(sh);
+    if (NSH == 2) {
+      // the two stages' rows of this lane at once: one address computation, packed arithmetic, the exact rounding of a
+      // near-tie or of a subnormal scale out of line
+      const int hiA = hh, hiB = HPS + hh;
+      const float2 uu = make_float2(us[hiA * DV + rv], us[hiB * DV + rv]);
+      const float4 rA = *reinterpret_cast<const float4*>(red + hiA * NW), rB = *reinterpret_cast<const float4*>(red + hiB * NW);
+      const float2 ss = make_float2(fp16_scale(fmaxf(fmaxf(rA.x, rA.y), fmaxf(rA.z, rA.w)), 127.0f),
+                                    fp16_scale(fmaxf(fmaxf(rB.x, rB.y), fmaxf(rB.z, rB.w)), 127.0f));
+      const float2 mg = make_float2(MAGIC, MAGIC);
+      const float2 tt = __ffma2_rn(uu, make_float2(rcp_approx(ss.x), rcp_approx(ss.y)), mg);
+      float2 cc = __fadd2_rn(tt, make_float2(-MAGIC, -MAGIC));
+      const float2 rem = __ffma2_rn(cc, make_float2(-ss.x, -ss.y), uu);
+      const float2 lim = __fmul2_rn(ss, make_float2(0.49998474f, 0.49998474f));
+      if (!(fabsf(rem.x) < lim.x) || !(fabsf(rem.y) < lim.y) || fminf(ss.x, ss.y) < FP16_MIN_NORMAL) {
+        cc.x = rq_exact_cold(uu.x, ss.x);
+        cc.y = rq_exact_cold(uu.y, ss.y);
+      }
+      uint8_t* ub = UBseq + ((long long)(h0 + hiA) * M + n0) * DV + rv;
+      ub[0] = static_cast<uint8_t>(static_cast<int>(cc.x));
+      ub[(long long)HPS * M * DV] = static_cast<uint8_t>(static_cast<int>(cc.y));
+      if (tid < gqa) {                                        // the heads' scalars: one lane per head
+        const int h = h0 + tid;
+        const float4 r4 = *reinterpret_cast<const float4*>(red + tid * NW);
+        UBSseq[h * M + n0] = f2h(fp16_scale(fmaxf(fmaxf(r4.x, r4.y), fmaxf(r4.z, r4.w)), 127.0f));
+        if (!VDEC) {
+          const float gnew = hd[tid * HD_W + 5];
+          GBseq[(long long)h * M + n0] = gnew;
+          GCseq[h] = gnew;
+        }
+        NPseq[h] = n0 + 1;
+      }
+    } else {
+      for (int sh = 0; sh < NSH; sh++) append_row(sh);
+    }
     SQB_STAMP(12);
     if (VDEC) {
       GBseq[((long long)h0 * M + n0) * DK + tid] = ga[tid];
