@@ -565,7 +565,6 @@ def main():
     ap.add_argument('--eager', action='store_true', help='launch eagerly instead of replaying a CUDA graph')
     ap.add_argument('--workload', default='gdn', choices=list(WORKLOADS),
                     help='gdn = the benchmark; mamba2 / kda / gga time the other kernel families on their shapes')
-    ap.add_argument('--mma-prefetch', type=int, default=None, help='tensor-core kernels: L2 prefetch distance in CTAs (-1 one wave, 0 off)')
     ap.add_argument('--mma-hpc', type=int, default=0, help='tensor-core kernels: value heads per CTA (0: a whole key head)')
     ap.add_argument('--kernel-path', type=int, default=0, choices=[0, 1, 2, 3, 4],
                     help='0 best kernel for the shape; 1 generic; 2 staged + fold launch (profiling / comparison)')
@@ -603,8 +602,6 @@ def main():
     assert torch.cuda.is_available(), 'bench.py needs a GPU (there is no CPU fallback)'
     torch.cuda.set_device(local)
     _cabi.set_option('kernel_path', args.kernel_path)
-    if args.mma_prefetch is not None:
-        _cabi.set_option('mma_prefetch_dist', args.mma_prefetch)
     if args.mma_hpc:
         _cabi.set_option('mma_heads_per_cta', args.mma_hpc)
     device = f'cuda:{local}'

@@ -247,7 +247,6 @@ int64_t sqb_launch_count(void);
    kernel_path 1 (and sends every GGA head to the tile kernel).  The paths agree up to the order of fp32 sums.
    "wait_limit_us": how long a device-side wait for a bulk copy may last before the CTA gives up (default 1 s).
    "mma_heads_per_cta": value heads a CTA of the tensor-core kernels takes (0: the default, two stages of 128 rows).
-   "mma_prefetch_dist": L2 prefetch distance in CTAs for the tensor-core kernels (0: off, the default; -1: one wave).
    "test_extra_tx": test hook; bytes a stage barrier is told to expect beyond what is copied, so that its wait runs
    out (a multiple of 16; 0 in any real run). */
 int sqb_set_option(const char *name, int value);

@@ -52,7 +52,6 @@ struct StepArgs {
   unsigned long long wait_ns;   // how long a wait for a bulk copy may take before the CTA gives up
   int hpc;                   // tensor-core kernels: value heads a CTA takes (divides hv / hk)
   int m_log2, gqa_full;      // tensor-core kernels: log2(m), value heads per key head
-  int prefetch_dist;         // tensor-core kernels: a CTA prefetches into L2 for the CTA this many blocks later (0: off)
   int test_extra_tx;         // test hook: bytes a stage barrier expects beyond what is copied (so its wait runs out)
   int axv;                   // tensor-core kernels: the scale groups run along d_v (32 rows per group)
 };

@@ -66,20 +66,6 @@ int launch_mma_one(const StepArgs& a, cudaStream_t stream) {
   b.hpc = mma_hpc(a);
   const long long ctas = static_cast<long long>(a.rows) * (a.HV / b.hpc);
   if (ctas > 2147483647LL) return 1;
-  if (b.prefetch_dist < 0) {
-    // one wave: the CTAs resident on the device at a time
-    static thread_local int wave[64];
-    int dev = 0;
-    cudaGetDevice(&dev);
-    int& w = wave[dev & 63];
-    if (!w) {
-      int nsm = 0, per = 0;
-      cudaDeviceGetAttribute(&nsm, cudaDevAttrMultiProcessorCount, dev);
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per, kern, NT, plan.total) != cudaSuccess || per < 1) per = 4;
-      w = nsm > 0 ? nsm * per : 592;
-    }
-    b.prefetch_dist = w;
-  }
   b.gqa_full = a.HV / a.HK;
   b.m_log2 = 0;
   while ((1 << b.m_log2) < a.M) b.m_log2++;

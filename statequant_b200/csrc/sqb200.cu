@@ -88,7 +88,6 @@ std::atomic<int> g_force_generic{0};     // set through sqb_set_option (tests ti
 std::atomic<int> g_kernel_path{0};       // see sqb_set_option in the header
 std::atomic<long long> g_wait_ns{1000000000ll};   // bound of a device-side wait for a bulk copy
 std::atomic<int> g_test_extra_tx{0};     // test hook: makes the stage barriers of the tensor-core kernels wait in vain
-std::atomic<int> g_mma_prefetch{0};      // tensor-core kernels: L2 prefetch distance in CTAs (0: off, -1: one wave)
 std::atomic<int> g_mma_hpc{0};           // tensor-core kernels: value heads per CTA (0: all of a key head)
 
 int fill_state(sqb::StepArgs& a, const sqb_state_t* st, int lpr_log2) {
@@ -97,7 +96,6 @@ int fill_state(sqb::StepArgs& a, const sqb_state_t* st, int lpr_log2) {
   a.wait_ns = static_cast<unsigned long long>(g_wait_ns.load(std::memory_order_relaxed));
   a.test_extra_tx = g_test_extra_tx.load(std::memory_order_relaxed);
   a.hpc = g_mma_hpc.load(std::memory_order_relaxed);
-  a.prefetch_dist = g_mma_prefetch.load(std::memory_order_relaxed);
   a.S = static_cast<uint8_t*>(st->S); a.SC = static_cast<uint8_t*>(st->SC);
   a.KB = static_cast<uint8_t*>(st->KB); a.KBS = static_cast<uint8_t*>(st->KBS);
   a.UB = static_cast<uint8_t*>(st->UB); a.UBS = static_cast<uint8_t*>(st->UBS);
@@ -241,7 +239,6 @@ int64_t sqb_launch_count(void) { return g_launches.load(); }
 int sqb_set_option(const char* name, int value) {
   if (name && !strcmp(name, "force_generic_kernel")) { g_force_generic = value; return 0; }
   if (name && !strcmp(name, "kernel_path") && value >= 0 && value <= 4) { g_kernel_path = value; return 0; }
-  if (name && !strcmp(name, "mma_prefetch_dist") && value >= -1) { g_mma_prefetch = value; return 0; }
   if (name && !strcmp(name, "mma_heads_per_cta") && value >= 0) { g_mma_hpc = value; return 0; }
   if (name && !strcmp(name, "wait_limit_us") && value > 0) { g_wait_ns = 1000ll * value; return 0; }
   if (name && !strcmp(name, "test_extra_tx") && value >= 0 && value % 16 == 0) { g_test_extra_tx = value; return 0; }

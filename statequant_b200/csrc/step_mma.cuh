@@ -101,13 +101,6 @@ __host__ __device__ inline SmemM smemm_plan(int kind, int bits, int upg, int DV,
 #define SQB_MMA_MINB4 6
 #endif
 
-__device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) {     // 16-byte aligned, a multiple of 16
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void prefetch_l2_line(const void* p) {
-  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
-}
-
 #ifndef SQB_MMA_MINB_FOLD
 #define SQB_MMA_MINB_FOLD 4
 #endif
@@ -161,40 +154,6 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
   if (gqa != gqf) { const int cpk = gqf / gqa; hk = blockIdx.y / cpk; part = blockIdx.y - hk * cpk; }
   const int h0 = hk * gqf + part * gqa;
   const bool first = part == 0;                   // the CTA that appends the key head's key
-  // Software prefetch, one wave ahead: the CTA that will run prefetch_dist blocks later (on some SM, a CTA lifetime or
-  // two from now) gets its slot's state, buffer and scalars and its activations pulled into L2 by fire-and-forget
-  // prefetches, so that its own copies and loads find them there.  The bytes in flight from HBM then live in L2, not
-  // in shared memory, of which there is too little to cover the loaded HBM latency.
-  if (warp == 3 && A.prefetch_dist > 0 &&
-      (long long)blockIdx.y * gridDim.x + blockIdx.x + A.prefetch_dist < (long long)gridDim.x * gridDim.y) {
-    const long long fl = (long long)blockIdx.y * gridDim.x + blockIdx.x + A.prefetch_dist;
-    const int fy = static_cast<int>(fl / gridDim.x), fb = static_cast<int>(fl - (long long)fy * gridDim.x);
-    const int cpk = gqf / gqa;
-    const int fhk = fy / cpk, fh0 = fhk * gqf + (fy - fhk * cpk) * gqa;
-    const long long fseq = A.idx != nullptr ? static_cast<long long>(A.idx[fb]) : static_cast<long long>(fb);
-    const int esz = A.dt_qk == DT_F32 ? 4 : 2, vsz = A.dt_v == DT_F32 ? 4 : 2;
-    // activations of the future CTA
-    if (lane < 4) prefetch_l2_line(A.q + (long long)fb * A.sq + ((long long)fhk * 128 + lane * 32) * esz);
-    else if (lane < 8) prefetch_l2_line(A.k + (long long)fb * A.sk + ((long long)fhk * 128 + (lane - 4) * 32) * esz);
-    else if (lane < 16) {
-      const long long o = (long long)fh0 * DV * vsz + (lane - 8) * 128;
-      if (o < (long long)(fh0 + gqa) * DV * vsz) prefetch_l2_line(A.v + (long long)fb * A.sv + o);
-    }
-    if (fseq > 0 || A.idx == nullptr) {
-      const int rowb = 128 * BITS / 8;
-      const uint8_t* cs = A.S + fseq * A.sS + (long long)fh0 * DV * rowb;
-      const int cbytes = gqa * DV * rowb;
-      for (int o = lane * 4096; o < cbytes; o += 32 * 4096) prefetch_l2_bulk(cs + o, min(4096, cbytes - o));
-      if (lane == 16) prefetch_l2_bulk(A.SC + fseq * A.sSC + (long long)fh0 * DV * (4 / UPG) * 2, gqa * DV * (4 / UPG) * 2);
-      else if (lane == 17) prefetch_l2_bulk(A.UB + fseq * A.sUB + (long long)fh0 * M * DV, gqa * M * DV);
-      else if (lane == 18) prefetch_l2_bulk(A.KB + fseq * A.sKB + (long long)fhk * M * 128, M * 128);
-      else if (lane == 19) prefetch_l2_line(A.GB + fseq * A.sGB + (long long)fh0 * M * 4 * (KIND == K_KDA ? 128 : 1));
-      else if (lane == 20) prefetch_l2_line(A.GCUR + fseq * A.sGC + (long long)fh0 * 4 * (KIND == K_KDA ? 128 : 1));
-      else if (lane == 21) prefetch_l2_line(A.NPTR + fseq * A.sN + (long long)fh0 * 4);
-      else if (lane == 22) prefetch_l2_line(A.KBS + fseq * A.sKBS + (long long)fhk * M * 2);
-      else if (lane == 23) prefetch_l2_line(A.UBS + fseq * A.sUBS + (long long)fh0 * M * 2);
-    }
-  }
   const int osz = dt_size(A.dt_out);
   const bool TFOLD = TFMT && M == 8;               // the fold, when it comes, runs on the tensor pipe
 
