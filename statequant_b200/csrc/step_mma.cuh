@@ -645,6 +645,61 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
     return cc * usc;
   };
 
+  if (!AXV && !FOLD && NSH == 2 && nst >= 2) {
+    // ---- a token that does not fold, two stages: both at once -----------------------------------------------------------
+    // Both stages were requested in the CTA's first instructions; once both have landed, the two tile passes, the two
+    // buffer terms and the two read-outs are independent chains in the same basic blocks, and the instruction scheduler
+    // interleaves them (a warp issues in order: one chain alone leaves it waiting on every tensor-core and
+    // shared-memory result).
+    if constexpr (!AXV) {
+      const int hiA = hh, hiB = HPS + hh;
+      uint8_t* stA = smraw + P.stage0;
+      uint8_t* stB = stA + P.stage_bytes;
+      const float vtA = cvt_raw(rvt[0], A.dt_v), vtB = cvt_raw(rvt[1], A.dt_v);
+      const float4 hdaA = *reinterpret_cast<const float4*>(hd + hiA * HD_W), hdbA = *reinterpret_cast<const float4*>(hd + hiA * HD_W + 4);
+      const float4 hdaB = *reinterpret_cast<const float4*>(hd + hiB * HD_W), hdbB = *reinterpret_cast<const float4*>(hd + hiB * HD_W + 4);
+      if (!mbar_wait(&bars[0], 0, A.wait_ns)) lost = true;
+      if (!mbar_wait(&bars[1], 0, A.wait_ns)) lost = true;
+      float tqA, tkA, tqB, tkB;
+      tile_pass<BITS, UPG, 16>(smem_u32(stA), reinterpret_cast<const unsigned short*>(stA + P.sc_off), bf, ci, warp, lane, tqA, tkA);
+      tile_pass<BITS, UPG, 16>(smem_u32(stB), reinterpret_cast<const unsigned short*>(stB + P.sc_off), bf, ci, warp, lane, tqB, tkB);
+      tqA = (tqA * iq1) * iq2; tqB = (tqB * iq1) * iq2;         // powers of two: exact
+      if (TWO) { tkA = (tkA * ik1) * ik2; tkB = (tkB * ik1) * ik2; }
+      if (!VDEC) { tqA = hdaA.w * tqA; tkA = hdaA.w * tkA; tqB = hdaB.w * tqB; tkB = hdaB.w * tkB; }
+      const int8_t* ubA = reinterpret_cast<const int8_t*>(stA + P.ub_off) + hh * M * DV + rv;
+      const int8_t* ubB = reinterpret_cast<const int8_t*>(stB + P.ub_off) + hh * M * DV + rv;
+      const float2 *dcA = dcu + hiA * M, *dcB = dcu + hiB * M;
+      for (int i = 0; i < n0; i++) {                           // live slots only; dead ones may hold garbage
+        const float2 dd = i == 0 ? dq01 : dqk[i];
+        const float2 duA = dcA[i], duB = dcB[i];
+        const float xA = static_cast<float>(ubA[i * DV]) * duA.y, xB = static_cast<float>(ubB[i * DV]) * duB.y;
+        tqA = fmaf(xA, duA.x * dd.x, tqA);
+        tqB = fmaf(xB, duB.x * dd.x, tqB);
+        if (TWO) { tkA = fmaf(xA, duA.x * dd.y, tkA); tkB = fmaf(xB, duB.x * dd.y, tkB); }
+      }
+      float uA, oA, uB, oB;
+      if (KIND == K_GDN) {
+        uA = hdaA.y * fmaf(-hdbA.x, tkA, vtA); oA = fmaf(kq, uA, hdbA.x * tqA);
+        uB = hdaB.y * fmaf(-hdbB.x, tkB, vtB); oB = fmaf(kq, uB, hdbB.x * tqB);
+      } else if (KIND == K_KDA) {
+        uA = hdaA.y * (vtA - tkA); oA = fmaf(kq, uA, tqA);
+        uB = hdaB.y * (vtB - tkB); oB = fmaf(kq, uB, tqB);
+      } else {
+        uA = hdaA.y * vtA; oA = fmaf(kq, uA, hdbA.x * tqA);      // beta holds dt
+        uB = hdaB.y * vtB; oB = fmaf(kq, uB, hdbB.x * tqB);
+        if (A.beta) { oA = fmaf(hdbA.z, vtA, oA); oB = fmaf(hdbB.z, vtB, oB); }
+      }
+      us[hiA * DV + rv] = uA;
+      us[hiB * DV + rv] = uB;
+      uint8_t* orow = A.out + (long long)b * A.so + (long long)(h0 + hiA) * DV * osz;
+      stf(orow, A.dt_out, rv, oA);
+      stf(orow + (long long)HPS * DV * osz, A.dt_out, rv, oB);
+      const uint32_t umask = HPS == 1 ? 0xffffffffu : (lane < 16 ? 0x0000ffffu : 0xffff0000u);
+      const float mA = __uint_as_float(__reduce_max_sync(umask, __float_as_uint(fabsf(uA))));
+      const float mB = __uint_as_float(__reduce_max_sync(umask, __float_as_uint(fabsf(uB))));
+      if ((lane & (HPS == 1 ? 31 : 15)) == 0) { red[hiA * NW + warp] = mA; red[hiB * NW + warp] = mB; }
+    }
+  } else
   for (int sh = 0; sh < NSH; sh++) {
     const int s = sh % nst;
     const uint32_t parity = (sh / nst) & 1;
