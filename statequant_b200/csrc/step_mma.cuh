@@ -645,13 +645,13 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
     return cc * usc;
   };
 
-  if (!AXV && !FOLD && NSH == 2 && nst >= 2) {
+  if (!FOLD && NSH == 2 && nst >= 2) {
     // ---- a token that does not fold, two stages: both at once -----------------------------------------------------------
     // Both stages were requested in the CTA's first instructions; once both have landed, the two tile passes, the two
     // buffer terms and the two read-outs are independent chains in the same basic blocks, and the instruction scheduler
     // interleaves them (a warp issues in order: one chain alone leaves it waiting on every tensor-core and
     // shared-memory result).
-    if constexpr (!AXV) {
+    {
       const int hiA = hh, hiB = HPS + hh;
       uint8_t* stA = smraw + P.stage0;
       uint8_t* stB = stA + P.stage_bytes;
@@ -661,10 +661,24 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
       if (!mbar_wait(&bars[0], 0, A.wait_ns)) lost = true;
       if (!mbar_wait(&bars[1], 0, A.wait_ns)) lost = true;
       float tqA, tkA, tqB, tkB;
-      tile_pass<BITS, UPG, 16>(smem_u32(stA), reinterpret_cast<const unsigned short*>(stA + P.sc_off), bf, ci, warp, lane, tqA, tkA);
-      tile_pass<BITS, UPG, 16>(smem_u32(stB), reinterpret_cast<const unsigned short*>(stB + P.sc_off), bf, ci, warp, lane, tqB, tkB);
-      tqA = (tqA * iq1) * iq2; tqB = (tqB * iq1) * iq2;         // powers of two: exact
-      if (TWO) { tkA = (tkA * ik1) * ik2; tkB = (tkB * ik1) * ik2; }
+      if constexpr (AXV) {
+        // every warp scales the vectors by its group's column scales, per stage (the fragment area is reused)
+        uint32_t bfB[8];
+        FxScale fqA, fkA, fqB, fkB;
+        uint32_t* area = reinterpret_cast<uint32_t*>(smraw + P.bfv) + warp * 256;
+        const unsigned short* one = reinterpret_cast<const unsigned short*>(misc + 9);
+        build_b_v<BITS, TWO>(area, reinterpret_cast<const unsigned short*>(stA + P.sc_off) + warp * 128, wq, wk, lane, bf, fqA, fkA);
+        build_b_v<BITS, TWO>(area, reinterpret_cast<const unsigned short*>(stB + P.sc_off) + warp * 128, wq, wk, lane, bfB, fqB, fkB);
+        tile_pass_v<BITS>(smem_u32(stA), one, bf, warp, lane, tqA, tkA);
+        tile_pass_v<BITS>(smem_u32(stB), one, bfB, warp, lane, tqB, tkB);
+        tqA = (tqA * fqA.i1) * fqA.i2; tqB = (tqB * fqB.i1) * fqB.i2;
+        if (TWO) { tkA = (tkA * fkA.i1) * fkA.i2; tkB = (tkB * fkB.i1) * fkB.i2; }
+      } else {
+        tile_pass<BITS, UPG, 16>(smem_u32(stA), reinterpret_cast<const unsigned short*>(stA + P.sc_off), bf, ci, warp, lane, tqA, tkA);
+        tile_pass<BITS, UPG, 16>(smem_u32(stB), reinterpret_cast<const unsigned short*>(stB + P.sc_off), bf, ci, warp, lane, tqB, tkB);
+        tqA = (tqA * iq1) * iq2; tqB = (tqB * iq1) * iq2;       // powers of two: exact
+        if (TWO) { tkA = (tkA * ik1) * ik2; tkB = (tkB * ik1) * ik2; }
+      }
       if (!VDEC) { tqA = hdaA.w * tqA; tkA = hdaA.w * tkA; tqB = hdaB.w * tqB; tkB = hdaB.w * tkB; }
       const int8_t* ubA = reinterpret_cast<const int8_t*>(stA + P.ub_off) + hh * M * DV + rv;
       const int8_t* ubB = reinterpret_cast<const int8_t*>(stB + P.ub_off) + hh * M * DV + rv;
