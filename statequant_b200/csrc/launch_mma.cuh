@@ -28,6 +28,14 @@ inline bool mma_shape_ok(const StepArgs& a, int bits, bool axk, bool kda, int ki
   return true;
 }
 
+// The fold inside the step kernel (mode 3): the formats whose fold runs on the tensor pipe carry no other fold in that
+// kernel, and that one takes a buffer of 8; with another buffer length they run as step kernel + fold launch (mode 0).
+inline bool mma_fold_inside(const StepArgs& a, int bits, int kind) {
+  const int upg = a.axv ? 1 : a.group / 32;
+  const bool tfmt = a.axv || (bits == 8 && upg == 1) || (bits == 4 && upg == 2);
+  return !tfmt || fold_on_tensor_pipe(kind, bits, upg, a.M, a.axv != 0);
+}
+
 // stages resident per CTA and the plan; false if the CTA does not fit
 // value heads a CTA takes (a.hpc set by the caller, if it is a divisor of the key head's value heads that fills whole
 // stages; else the default below)

@@ -191,7 +191,7 @@ int launch(const sqb::StepArgs& a0, int bits, bool axk, cudaStream_t stream) {
     a.axv = axk ? 0 : 1;
     sqb::SmemM plan;
     int nst;
-    if (path == 4 || path == 0) {
+    if ((path == 4 || path == 0) && sqb::mma_fold_inside(a, bits, KIND)) {
       // tensor-core kernel with the fold inside: one launch, the stored state read once per token
       if (sqb::mma_plan<KIND>(a, bits, 3, plan, nst)) {
         const int rc = launch_mma_kind<KIND>(a, bits, 3, stream);

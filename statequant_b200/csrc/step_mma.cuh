@@ -155,7 +155,9 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
   const int h0 = hk * gqf + part * gqa;
   const bool first = part == 0;                   // the CTA that appends the key head's key
   const int osz = dt_size(A.dt_out);
-  const bool TFOLD = TFMT && M == 8;               // the fold, when it comes, runs on the tensor pipe
+  // the fold, when it comes, runs on the tensor pipe for the formats it takes (the host sends these here only with a
+  // buffer of 8, cf. mma_fold_inside), else in fp32
+  constexpr bool TFOLD = TFMT;
 
 #ifdef SQB_TRACE
   const long long t_start = clock64();
@@ -609,7 +611,7 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
       if (lane == 0) KBSh[n0] = f2h(kscale);
     }
     if (FOLD) {
-      if (TFOLD) {                            // the tensor-pipe fold takes the codes and the scale
+      if constexpr (TFOLD) {                  // the tensor-pipe fold takes the codes and the scale
         *reinterpret_cast<uint32_t*>(smraw + P.kcur + lane * 4) = kword;
         if (lane == 0) misc[8] = kscale;
       } else {
@@ -781,8 +783,8 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
         GBseq[((long long)h * M + n0) * DK + tid] = ga[tid];
         GCseq[(long long)h * DK + tid] = 0.f;
       }
-      if (TFMT && TFOLD) {
-        if constexpr (TFMT) {
+      if constexpr (TFMT) {
+        {
           // ---- the fold on the tensor pipe (fold_mma.cuh) ----
           uint32_t* KBf = reinterpret_cast<uint32_t*>(smraw + P.kbf);
           float* tab = fsm + P.tab;
@@ -833,7 +835,7 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
             if (sh + nst < NSH || sh + 1 == NSH) bulk_wait_read();   // before the stage is refilled, and before leaving
           }
         }
-      } else if constexpr (!AXV) {
+      } else {
       float* Lf = fsm + P.L;
       float* fdec = fsm + P.fdec;
       const int LM = fold_lm(M);
