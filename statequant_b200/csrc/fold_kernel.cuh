@@ -13,6 +13,7 @@
 // async copies).  A launch in which no head is due costs one such scan.
 #pragma once
 #include "step_tma.cuh"
+#include "fold_mma.cuh"
 
 namespace sqb {
 
@@ -32,7 +33,7 @@ __host__ __device__ inline SmemF smemf_plan(bool vdec, int bits, int axk, int gr
   s.kb_b = al16i(M * DK * bsz);
   s.gb_b = vdec ? M * DK * 4 : 0;
   s.gc_b = vdec ? DK * 4 : 0;
-  s.o_sc = s.codes_b;
+  s.o_sc = s.codes_b + 128;                 // (room for the padded-piece layout of the tensor-pipe fold)
   s.o_ub = s.o_sc + s.scales_b;
   s.o_kb = s.o_ub + s.ub_b;
   s.o_gb = s.o_kb + s.kb_b;
@@ -60,12 +61,14 @@ struct FoldArgs {
   const int* idx;
   int group, qbuf, M, HV, HK, DV, rows;
   int* status;
+  int tens;                  // the fold on the tensor pipe (fold_mma.cuh): Gated DeltaNet / Mamba2 heads of 128 x 128, buffer of 8
   float* out;                // read mode: fp32 [rows, HV, d_v, d_k], the state advanced across its pending buffer
 };
 
 template <bool VDEC, int BITS, bool AXK, int LPR>
 __global__ void __launch_bounds__(NT, 4) fold_kernel(const __grid_constant__ FoldArgs A, const __grid_constant__ SmemF P) {
   constexpr int DK = LPR * 16;
+  constexpr bool TENS_OK = !VDEC && AXK && LPR == 8;       // instantiations that carry the tensor-pipe fold
   extern __shared__ __align__(128) uint8_t smraw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int DV = A.DV, M = A.M, HV = A.HV, G = A.group;
@@ -104,7 +107,12 @@ __global__ void __launch_bounds__(NT, 4) fold_kernel(const __grid_constant__ Fol
     const long long seq = slot_of(pair);
     uint8_t* st = smraw + P.stage0 + s * P.stage_bytes;
     mbar_expect_tx(&bars[s], stage_tx);
-    bulk_g2s(st, A.S + seq * A.sS + (long long)h * P.codes_b, P.codes_b, &bars[s]);
+    if (TENS_OK && A.tens) {                   // eight pieces of 16 rows, 16 bytes apart (mma_pass.cuh)
+      constexpr int PB = 16 * (DK * BITS / 8);
+      for (int l = 0; l < 8; l++) bulk_g2s(st + l * (PB + 16), A.S + seq * A.sS + (long long)h * P.codes_b + l * PB, PB, &bars[s]);
+    } else {
+      bulk_g2s(st, A.S + seq * A.sS + (long long)h * P.codes_b, P.codes_b, &bars[s]);
+    }
     bulk_g2s(st + P.o_sc, A.SC + seq * A.sSC + (long long)h * scn * 2, scn * 2, &bars[s]);
     bulk_g2s(st + P.o_ub, A.UB + seq * A.sUB + (long long)h * M * DV * bsz, M * DV * bsz, &bars[s]);
     bulk_g2s(st + P.o_kb, A.KB + seq * A.sKB + (long long)hk * M * DK * bsz, M * DK * bsz, &bars[s]);
@@ -168,6 +176,39 @@ __global__ void __launch_bounds__(NT, 4) fold_kernel(const __grid_constant__ Fol
         if (e + 1 < cnt) mbar_wait(&bars[s ^ 1], (phases >> (s ^ 1)) & 1);   // leave no copy in flight
         failed = true;
         break;
+      }
+      if constexpr (TENS_OK) {
+        if (A.tens) {
+          // ---- the fold on the tensor pipe, from the stage as padded pieces, written back by bulk copies ----
+          constexpr int UPG = BITS == 8 ? 1 : 2, ROWB = DK * BITS / 8, PITCH = 16 * ROWB + 16;
+          float* tab = R;                              // dec_i, value scales, alpha (R and L are free in this mode)
+          uint32_t* KBf = reinterpret_cast<uint32_t*>(R + 32);
+          float* udq = L;
+          if (tid < 8) {
+            tab[tid] = tid == 7 ? 1.0f : expf(gnew - GBh[tid]);
+            tab[8 + tid] = h2f(UBSh[tid]);
+            ksf[tid] = h2f(KBSh[tid]);
+            if (tid == 0) tab[16] = expf(gnew);
+          }
+          udq[tid] = static_cast<float>(reinterpret_cast<const int8_t*>(ubt)[7 * DV + tid]) * h2f(UBSh[7]);   // d_v = 128 = NT
+          build_key_frags<BITS>(KBf, reinterpret_cast<const int8_t*>(kbt), reinterpret_cast<const int8_t*>(kbt) + 7 * DK, tid);
+          __syncthreads();
+          fold_stage_mma<BITS, UPG, 128, false>(smem_u32(st), reinterpret_cast<unsigned short*>(st + P.o_sc),
+                                                reinterpret_cast<const int8_t*>(ubt), udq, tab, ksf, KBf, warp, lane);
+          if (tid == 0) { *GCh = 0.f; reinterpret_cast<int*>(A.NPTR + seq * A.sN)[h] = 0; }
+          __syncthreads();
+          if (warp == 0) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            uint8_t* Sg = A.S + seq * A.sS + (long long)h * P.codes_b;
+            if (lane < 8) bulk_s2g(Sg + lane * 16 * ROWB, st + lane * PITCH, 16 * ROWB);
+            else if (lane == 8) bulk_s2g(A.SC + seq * A.sSC + (long long)h * scn * 2, st + P.o_sc, scn * 2);
+            bulk_commit();
+            bulk_wait_read();                          // the stage may be refilled, and the CTA may leave
+            __syncwarp();
+            if (lane == 0 && e + 2 < cnt) issue(s, list[e + 2]);
+          }
+          continue;
+        }
       }
       if (tid < M) {
         if (!VDEC) dec[tid] = tid >= nlive ? 0.f : (!reading && tid == M - 1 ? 1.0f : expf(gnew - GBh[tid]));
