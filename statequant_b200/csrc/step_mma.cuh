@@ -6,7 +6,8 @@
 // state rows (one head of d_v 128, two heads of d_v 64).  A stage -- codes as 8 padded pieces, scales, buffered
 // values -- arrives by bulk async copies on one mbarrier; the copies of the first stages and of the key tile are
 // issued by the lanes of warps 2 and 1 in the CTA's first instructions.  Per stage each warp takes a tile of 32 rows
-// through the tensor-core pass and finishes one row per lane (buffer term, u, o).
+// through the tensor-core pass and finishes one row per lane (buffer term, u, o).  A CTA with exactly two stages takes
+// both at once on a token that does not fold: two independent chains per warp instead of one after the other.
 //
 // MODE 0: every token is stepped and appended (after the last stage); on a slot's m-th token the head's counter is
 //         left at m for the fold launch that follows (fold_kernel.cuh).
