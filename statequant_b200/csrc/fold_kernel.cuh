@@ -184,6 +184,28 @@ __global__ void __launch_bounds__(NT, 4) fold_kernel(const __grid_constant__ Fol
           float* tab = R;                              // dec_i, value scales, alpha (R and L are free in this mode)
           uint32_t* KBf = reinterpret_cast<uint32_t*>(R + 32);
           float* udq = L;
+          if (reading) {
+            // the state advanced across the nlive <= 7 pending slots; dead slots (any bytes) count as zero
+            if (tid < 8) {
+              const bool lv = tid < nlive;
+              tab[tid] = lv ? expf(gnew - GBh[tid]) : 0.f;
+              tab[8 + tid] = lv ? h2f(UBSh[tid]) : 0.f;
+              ksf[tid] = lv ? h2f(KBSh[tid]) : 0.f;
+              if (tid == 0) tab[16] = expf(gnew);
+            }
+            udq[tid] = 0.f;
+            build_key_frags<BITS>(KBf, reinterpret_cast<const int8_t*>(kbt), reinterpret_cast<const int8_t*>(kbt) + 7 * DK, tid);
+            __syncthreads();
+            fold_stage_mma<BITS, UPG, 128, false, true>(smem_u32(st), reinterpret_cast<unsigned short*>(st + P.o_sc),
+                                                        reinterpret_cast<const int8_t*>(ubt), udq, tab, ksf, KBf, warp, lane, nullptr,
+                                                        A.out + (long long)pair * DV * DK);
+            __syncthreads();                           // the stage, the tables and the fragments are free
+            if (tid == 0 && e + 2 < cnt) {
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              issue(s, list[e + 2]);
+            }
+            continue;
+          }
           if (tid < 8) {
             tab[tid] = tid == 7 ? 1.0f : expf(gnew - GBh[tid]);
             tab[8 + tid] = h2f(UBSh[tid]);

@@ -29,7 +29,7 @@ int launch_fold_one(const StepArgs& a, cudaStream_t stream, float* out) {
   f.idx = a.idx; f.group = a.group; f.qbuf = a.qbuf; f.M = a.M; f.HV = a.HV; f.HK = a.HK; f.DV = a.DV; f.rows = a.rows;
   f.status = a.status;
   f.out = out;
-  f.tens = !VDEC && AXK && LPR == 8 && a.DV == 128 && a.M == 8 && a.qbuf && out == nullptr &&
+  f.tens = !VDEC && AXK && LPR == 8 && a.DV == 128 && a.M == 8 && a.qbuf &&
            ((BITS == 8 && a.group == 32) || (BITS == 4 && a.group == 64));
   const long long pairs = static_cast<long long>(a.rows) * a.HV;
   int per_sm = (220 * 1024) / (plan.total + 1024);

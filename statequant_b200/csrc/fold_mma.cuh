@@ -103,10 +103,12 @@ __device__ __forceinline__ void build_key_frags_kda(uint32_t* KBf, const int8_t*
 // VDEC (KDA): decays per key channel: the start value is (code scale) ae[k], ae = exp(gnew); L carries no decay and no
 // key scale (both are in the key fragments, three bf16 planes: build_key_frags_kda), and a product L Kd is taken as
 // p1 r1 + p1 r2 + p2 r1 + p1 r3 + p2 r2 + p3 r1 (the three terms left out are below 2^-24 of it).
-template <int BITS, int UPG, int DV, bool VDEC = false>
+// READ: nothing is rounded or written back; the accumulators, i.e. the state advanced across the buffer, go to
+// out [128 stage rows][128] fp32 instead (a thread's four adjacent columns of a row as one 16-byte store).
+template <int BITS, int UPG, int DV, bool VDEC = false, bool READ = false>
 __device__ __forceinline__ void fold_stage_mma(uint32_t st_addr, unsigned short* scs, const int8_t* ubt, const float* udq,
                                                const float* tab, const float* ksf, const uint32_t* KBf, int w, int lane,
-                                               const float* ae = nullptr) {
+                                               const float* ae = nullptr, float* out = nullptr) {
   constexpr int NG = 4 / UPG, ROWB = 128 * BITS / 8, PITCH = 16 * ROWB + 16;
   constexpr int NQ = BITS == 8 ? 4 : 8, NSPAN = BITS == 8 ? 4 : 2, TABW = 20;
   constexpr float QMAX = BITS == 4 ? 7.0f : 127.0f, MB = BITS == 4 ? MAGIC + 8.0f : MAGIC;
@@ -223,6 +225,25 @@ __device__ __forceinline__ void fold_stage_mma(uint32_t st_addr, unsigned short*
           mma_bf16(acc[q], A1[0], A1[1], A2[0], A2[1], kw, kw);
           mma_bf16(acc[q], A3[0], A3[1], 0u, 0u, kw, kw);
         }
+      }
+      if constexpr (READ) {
+        float* o0 = out + (long long)row0 * 128 + (BITS == 8 ? 32 * j + 4 * t : 64 * j + 8 * t);
+#pragma unroll
+        for (int hx = 0; hx < 2; hx++) {
+          if constexpr (BITS == 8) {
+            float* p = o0 + 16 * hx;
+            *reinterpret_cast<float4*>(p) = make_float4(acc[2 * hx][0], acc[2 * hx][1], acc[2 * hx + 1][0], acc[2 * hx + 1][1]);
+            *reinterpret_cast<float4*>(p + 128) = make_float4(acc[2 * hx][2], acc[2 * hx][3], acc[2 * hx + 1][2], acc[2 * hx + 1][3]);
+          } else {
+            float* p = o0 + 32 * hx;
+            const int q = 4 * hx;
+            *reinterpret_cast<float4*>(p) = make_float4(acc[q][0], acc[q][1], acc[q + 1][0], acc[q + 1][1]);
+            *reinterpret_cast<float4*>(p + 4) = make_float4(acc[q + 2][0], acc[q + 2][1], acc[q + 3][0], acc[q + 3][1]);
+            *reinterpret_cast<float4*>(p + 128) = make_float4(acc[q][2], acc[q][3], acc[q + 1][2], acc[q + 1][3]);
+            *reinterpret_cast<float4*>(p + 132) = make_float4(acc[q + 2][2], acc[q + 2][3], acc[q + 3][2], acc[q + 3][3]);
+          }
+        }
+        continue;
       }
       // ---- fresh scales: absmax over the group = this span, over the quad ----
       float am0 = 0.f, am1 = 0.f;
