@@ -59,9 +59,20 @@ inline bool mma_plan(const StepArgs& a, int bits, int mode, SmemM& plan, int& ns
   return plan.total <= 220 * 1024;
 }
 
+template <int KIND, int BITS, int UPG, int DV, int MODE, bool AXV, bool BIO>
+int launch_mma_one_io(const StepArgs& a, cudaStream_t stream);
+
+// bf16 activations and output take the kernel with those element types compiled in
 template <int KIND, int BITS, int UPG, int DV, int MODE, bool AXV = false>
 int launch_mma_one(const StepArgs& a, cudaStream_t stream) {
-  auto kern = step_mma_kernel<KIND, BITS, UPG, DV, MODE, AXV>;
+  if (a.dt_qk == DT_BF16 && a.dt_v == DT_BF16 && a.dt_out == DT_BF16)
+    return launch_mma_one_io<KIND, BITS, UPG, DV, MODE, AXV, true>(a, stream);
+  return launch_mma_one_io<KIND, BITS, UPG, DV, MODE, AXV, false>(a, stream);
+}
+
+template <int KIND, int BITS, int UPG, int DV, int MODE, bool AXV, bool BIO>
+int launch_mma_one_io(const StepArgs& a, cudaStream_t stream) {
+  auto kern = step_mma_kernel<KIND, BITS, UPG, DV, MODE, AXV, BIO>;
   SmemM plan;
   int nst;
   if (!mma_plan<KIND>(a, BITS, MODE, plan, nst)) return 1;

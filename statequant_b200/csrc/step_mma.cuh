@@ -129,7 +129,9 @@ static __device__ __noinline__ void mma_bail(uint8_t* orow, int dt, int n, uint6
   }
 }
 
-template <int KIND, int BITS, int UPG, int DV, int MODE, bool AXV = false>
+// BIO: q / k / v and the output are bf16 (what a serving engine passes): the element types of the activation loads and
+// stores are then compile-time constants instead of three-way run-time dispatches at every access.
+template <int KIND, int BITS, int UPG, int DV, int MODE, bool AXV = false, bool BIO = false>
 __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((BITS == 8 && UPG == 1) || (BITS == 4 && UPG == 2)) ? SQB_MMA_MINB_TFOLD : SQB_MMA_MINB_FOLD))
                                                : (BITS == 4 ? SQB_MMA_MINB4 : SQB_MMA_MINB8))
     step_mma_kernel(const __grid_constant__ StepArgs A, const __grid_constant__ SmemM P, const int nst) {
@@ -144,6 +146,8 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
   static_assert(!AXV || (UPG == 1 && !VDEC), "scales along v: groups of 32 rows (the stage's scales are [4][128], as many bytes as UPG = 1)");
 
   extern __shared__ __align__(128) uint8_t smraw[];
+  const int dt_qk = BIO ? static_cast<int>(DT_BF16) : A.dt_qk, dt_v = BIO ? static_cast<int>(DT_BF16) : A.dt_v,
+            dt_out = BIO ? static_cast<int>(DT_BF16) : A.dt_out;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int M = A.M;
   // grid: x = batch row, y = (key head, part of its value heads); no division on the way to the first fetch
@@ -155,7 +159,7 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
   if (gqa != gqf) { const int cpk = gqf / gqa; hk = blockIdx.y / cpk; part = blockIdx.y - hk * cpk; }
   const int h0 = hk * gqf + part * gqa;
   const bool first = part == 0;                   // the CTA that appends the key head's key
-  const int osz = dt_size(A.dt_out);
+  const int osz = dt_size(dt_out);
   // the fold, when it comes, runs on the tensor pipe for the formats it takes (the host sends these here only with a
   // buffer of 8, cf. mma_fold_inside), else in fp32
   constexpr bool TFOLD = TFMT;
@@ -174,14 +178,14 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
   Raw4 rq, rk;
   rq.v = make_uint4(0u, 0u, 0u, 0u); rk.v = rq.v; rq.vec = false; rk.vec = false;
   if (warp == 0 || warp == 3) {
-    rq = ld4_raw(A.q + (long long)b * A.sq, A.dt_qk, (long long)hk * DK + lane * CW);
-    rk = ld4_raw(A.k + (long long)b * A.sk, A.dt_qk, (long long)hk * DK + lane * CW);
+    rq = ld4_raw(A.q + (long long)b * A.sq, dt_qk, (long long)hk * DK + lane * CW);
+    rk = ld4_raw(A.k + (long long)b * A.sk, dt_qk, (long long)hk * DK + lane * CW);
   }
   long long seq = b;
   if (A.idx != nullptr) {
     seq = A.idx[b];
     if (seq <= 0) {
-      zero_out_rows(A.out + (long long)b * A.so + (long long)h0 * DV * osz, A.dt_out, gqa * DV);
+      zero_out_rows(A.out + (long long)b * A.so + (long long)h0 * DV * osz, dt_out, gqa * DV);
       return;
     }
   }
@@ -248,8 +252,8 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
   // loads once its urgent fetches are out
   uint32_t rvt[2];
   auto load_v = [&]() {
-    rvt[0] = ld1_raw(A.v + (long long)b * A.sv, A.dt_v, (long long)(h0 + hh) * DV + rv);
-    rvt[1] = ld1_raw(A.v + (long long)b * A.sv, A.dt_v, (long long)(h0 + (NSH > 1 ? HPS : 0) + hh) * DV + rv);
+    rvt[0] = ld1_raw(A.v + (long long)b * A.sv, dt_v, (long long)(h0 + hh) * DV + rv);
+    rvt[1] = ld1_raw(A.v + (long long)b * A.sv, dt_v, (long long)(h0 + (NSH > 1 ? HPS : 0) + hh) * DV + rv);
   };
   // The key tile (and KDA's decay tile) is fetched by warp 2; the warp that takes the buffered keys' dot products
   // (warp 0; KDA: warp 3) meets warp 2 at named barrier 1 (64 threads) before it waits for the tile, so that its wait
@@ -385,8 +389,8 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
     // pipe; KDA: the key that goes into the buffer
     load_v();
     float qr[CW], kr[CW];
-    cvt4_raw(rq, A.dt_qk, qr);
-    cvt4_raw(rk, A.dt_qk, kr);
+    cvt4_raw(rq, dt_qk, qr);
+    cvt4_raw(rk, dt_qk, kr);
     float gnr[CW] = {0.f, 0.f, 0.f, 0.f};
     float s0 = 0.f, s1 = 0.f;
     if constexpr (VDEC) {
@@ -502,8 +506,8 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
     // warp 3
     load_v();
     float qr[CW], kr[CW];
-    cvt4_raw(rq, A.dt_qk, qr);
-    cvt4_raw(rk, A.dt_qk, kr);
+    cvt4_raw(rq, dt_qk, qr);
+    cvt4_raw(rk, dt_qk, kr);
     if constexpr (!VDEC) {
       // the key that goes into the buffer, rounded: its normalisation is redone here (the arithmetic of warp 0, so
       // the same bits)
@@ -553,7 +557,7 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
   SQB_STAMP(4);
   // a copy that never completed: wait (bounded) for what may still be in flight, count it, leave
   auto bail = [&]() {
-    mma_bail(A.out + (long long)b * A.so + (long long)h0 * DV * osz, A.dt_out, gqa * DV, bars, min(nst, NSH), nst, A.wait_ns,
+    mma_bail(A.out + (long long)b * A.so + (long long)h0 * DV * osz, dt_out, gqa * DV, bars, min(nst, NSH), nst, A.wait_ns,
              A.status);
   };
   if (misc[2] != 0.f) { bail(); return; }
@@ -658,7 +662,7 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
       const int hiA = hh, hiB = HPS + hh;
       uint8_t* stA = smraw + P.stage0;
       uint8_t* stB = stA + P.stage_bytes;
-      const float vtA = cvt_raw(rvt[0], A.dt_v), vtB = cvt_raw(rvt[1], A.dt_v);
+      const float vtA = cvt_raw(rvt[0], dt_v), vtB = cvt_raw(rvt[1], dt_v);
       const float4 hdaA = *reinterpret_cast<const float4*>(hd + hiA * HD_W), hdbA = *reinterpret_cast<const float4*>(hd + hiA * HD_W + 4);
       const float4 hdaB = *reinterpret_cast<const float4*>(hd + hiB * HD_W), hdbB = *reinterpret_cast<const float4*>(hd + hiB * HD_W + 4);
       if (!mbar_wait(&bars[0], 0, A.wait_ns)) lost = true;
@@ -709,8 +713,8 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
       us[hiA * DV + rv] = uA;
       us[hiB * DV + rv] = uB;
       uint8_t* orow = A.out + (long long)b * A.so + (long long)(h0 + hiA) * DV * osz;
-      stf(orow, A.dt_out, rv, oA);
-      stf(orow + (long long)HPS * DV * osz, A.dt_out, rv, oB);
+      stf(orow, dt_out, rv, oA);
+      stf(orow + (long long)HPS * DV * osz, dt_out, rv, oB);
       const uint32_t umask = HPS == 1 ? 0xffffffffu : (lane < 16 ? 0x0000ffffu : 0xffff0000u);
       const float mA = __uint_as_float(__reduce_max_sync(umask, __float_as_uint(fabsf(uA))));
       const float mB = __uint_as_float(__reduce_max_sync(umask, __float_as_uint(fabsf(uB))));
@@ -724,7 +728,7 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
     uint8_t* st = smraw + P.stage0 + s * P.stage_bytes;
     const unsigned short* scs = reinterpret_cast<const unsigned short*>(st + P.sc_off);
     const int8_t* ubt = reinterpret_cast<const int8_t*>(st + P.ub_off) + hh * M * DV;
-    const float vt = sh < 2 ? cvt_raw(rvt[sh], A.dt_v) : ldf(A.v + (long long)b * A.sv, A.dt_v, (long long)h * DV + rv);
+    const float vt = sh < 2 ? cvt_raw(rvt[sh], dt_v) : ldf(A.v + (long long)b * A.sv, dt_v, (long long)h * DV + rv);
     const float4 hda = *reinterpret_cast<const float4*>(hd + hi * HD_W);          // g, beta | dt, gcur, alpha
     const float4 hdb = *reinterpret_cast<const float4*>(hd + hi * HD_W + 4);      // a, gnew, D, -
     const float beta = hda.y, alpha = hda.w, a = hdb.x, Dv = hdb.z;
@@ -767,7 +771,7 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
       if (A.beta) o = fmaf(Dv, vt, o);
     }
     us[hi * DV + rv] = u;
-    stf(A.out + (long long)b * A.so + (long long)h * DV * osz, A.dt_out, rv, o);
+    stf(A.out + (long long)b * A.so + (long long)h * DV * osz, dt_out, rv, o);
     // largest |u| of the head's rows in this warp: non-negative floats order like their bit patterns (a NaN ends up
     // as the maximum, as it should)
     const uint32_t umask = HPS == 1 ? 0xffffffffu : (lane < 16 ? 0x0000ffffu : 0xffff0000u);
