@@ -149,7 +149,8 @@ __global__ void __launch_bounds__(NT, MODE == 3 ? (AXV ? SQB_MMA_MINB_AXV : (((B
   const int dt_qk = BIO ? static_cast<int>(DT_BF16) : A.dt_qk, dt_v = BIO ? static_cast<int>(DT_BF16) : A.dt_v,
             dt_out = BIO ? static_cast<int>(DT_BF16) : A.dt_out;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int M = A.M;
+  // the buffer length: 8 in the kernels whose fold is the tensor-pipe one (the host sends no other there)
+  const int M = (MODE == 3 && TFMT) ? 8 : A.M;
   // grid: x = batch row, y = (key head, part of its value heads); no division on the way to the first fetch
   const int gqa = A.hpc;                          // value heads of this CTA: all heads of a key head, or a part of them
   const int gqf = A.gqa_full;                     // value heads per key head
